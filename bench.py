@@ -1,0 +1,316 @@
+#!/usr/bin/env python3
+"""Benchmark of the DIN-style CTR inference hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one batch of `--requests` requests (1 user x 1000 candidate items
+each) through embedding pooling -> fused attention unit -> MLP tower.
+Prints ONE JSON line: DIN predictions/s (whole job over all ranks), the
+end-to-end figure with host buffers, the roofline of the dominant kernel, the
+embedding-pool bandwidth on the sum-pooling configuration, the CPU baseline and
+the clocks seen during the timed region.
+
+With N > 1 the script expects to be launched by torch.distributed.run; every
+rank serves its own requests on its own GPU (replicas, no data-path collective).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+ATT_FLOP_PER_PAIR = 2 * (144 * 80 + 80 * 40 + 40)      # attention MLP 144-80-40-1 per (candidate, step)
+N_CAND, T_STEPS = 1000, 100
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "tf_burst": d["bf16_tflops"], "tf_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tf_burst": 1590.0, "tf_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0])); mx = float(r[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    import numpy as np
+    import torch
+    import pkg
+    pkg.load()
+    from x_deeplearning_b200 import din, ops, workloads
+
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    pk = peaks()
+    R, K, W, NB = args.requests, args.steps, args.warmup, args.batches
+
+    model = workloads.din_model(seed=0)
+    net = din.DinModel(model)
+    staged = [net.stage(workloads.din_requests(model, 1000 * rank + 17 + i, R, N_CAND)) for i in range(NB)]
+    plans = [net.upload(staged[i], slot=i) for i in range(NB)]
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        import torch.distributed as dist
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident throughput (inputs already in HBM) --------------------------------
+    for i in range(W):
+        net.forward_device(plans[i % NB])
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0.record()
+    for i in range(K):
+        net.forward_device(plans[i % NB], marks=marks[i])
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    dev_ms = max_over_ranks(e0.elapsed_time(e1))
+    assert ops.device_status() == 0, "a bounded wait ran out inside a tensor-core kernel"
+    pool_ms = statistics.mean(m[0].elapsed_time(m[1]) for m in marks)
+    att_ms = statistics.mean(m[2].elapsed_time(m[3]) for m in marks)
+
+    # ---- end to end: pinned host ids -> device -> probabilities on the host ------------------
+    for i in range(W):
+        net.forward(staged[i % NB])
+    barrier()
+    e0.record()
+    sink = 0.0
+    for i in range(K):
+        prob = net.forward(staged[i % NB])          # includes the H2D copies and the D2H read
+        sink += float(prob[0, 0])
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+
+    preds = R * N_CAND * K * world
+    att_flops = ATT_FLOP_PER_PAIR * N_CAND * T_STEPS * R
+    achieved_tf = att_flops / (att_ms * 1e-3) / 1e12
+    line = {
+        "metric": "DIN predictions/sec", "value": preds / (dev_ms * 1e-3), "unit": "predictions/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "DIN-style model, 1 user x 1000 candidates per request, T=100, tables 5M/10k/8x100k x 18 fp16",
+                   "requests_per_step": R, "parallelism": "replicas x%d (one process per GPU, no collective)" % world,
+                   "l2": "rotating %d pre-generated batches; tables (240 MB) and per-step intermediates exceed L2" % NB},
+        "e2e": {"value": preds / (e2e_ms * 1e-3), "unit": "predictions/s",
+                "h2d_bytes_per_step": int(sum(staged[0][k].numel() * staged[0][k].element_size() for k in
+                                              ("user_ids", "hist_item", "hist_cate", "cand_item", "cand_cate",
+                                               "seq_len"))),
+                "d2h_bytes_per_step": R * N_CAND * 2 * 4, "ms_per_step": e2e_ms / K},
+        "gpu_launches": din.DinModel.LAUNCHES_PER_FORWARD * K,
+        "roofline": {"kernel": "din_att_tc_kernel", "bound": "tensor", "achieved": achieved_tf,
+                     "peak": pk["tf_sustained"], "unit": "TFLOP/s", "frac": achieved_tf / pk["tf_sustained"],
+                     "traffic": None, "peak_source": pk["source"] + " (sustained bf16)", "ms_per_launch": att_ms,
+                     "pool_ms_per_step": pool_ms},
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        line["embedding_pool"] = bench_pool(pk)
+        line["cpu_baseline"] = cpu_baseline_din(model, workloads, cores=1, budget_s=args.cpu_seconds)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def bench_pool(pk):
+    """Sum-pooling configuration (1M x 16 fp32, 512 x 20 segments) and a 128x larger batch of it:
+    achieved HBM GB/s of pool_kernel from CUDA events, algorithmic bytes per launch."""
+    import numpy as np
+    import torch
+    from x_deeplearning_b200 import ops, workloads
+    out = {}
+    for label, batch, reps in (("config", 512, 200), ("scaled_batch_65536", 65536, 20)):
+        cfg = workloads.embedding_config(seed=0, batch=batch)
+        table = ops.Table(torch.from_numpy(cfg["table"]), torch.float32)
+        y = torch.zeros((batch, 320), device="cuda")
+        groups, n_ids = [], 0
+        for g, grp in enumerate(cfg["groups"]):
+            n_ids += len(grp["ids"])
+            groups.append(ops.make_group(table, torch.from_numpy(grp["ids"]).cuda(), torch.from_numpy(grp["values"]).cuda(),
+                                         torch.from_numpy(grp["offsets"]).cuda(), [dict(udf=0, out=y, col=16 * g)],
+                                         torch.float32, segments_are_offsets=True))
+        plan = ops.PoolPlan(groups)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        for _ in range(5):
+            plan.run()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        torch.cuda.synchronize()
+        for a, b in ev:
+            if label == "config":
+                flush.zero_()                      # 256 MB write: evicts the 64 MB table from L2
+            a.record(); plan.run(); b.record()
+        torch.cuda.synchronize()
+        ms = statistics.median(a.elapsed_time(b) for a, b in ev)
+        nbytes = n_ids * (8 + 4 + 64) + batch * 20 * 4 + batch * 320 * 4
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[label] = {"ms_per_launch": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs,
+                      "frac_of_measured_copy_peak": gbs / pk["hbm_gbs"], "frac_of_8tbs_nominal": gbs / 8000.0,
+                      "l2": "flushed before each launch" if label == "config" else "inputs exceed L2"}
+        del table, y, groups, plan
+    out["peak_gbs"] = pk["hbm_gbs"]
+    out["peak_source"] = pk["source"]
+    return out
+
+
+def cpu_baseline_din(model, workloads, cores, budget_s):
+    """The CPU oracle (port of the reference path) on a bounded sample of the same workload."""
+    import din_oracle
+    n_cand = 100                                        # 100 of the 1000 candidates of one request
+    req = workloads.din_requests(model, 99, 1, n_cand)
+    din_oracle.forward(model, req)
+    t0, n = time.time(), 0
+    while time.time() - t0 < budget_s:
+        din_oracle.forward(model, req)
+        n += 1
+    dt = time.time() - t0
+    return {"value": n * n_cand / dt, "unit": "predictions/s", "cores": cores, "kind": "port",
+            "sample": "%d passes of 1 request x %d candidates (T=100) in %.1f s; plain-C fp32 restatement "
+                      "(oracle/oracle.c), single thread" % (n, n_cand, dt)}
+
+
+# ---------------------------------------------------------------------------------------------
+_REF_MODEL = None      # set before the worker processes fork, so the tables are shared copy-on-write
+
+
+def _ref_worker(a):
+    seed, n_cand, reps = a
+    import din_oracle
+    from x_deeplearning_b200 import workloads
+    model = _REF_MODEL
+    req = workloads.din_requests(model, seed, 1, n_cand)
+    for _ in range(reps):
+        din_oracle.forward(model, req)
+    return n_cand * reps
+
+
+def run_reference(args):
+    """The reference's CPU path (oracle port: the dense operators of the reference need generated
+    protobuf code and a BLAS that are not available, so they do not compile here) on all host cores."""
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    import multiprocessing as mp
+    import pkg
+    pkg.load()
+    from x_deeplearning_b200 import workloads
+    import orc
+    orc.lib()
+    cores = os.cpu_count() or 1
+    global _REF_MODEL
+    n_cand = 200
+    _REF_MODEL = workloads.din_model(seed=0)
+    ctx = mp.get_context("fork")
+    with ctx.Pool(cores) as pool:
+        jobs = lambda: [(100 + i, n_cand, 1) for i in range(cores)]
+        for _ in range(max(1, min(args.warmup, 1))):
+            pool.map(_ref_worker, jobs())
+        t0 = time.time()
+        preds = 0
+        for _ in range(args.steps):
+            preds += sum(pool.map(_ref_worker, jobs()))
+        dt = time.time() - t0
+    v = preds / dt
+    sample = "each step: %d processes x 1 request x %d candidates (T=100)" % (cores, n_cand)
+    print(json.dumps({
+        "impl": "reference", "metric": "DIN predictions/sec", "value": v, "unit": "predictions/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "DIN-style model, 1 user x 1000 candidates per request, T=100, tables 5M/10k/8x100k x 18",
+                   "sample": sample},
+        "cpu_baseline": {"value": v, "unit": "predictions/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "predictions/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--requests", type=int, default=64, help="requests per step (each 1 user x 1000 candidates)")
+    ap.add_argument("--batches", type=int, default=8, help="distinct pre-generated request batches that are cycled")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and pooling side measurements")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,273 @@
+/*
+ * xdlb200.h - C ABI of libxdlb200.so: hand-written sm_100a CUDA kernels for the
+ * CTR-inference hot path of Blaze (alibaba/x-deeplearning, directory blaze/).
+ *
+ * Conventions
+ *   - every pointer named in an argument struct is a DEVICE pointer unless its
+ *     comment says "host";
+ *   - every entry point returns 0 when the work was enqueued on `stream`, and a
+ *     negative xb_status when an argument was rejected (nothing is launched);
+ *     xb_last_error() returns the reason for the calling thread;
+ *   - nothing here synchronises the stream, and the compute entry points do not
+ *     allocate: scratch memory is passed in by the caller;
+ *   - data types use Blaze's DataType numbering (blaze/blaze/proto/blaze.proto:6-20).
+ *
+ * Each entry point names the reference interface (path inside the reference
+ * project, file:line) that a Blaze CUDA operator would replace with it.
+ */
+#ifndef XDLB200_H_
+#define XDLB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* xb_stream_t; /* cudaStream_t */
+
+enum xb_status {
+  XB_OK = 0,
+  XB_ERR_ARG = -1,       /* bad argument (shape, dtype, alignment, null pointer) */
+  XB_ERR_UNSUPPORTED = -2,
+  XB_ERR_CUDA = -3,      /* a CUDA runtime/driver call failed */
+  XB_ERR_SCRATCH = -4,   /* scratch buffer too small */
+  XB_ERR_LIMIT = -5      /* size beyond a documented maximum */
+};
+
+enum xb_dtype {
+  XB_F32 = 1,
+  XB_I32 = 2,
+  XB_I64 = 10,
+  XB_F16 = 12,
+  XB_BF16 = 14           /* extension: not a Blaze type */
+};
+
+/* Reason of the last non-zero return on this thread ("" if none). */
+const char* xb_last_error(void);
+/* Library version and the SM architecture the kernels were compiled for. */
+const char* xb_version(void);
+/* Device-side status of the tensor-core kernels on the current device. Every
+ * wait inside them (mbarrier, TMEM) is bounded; a wait that runs out records
+ * (site << 8 | 1) and the kernel tears down and returns instead of hanging.
+ * *status is 0 when no wait ever ran out. Synchronise the stream first.
+ * xb_device_status_clear() resets the word. */
+int xb_device_status(int* status);
+int xb_device_status_clear(void);
+
+/* ------------------------------------------------------------------------- */
+/* Embedding tables in HBM.
+ * Replaces the in-memory image of QuickEmbeddingDict (hash table + weight blob,
+ * blaze/blaze/store/quick_embedding/quick_embedding_dict.h:18-110).
+ * Rows are stored at a fixed pitch that is a multiple of 16 bytes so a row is
+ * fetched with 128-bit loads. The key index is open addressing over
+ * (key,row) slots; with slot_keys == NULL keys are row numbers. */
+typedef struct xb_table_desc {
+  const void* weights;          /* row r at weights + r * row_pitch_bytes */
+  int64_t rows;
+  int32_t dim;
+  int32_t dtype;                /* XB_F32 or XB_F16 storage */
+  int64_t row_pitch_bytes;      /* multiple of 16 */
+  const int64_t* slot_keys;     /* [slots] or NULL for identity keys */
+  const int32_t* slot_rows;     /* [slots], -1 = empty */
+  int64_t slots;                /* power of two */
+} xb_table_desc;
+
+/* Pitch the library uses for a (dim, dtype) table. */
+int64_t xb_table_row_pitch(int32_t dim, int32_t dtype);
+/* Allocates device memory and uploads a table. `weights_host` is row-major
+ * [rows, dim] fp32 on the HOST and is converted to `dtype`; `keys_host`
+ * ([rows] int64, host) may be NULL for identity keys. On success *out owns
+ * the device buffers until xb_table_destroy. A repeated key keeps its first row. */
+int xb_table_create(xb_table_desc** out, int64_t rows, int32_t dim, int32_t dtype,
+                    const float* weights_host, const int64_t* keys_host);
+void xb_table_destroy(xb_table_desc* t);
+/* Host-side builder of the open-addressing index: fills slot_keys/slot_rows
+ * (host arrays of `slots` entries, slots a power of two >= 2*rows). */
+int xb_table_build_index_host(const int64_t* keys_host, int64_t rows, int64_t slots,
+                              int64_t* slot_keys_host, int32_t* slot_rows_host);
+
+/* ------------------------------------------------------------------------- */
+/* Embedding pooling.
+ * Replaces SparsePuller::Get (blaze/blaze/store/sparse_puller.h:77-83) as
+ * implemented by QuickEmbeddingDict::Get
+ * (blaze/blaze/store/quick_embedding/quick_embedding_dict.cc:89-147) with the
+ * kSum/kAvg/kAssign processors (udf_processor.h:41-151). One xb_pool_group is one
+ * SparsePullerInput/SparsePullerOutput pair; xb_pool_item is one
+ * SparsePullerInput::Param + SparsePullerOutput::OutItem. */
+enum { XB_UDF_SUM = 0, XB_UDF_AVG = 1, XB_UDF_ASSIGN = 2 };
+enum { XB_TRUNC_ORDER = 0, XB_TRUNC_REVERSE = 1 };
+#define XB_MAX_POOL_ITEMS 4
+#define XB_MAX_POOL_GROUPS 32   /* groups per call; call again for more */
+
+typedef struct xb_pool_item {
+  int32_t udf;             /* XB_UDF_* */
+  int32_t trunc_dir;       /* XB_TRUNC_*, kAssign only */
+  int32_t trunc_num;       /* kAssign only */
+  int32_t assign_stride;   /* elements between assigned rows; 0 = dim (Blaze layout) */
+  void* out;               /* at the item's column offset inside its block */
+  int64_t stride;          /* block row stride, elements */
+} xb_pool_item;
+
+typedef struct xb_pool_group {
+  const xb_table_desc* table;  /* HOST pointer; NULL = table-name miss: outputs are zero-filled */
+  const void* ids;             /* [n_ids] */
+  const float* values;         /* [n_ids] fp32 per-id weights, NULL = all 1.0 */
+  const int32_t* segments;     /* [batch] counts, or [batch+1] exclusive offsets */
+  int64_t n_ids;
+  int64_t batch;
+  int32_t dim;                 /* the group's configured dim (EmbeddingFeatureGroupConfig.dim); must
+                                  equal table->dim when the table exists */
+  int32_t id_dtype;            /* XB_I64 or XB_I32 */
+  int32_t segments_are_offsets;
+  int32_t out_dtype;           /* XB_F32 or XB_F16 */
+  int32_t n_items;
+  xb_pool_item items[XB_MAX_POOL_ITEMS];
+} xb_pool_group;
+
+/* Bytes of scratch xb_embedding_pool needs for these groups (offsets of the
+ * groups that pass counts). */
+size_t xb_embedding_pool_scratch_bytes(const xb_pool_group* groups, int32_t n_groups);
+/* Every output element of every item is written (zero where nothing pools),
+ * so the caller needs no memset (the reference op memsets first,
+ * blaze/blaze/operator/sparse_op/embedding/embedding_op.h:181). */
+int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, void* scratch,
+                      size_t scratch_bytes, xb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* GEMM family with fused bias + activation epilogue.
+ * Replaces GemmOp::RunOnDevice (blaze/blaze/operator/op/gemm_op.h:33-107),
+ * FusedParallelGemmOp::RunOnDevice (blaze/blaze/operator/fused_op/
+ * fused_parallel_gemm_op.h:43-133), the strided-batched calls behind MatMul /
+ * FusedParallelMatMul (blaze/blaze/math/gemm.h:50-79, math/broadcast.h:156-381)
+ * and, through `epilogue`, a following Dice / PRelu / Sigmoid operator
+ * (operator/op/dice_op.cu:11-21, prelu_op.cu:10-23, sigmoid_op.cu:11-17).
+ *   Y[b] = act(alpha * op(A[b]) * op(B[b]) + beta * bias[b]),  b < batch
+ * All matrices are row-major with explicit leading dimensions; a batch stride of
+ * 0 re-uses the operand for every b (shared A of FusedParallelGemm). Y may point
+ * at a column offset of a wider matrix (ldy > N) which gives axis-1 concat of the
+ * branches for free. */
+enum { XB_EPI_NONE = 0, XB_EPI_PRELU = 1, XB_EPI_DICE = 2, XB_EPI_SIGMOID = 3 };
+enum { XB_BIAS_NONE = 0, XB_BIAS_ROW = 1 /* [N] */, XB_BIAS_FULL = 2 /* [M,N] */ };
+enum { XB_GEMM_AUTO = 0, XB_GEMM_SIMT = 1, XB_GEMM_TCGEN05 = 2 };
+
+typedef struct xb_gemm_args {
+  int32_t M, N, K;
+  int32_t trans_a, trans_b;
+  float alpha, beta;
+  const void* A; int64_t lda; int64_t stride_a;
+  const void* B; int64_t ldb; int64_t stride_b;
+  const void* bias; int64_t ldbias; int64_t stride_bias; int32_t bias_kind;
+  void* Y; int64_t ldy; int64_t stride_y;
+  int32_t batch;
+  int32_t ab_dtype;        /* XB_F32, XB_F16 or XB_BF16: A and B */
+  int32_t bias_dtype;      /* dtype of bias */
+  int32_t y_dtype;
+  int32_t epilogue;        /* XB_EPI_* */
+  const float* ep_a;       /* PRelu: slopes [ep_count]; Dice: gamma [N] */
+  const float* ep_b;       /* Dice: mean [N] */
+  const float* ep_c;       /* Dice: var [N] */
+  int32_t ep_count;        /* PRelu: number of slopes (1 = shared, else N) */
+  int32_t dice_nosqrt;
+  int64_t stride_ep;       /* per-batch stride of ep_a/b/c, elements (0 = shared) */
+  int32_t engine;          /* XB_GEMM_AUTO picks tcgen05 when the layout allows */
+} xb_gemm_args;
+
+int xb_gemm(const xb_gemm_args* args, xb_stream_t stream);
+/* 1 when XB_GEMM_AUTO would run these arguments on the tcgen05 engine. */
+int xb_gemm_uses_tcgen05(const xb_gemm_args* args);
+
+/* Pack a row-major [K,N] weight into the K-major [N, ldk] layout (ldk >= K,
+ * multiple of 8, zero padded) the tcgen05 engine reads, with dtype conversion.
+ * Done once when constants are loaded (blaze/blaze/operator/op/constant_fill_op.h:20-37). */
+int xb_pack_weight_kmajor(const void* W, int32_t w_dtype, int32_t K, int32_t N, int64_t ldw,
+                          void* out, int32_t out_dtype, int64_t ldk, int32_t batch,
+                          int64_t stride_w, int64_t stride_out, xb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Fused DIN attention unit.
+ * Replaces rows 7-16 of the shipped DIN graph
+ * (blaze/tools/example_model/din/model/graph_ulf.txt: Sub, Mul, BroadcastTo x2,
+ * Concat, Gemm x3 with activations, Where, Softmax, MatMul) - operators
+ * blaze/blaze/operator/op/elementwise_op.h:63-307, concat_op.h:34-131,
+ * gemm_op.h:33-107, softmax_op.cc:21-78, matmul_op.h:31-144.
+ * For request r: q[r] [n_cand, d], k[r] [T, d];
+ *   x = [q, k, q-k, q*k] (4d), s = W2'act(W1'act(W0'x+b0)+b1)+b2,
+ *   out[n] = sum_t s[n,t] * k[t]     (optionally masked softmax over t first).
+ * The 4d-wide concat is built in shared memory and never written to HBM. */
+enum { XB_ACT_NONE = 0, XB_ACT_SIGMOID = 1, XB_ACT_DICE = 2 };
+
+typedef struct xb_din_att_weights {
+  /* K-major packed fp16 weights: W0 [h0, 4d], W1 [h1, h0]; W2 fp32 [h1] */
+  const void* W0; const void* W1; const float* W2;
+  const float *b0, *b1;  float b2;
+  const float *gamma0, *mean0, *var0;   /* Dice, [h0] */
+  const float *gamma1, *mean1, *var1;   /* Dice, [h1] */
+} xb_din_att_weights;
+
+typedef struct xb_din_att_args {
+  const void* q;  int64_t ldq;          /* fp16 [requests*n_cand, d] */
+  const void* k;  int64_t ldk;          /* fp16 [requests*T, d] */
+  const int32_t* seq_len;               /* [requests] valid steps, NULL = T */
+  void* out; int64_t ldo;               /* fp16 [requests*n_cand, d] */
+  float* scores;                        /* optional fp32 [requests*n_cand, T], NULL to skip */
+  int32_t requests, n_cand, T, d, h0, h1;
+  int32_t act;                          /* XB_ACT_* */
+  int32_t use_softmax;                  /* masked softmax over t (shipped graph) */
+  int32_t engine;                       /* XB_GEMM_AUTO / _SIMT / _TCGEN05 */
+  xb_din_att_weights w;
+} xb_din_att_args;
+
+int xb_din_attention(const xb_din_att_args* args, xb_stream_t stream);
+
+/* Fused assembly of the DIN tower input. Replaces rows 17-22 of the shipped DIN
+ * graph (ReduceSum over the behaviour rows, Mul, Concat, Fuse x2:
+ * blaze/blaze/operator/op/reduce_sum_op.h:17-86, elementwise_op.h:63-307,
+ * concat_op.h:34-131, fuse_op.h:28-83). For request r and candidate n:
+ *   X[r*n_cand+n] = [user[r] (du) | q | his_sum[r] | q*his_sum[r] | att | q-his_sum[r] | 0...]
+ * with his_sum[r] = sum_t k[r,t]; columns [du+5d, ldx) are zero-filled so X can
+ * feed the tcgen05 GEMM engine (ldx a multiple of 8). All tensors fp16. */
+int xb_din_tower_input(const void* user, int64_t ldu, const void* q, int64_t ldq, const void* k,
+                       int64_t ldk, const void* att, int64_t ldatt, void* X, int64_t ldx,
+                       int32_t requests, int32_t n_cand, int32_t T, int32_t d, int32_t du,
+                       xb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* Stand-alone operators for graphs that were not fused. x/y share `dtype`;
+ * per-column parameters share it too (Blaze keeps them in the model dtype). */
+/* DiceOp, blaze/blaze/operator/op/dice_op.h:41-98 */
+int xb_dice(const void* x, void* y, int64_t rows, int32_t c, const void* gamma, const void* mean,
+            const void* var, int32_t nosqrt, int32_t dtype, xb_stream_t stream);
+/* PReluOp, blaze/blaze/operator/op/prelu_op.h:25-64 */
+int xb_prelu(const void* x, void* y, int64_t size, const void* w, int64_t inner, int32_t dtype,
+             int32_t w_dtype, xb_stream_t stream);
+/* SigmoidOp, blaze/blaze/operator/op/sigmoid_op.cu:11-17 */
+int xb_sigmoid(const void* x, void* y, int64_t size, int32_t dtype, xb_stream_t stream);
+/* SoftmaxOp, blaze/blaze/operator/op/softmax_op.cu:25-67: softmax over c with outer n, inner w */
+int xb_softmax(const void* x, void* y, int64_t n, int32_t c, int64_t w, int32_t dtype, xb_stream_t stream);
+/* BatchNormalizationOp (inference), blaze/blaze/operator/op/batch_normalization_op.cu:12 */
+int xb_batchnorm(const void* x, void* y, int64_t size, int32_t c, const void* gamma, const void* beta,
+                 const void* mean, const void* var, float eps, int32_t nosqrt, int32_t dtype,
+                 xb_stream_t stream);
+/* Elementwise with numpy broadcasting over <= 4 dims,
+ * blaze/blaze/operator/op/elementwise_op.h:63-307. `where`: a is int32 condition. */
+enum { XB_EW_ADD = 0, XB_EW_SUB, XB_EW_MUL, XB_EW_DIV, XB_EW_MAX, XB_EW_MIN, XB_EW_EQ, XB_EW_NE,
+       XB_EW_BROADCAST_TO, XB_EW_WHERE };
+int xb_elementwise(int32_t op, const void* a, const int64_t* a_strides, const void* b,
+                   const int64_t* b_strides, const void* c, const int64_t* c_strides, void* y,
+                   const int64_t* y_shape /* 4 dims */, int32_t dtype, xb_stream_t stream);
+/* Strided 2-D copy with dtype conversion: Concat / Slice / Split / Fuse /
+ * FusedSliceConcat are expressed as one or more of these
+ * (blaze/blaze/operator/op/concat_op.cu:32-43, slice_op.cu:10, fuse_op.cu:10-18,
+ * fused_op/fused_slice_concat_op.cu:24-140). src row stride 0 broadcasts one row. */
+int xb_copy2d(const void* src, int64_t src_ld, int32_t src_dtype, void* dst, int64_t dst_ld,
+              int32_t dst_dtype, int64_t rows, int64_t cols, xb_stream_t stream);
+/* ReduceSum over the middle axis of [outer, r, inner], blaze/blaze/math/reduce.cu:12-113 */
+int xb_reduce_sum(const void* x, void* y, int64_t outer, int64_t r, int64_t inner, int32_t dtype,
+                  xb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XDLB200_H_ */

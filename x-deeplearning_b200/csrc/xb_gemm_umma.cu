@@ -1,0 +1,341 @@
+// tcgen05 GEMM engine with fused bias + activation epilogue, and the xb_gemm
+// dispatcher.
+//
+//   Y[b] = act(alpha * A[b] * B[b]^T + beta * bias[b])
+//   A [M,K] row-major (K-major), B [N,K] row-major (K-major), fp16 or bf16,
+//   fp32 accumulation in tensor memory.
+//
+// One CTA computes one 128 x BLOCK_N output tile. Warp 0 streams 128x64 A
+// tiles and BLOCK_Nx64 B tiles through a 4-stage shared-memory ring with TMA
+// (128-byte swizzle, out-of-range rows/columns zero-filled by the TMA unit,
+// so M, N and K tails need no padding in HBM). Warp 1 issues tcgen05.mma
+// (128 x BLOCK_N x 16 per instruction) into a TMEM accumulator and releases
+// ring slots with tcgen05.commit. Warps 2-5 read the accumulator with
+// tcgen05.ld (one output row per thread), apply bias and activation and store
+// with an arbitrary row stride, which is what lets parallel branches write
+// side by side into one wide output (axis-1 concat) or stacked (axis 0).
+#include <cstring>
+
+#include "xb_common.cuh"
+#include "xb_umma.cuh"
+
+namespace xb {
+
+int gemm_simt(const xb_gemm_args& a, cudaStream_t stream);
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;
+
+struct UmmaGemmParams {
+  int M, N, K, block_n, tmem_cols;
+  float alpha, beta;
+  int a_batched, b_batched;
+  const void* bias; int64_t ldbias, stride_bias; int bias_kind, bias_dtype;
+  void* Y; int64_t ldy, stride_y; int y_dtype;
+  EpiParams epi; int64_t stride_ep;
+  uint32_t idesc;
+};
+
+template <typename TOut>
+__device__ __forceinline__ void store_row16(TOut* dst, const float (&v)[16], int valid, bool vec_ok) {
+  if (sizeof(TOut) == 2 && vec_ok && valid == 16) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      TOut lo = from_f32<TOut>(v[2 * i]), hi = from_f32<TOut>(v[2 * i + 1]);
+      w[i] = (uint32_t)(*reinterpret_cast<uint16_t*>(&lo)) | ((uint32_t)(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+    }
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    d[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    d[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else if (sizeof(TOut) == 4 && vec_ok && valid == 16) {
+    float4* d = reinterpret_cast<float4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+    for (int i = 0; i < valid; ++i) dst[i] = from_f32<TOut>(v[i]);
+  }
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(192, 1)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ UmmaGemmParams p) {
+  using namespace umma;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int b_stage_bytes = p.block_n * BLOCK_K * 2;
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ uint32_t tmem_base_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BLOCK_M, n0 = blockIdx.y * p.block_n, b = blockIdx.z;
+  const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+    mbar_init(smem_u32(&acc_bar), 1);
+    fence_barrier_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), (uint32_t)p.tmem_cols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_acc = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, 1)) break;
+        mbar_arrive_expect_tx(smem_u32(&full_bar[s]), (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
+        tma_load_3d(smem_u32(smem_a + s * A_STAGE_BYTES), &map_a, smem_u32(&full_bar[s]), kb * BLOCK_K, m0,
+                    p.a_batched ? b : 0);
+        tma_load_3d(smem_u32(smem_b + s * b_stage_bytes), &map_b, smem_u32(&full_bar[s]), kb * BLOCK_K, n0,
+                    p.b_batched ? b : 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+        ok = mbar_wait(smem_u32(&full_bar[s]), ph, 2);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem_a + s * A_STAGE_BYTES);
+        const uint32_t b_addr = smem_u32(smem_b + s * b_stage_bytes);
+#pragma unroll
+        for (int k = 0; k < BLOCK_K / 16; ++k) {
+          const uint64_t da = make_desc_sw128(a_addr + k * 32, 1024);
+          const uint64_t db = make_desc_sw128(b_addr + k * 32, 1024);
+          mma_f16_ss(tmem_acc, da, db, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(smem_u32(&empty_bar[s]));     // slot free once these MMAs have read it
+      }
+      mma_commit(smem_u32(&acc_bar));            // accumulator complete
+    }
+  } else {
+    // epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32)
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int gm = m0 + row;
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_bar), 0, 3));   // warp-uniform
+    tc_fence_after_sync();
+    if (ok) {
+      EpiParams epi = p.epi;
+      if (epi.a) epi.a += (int64_t)b * p.stride_ep;
+      if (epi.b) epi.b += (int64_t)b * p.stride_ep;
+      if (epi.c) epi.c += (int64_t)b * p.stride_ep;
+      TOut* yrow = reinterpret_cast<TOut*>(p.Y) + (int64_t)b * p.stride_y + (int64_t)gm * p.ldy;
+      const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0) && ((p.ldy * sizeof(TOut)) % 16 == 0) &&
+                          ((p.stride_y * sizeof(TOut)) % 16 == 0);
+      for (int c = 0; c < p.block_n; c += 16) {
+        float v[16];
+        tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);   // whole warp, uniform
+        const int gn0 = n0 + c;
+        int valid = p.N - gn0;
+        valid = valid > 16 ? 16 : valid;
+        if (gm < p.M && valid > 0) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (i < valid) {
+              const int gn = gn0 + i;
+              float x = p.alpha * v[i];
+              if (p.bias_kind == XB_BIAS_ROW)
+                x += p.beta * load_as_f32(p.bias, (int64_t)b * p.stride_bias + gn, p.bias_dtype);
+              else if (p.bias_kind == XB_BIAS_FULL)
+                x += p.beta * load_as_f32(p.bias, (int64_t)b * p.stride_bias + (int64_t)gm * p.ldbias + gn,
+                                          p.bias_dtype);
+              v[i] = apply_epilogue(epi, x, gn);
+            }
+          }
+          store_row16<TOut>(yrow + gn0, v, valid, vec_ok && ((gn0 * sizeof(TOut)) % 16 == 0));
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_acc, (uint32_t)p.tmem_cols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// [batch, rows, K] tensor of 2-byte elements, box {64, box_rows, 1}, 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, int is_bf16, int64_t K, int64_t rows, int64_t ld, int64_t batch,
+             int64_t batch_stride, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(XB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? batch_stride : ld * rows) * 2};
+  if (strides[1] == 0) strides[1] = strides[0];
+  cuuint32_t box[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(XB_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+int pick_block_n(int N) {
+  if (N <= 256) return (N + 15) / 16 * 16;
+  return (N % 256 == 0) ? 256 : 128;
+}
+
+bool umma_eligible(const xb_gemm_args& a) {
+  if (a.ab_dtype != XB_F16 && a.ab_dtype != XB_BF16) return false;
+  if (a.trans_a || !a.trans_b) return false;
+  if (a.y_dtype != XB_F16 && a.y_dtype != XB_BF16 && a.y_dtype != XB_F32) return false;
+  if (a.lda % 8 || a.ldb % 8 || a.stride_a % 8 || a.stride_b % 8) return false;
+  if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15)) return false;
+  if (a.lda < a.K || a.ldb < a.K) return false;
+  return true;
+}
+
+template <typename TOut>
+int launch_umma(const CUtensorMap& ma, const CUtensorMap& mb, const UmmaGemmParams& p, dim3 grid, size_t smem,
+                cudaStream_t s) {
+  static bool attr_set = false;   // per instantiation
+  if (!attr_set) {
+    XB_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_set = true;
+  }
+  gemm_umma_kernel<TOut><<<grid, 192, smem, s>>>(ma, mb, p);
+  return check_launch("gemm_umma_kernel");
+}
+
+int gemm_umma(const xb_gemm_args& a, cudaStream_t stream) {
+  UmmaGemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.block_n = pick_block_n(a.N);
+  p.tmem_cols = 32;
+  while (p.tmem_cols < p.block_n) p.tmem_cols <<= 1;
+  p.alpha = a.alpha; p.beta = a.beta;
+  p.a_batched = a.stride_a != 0; p.b_batched = a.stride_b != 0;
+  p.bias = a.bias; p.ldbias = a.ldbias; p.stride_bias = a.stride_bias;
+  p.bias_kind = a.bias ? a.bias_kind : XB_BIAS_NONE; p.bias_dtype = a.bias_dtype;
+  p.Y = a.Y; p.ldy = a.ldy; p.stride_y = a.stride_y; p.y_dtype = a.y_dtype;
+  p.epi.kind = a.epilogue; p.epi.a = a.ep_a; p.epi.b = a.ep_b; p.epi.c = a.ep_c;
+  p.epi.count = a.ep_count; p.epi.nosqrt = a.dice_nosqrt; p.stride_ep = a.stride_ep;
+  const int is_bf16 = a.ab_dtype == XB_BF16;
+  p.idesc = umma::make_idesc(BLOCK_M, p.block_n, is_bf16);
+  CUtensorMap ma, mb;
+  if (int rc = make_map(&ma, a.A, is_bf16, a.K, a.M, a.lda, p.a_batched ? a.batch : 1, a.stride_a, BLOCK_M)) return rc;
+  if (int rc = make_map(&mb, a.B, is_bf16, a.K, a.N, a.ldb, p.b_batched ? a.batch : 1, a.stride_b, p.block_n)) return rc;
+  dim3 grid((a.M + BLOCK_M - 1) / BLOCK_M, (a.N + p.block_n - 1) / p.block_n, a.batch);
+  XB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, XB_ERR_LIMIT, "xb_gemm: N tiles or batch beyond the grid limit");
+  const size_t smem = (size_t)STAGES * (A_STAGE_BYTES + p.block_n * BLOCK_K * 2) + 1024;
+  switch (a.y_dtype) {
+    case XB_F16: return launch_umma<__half>(ma, mb, p, grid, smem, stream);
+    case XB_BF16: return launch_umma<__nv_bfloat16>(ma, mb, p, grid, smem, stream);
+    default: return launch_umma<float>(ma, mb, p, grid, smem, stream);
+  }
+}
+
+}  // namespace
+
+int gemm_umma_status(int* out) { return umma::read_status_word(out); }
+int gemm_umma_clear_status() { return umma::clear_status_word(); }
+
+}  // namespace xb
+
+using namespace xb;
+
+namespace xb {
+int att_status(int* out);
+int att_clear_status();
+}  // namespace xb
+
+extern "C" int xb_device_status(int* status) {
+  XB_REQUIRE(status, XB_ERR_ARG, "xb_device_status: null pointer");
+  int a = 0, b = 0;
+  XB_REQUIRE(gemm_umma_status(&a) == 0 && att_status(&b) == 0, XB_ERR_CUDA, "xb_device_status: read failed");
+  *status = a ? a : b;
+  return 0;
+}
+
+extern "C" int xb_device_status_clear(void) {
+  XB_REQUIRE(gemm_umma_clear_status() == 0 && att_clear_status() == 0, XB_ERR_CUDA, "xb_device_status_clear failed");
+  return 0;
+}
+
+static int validate_gemm(const xb_gemm_args* a) {
+  XB_REQUIRE(a, XB_ERR_ARG, "xb_gemm: null arguments");
+  XB_REQUIRE(a->M >= 0 && a->N >= 0 && a->K >= 0 && a->batch >= 0, XB_ERR_ARG, "xb_gemm: negative size");
+  XB_REQUIRE(a->A && a->B && a->Y, XB_ERR_ARG, "xb_gemm: null matrix");
+  XB_REQUIRE(a->ab_dtype == XB_F32 || a->ab_dtype == XB_F16 || a->ab_dtype == XB_BF16, XB_ERR_UNSUPPORTED,
+             "xb_gemm: operand dtype %d", a->ab_dtype);
+  XB_REQUIRE(a->y_dtype == XB_F32 || a->y_dtype == XB_F16 || a->y_dtype == XB_BF16, XB_ERR_UNSUPPORTED,
+             "xb_gemm: output dtype %d", a->y_dtype);
+  XB_REQUIRE(a->epilogue >= XB_EPI_NONE && a->epilogue <= XB_EPI_SIGMOID, XB_ERR_UNSUPPORTED,
+             "xb_gemm: epilogue %d", a->epilogue);
+  XB_REQUIRE(a->epilogue != XB_EPI_PRELU || (a->ep_a && (a->ep_count == 1 || a->ep_count == a->N)), XB_ERR_ARG,
+             "xb_gemm: PRelu needs 1 or N slopes");
+  XB_REQUIRE(a->epilogue != XB_EPI_DICE || (a->ep_a && a->ep_b && a->ep_c), XB_ERR_ARG,
+             "xb_gemm: Dice needs gamma, mean and var");
+  XB_REQUIRE(!a->bias || a->bias_kind == XB_BIAS_ROW || a->bias_kind == XB_BIAS_FULL, XB_ERR_ARG,
+             "xb_gemm: bias kind %d", a->bias_kind);
+  XB_REQUIRE(!a->bias || dtype_size(a->bias_dtype) != 0, XB_ERR_UNSUPPORTED, "xb_gemm: bias dtype %d", a->bias_dtype);
+  const int64_t a_cols = a->trans_a ? a->M : a->K, b_cols = a->trans_b ? a->K : a->N;
+  XB_REQUIRE(a->lda >= a_cols && a->ldb >= b_cols && a->ldy >= a->N, XB_ERR_ARG,
+             "xb_gemm: leading dimension smaller than the row (lda=%lld ldb=%lld ldy=%lld)", (long long)a->lda,
+             (long long)a->ldb, (long long)a->ldy);
+  return 0;
+}
+
+extern "C" int xb_gemm_uses_tcgen05(const xb_gemm_args* a) {
+  if (!a || a->engine == XB_GEMM_SIMT) return 0;
+  return umma_eligible(*a) ? 1 : 0;
+}
+
+extern "C" int xb_gemm(const xb_gemm_args* a, xb_stream_t stream) {
+  if (int rc = validate_gemm(a)) return rc;
+  if (a->M == 0 || a->N == 0 || a->batch == 0) return 0;
+  if (a->engine == XB_GEMM_TCGEN05) {
+    XB_REQUIRE(umma_eligible(*a), XB_ERR_UNSUPPORTED,
+               "xb_gemm: tcgen05 engine needs fp16/bf16, A [M,K] and B [N,K] row-major, 16-byte aligned, "
+               "leading dimensions and batch strides multiples of 8");
+    XB_REQUIRE(a->K > 0, XB_ERR_ARG, "xb_gemm: K = 0");
+    return gemm_umma(*a, (cudaStream_t)stream);
+  }
+  // small problems are launch-bound either way; the CUDA-core engine has no TMA descriptor cost
+  if (a->engine == XB_GEMM_AUTO && umma_eligible(*a) && a->K > 0 &&
+      (int64_t)a->M * a->N * a->batch >= 128 * 64)
+    return gemm_umma(*a, (cudaStream_t)stream);
+  return gemm_simt(*a, (cudaStream_t)stream);
+}

@@ -1,0 +1,444 @@
+// Embedding pooling over variable-length id lists, and the HBM table image.
+//
+// Kernel shape: a warp is split into teams of TL lanes, one team per
+// (sample, feature-group) segment; a team is split into sub-teams of LPR lanes
+// that each fetch one table row with 128-bit loads (lane c reads bytes
+// [16c,16c+16) of the row). Sub-team s walks ids s, s+NS, s+2NS... of the
+// segment in order and accumulates in fp32; the NS partial sums are combined
+// with a fixed xor-butterfly, so a result does not depend on scheduling.
+// HBM-bound: per id the kernel moves 8 B id + 4 B value + one row.
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "xb_common.cuh"
+
+namespace xb {
+
+struct PoolItemDev {
+  int32_t udf, trunc_dir, trunc_num, assign_stride;
+  void* out;
+  int64_t stride;
+};
+
+struct PoolGroupDev {
+  const char* weights;
+  const int64_t* slot_keys;
+  const int32_t* slot_rows;
+  const void* ids;
+  const float* values;
+  const int32_t* offsets;      // exclusive offsets [batch+1]
+  int64_t rows, pitch, slot_mask, batch;
+  int64_t warp_begin;          // first warp of this group in the launch
+  int32_t dim, tdtype, id_dtype, out_dtype, n_items, has_table;
+  int32_t lpr;                 // lanes per row
+  int32_t tl;                  // lanes per segment (team)
+  PoolItemDev items[XB_MAX_POOL_ITEMS];
+};
+
+struct PoolParams {
+  int32_t n_groups;
+  int64_t total_warps;
+  PoolGroupDev g[XB_MAX_POOL_GROUPS];
+};
+
+struct ScanParams {
+  int32_t n;
+  const int32_t* counts[XB_MAX_POOL_GROUPS];
+  int32_t* offsets[XB_MAX_POOL_GROUPS];
+  int64_t batch[XB_MAX_POOL_GROUPS];
+};
+
+__device__ __forceinline__ uint64_t mix64(uint64_t x) {
+  x ^= x >> 33; x *= 0xff51afd7ed558ccdULL; x ^= x >> 33;
+  x *= 0xc4ceb9fe1a85ec53ULL; x ^= x >> 33; return x;
+}
+
+// counts -> exclusive offsets, one CTA per group. 256 threads x 4 counts per pass.
+__global__ void __launch_bounds__(256) scan_counts_kernel(const __grid_constant__ ScanParams p) {
+  const int g = blockIdx.x;
+  const int32_t* __restrict__ counts = p.counts[g];
+  int32_t* __restrict__ offsets = p.offsets[g];
+  const int64_t batch = p.batch[g];
+  __shared__ int32_t warp_sums[8];
+  __shared__ int32_t carry_s;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t base = 0; base < batch; base += 1024) {
+    int64_t i0 = base + (int64_t)threadIdx.x * 4;
+    int32_t c[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) c[e] = (i0 + e < batch) ? counts[i0 + e] : 0;
+    int32_t tsum = c[0] + c[1] + c[2] + c[3];
+    int32_t incl = tsum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      int32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    int32_t wbase = 0;
+    for (int w = 0; w < warp; ++w) wbase += warp_sums[w];
+    int32_t carry = carry_s;
+    int32_t excl = carry + wbase + incl - tsum;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (i0 + e < batch) offsets[i0 + e] = excl;
+      excl += c[e];
+    }
+    __syncthreads();
+    if (threadIdx.x == 255) carry_s = carry + wbase + incl;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) offsets[batch] = carry_s;
+}
+
+__device__ __forceinline__ int64_t lookup_row(const PoolGroupDev& g, int64_t key) {
+  if (g.slot_keys == nullptr) return (key >= 0 && key < g.rows) ? key : -1;
+  uint64_t h = mix64((uint64_t)key) & (uint64_t)g.slot_mask;
+  // bounded probe: an index built by xb_table_build_index_host is at most half full
+  for (int64_t probes = 0; probes <= g.slot_mask; ++probes) {
+    int32_t r = __ldg(g.slot_rows + h);
+    if (r < 0) return -1;
+    if (__ldg(g.slot_keys + h) == key) return r;
+    h = (h + 1) & (uint64_t)g.slot_mask;
+  }
+  return -1;
+}
+
+__device__ __forceinline__ void unpack_chunk(const uint4& raw, int tdtype, float (&w)[8]) {
+  if (tdtype == XB_F32) {
+    w[0] = __uint_as_float(raw.x); w[1] = __uint_as_float(raw.y);
+    w[2] = __uint_as_float(raw.z); w[3] = __uint_as_float(raw.w);
+    w[4] = w[5] = w[6] = w[7] = 0.f;
+  } else {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 f = __half22float2(h[e]);
+      w[2 * e] = f.x; w[2 * e + 1] = f.y;
+    }
+  }
+}
+
+__device__ __forceinline__ uint4 load_row_chunk(const PoolGroupDev& g, int64_t row, int chunk) {
+  const uint4* p = reinterpret_cast<const uint4*>(g.weights + row * g.pitch) + chunk;
+  return __ldg(p);
+}
+
+__device__ __forceinline__ void store_out(void* out, int64_t idx, int out_dtype, float v) {
+  if (out_dtype == XB_F32) reinterpret_cast<float*>(out)[idx] = v;
+  else reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+}
+
+__global__ void __launch_bounds__(256) pool_kernel(const __grid_constant__ PoolParams p) {
+  const int64_t warp_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp_id >= p.total_warps) return;      // whole warp leaves together
+  const int lane = threadIdx.x & 31;
+  int gi = 0;
+  while (gi + 1 < p.n_groups && p.g[gi + 1].warp_begin <= warp_id) ++gi;
+  const PoolGroupDev& g = p.g[gi];
+
+  const int tl = g.tl, lpr = g.lpr;
+  const int team = lane / tl, tlane = lane % tl;
+  const int sub = tlane / lpr, chunk = tlane % lpr;
+  const int ns = tl / lpr;
+  const int epc = (g.tdtype == XB_F32) ? 4 : 8;          // elements per 16-byte chunk
+  const int col0 = chunk * epc;
+  const int64_t seg = (warp_id - g.warp_begin) * (32 / tl) + team;
+  const bool active = seg < g.batch;
+  const bool loads = active && g.has_table && col0 < g.dim;
+
+  int64_t start = 0, num = 0;
+  if (active) {
+    start = g.offsets[seg];
+    num = (int64_t)g.offsets[seg + 1] - start;
+  }
+
+  // kAssign items: clear the item's span first (the reference memsets it in
+  // InitProcess), then every fetched row is written straight to its slot.
+  bool any_assign = false;
+  for (int k = 0; k < g.n_items; ++k) {
+    const PoolItemDev& it = g.items[k];
+    if (it.udf != XB_UDF_ASSIGN) continue;
+    any_assign = true;
+    if (active) {
+      const int as = it.assign_stride ? it.assign_stride : g.dim;
+      const int64_t base = seg * it.stride;
+      for (int i = tlane; i < it.trunc_num * g.dim; i += tl) {
+        int t = i / g.dim, e = i - t * g.dim;
+        store_out(it.out, base + (int64_t)t * as + e, g.out_dtype, 0.f);
+      }
+    }
+  }
+  if (any_assign) __syncwarp();
+
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+
+  if (loads) {
+    const bool id64 = g.id_dtype == XB_I64;
+    for (int64_t j = sub; j < num; j += 2 * ns) {
+      // two ids in flight per sub-team
+      const int64_t j1 = j + ns;
+      const bool has1 = j1 < num;
+      int64_t key0 = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j)
+                          : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + start + j);
+      int64_t key1 = 0;
+      if (has1) key1 = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j1)
+                            : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + start + j1);
+      float v0 = g.values ? __ldg(g.values + start + j) : 1.f;
+      float v1 = (has1 && g.values) ? __ldg(g.values + start + j1) : 1.f;
+      int64_t r0 = lookup_row(g, key0);
+      int64_t r1 = has1 ? lookup_row(g, key1) : -1;
+      uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = make_uint4(0, 0, 0, 0);
+      if (r0 >= 0) raw0 = load_row_chunk(g, r0, chunk);
+      if (r1 >= 0) raw1 = load_row_chunk(g, r1, chunk);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int64_t r = u ? r1 : r0;
+        if (r < 0) continue;                    // missing key contributes nothing
+        const int64_t jj = u ? j1 : j;
+        const float v = u ? v1 : v0;
+        float w[8];
+        unpack_chunk(u ? raw1 : raw0, g.tdtype, w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = acc[e] + v * w[e];
+        for (int k = 0; k < g.n_items; ++k) {
+          const PoolItemDev& it = g.items[k];
+          if (it.udf != XB_UDF_ASSIGN) continue;
+          const int64_t tn = it.trunc_num;
+          int64_t slot;
+          if (it.trunc_dir == XB_TRUNC_ORDER) {
+            if (jj >= tn) continue;
+            slot = jj;
+          } else {
+            if (num - jj > tn) continue;
+            slot = tn - (num - jj);
+          }
+          const int as = it.assign_stride ? it.assign_stride : g.dim;
+          const int64_t o = seg * it.stride + slot * as + col0;
+          for (int e = 0; e < epc; ++e)
+            if (col0 + e < g.dim) store_out(it.out, o + e, g.out_dtype, v * w[e]);
+        }
+      }
+    }
+  }
+
+  // fixed-order combine of the sub-team partial sums
+  __syncwarp();
+  for (int off = lpr; off < tl; off <<= 1) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+  }
+
+  if (active && sub == 0 && col0 < g.dim) {
+    for (int k = 0; k < g.n_items; ++k) {
+      const PoolItemDev& it = g.items[k];
+      if (it.udf == XB_UDF_ASSIGN) continue;
+      float scale = 1.f;
+      if (it.udf == XB_UDF_AVG && num != 0) scale = (float)(1.0 / (double)num);
+      const int64_t o = seg * it.stride + col0;
+      for (int e = 0; e < epc; ++e) {
+        if (col0 + e < g.dim) {
+          float r = (it.udf == XB_UDF_AVG && num != 0) ? acc[e] * scale : acc[e];
+          store_out(it.out, o + e, g.out_dtype, r);
+        }
+      }
+    }
+  }
+}
+
+static int next_pow2(int v) { int p = 1; while (p < v) p <<= 1; return p; }
+
+}  // namespace xb
+
+using namespace xb;
+
+extern "C" int64_t xb_table_row_pitch(int32_t dim, int32_t dtype) {
+  size_t es = dtype_size(dtype);
+  if (es == 0 || dim <= 0) return 0;
+  return (int64_t)(((size_t)dim * es + 15) / 16 * 16);
+}
+
+extern "C" int xb_table_build_index_host(const int64_t* keys, int64_t rows, int64_t slots,
+                                         int64_t* slot_keys, int32_t* slot_rows) {
+  XB_REQUIRE(keys && slot_keys && slot_rows, XB_ERR_ARG, "xb_table_build_index_host: null pointer");
+  XB_REQUIRE(slots >= 2 * rows && (slots & (slots - 1)) == 0, XB_ERR_ARG,
+             "xb_table_build_index_host: slots=%lld must be a power of two >= 2*rows", (long long)slots);
+  XB_REQUIRE(rows < (int64_t)1 << 31, XB_ERR_LIMIT, "xb_table_build_index_host: rows beyond int32");
+  for (int64_t i = 0; i < slots; ++i) { slot_rows[i] = -1; slot_keys[i] = 0; }
+  const uint64_t mask = (uint64_t)slots - 1;
+  for (int64_t r = 0; r < rows; ++r) {
+    uint64_t x = (uint64_t)keys[r];
+    x ^= x >> 33; x *= 0xff51afd7ed558ccdULL; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ULL; x ^= x >> 33;
+    uint64_t h = x & mask;
+    while (slot_rows[h] != -1 && slot_keys[h] != keys[r]) h = (h + 1) & mask;
+    if (slot_rows[h] == -1) { slot_keys[h] = keys[r]; slot_rows[h] = (int32_t)r; }
+  }
+  return 0;
+}
+
+extern "C" int xb_table_create(xb_table_desc** out, int64_t rows, int32_t dim, int32_t dtype,
+                               const float* w, const int64_t* keys) {
+  XB_REQUIRE(out && w && rows > 0 && dim > 0, XB_ERR_ARG, "xb_table_create: bad arguments");
+  XB_REQUIRE(dtype == XB_F32 || dtype == XB_F16, XB_ERR_UNSUPPORTED, "xb_table_create: dtype %d", dtype);
+  const int64_t pitch = xb_table_row_pitch(dim, dtype);
+  xb_table_desc* t = (xb_table_desc*)calloc(1, sizeof(xb_table_desc));
+  t->rows = rows; t->dim = dim; t->dtype = dtype; t->row_pitch_bytes = pitch;
+  void* dw = nullptr;
+  cudaError_t e = cudaMalloc(&dw, (size_t)rows * pitch);
+  if (e != cudaSuccess) { free(t); return fail(XB_ERR_CUDA, "xb_table_create: cudaMalloc %s", cudaGetErrorString(e)); }
+  // stage in bounded host chunks so a multi-GB table never needs a second full copy
+  const int64_t chunk_rows = std::max<int64_t>(1, (64 << 20) / pitch);
+  std::vector<char> stage((size_t)chunk_rows * pitch);
+  for (int64_t r0 = 0; r0 < rows; r0 += chunk_rows) {
+    const int64_t n = std::min(chunk_rows, rows - r0);
+    memset(stage.data(), 0, (size_t)n * pitch);
+    for (int64_t r = 0; r < n; ++r) {
+      const float* src = w + (r0 + r) * dim;
+      if (dtype == XB_F32) memcpy(stage.data() + r * pitch, src, sizeof(float) * dim);
+      else {
+        __half* d = reinterpret_cast<__half*>(stage.data() + r * pitch);
+        for (int c = 0; c < dim; ++c) d[c] = __float2half_rn(src[c]);
+      }
+    }
+    e = cudaMemcpy((char*)dw + r0 * pitch, stage.data(), (size_t)n * pitch, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaFree(dw); free(t); return fail(XB_ERR_CUDA, "xb_table_create: copy %s", cudaGetErrorString(e)); }
+  }
+  t->weights = dw;
+  if (keys) {
+    int64_t slots = 16;
+    while (slots < 2 * rows) slots <<= 1;
+    std::vector<int64_t> sk((size_t)slots);
+    std::vector<int32_t> sr((size_t)slots);
+    int rc = xb_table_build_index_host(keys, rows, slots, sk.data(), sr.data());
+    if (rc) { cudaFree(dw); free(t); return rc; }
+    void *dk = nullptr, *dr = nullptr;
+    if (cudaMalloc(&dk, slots * 8) != cudaSuccess || cudaMalloc(&dr, slots * 4) != cudaSuccess ||
+        cudaMemcpy(dk, sk.data(), slots * 8, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(dr, sr.data(), slots * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+      cudaFree(dw); if (dk) cudaFree(dk); if (dr) cudaFree(dr); free(t);
+      return fail(XB_ERR_CUDA, "xb_table_create: index upload failed");
+    }
+    t->slot_keys = (const int64_t*)dk; t->slot_rows = (const int32_t*)dr; t->slots = slots;
+  }
+  *out = t;
+  return 0;
+}
+
+extern "C" void xb_table_destroy(xb_table_desc* t) {
+  if (!t) return;
+  if (t->weights) cudaFree((void*)t->weights);
+  if (t->slot_keys) cudaFree((void*)t->slot_keys);
+  if (t->slot_rows) cudaFree((void*)t->slot_rows);
+  free(t);
+}
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+extern "C" size_t xb_embedding_pool_scratch_bytes(const xb_pool_group* groups, int32_t n_groups) {
+  size_t total = 0;
+  for (int i = 0; i < n_groups; ++i)
+    if (!groups[i].segments_are_offsets) total += align256(((size_t)groups[i].batch + 1) * 4);
+  return total;
+}
+
+extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, void* scratch,
+                                 size_t scratch_bytes, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(groups && n_groups > 0, XB_ERR_ARG, "xb_embedding_pool: no groups");
+  XB_REQUIRE(n_groups <= XB_MAX_POOL_GROUPS, XB_ERR_LIMIT,
+             "xb_embedding_pool: %d groups in one call, at most %d", n_groups, XB_MAX_POOL_GROUPS);
+  XB_REQUIRE(xb_embedding_pool_scratch_bytes(groups, n_groups) <= scratch_bytes, XB_ERR_SCRATCH,
+             "xb_embedding_pool: scratch %zu bytes, need %zu", scratch_bytes,
+             xb_embedding_pool_scratch_bytes(groups, n_groups));
+  static thread_local PoolParams p;
+  static thread_local ScanParams sp;
+  p.n_groups = 0;
+  sp.n = 0;
+  size_t soff = 0;
+  int64_t warps = 0;
+  for (int i = 0; i < n_groups; ++i) {
+    const xb_pool_group& h = groups[i];
+    XB_REQUIRE(h.batch >= 0 && h.n_ids >= 0, XB_ERR_ARG, "xb_embedding_pool: group %d negative size", i);
+    if (h.batch == 0) continue;                // empty group: nothing to write
+    XB_REQUIRE(h.n_items >= 1 && h.n_items <= XB_MAX_POOL_ITEMS, XB_ERR_ARG,
+               "xb_embedding_pool: group %d has %d items (1..%d)", i, h.n_items, XB_MAX_POOL_ITEMS);
+    XB_REQUIRE(h.segments, XB_ERR_ARG, "xb_embedding_pool: group %d without segments", i);
+    XB_REQUIRE(h.n_ids == 0 || h.ids, XB_ERR_ARG, "xb_embedding_pool: group %d without ids", i);
+    XB_REQUIRE(h.id_dtype == XB_I64 || h.id_dtype == XB_I32, XB_ERR_UNSUPPORTED,
+               "xb_embedding_pool: group %d id dtype %d (int64 or int32)", i, h.id_dtype);
+    XB_REQUIRE(h.out_dtype == XB_F32 || h.out_dtype == XB_F16, XB_ERR_UNSUPPORTED,
+               "xb_embedding_pool: group %d output dtype %d", i, h.out_dtype);
+    XB_REQUIRE(h.batch < ((int64_t)1 << 31) && h.n_ids < ((int64_t)1 << 31), XB_ERR_LIMIT,
+               "xb_embedding_pool: group %d beyond int32 offsets", i);
+    PoolGroupDev& d = p.g[p.n_groups];
+    memset(&d, 0, sizeof(d));
+    d.has_table = h.table != nullptr;
+    XB_REQUIRE(h.dim >= 1 && h.dim <= 256, XB_ERR_LIMIT, "xb_embedding_pool: group %d dim %d (1..256)", i, h.dim);
+    const int dim = h.dim;
+    if (h.table) {
+      const xb_table_desc& t = *h.table;
+      XB_REQUIRE(t.dtype == XB_F32 || t.dtype == XB_F16, XB_ERR_UNSUPPORTED, "table dtype %d", t.dtype);
+      XB_REQUIRE(t.dim == dim, XB_ERR_ARG, "xb_embedding_pool: group %d dim %d, table dim %d", i, dim, t.dim);
+      XB_REQUIRE(t.row_pitch_bytes % 16 == 0 && t.row_pitch_bytes >= (int64_t)(t.dim * dtype_size(t.dtype)),
+                 XB_ERR_ARG, "xb_embedding_pool: table pitch %lld not a multiple of 16 covering dim %d",
+                 (long long)t.row_pitch_bytes, t.dim);
+      XB_REQUIRE(((uintptr_t)t.weights & 15) == 0, XB_ERR_ARG, "xb_embedding_pool: table not 16-byte aligned");
+      XB_REQUIRE(t.slot_keys == nullptr || (t.slots > 0 && (t.slots & (t.slots - 1)) == 0), XB_ERR_ARG,
+                 "xb_embedding_pool: index slots must be a power of two");
+      d.weights = (const char*)t.weights; d.rows = t.rows; d.pitch = t.row_pitch_bytes;
+      d.slot_keys = t.slot_keys; d.slot_rows = t.slot_rows; d.slot_mask = t.slots - 1;
+      d.tdtype = t.dtype;
+    } else {
+      d.tdtype = XB_F16;   // only fixes the lane geometry: nothing is fetched for a missing table
+    }
+    d.dim = dim;
+    const int epc = d.tdtype == XB_F32 ? 4 : 8;
+    d.lpr = next_pow2((dim + epc - 1) / epc);
+    if (d.lpr > 32) return fail(XB_ERR_LIMIT, "xb_embedding_pool: row too wide");
+    const double avg = (double)h.n_ids / (double)h.batch;
+    int ns = 1;
+    while (ns < 32 / d.lpr && ns < avg) ns <<= 1;
+    d.tl = d.lpr * ns;
+    d.ids = h.ids; d.values = h.values; d.batch = h.batch;
+    d.id_dtype = h.id_dtype; d.out_dtype = h.out_dtype; d.n_items = h.n_items;
+    for (int k = 0; k < h.n_items; ++k) {
+      const xb_pool_item& it = h.items[k];
+      XB_REQUIRE(it.out, XB_ERR_ARG, "xb_embedding_pool: group %d item %d without output", i, k);
+      XB_REQUIRE(it.udf >= XB_UDF_SUM && it.udf <= XB_UDF_ASSIGN, XB_ERR_UNSUPPORTED,
+                 "Unsupported udf type: %d", it.udf);
+      XB_REQUIRE(it.udf != XB_UDF_ASSIGN || it.trunc_num > 0, XB_ERR_ARG,
+                 "xb_embedding_pool: kAssign needs trunc_num > 0");
+      d.items[k].udf = it.udf; d.items[k].trunc_dir = it.trunc_dir; d.items[k].trunc_num = it.trunc_num;
+      d.items[k].assign_stride = it.udf == XB_UDF_ASSIGN ? it.assign_stride : 0;
+      d.items[k].out = it.out; d.items[k].stride = it.stride;
+    }
+    if (h.segments_are_offsets) {
+      d.offsets = h.segments;
+    } else {
+      int32_t* off = reinterpret_cast<int32_t*>((char*)scratch + soff);
+      soff += align256(((size_t)h.batch + 1) * 4);
+      sp.counts[sp.n] = h.segments; sp.offsets[sp.n] = off; sp.batch[sp.n] = h.batch; ++sp.n;
+      d.offsets = off;
+    }
+    d.warp_begin = warps;
+    const int spw = 32 / d.tl;
+    warps += (h.batch + spw - 1) / spw;
+    ++p.n_groups;
+  }
+  if (p.n_groups == 0) return 0;
+  p.total_warps = warps;
+  if (sp.n) {
+    scan_counts_kernel<<<sp.n, 256, 0, stream>>>(sp);
+    if (int rc = check_launch("scan_counts_kernel")) return rc;
+  }
+  const int64_t blocks = (warps + 7) / 8;
+  XB_REQUIRE(blocks < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_embedding_pool: too many segments");
+  pool_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
+  return check_launch("pool_kernel");
+}

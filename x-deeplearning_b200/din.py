@@ -1,0 +1,142 @@
+"""DIN-style CTR model on the C-ABI kernels: embedding pooling -> fused attention
+unit -> fused tower-input assembly -> three GEMMs with Dice / softmax epilogues.
+
+A thin driver used by bench.py and the parity tests; every step is one call
+into libxdlb200.so on the current CUDA stream. Buffers are allocated once per
+(requests, n_cand) shape, so a forward pass allocates nothing.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import capi, ops
+from .capi import check, lib
+
+
+class DinModel:
+    def __init__(self, model, device="cuda", engine=capi.XB_GEMM_AUTO):
+        self.dev = device
+        self.engine = engine
+        D = model["dims"]
+        self.D = D
+        t = torch.from_numpy
+        self.item = ops.Table(t(model["item"]), torch.float16, device=device)
+        self.cate = ops.Table(t(model["cate"]), torch.float16, device=device)
+        self.user = [ops.Table(t(w), torch.float16, device=device) for w in model["user"]]
+        a = model["att"]
+        self.att = ops.DinAttention(t(a["W0"]), t(a["b0"]), t(a["W1"]), t(a["b1"]), t(a["W2"]), float(a["b2"][0]),
+                                    dice0=[t(a["g0"]), t(a["m0"]), t(a["v0"])],
+                                    dice1=[t(a["g1"]), t(a["m1"]), t(a["v1"])], act=capi.XB_ACT_DICE, device=device)
+        tw = model["tower"]
+        self.tin = D["user_groups"] * D["emb"] + 5 * D["d"]
+        self.ldx = (self.tin + 7) // 8 * 8
+        f32 = lambda x: t(np.ascontiguousarray(x)).to(device=device, dtype=torch.float32)
+        # weights are constants: pack once to the K-major layout the tcgen05 engine reads
+        self.W1 = ops.pack_weight_kmajor(t(tw["W1"]).to(device), torch.float16, ldk=self.ldx)
+        self.W2 = ops.pack_weight_kmajor(t(tw["W2"]).to(device), torch.float16)
+        self.W3 = ops.pack_weight_kmajor(t(tw["W3"]).to(device), torch.float16)
+        self.b1, self.b2, self.b3 = f32(tw["b1"]), f32(tw["b2"]), f32(tw["b3"])
+        self.dice1 = [f32(x) for x in tw["dice1"]]
+        self.dice2 = [f32(x) for x in tw["dice2"]]
+        self._plans = {}
+
+    # -- per-shape buffers and the pooling plan ------------------------------------------------
+    def _plan(self, R, n_cand, n_hist, slot=0):
+        key = (R, n_cand, n_hist, slot)
+        if key in self._plans:
+            return self._plans[key]
+        D, dev = self.D, self.dev
+        e, d, T, G = D["emb"], D["d"], D["T"], D["user_groups"]
+        i64 = lambda n: torch.empty(n, dtype=torch.int64, device=dev)
+        p = {"R": R, "n_cand": n_cand}
+        p["user_ids"] = torch.empty((G, R), dtype=torch.int64, device=dev)
+        p["hist_item"], p["hist_cate"] = i64(n_hist), i64(n_hist)
+        p["cand_item"], p["cand_cate"] = i64(R * n_cand), i64(R * n_cand)
+        p["seq_len"] = torch.empty(R, dtype=torch.int32, device=dev)
+        p["ones_R"] = torch.ones(R, dtype=torch.int32, device=dev)
+        p["ones_C"] = torch.ones(R * n_cand, dtype=torch.int32, device=dev)
+        h = lambda *s: torch.empty(s, dtype=torch.float16, device=dev)
+        p["user_emb"], p["k"], p["q"] = h(R, G * e), h(R, T * d), h(R * n_cand, d)
+        p["att"], p["X"] = h(R * n_cand, d), h(R * n_cand, self.ldx)
+        p["y1"], p["y2"] = h(R * n_cand, D["tower"][0]), h(R * n_cand, D["tower"][1])
+        p["logit"] = torch.empty((R * n_cand, D["tower"][2]), dtype=torch.float32, device=dev)
+        p["prob"] = torch.empty_like(p["logit"])
+        S, A = capi.XB_UDF_SUM, capi.XB_UDF_ASSIGN
+        groups = []
+        for g in range(G):
+            groups.append(ops.make_group(self.user[g], p["user_ids"][g], None, p["ones_R"],
+                                         [dict(udf=S, out=p["user_emb"], col=g * e)], torch.float16))
+        # behaviour rows go straight into k [R, T, d]: item at column 0, category at column e of each step
+        groups.append(ops.make_group(self.item, p["hist_item"], None, p["seq_len"],
+                                     [dict(udf=A, trunc_num=T, trunc_dir=capi.XB_TRUNC_REVERSE, assign_stride=d,
+                                           out=p["k"], col=0)], torch.float16))
+        groups.append(ops.make_group(self.cate, p["hist_cate"], None, p["seq_len"],
+                                     [dict(udf=A, trunc_num=T, trunc_dir=capi.XB_TRUNC_REVERSE, assign_stride=d,
+                                           out=p["k"], col=e)], torch.float16))
+        groups.append(ops.make_group(self.item, p["cand_item"], None, p["ones_C"],
+                                     [dict(udf=S, out=p["q"], col=0)], torch.float16))
+        groups.append(ops.make_group(self.cate, p["cand_cate"], None, p["ones_C"],
+                                     [dict(udf=S, out=p["q"], col=e)], torch.float16))
+        p["pool"] = ops.PoolPlan(groups, device=dev)
+        self._plans[key] = p
+        return p
+
+    def h2d_bytes(self, req):
+        return int(req["user_ids"].nbytes + req["hist_item"].nbytes + req["hist_cate"].nbytes +
+                   req["cand_item"].nbytes + req["cand_cate"].nbytes + req["seq_len"].nbytes)
+
+    def stage(self, req):
+        """Pinned host copies of one batch of requests (what a serving front end would hold)."""
+        pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+        return {"requests": req["requests"], "n_cand": req["n_cand"],
+                "user_ids": pin(req["user_ids"].T), "hist_item": pin(req["hist_item"]),
+                "hist_cate": pin(req["hist_cate"]), "cand_item": pin(req["cand_item"]),
+                "cand_cate": pin(req["cand_cate"]), "seq_len": pin(req["seq_len"])}
+
+    def upload(self, staged, slot=0):
+        """Host -> device copy of one staged batch into buffer set `slot` (async on the current stream)."""
+        p = self._plan(staged["requests"], staged["n_cand"], staged["hist_item"].numel(), slot)
+        for name in ("user_ids", "hist_item", "hist_cate", "cand_item", "cand_cate", "seq_len"):
+            p[name].copy_(staged[name], non_blocking=True)
+        return p
+
+    def forward_device(self, p, att_engine=None, marks=None):
+        """The hot path on inputs already resident in HBM. Returns probabilities [R*n_cand, 2] fp32.
+        `marks`, when given, is a list of four CUDA events recorded on the current stream around the
+        pooling launches (0,1) and the attention kernel (2,3) for per-kernel timing."""
+        D = self.D
+        R, n_cand, T, d = p["R"], p["n_cand"], D["T"], D["d"]
+        s = ops.stream()
+        if marks:
+            marks[0].record()
+        p["pool"].run()
+        if marks:
+            marks[1].record()
+            marks[2].record()
+        # the kAssign rows are right-aligned: a request with seq_len < T has its valid steps at the end
+        self.att(p["q"], p["k"].view(R * T, d), R, n_cand, T, out=p["att"],
+                 engine=self.engine if att_engine is None else att_engine)
+        if marks:
+            marks[3].record()
+        check(lib().xb_din_tower_input(ops.ptr(p["user_emb"]), p["user_emb"].stride(0), ops.ptr(p["q"]), d,
+                                       ops.ptr(p["k"]), d, ops.ptr(p["att"]), d, ops.ptr(p["X"]), self.ldx, R,
+                                       n_cand, T, d, D["user_groups"] * D["emb"], s))
+        E = capi
+        ops.gemm(p["X"], self.W1, Y=p["y1"], bias=self.b1, trans_b=True, epilogue=E.XB_EPI_DICE, ep=self.dice1,
+                 engine=self.engine, K=self.ldx, M=R * n_cand, N=D["tower"][0])
+        ops.gemm(p["y1"], self.W2, Y=p["y2"], bias=self.b2, trans_b=True, epilogue=E.XB_EPI_DICE, ep=self.dice2,
+                 engine=self.engine, K=D["tower"][0], M=R * n_cand, N=D["tower"][1])
+        ops.gemm(p["y2"], self.W3, Y=p["logit"], bias=self.b3, trans_b=True, engine=self.engine,
+                 K=D["tower"][1], M=R * n_cand, N=D["tower"][2])
+        check(lib().xb_softmax(ops.ptr(p["logit"]), ops.ptr(p["prob"]), R * n_cand, D["tower"][2], 1, capi.XB_F32, s))
+        return p["prob"]
+
+    # kernels launched by one forward_device call (pool scan + pool + attention + assemble + 3 GEMM + softmax)
+    LAUNCHES_PER_FORWARD = 8
+
+    def forward(self, staged):
+        """End to end: host ids -> device -> probabilities back on the host."""
+        p = self.upload(staged)
+        prob = self.forward_device(p)
+        return prob.to("cpu", non_blocking=False)
