@@ -28,8 +28,9 @@ def test_activations(dtype, tol):
     c = lambda a: torch.from_numpy(a).to("cuda", dtype)
     r = lambda a: c(a).float().cpu().numpy()
     dx, y = c(x), torch.empty((37, 80), dtype=dtype, device="cuda")
+    dg, dmu, dvar = c(g), c(mu), c(var)          # keep the device tensors alive while their pointers are in use
     s, dt = ops.stream(), ops.dt(dx)
-    capi.check(L.xb_dice(ops.ptr(dx), ops.ptr(y), 37, 80, ops.ptr(c(g)), ops.ptr(c(mu)), ops.ptr(c(var)), 0, dt, s))
+    capi.check(L.xb_dice(ops.ptr(dx), ops.ptr(y), 37, 80, ops.ptr(dg), ops.ptr(dmu), ops.ptr(dvar), 0, dt, s))
     np.testing.assert_allclose(y.float().cpu().numpy(), orc.dice(r(x), r(g), r(mu), r(var)), rtol=tol, atol=tol)
     w = c(g)
     capi.check(L.xb_prelu(ops.ptr(dx), ops.ptr(y), 37 * 80, ops.ptr(w), 80, dt, dt, s))
@@ -38,8 +39,8 @@ def test_activations(dtype, tol):
     np.testing.assert_allclose(y.float().cpu().numpy(), orc.sigmoid(r(x)), rtol=tol, atol=tol)
     capi.check(L.xb_softmax(ops.ptr(dx), ops.ptr(y), 37, 80, 1, dt, s))
     np.testing.assert_allclose(y.float().cpu().numpy(), orc.softmax(r(x), 1), rtol=tol * 5, atol=tol)
-    capi.check(L.xb_batchnorm(ops.ptr(dx), ops.ptr(y), 37 * 80, 80, ops.ptr(c(g)), ops.ptr(c(mu)), ops.ptr(c(mu)),
-                              ops.ptr(c(var)), 0.001, 0, dt, s))
+    capi.check(L.xb_batchnorm(ops.ptr(dx), ops.ptr(y), 37 * 80, 80, ops.ptr(dg), ops.ptr(dmu), ops.ptr(dmu),
+                              ops.ptr(dvar), 0.001, 0, dt, s))
     np.testing.assert_allclose(y.float().cpu().numpy(), orc.batchnorm(r(x), r(g), r(mu), r(mu), r(var)), rtol=tol * 5, atol=tol * 5)
 
 
