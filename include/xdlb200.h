@@ -135,6 +135,29 @@ size_t xb_embedding_pool_scratch_bytes(const xb_pool_group* groups, int32_t n_gr
 int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, void* scratch,
                       size_t scratch_bytes, xb_stream_t stream);
 
+/* xb_embedding_pool for callers that cannot hand over device scratch: an operator
+ * that runs inside someone else's memory plan (a serving process whose device
+ * memory was carved up at start-up, a plug-in that is given input and output
+ * buffers and nothing else, code running while the framework's allocator is
+ * locked) has nowhere to get the offsets buffer from and may not call cudaMalloc.
+ * This entry point has no counterpart in the reference. It keeps the
+ * counts->offsets scratch in a 1 MiB array that is part of the library image
+ * (every GPU that loads the library holds that 1 MiB until the process exits),
+ * and it calls no allocator of any kind.
+ *   - Limit: the groups that pass counts may need at most
+ *     xb_embedding_pool_static_max_bytes() in total (each such group takes
+ *     4*(batch+1) bytes rounded up to 256); a larger request is rejected with
+ *     XB_ERR_LIMIT. Groups that pass exclusive offsets need none.
+ *   - The first call on each device looks the array's address up; make that
+ *     first call outside any stream capture.
+ *   - All calls share the one array and it keeps whatever the previous call
+ *     left. Nothing in it has to start at zero (every offset that is read is
+ *     written by the same call first), but two calls that overlap on the GPU
+ *     (different streams, or another thread) race on it: serialise them.
+ * Inputs, outputs and results are exactly those of xb_embedding_pool. */
+size_t xb_embedding_pool_static_max_bytes(void);
+int xb_embedding_pool_static(const xb_pool_group* groups, int32_t n_groups, xb_stream_t stream);
+
 /* ------------------------------------------------------------------------- */
 /* GEMM family with fused bias + activation epilogue.
  * Replaces GemmOp::RunOnDevice (blaze/blaze/operator/op/gemm_op.h:33-107),

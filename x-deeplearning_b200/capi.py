@@ -68,6 +68,8 @@ SYMBOLS = {
     "xb_table_build_index_host": (i32, [vp, i64, i64, vp, vp]),
     "xb_embedding_pool_scratch_bytes": (C.c_size_t, [C.POINTER(PoolGroup), i32]),
     "xb_embedding_pool": (i32, [C.POINTER(PoolGroup), i32, vp, C.c_size_t, vp]),
+    "xb_embedding_pool_static_max_bytes": (C.c_size_t, []),
+    "xb_embedding_pool_static": (i32, [C.POINTER(PoolGroup), i32, vp]),
     "xb_gemm": (i32, [C.POINTER(GemmArgs), vp]),
     "xb_gemm_uses_tcgen05": (i32, [C.POINTER(GemmArgs)]),
     "xb_pack_weight_kmajor": (i32, [vp, i32, i32, i32, i64, vp, i32, i64, i32, i64, i64, vp]),

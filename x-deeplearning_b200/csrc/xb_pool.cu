@@ -442,3 +442,34 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
   pool_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
   return check_launch("pool_kernel");
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant: the counts->offsets scratch lives in a file-scope
+// device array instead of caller-provided memory.
+#define XB_POOL_STATIC_SCRATCH_BYTES (1u << 20)
+static __device__ __align__(256) unsigned char g_pool_static_scratch[XB_POOL_STATIC_SCRATCH_BYTES];
+
+extern "C" size_t xb_embedding_pool_static_max_bytes(void) { return XB_POOL_STATIC_SCRATCH_BYTES; }
+
+extern "C" int xb_embedding_pool_static(const xb_pool_group* groups, int32_t n_groups, xb_stream_t stream) {
+  // In host code the array's name is only a handle; its device address has to be asked for,
+  // once per device, while that device is current.
+  static void* dev_ptr[64] = {nullptr};
+  int dev = -1;
+  XB_CUDA(cudaGetDevice(&dev));
+  XB_REQUIRE(dev >= 0 && dev < 64, XB_ERR_LIMIT, "xb_embedding_pool_static: device ordinal %d out of range", dev);
+  if (dev_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_pool_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(XB_ERR_CUDA, "xb_embedding_pool_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    dev_ptr[dev] = p;
+  }
+  XB_REQUIRE(groups && n_groups > 0, XB_ERR_ARG, "xb_embedding_pool_static: no groups");
+  const size_t need = xb_embedding_pool_scratch_bytes(groups, n_groups);
+  XB_REQUIRE(need <= XB_POOL_STATIC_SCRATCH_BYTES, XB_ERR_LIMIT,
+             "xb_embedding_pool_static: these groups need %zu bytes of offset scratch, the built-in buffer holds %u "
+             "(pass exclusive offsets instead of counts, split the call, or use xb_embedding_pool)",
+             need, XB_POOL_STATIC_SCRATCH_BYTES);
+  return xb_embedding_pool(groups, n_groups, dev_ptr[dev], XB_POOL_STATIC_SCRATCH_BYTES, stream);
+}
