@@ -294,6 +294,50 @@ def run_reference(args):
     }))
 
 
+def run_micro(args):
+    """Small stand-alone cases of single kernels, sized for a profiler capture that ends by itself
+    (a few launches, inputs larger than L2 where DRAM figures matter, well under a few GB)."""
+    import numpy as np
+    import torch
+    import pkg
+    pkg.load()
+    from x_deeplearning_b200 import capi, din, ops, workloads
+    torch.cuda.set_device(0)
+    reps = args.steps
+    if args.micro == "att":
+        model = workloads.din_model(seed=0, item_rows=200_000, cate_rows=10_000, user_rows=10_000, emb_sigma=0.5)
+        net = din.DinModel(model)
+        p = net.upload(net.stage(workloads.din_requests(model, 3, args.requests, N_CAND)))
+        net.forward_device(p)
+        torch.cuda.synchronize()
+        for _ in range(reps):
+            net.att(p["q"], p["k"].view(-1, 36), p["R"], N_CAND, T_STEPS, out=p["att"])
+    elif args.micro == "pool":
+        cfg = workloads.embedding_config(seed=0, batch=65536)
+        table = ops.Table(torch.from_numpy(cfg["table"]), torch.float32)
+        y = torch.zeros((65536, 320), device="cuda")
+        groups = [ops.make_group(table, torch.from_numpy(g["ids"]).cuda(), torch.from_numpy(g["values"]).cuda(),
+                                 torch.from_numpy(g["offsets"]).cuda(), [dict(udf=0, out=y, col=16 * i)],
+                                 torch.float32, segments_are_offsets=True) for i, g in enumerate(cfg["groups"])]
+        plan = ops.PoolPlan(groups)
+        for _ in range(reps):
+            plan.run()
+    elif args.micro == "gemm":
+        P, M, K, N = 8, 65536, 256, 128            # the parallel-GEMM configuration with M scaled 16x (A = 268 MB)
+        A = torch.randn((P, M, K), device="cuda", dtype=torch.float16)
+        Wk = torch.randn((P, N, K), device="cuda", dtype=torch.float16) / 16
+        bias = torch.randn((P, N), device="cuda") * 0.01
+        slope = torch.full((1,), 0.25, device="cuda")
+        Y = torch.empty((M, P * N), device="cuda", dtype=torch.float16)
+        for _ in range(reps):
+            ops.gemm(A, Wk, Y=Y, bias=bias, trans_b=True, batch=P, M=M, N=N, K=K, lda=K, ldb=K, ldy=P * N,
+                     strides=(M * K, N * K, N, N), bias_kind=capi.XB_BIAS_ROW, epilogue=capi.XB_EPI_PRELU,
+                     ep=(slope, None, None), ep_count=1, engine=capi.XB_GEMM_TCGEN05)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    print(json.dumps({"micro": args.micro, "launches": reps, "status": "ok"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -304,7 +348,11 @@ def main():
     ap.add_argument("--batches", type=int, default=8, help="distinct pre-generated request batches that are cycled")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and pooling side measurements")
+    ap.add_argument("--micro", choices=["att", "pool", "gemm"], help="run --steps launches of one kernel on a small case "
+                    "(for profiler captures) instead of the benchmark")
     args = ap.parse_args()
+    if args.micro:
+        return run_micro(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
