@@ -304,12 +304,14 @@ def run_micro(args):
     from x_deeplearning_b200 import capi, din, ops, workloads
     torch.cuda.set_device(0)
     reps = args.steps
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if args.micro == "att":
         model = workloads.din_model(seed=0, item_rows=200_000, cate_rows=10_000, user_rows=10_000, emb_sigma=0.5)
         net = din.DinModel(model)
         p = net.upload(net.stage(workloads.din_requests(model, 3, args.requests, N_CAND)))
         net.forward_device(p)
         torch.cuda.synchronize()
+        t0.record()
         for _ in range(reps):
             net.att(p["q"], p["k"].view(-1, 36), p["R"], N_CAND, T_STEPS, out=p["att"])
     elif args.micro == "pool":
@@ -320,6 +322,8 @@ def run_micro(args):
                                  torch.from_numpy(g["offsets"]).cuda(), [dict(udf=0, out=y, col=16 * i)],
                                  torch.float32, segments_are_offsets=True) for i, g in enumerate(cfg["groups"])]
         plan = ops.PoolPlan(groups)
+        plan.run()
+        t0.record()
         for _ in range(reps):
             plan.run()
     elif args.micro == "gemm":
@@ -329,13 +333,19 @@ def run_micro(args):
         bias = torch.randn((P, N), device="cuda") * 0.01
         slope = torch.full((1,), 0.25, device="cuda")
         Y = torch.empty((M, P * N), device="cuda", dtype=torch.float16)
+        run = lambda: ops.gemm(A, Wk, Y=Y, bias=bias, trans_b=True, batch=P, M=M, N=N, K=K, lda=K, ldb=K, ldy=P * N,
+                               strides=(M * K, N * K, N, N), bias_kind=capi.XB_BIAS_ROW, epilogue=capi.XB_EPI_PRELU,
+                               ep=(slope, None, None), ep_count=1, engine=capi.XB_GEMM_TCGEN05)
+        run()
+        t0.record()
         for _ in range(reps):
             ops.gemm(A, Wk, Y=Y, bias=bias, trans_b=True, batch=P, M=M, N=N, K=K, lda=K, ldb=K, ldy=P * N,
                      strides=(M * K, N * K, N, N), bias_kind=capi.XB_BIAS_ROW, epilogue=capi.XB_EPI_PRELU,
                      ep=(slope, None, None), ep_count=1, engine=capi.XB_GEMM_TCGEN05)
+    t1.record()
     torch.cuda.synchronize()
     assert ops.device_status() == 0
-    print(json.dumps({"micro": args.micro, "launches": reps, "status": "ok"}))
+    print(json.dumps({"micro": args.micro, "launches": reps, "status": "ok", "ms_per_launch": t0.elapsed_time(t1) / reps}))
 
 
 def main():

@@ -14,6 +14,7 @@
 // tcgen05.ld (one output row per thread), apply bias and activation and store
 // with an arbitrary row stride, which is what lets parallel branches write
 // side by side into one wide output (axis-1 concat) or stacked (axis 0).
+#include <algorithm>
 #include <cstring>
 
 #include "xb_common.cuh"
@@ -31,7 +32,7 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;
 
 struct UmmaGemmParams {
-  int M, N, K, block_n, tmem_cols;
+  int M, N, K, block_n, tmem_cols, tiles_m, tiles_n, batch;
   float alpha, beta;
   int a_batched, b_batched;
   const void* bias; int64_t ldbias, stride_bias; int bias_kind, bias_dtype;
@@ -61,8 +62,26 @@ __device__ __forceinline__ void store_row16(TOut* dst, const float (&v)[16], int
   }
 }
 
+// bias and per-column activation parameters of 16 consecutive columns, as fp32
+__device__ __forceinline__ void load16(const float* __restrict__ src, int n_valid, float (&dst)[16]) {
+  if (n_valid == 16 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const float4* s4 = reinterpret_cast<const float4*>(src);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 t = __ldg(s4 + i);
+      dst[4 * i] = t.x; dst[4 * i + 1] = t.y; dst[4 * i + 2] = t.z; dst[4 * i + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) dst[i] = i < n_valid ? __ldg(src + i) : 0.f;
+  }
+}
+
+constexpr int EPI_WARPS = 8;
+constexpr int GEMM_THREADS = 64 + EPI_WARPS * 32;
+
 template <typename TOut>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ UmmaGemmParams p) {
   using namespace umma;
@@ -73,16 +92,19 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
-  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BLOCK_M, n0 = blockIdx.y * p.block_n, b = blockIdx.z;
   const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int64_t tiles_mn = (int64_t)p.tiles_m * p.tiles_n;
+  const int64_t total_tiles = tiles_mn * p.batch;
+  const uint32_t acc_stride = (uint32_t)p.tmem_cols / 2;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-    mbar_init(smem_u32(&acc_bar), 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&acc_full[s]), 1); mbar_init(smem_u32(&acc_empty[s]), EPI_WARPS * 32); }
     fence_barrier_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -91,80 +113,135 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_acc = tmem_base_s;
+  const uint32_t tmem_base = tmem_base_s;
 
+  // every role walks the same tile sequence: m fastest, so concurrent CTAs share the B tile in L2
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, 1)) break;
-        mbar_arrive_expect_tx(smem_u32(&full_bar[s]), (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
-        tma_load_3d(smem_u32(smem_a + s * A_STAGE_BYTES), &map_a, smem_u32(&full_bar[s]), kb * BLOCK_K, m0,
-                    p.a_batched ? b : 0);
-        tma_load_3d(smem_u32(smem_b + s * b_stage_bytes), &map_b, smem_u32(&full_bar[s]), kb * BLOCK_K, n0,
-                    p.b_batched ? b : 0);
+      int kbg = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int b = (int)(tile / tiles_mn);
+        const int64_t rem = tile - (int64_t)b * tiles_mn;
+        const int m0 = (int)(rem % p.tiles_m) * BLOCK_M, n0 = (int)(rem / p.tiles_m) * p.block_n;
+        for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
+          const int s = kbg % STAGES;
+          const uint32_t ph = (uint32_t)(kbg / STAGES) & 1u;
+          ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, 1);
+          if (!ok) break;
+          mbar_arrive_expect_tx(smem_u32(&full_bar[s]), (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
+          tma_load_3d(smem_u32(smem_a + s * A_STAGE_BYTES), &map_a, smem_u32(&full_bar[s]), kb * BLOCK_K, m0,
+                      p.a_batched ? b : 0);
+          tma_load_3d(smem_u32(smem_b + s * b_stage_bytes), &map_b, smem_u32(&full_bar[s]), kb * BLOCK_K, n0,
+                      p.b_batched ? b : 0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      int kbg = 0, it = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-        ok = mbar_wait(smem_u32(&full_bar[s]), ph, 2);
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int as = it & 1;
+        ok = mbar_wait(smem_u32(&acc_empty[as]), ((uint32_t)(it >> 1) & 1u) ^ 1u, 4);   // epilogue drained it
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(smem_a + s * A_STAGE_BYTES);
-        const uint32_t b_addr = smem_u32(smem_b + s * b_stage_bytes);
+        const uint32_t tmem_acc = tmem_base + as * acc_stride;
+        for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
+          const int s = kbg % STAGES;
+          const uint32_t ph = (uint32_t)(kbg / STAGES) & 1u;
+          ok = mbar_wait(smem_u32(&full_bar[s]), ph, 2);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem_a + s * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(smem_b + s * b_stage_bytes);
 #pragma unroll
-        for (int k = 0; k < BLOCK_K / 16; ++k) {
-          const uint64_t da = make_desc_sw128(a_addr + k * 32, 1024);
-          const uint64_t db = make_desc_sw128(b_addr + k * 32, 1024);
-          mma_f16_ss(tmem_acc, da, db, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BLOCK_K / 16; ++k) {
+            const uint64_t da = make_desc_sw128(a_addr + k * 32, 1024);
+            const uint64_t db = make_desc_sw128(b_addr + k * 32, 1024);
+            mma_f16_ss(tmem_acc, da, db, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit(smem_u32(&empty_bar[s]));     // slot free once these MMAs have read it
         }
-        mma_commit(smem_u32(&empty_bar[s]));     // slot free once these MMAs have read it
+        mma_commit(smem_u32(&acc_full[as]));       // accumulator complete
       }
-      mma_commit(smem_u32(&acc_bar));            // accumulator complete
     }
   } else {
-    // epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32)
+    // epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32); the two warpgroups split the columns
+    const int ew = warp - 2;
     const int q = warp & 3;
+    const int half_id = ew >> 2;
     const int row = q * 32 + lane;
-    const int gm = m0 + row;
-    const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_bar), 0, 3));   // warp-uniform
-    tc_fence_after_sync();
-    if (ok) {
-      EpiParams epi = p.epi;
-      if (epi.a) epi.a += (int64_t)b * p.stride_ep;
-      if (epi.b) epi.b += (int64_t)b * p.stride_ep;
-      if (epi.c) epi.c += (int64_t)b * p.stride_ep;
-      TOut* yrow = reinterpret_cast<TOut*>(p.Y) + (int64_t)b * p.stride_y + (int64_t)gm * p.ldy;
-      const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0) && ((p.ldy * sizeof(TOut)) % 16 == 0) &&
+    // 16-column chunks [c_begin, c_end) of this warpgroup
+    const int chunks = p.block_n / 16;
+    const int c_begin = half_id ? (chunks + 1) / 2 : 0, c_end = half_id ? chunks : (chunks + 1) / 2;
+    const bool vec_base = ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0) && ((p.ldy * sizeof(TOut)) % 16 == 0) &&
                           ((p.stride_y * sizeof(TOut)) % 16 == 0);
-      for (int c = 0; c < p.block_n; c += 16) {
+    int it = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const int b = (int)(tile / tiles_mn);
+      const int64_t rem = tile - (int64_t)b * tiles_mn;
+      const int m0 = (int)(rem % p.tiles_m) * BLOCK_M, n0 = (int)(rem / p.tiles_m) * p.block_n;
+      const int as = it & 1;
+      const int gm = m0 + row;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_full[as]), (uint32_t)(it >> 1) & 1u, 3));
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tmem_acc = tmem_base + as * acc_stride + ((uint32_t)(q * 32) << 16);
+      const float* ea = p.epi.a ? p.epi.a + (int64_t)b * p.stride_ep : nullptr;
+      const float* eb = p.epi.b ? p.epi.b + (int64_t)b * p.stride_ep : nullptr;
+      const float* ec = p.epi.c ? p.epi.c + (int64_t)b * p.stride_ep : nullptr;
+      TOut* yrow = reinterpret_cast<TOut*>(p.Y) + (int64_t)b * p.stride_y + (int64_t)gm * p.ldy;
+      for (int ci = c_begin; ci < c_end; ++ci) {
+        const int c = ci * 16;
         float v[16];
-        tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);   // whole warp, uniform
+        tmem_ld16(tmem_acc + (uint32_t)c, v);             // whole warp, uniform
         const int gn0 = n0 + c;
         int valid = p.N - gn0;
         valid = valid > 16 ? 16 : valid;
-        if (gm < p.M && valid > 0) {
+        if (valid <= 0) continue;                          // uniform across the warp
+        float bias[16];
+        if (p.bias_kind == XB_BIAS_ROW && p.bias_dtype == XB_F32) {
+          load16(reinterpret_cast<const float*>(p.bias) + (int64_t)b * p.stride_bias + gn0, valid, bias);
+        } else if (p.bias_kind == XB_BIAS_NONE) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            if (i < valid) {
-              const int gn = gn0 + i;
-              float x = p.alpha * v[i];
-              if (p.bias_kind == XB_BIAS_ROW)
-                x += p.beta * load_as_f32(p.bias, (int64_t)b * p.stride_bias + gn, p.bias_dtype);
-              else if (p.bias_kind == XB_BIAS_FULL)
-                x += p.beta * load_as_f32(p.bias, (int64_t)b * p.stride_bias + (int64_t)gm * p.ldbias + gn,
-                                          p.bias_dtype);
-              v[i] = apply_epilogue(epi, x, gn);
-            }
-          }
-          store_row16<TOut>(yrow + gn0, v, valid, vec_ok && ((gn0 * sizeof(TOut)) % 16 == 0));
+          for (int i = 0; i < 16; ++i) bias[i] = 0.f;
+        } else {
+          const int64_t base = (int64_t)b * p.stride_bias + (p.bias_kind == XB_BIAS_FULL ? (int64_t)gm * p.ldbias : 0) + gn0;
+          const bool row_ok = p.bias_kind == XB_BIAS_ROW || gm < p.M;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) bias[i] = (row_ok && i < valid) ? load_as_f32(p.bias, base + i, p.bias_dtype) : 0.f;
         }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = fmaf(p.alpha, v[i], p.beta * bias[i]);
+        if (p.epi.kind == XB_EPI_PRELU) {
+          if (p.epi.count == 1) {
+            const float w = __ldg(ea);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = act_prelu(v[i], w);
+          } else {
+            float w[16];
+            load16(ea + gn0, valid, w);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = act_prelu(v[i], w[i]);
+          }
+        } else if (p.epi.kind == XB_EPI_DICE) {
+          float g[16], mu[16], var[16];
+          load16(ea + gn0, valid, g);
+          load16(eb + gn0, valid, mu);
+          load16(ec + gn0, valid, var);
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            v[i] = act_dice(v[i], g[i], mu[i], p.epi.nosqrt ? __fdividef(1.f, var[i]) : rsqrtf(var[i] + 1e-8f));
+        } else if (p.epi.kind == XB_EPI_SIGMOID) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = act_sigmoid(v[i]);
+        }
+        if (gm < p.M) store_row16<TOut>(yrow + gn0, v, valid, vec_base && ((gn0 * sizeof(TOut)) % 16 == 0));
       }
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&acc_empty[as]));
     }
   }
 
@@ -172,7 +249,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_acc, (uint32_t)p.tmem_cols);
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
 }
 
@@ -234,7 +311,7 @@ int launch_umma(const CUtensorMap& ma, const CUtensorMap& mb, const UmmaGemmPara
     XB_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_set = true;
   }
-  gemm_umma_kernel<TOut><<<grid, 192, smem, s>>>(ma, mb, p);
+  gemm_umma_kernel<TOut><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, p);
   return check_launch("gemm_umma_kernel");
 }
 
@@ -243,8 +320,8 @@ int gemm_umma(const xb_gemm_args& a, cudaStream_t stream) {
   memset(&p, 0, sizeof(p));
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.block_n = pick_block_n(a.N);
-  p.tmem_cols = 32;
-  while (p.tmem_cols < p.block_n) p.tmem_cols <<= 1;
+  p.tmem_cols = 64;                                      // two accumulator stages, each at least 32 columns
+  while (p.tmem_cols < 2 * p.block_n) p.tmem_cols <<= 1;
   p.alpha = a.alpha; p.beta = a.beta;
   p.a_batched = a.stride_a != 0; p.b_batched = a.stride_b != 0;
   p.bias = a.bias; p.ldbias = a.ldbias; p.stride_bias = a.stride_bias;
@@ -257,8 +334,13 @@ int gemm_umma(const xb_gemm_args& a, cudaStream_t stream) {
   CUtensorMap ma, mb;
   if (int rc = make_map(&ma, a.A, is_bf16, a.K, a.M, a.lda, p.a_batched ? a.batch : 1, a.stride_a, BLOCK_M)) return rc;
   if (int rc = make_map(&mb, a.B, is_bf16, a.K, a.N, a.ldb, p.b_batched ? a.batch : 1, a.stride_b, p.block_n)) return rc;
-  dim3 grid((a.M + BLOCK_M - 1) / BLOCK_M, (a.N + p.block_n - 1) / p.block_n, a.batch);
-  XB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, XB_ERR_LIMIT, "xb_gemm: N tiles or batch beyond the grid limit");
+  p.tiles_m = (a.M + BLOCK_M - 1) / BLOCK_M;
+  p.tiles_n = (a.N + p.block_n - 1) / p.block_n;
+  p.batch = a.batch;
+  const int64_t total = (int64_t)p.tiles_m * p.tiles_n * p.batch;
+  // persistent: one CTA per SM walks the tiles; the accumulator is double-buffered in TMEM so the
+  // epilogue of one tile overlaps the loads and MMAs of the next
+  dim3 grid((unsigned)std::min<int64_t>(total, sm_count()));
   const size_t smem = (size_t)STAGES * (A_STAGE_BYTES + p.block_n * BLOCK_K * 2) + 1024;
   switch (a.y_dtype) {
     case XB_F16: return launch_umma<__half>(ma, mb, p, grid, smem, stream);
