@@ -257,6 +257,21 @@ int xb_din_tower_input(const void* user, int64_t ldu, const void* q, int64_t ldq
                        xb_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
+/* Recurrent layers of the DIEN-style model. x, y [batch, T, H] in `dtype` (XB_F32 or
+ * XB_F16); weights and biases in the same dtype; H <= 64.
+ * xb_gru replaces GRUOp (blaze/blaze/operator/op/gru_op.h:41-158, CPU kernel
+ * gru_op.cc:33-93, CUDA kernels gru_op.cu): i2h, h2h [H, 3H] with gate order
+ * (r, z, candidate), h' = c + z (h - c); leading steps whose first H input
+ * pre-activations are all zero emit zeros.
+ * xb_augru has no operator in Blaze; it follows the training-side cell
+ * (xdl-algorithm-solution/DIEN/script/utils.py:139-207): Wg [2H, 2H], Wc [2H, H],
+ * att [batch, T] attention scores, u' = (1 - att) u, h' = u' h + (1 - u') c. */
+int xb_gru(const void* x, void* y, int64_t batch, int32_t T, int32_t H, const void* i2h, const void* h2h,
+           const void* i2h_bias, const void* h2h_bias, int32_t dtype, xb_stream_t stream);
+int xb_augru(const void* x, const void* att, void* y, int64_t batch, int32_t T, int32_t H, const void* Wg,
+             const void* bg, const void* Wc, const void* bc, int32_t dtype, xb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
 /* Stand-alone operators for graphs that were not fused. x/y share `dtype`;
  * per-column parameters share it too (Blaze keeps them in the model dtype). */
 /* DiceOp, blaze/blaze/operator/op/dice_op.h:41-98 */

@@ -75,6 +75,8 @@ SYMBOLS = {
     "xb_pack_weight_kmajor": (i32, [vp, i32, i32, i32, i64, vp, i32, i64, i32, i64, i64, vp]),
     "xb_din_attention": (i32, [C.POINTER(DinAttArgs), vp]),
     "xb_din_tower_input": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, vp]),
+    "xb_gru": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp, i32, vp]),
+    "xb_augru": (i32, [vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, i32, vp]),
     "xb_dice": (i32, [vp, vp, i64, i32, vp, vp, vp, i32, i32, vp]),
     "xb_prelu": (i32, [vp, vp, i64, vp, i64, i32, i32, vp]),
     "xb_sigmoid": (i32, [vp, vp, i64, i32, vp]),

@@ -1,0 +1,68 @@
+/* C API of the B200 host runtime: the entry points of Blaze's
+ * blaze/blaze/api/c_api/c_api_predictor.h and c_api_error.h with the same names
+ * and argument meaning (0 = success, -1 = failure, reason through
+ * Blaze_GetLastErrorString), plus Blaze_B200_* extensions for registering
+ * in-memory embedding tables and text NetDefs (used by tests and benchmarks). */
+#ifndef BLAZE_B200_C_API_PREDICTOR_H_
+#define BLAZE_B200_C_API_PREDICTOR_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* PredictorManagerHandle;
+typedef void* PredictorHandle;
+
+const char* Blaze_GetLastErrorString(void);
+
+int Blaze_InitScheduler(int enable_batching, int max_batch_size, int batch_timeout_micros, int num_threads_for_cpu,
+                        int num_threads_for_cuda, int num_threads_for_pipe);
+int Blaze_PredictorManagerCreate(PredictorManagerHandle* handle);
+int Blaze_PredictorManagerDelete(PredictorManagerHandle handle);
+int Blaze_PredictorManagerSetDataType(PredictorManagerHandle handle, int data_type);
+int Blaze_PredictorManagerSetRunMode(PredictorManagerHandle handle, const char* run_mode);
+int Blaze_LoadSparseModelWeight(PredictorManagerHandle handle, const char* sparse_model_weight_file);
+int Blaze_PredcitorManagerLoadModel(PredictorManagerHandle handle, const char* blaze_model_file, int optimization_pass);
+int Blaze_PredictorManagerLoadDeepNetModel(PredictorManagerHandle handle, const char* deepnet_conf_file,
+                                           const char* deepnet_param_file, int optimization_pass);
+int Blaze_PredictorCreate(PredictorManagerHandle predictor_mgr, int device_type, int device_id, PredictorHandle* handle);
+int Blaze_PredictorDelete(PredictorHandle handle);
+int Blaze_PredictorReshapeInput(PredictorHandle handle, const char* name, const int* data, int num);
+int Blaze_PredictorFeed(PredictorHandle handle, const char* name, void* data, int len);
+int Blaze_PredictorForward(PredictorHandle handle);
+int Blaze_PredictorOutputShape(PredictorHandle handle, const char* name, size_t* ndim, size_t** shape);
+int Blaze_PredictorOutputDataType(PredictorHandle handle, const char* name, int* data_type);
+int Blaze_PredictorOutput(PredictorHandle handle, const char* name, void* data, size_t len);
+int Blaze_PredictorParamName(PredictorHandle handle, size_t* ndim, const char*** name);
+int Blaze_PredictorParamShape(PredictorHandle handle, const char* name, size_t* ndim, size_t** shape);
+int Blaze_PredictorParamDataType(PredictorHandle handle, const char* name, int* data_type);
+int Blaze_PredictorParam(PredictorHandle handle, const char* name, void* data, size_t len);
+int Blaze_PredictorListInputNames(PredictorHandle handle, size_t* ndim, const char*** names);
+int Blaze_PredictorListOutputNames(PredictorHandle handle, size_t* ndim, const char*** names);
+int Blaze_PredictorRegisterObservers(PredictorHandle handle, size_t ndim, const char** names);
+int Blaze_PredictorDumpObservers(PredictorHandle handle, size_t* ndim, const char*** key, const char*** value);
+
+/* ---- extensions ---------------------------------------------------------- */
+/* Model given as NetDef text (protobuf text format) instead of a file. */
+int Blaze_B200_LoadModelFromText(PredictorManagerHandle handle, const char* netdef_text, int optimization_pass);
+/* Sparse puller of the given registered type ("b200_sparse_puller", "qed_sparse_puller",
+ * "mock_sparse_puller"); uri may be NULL for types that need no file. */
+int Blaze_B200_LoadSparseModelWeight(PredictorManagerHandle handle, const char* uri, const char* type);
+/* Registers an in-memory fp32 [rows, dim] table (host pointers) with the manager's puller
+ * (type b200/qed); storage_dtype 1 = fp32, 12 = fp16; keys may be NULL (row numbers). */
+int Blaze_B200_AddTable(PredictorManagerHandle handle, const char* table_name, int64_t rows, int dim,
+                        int storage_dtype, const float* weights, const int64_t* keys);
+/* Feed whose source is already in device memory (no host staging). */
+int Blaze_B200_PredictorFeedDevice(PredictorHandle handle, const char* name, const void* device_data, size_t len);
+/* Device pointer of an output (valid until the next Forward); no device-to-host copy. */
+int Blaze_B200_PredictorOutputDevice(PredictorHandle handle, const char* name, void** device_data, size_t* len);
+/* Number of kernel-library calls issued by the last Forward. */
+int Blaze_B200_PredictorLastLaunchCount(PredictorHandle handle, int* count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
