@@ -113,7 +113,7 @@ typedef struct xb_pool_item {
 typedef struct xb_pool_group {
   const xb_table_desc* table;  /* HOST pointer; NULL = table-name miss: outputs are zero-filled */
   const void* ids;             /* [n_ids] */
-  const float* values;         /* [n_ids] fp32 per-id weights, NULL = all 1.0 */
+  const void* values;          /* [n_ids] per-id weights (values_dtype), NULL = all 1.0 */
   const int32_t* segments;     /* [batch] counts, or [batch+1] exclusive offsets */
   int64_t n_ids;
   int64_t batch;
@@ -123,6 +123,7 @@ typedef struct xb_pool_group {
   int32_t segments_are_offsets;
   int32_t out_dtype;           /* XB_F32 or XB_F16 */
   int32_t n_items;
+  int32_t values_dtype;        /* XB_F32 (0 also means fp32) or XB_F16 */
   xb_pool_item items[XB_MAX_POOL_ITEMS];
 } xb_pool_group;
 

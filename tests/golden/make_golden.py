@@ -34,7 +34,8 @@ def tokenize(text):
         if m.group(1):
             continue
         if m.group(2) is not None:
-            out.append(("s", m.group(2)[1:-1]))
+            # protobuf text strings use C escapes
+            out.append(("s", m.group(2)[1:-1].encode("latin1").decode("unicode_escape")))
         elif m.group(3):
             out.append((m.group(3), None))
         else:

@@ -33,7 +33,7 @@ class PoolItem(C.Structure):
 class PoolGroup(C.Structure):
     _fields_ = [("table", C.POINTER(TableDesc)), ("ids", vp), ("values", vp), ("segments", vp), ("n_ids", i64),
                 ("batch", i64), ("dim", i32), ("id_dtype", i32), ("segments_are_offsets", i32), ("out_dtype", i32),
-                ("n_items", i32), ("items", PoolItem * XB_MAX_POOL_ITEMS)]
+                ("n_items", i32), ("values_dtype", i32), ("items", PoolItem * XB_MAX_POOL_ITEMS)]
 
 
 class GemmArgs(C.Structure):

@@ -26,13 +26,14 @@ struct PoolGroupDev {
   const int64_t* slot_keys;
   const int32_t* slot_rows;
   const void* ids;
-  const float* values;
+  const void* values;
   const int32_t* offsets;      // exclusive offsets [batch+1]
   int64_t rows, pitch, slot_mask, batch;
   int64_t warp_begin;          // first warp of this group in the launch
   int32_t dim, tdtype, id_dtype, out_dtype, n_items, has_table;
   int32_t lpr;                 // lanes per row
   int32_t tl;                  // lanes per segment (team)
+  int32_t vhalf;               // per-id weights are fp16
   PoolItemDev items[XB_MAX_POOL_ITEMS];
 };
 
@@ -190,8 +191,16 @@ __global__ void __launch_bounds__(256) pool_kernel(const __grid_constant__ PoolP
       int64_t key1 = 0;
       if (has1) key1 = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j1)
                             : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + start + j1);
-      float v0 = g.values ? __ldg(g.values + start + j) : 1.f;
-      float v1 = (has1 && g.values) ? __ldg(g.values + start + j1) : 1.f;
+      float v0 = 1.f, v1 = 1.f;
+      if (g.values) {
+        if (g.vhalf) {
+          v0 = __half2float(reinterpret_cast<const __half*>(g.values)[start + j]);
+          if (has1) v1 = __half2float(reinterpret_cast<const __half*>(g.values)[start + j1]);
+        } else {
+          v0 = __ldg(reinterpret_cast<const float*>(g.values) + start + j);
+          if (has1) v1 = __ldg(reinterpret_cast<const float*>(g.values) + start + j1);
+        }
+      }
       int64_t r0 = lookup_row(g, key0);
       int64_t r1 = has1 ? lookup_row(g, key1) : -1;
       uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = make_uint4(0, 0, 0, 0);
@@ -405,7 +414,9 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     int ns = 1;
     while (ns < 32 / d.lpr && ns < avg) ns <<= 1;
     d.tl = d.lpr * ns;
-    d.ids = h.ids; d.values = h.values; d.batch = h.batch;
+    XB_REQUIRE(h.values_dtype == 0 || h.values_dtype == XB_F32 || h.values_dtype == XB_F16, XB_ERR_UNSUPPORTED,
+               "xb_embedding_pool: group %d values dtype %d", i, h.values_dtype);
+    d.ids = h.ids; d.values = h.values; d.batch = h.batch; d.vhalf = h.values_dtype == XB_F16;
     d.id_dtype = h.id_dtype; d.out_dtype = h.out_dtype; d.n_items = h.n_items;
     for (int k = 0; k < h.n_items; ++k) {
       const xb_pool_item& it = h.items[k];

@@ -1,0 +1,100 @@
+"""The DIN-style model as a Blaze NetDef for the host runtime (Predictor API).
+
+Graph (fp16 model): two Embedding operators as in the shipped DIN graph
+(blaze/tools/example_model/din/model/graph_ulf.txt: a user-side op with the uid
+block and the two kAssign behaviour blocks, an ad-side op with the item|category
+block), Reshape x2 + Concat to k [R, T, 36], then the fused DinAttention and
+DinTowerInput operators and the tower Gemm -> Dice, Gemm -> Dice, Gemm -> Softmax
+(the Dice nodes are folded into the Gemm epilogues by LoadModel's fusion pass).
+"""
+import numpy as np
+
+from . import blaze_api as api
+
+F16, F32, I32, I64 = 12, 1, 2, 10
+
+
+def _fg(name, table, dim):
+    return 'feature_group_config { feature_group: "%s" table_name: "%s" dim: %d }\n' % (name, table, dim)
+
+
+def _item(fg, udf, trunc_num=None):
+    extra = "" if trunc_num is None else " trunc_num: %d" % trunc_num
+    return '  embedding_block_config_item { feature_group: "%s" udf_type: %d%s }\n' % (fg, udf, extra)
+
+
+def build(model):
+    """Returns (netdef_text, input_names) for `model` (workloads.din_model)."""
+    D = model["dims"]
+    e, d, T, G = D["emb"], D["d"], D["T"], D["user_groups"]
+    users = ["u%d" % g for g in range(G)]
+    triple = lambda n: [n + ".ids", n + ".values", n + ".segments"]
+    ops = []
+    # user-side Embedding: uid block (G kSum items), mid_list and cat_list kAssign blocks
+    conf = "".join(_fg(u, "user%d" % g, e) for g, u in enumerate(users))
+    conf += _fg("mid_list", "item", e) + _fg("cat_list", "cate", e)
+    conf += "block_config {\n" + "".join(_item(u, 0) for u in users) + "}\n"
+    conf += "block_config {\n" + _item("mid_list", 2, T) + "}\n"
+    conf += "block_config {\n" + _item("cat_list", 2, T) + "}\n"
+    user_in = sum([triple(u) for u in users], []) + triple("mid_list") + triple("cat_list")
+    ops.append(api.op_text("Embedding", user_in, ["uid_emb", "mid_list_emb", "cat_list_emb"], {"embedding_config": conf},
+                           "user_embedding"))
+    conf = _fg("mid", "item", e) + _fg("cat", "cate", e) + "block_config {\n" + _item("mid", 0) + _item("cat", 0) + "}\n"
+    ops.append(api.op_text("Embedding", triple("mid") + triple("cat"), ["ad_emb"], {"embedding_config": conf}, "ad_embedding"))
+    ops.append(api.op_text("Reshape", ["mid_list_emb"], ["mid_list_3d"], {"shape": [-1, T, e]}))
+    ops.append(api.op_text("Reshape", ["cat_list_emb"], ["cat_list_3d"], {"shape": [-1, T, e]}))
+    ops.append(api.op_text("Concat", ["mid_list_3d", "cat_list_3d"], ["his_emb"], {"axis": 2}))
+    a = model["att"]
+    names = []
+    for n in ("W0", "b0", "W1", "b1", "W2", "b2", "g0", "m0", "v0", "g1", "m1", "v1"):
+        ops.append(api.constant_text("att_" + n, a[n], F16))
+        names.append("att_" + n)
+    ops.append(api.op_text("DinAttention", ["ad_emb", "his_emb"] + names, ["att"], {"act": 2}))
+    ops.append(api.op_text("DinTowerInput", ["uid_emb", "ad_emb", "his_emb", "att"], ["tower_in"]))
+    tw = model["tower"]
+    tin = G * e + 5 * d
+    ld = (tin + 7) // 8 * 8
+    W1 = np.zeros((ld, tw["W1"].shape[1]), np.float32)        # rows of the zero padding columns of tower_in
+    W1[:tin] = tw["W1"]
+    for name, arr in (("W1", W1), ("b1", tw["b1"]), ("W2", tw["W2"]), ("b2", tw["b2"]), ("W3", tw["W3"]), ("b3", tw["b3"])):
+        ops.append(api.constant_text("t_" + name, arr, F16))
+    for i, key in ((1, "dice1"), (2, "dice2")):
+        for n, arr in zip(("g", "m", "v"), tw[key]):
+            ops.append(api.constant_text("t_%s%d" % (n, i), arr, F16))
+    ops.append(api.op_text("Gemm", ["tower_in", "t_W1", "t_b1"], ["h1"]))
+    ops.append(api.op_text("Dice", ["h1", "t_g1", "t_m1", "t_v1"], ["y1"]))
+    ops.append(api.op_text("Gemm", ["y1", "t_W2", "t_b2"], ["h2"]))
+    ops.append(api.op_text("Dice", ["h2", "t_g2", "t_m2", "t_v2"], ["y2"]))
+    ops.append(api.op_text("Gemm", ["y2", "t_W3", "t_b3"], ["logit"]))
+    ops.append(api.op_text("Softmax", ["logit"], ["output"], {"axis": 1}))
+    feeds = []
+    for n in users + ["mid_list", "cat_list", "mid", "cat"]:
+        feeds += [(n + ".ids", I64), (n + ".values", F16), (n + ".segments", I32)]
+    return api.netdef_text(ops, feeds, [("output", F16)], name="din"), [n for n, _ in feeds]
+
+
+def register_tables(mgr, model):
+    mgr.load_sparse(None, "b200_sparse_puller")
+    mgr.add_table("item", model["item"], F16)
+    mgr.add_table("cate", model["cate"], F16)
+    for g, w in enumerate(model["user"]):
+        mgr.add_table("user%d" % g, w, F16)
+
+
+def feeds_of(model, req):
+    """{feed name: numpy array} for one batch of requests (workloads.din_requests)."""
+    D = model["dims"]
+    R, n_cand = req["requests"], req["n_cand"]
+    out = {}
+
+    def put(name, ids, segments):
+        out[name + ".ids"] = np.ascontiguousarray(ids, np.int64)
+        out[name + ".values"] = np.ones(len(ids), np.float16)
+        out[name + ".segments"] = np.ascontiguousarray(segments, np.int32)
+    for g in range(D["user_groups"]):
+        put("u%d" % g, req["user_ids"][:, g], np.ones(R, np.int32))
+    put("mid_list", req["hist_item"], req["seq_len"])
+    put("cat_list", req["hist_cate"], req["seq_len"])
+    put("mid", req["cand_item"], np.ones(R * n_cand, np.int32))
+    put("cat", req["cand_cate"], np.ones(R * n_cand, np.int32))
+    return out

@@ -544,7 +544,7 @@ class EmbeddingOp final : public Operator<CUDAContext> {
       Blob *ids = Input(f->second * 3), *vals = Input(f->second * 3 + 1), *seg = Input(f->second * 3 + 2);
       in[g].key = ids->as<void>(); in[g].key_size = ids->size();
       in[g].key_num = seg->as<void>(); in[g].key_num_size = seg->size();
-      in[g].value = ValuesF32(vals, g, s);
+      in[g].value = vals->as<void>();
       in[g].key_type = ids->data_type(); in[g].value_type = vtype; in[g].num_type = seg->data_type();
       in[g].dim = fg.dim;
       for (const auto& use : fg.uses) {
@@ -564,21 +564,6 @@ class EmbeddingOp final : public Operator<CUDAContext> {
   }
 
  private:
-  // the pooling kernel reads fp32 per-id weights; an fp16 model's values are widened first
-  void* ValuesF32(Blob* vals, size_t g, cudaStream_t s) {
-    if (vals->data_type() == kFloat) return vals->as<void>();
-    if (widened_.size() <= g) widened_.resize(g + 1);
-    if (!widened_[g]) widened_[g].reset(new Blob(vals->device_option()));
-    widened_[g]->set_data_type(kFloat);
-    widened_[g]->Reshape(vals->shape());
-    if (vals->size()) {
-      XB_CHECK(xb_copy2d(vals->as<void>(), (int64_t)vals->size(), XB_F16, widened_[g]->as<void>(), (int64_t)vals->size(), XB_F32, 1,
-                         (int64_t)vals->size(), s));
-      ++launches;
-    }
-    return widened_[g]->as<void>();
-  }
-
   struct Item { size_t fg; int udf; int trunc_dir; int trunc_num; size_t offset; };
   struct Block { std::vector<Item> items; size_t stride = 0; bool needs_clear = false; };
   struct FeatureGroup { std::string name, table; int dim = 18; std::vector<std::pair<size_t, size_t>> uses; };
@@ -586,7 +571,6 @@ class EmbeddingOp final : public Operator<CUDAContext> {
   std::vector<FeatureGroup> groups_;
   std::vector<Block> blocks_;
   std::unordered_map<std::string, size_t> fg_index_, input_fg_;
-  std::vector<std::unique_ptr<Blob>> widened_;
 };
 REGISTER_CUDA_OPERATOR(Embedding, EmbeddingOp);
 OPERATOR_SCHEMA(Embedding).NumInputs(3, 384).NumOutputs(1, 128);

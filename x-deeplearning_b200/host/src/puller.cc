@@ -104,7 +104,7 @@ class B200SparsePuller : public SparsePuller {
       xb_pool_group g;
       memset(&g, 0, sizeof(g));
       g.table = Find(in.name, in.dim, device_id);                     // nullptr: table-name miss -> zeros
-      g.ids = in.key; g.values = reinterpret_cast<const float*>(in.value);
+      g.ids = in.key; g.values = in.value; g.values_dtype = in.value_type;
       g.segments = reinterpret_cast<const int32_t*>(in.key_num);
       g.n_ids = (int64_t)in.key_size; g.batch = (int64_t)in.key_num_size;
       g.dim = in.dim; g.id_dtype = in.key_type; g.out_dtype = in.value_type;

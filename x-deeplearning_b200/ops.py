@@ -68,6 +68,7 @@ def make_group(table, ids, values, segments, items, out_dtype, segments_are_offs
     g.segments_are_offsets = int(segments_are_offsets)
     g.out_dtype = _DT[out_dtype]
     g.n_items = len(items)
+    g.values_dtype = dt(values) if values is not None else 0
     for k, it in enumerate(items):
         o = it["out"]
         assert o.dtype == out_dtype and o.dim() == 2 and o.stride(1) == 1
