@@ -228,6 +228,8 @@ typedef struct xb_din_att_weights {
   const float *b0, *b1;  float b2;
   const float *gamma0, *mean0, *var0;   /* Dice, [h0] */
   const float *gamma1, *mean1, *var1;   /* Dice, [h1] */
+  const void* packed;                   /* optional: output of xb_din_attention_pack for these weights and
+                                           `act`; saves re-laying the operands out in every CTA */
 } xb_din_att_weights;
 
 typedef struct xb_din_att_args {
@@ -244,6 +246,10 @@ typedef struct xb_din_att_args {
 } xb_din_att_args;
 
 int xb_din_attention(const xb_din_att_args* args, xb_stream_t stream);
+/* Lays the weights of `args` (d, h0, h1, act, w.*) out once in the form the tcgen05 engine keeps in
+ * shared memory. xb_din_attention_packed_bytes returns 0 for shapes that engine does not take. */
+size_t xb_din_attention_packed_bytes(int32_t d, int32_t h0, int32_t h1);
+int xb_din_attention_pack(const xb_din_att_args* args, void* packed, size_t bytes, xb_stream_t stream);
 
 /* Fused assembly of the DIN tower input. Replaces rows 17-22 of the shipped DIN
  * graph (ReduceSum over the behaviour rows, Mul, Concat, Fuse x2:

@@ -47,7 +47,7 @@ class GemmArgs(C.Structure):
 
 class DinAttWeights(C.Structure):
     _fields_ = [("W0", vp), ("W1", vp), ("W2", vp), ("b0", vp), ("b1", vp), ("b2", f32), ("gamma0", vp),
-                ("mean0", vp), ("var0", vp), ("gamma1", vp), ("mean1", vp), ("var1", vp)]
+                ("mean0", vp), ("var0", vp), ("gamma1", vp), ("mean1", vp), ("var1", vp), ("packed", vp)]
 
 
 class DinAttArgs(C.Structure):
@@ -74,6 +74,8 @@ SYMBOLS = {
     "xb_gemm_uses_tcgen05": (i32, [C.POINTER(GemmArgs)]),
     "xb_pack_weight_kmajor": (i32, [vp, i32, i32, i32, i64, vp, i32, i64, i32, i64, i64, vp]),
     "xb_din_attention": (i32, [C.POINTER(DinAttArgs), vp]),
+    "xb_din_attention_packed_bytes": (C.c_size_t, [i32, i32, i32]),
+    "xb_din_attention_pack": (i32, [C.POINTER(DinAttArgs), vp, C.c_size_t, vp]),
     "xb_din_tower_input": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, vp]),
     "xb_gru": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp, i32, vp]),
     "xb_augru": (i32, [vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, i32, vp]),

@@ -29,6 +29,7 @@ struct AttParams {
   // tcgen05 engine
   int tiles_per_req;
   uint32_t idesc1, idesc2, idesc3;
+  const void* packed;      // weight operands laid out by xb_din_attention_pack, or null
 };
 
 __device__ __forceinline__ float att_act(int act, float x, float g, float a, float bneg) {
@@ -163,6 +164,7 @@ extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
   p.b0 = a->w.b0; p.b1 = a->w.b1; p.b2 = a->w.b2;
   p.g0 = a->w.gamma0; p.m0 = a->w.mean0; p.v0 = a->w.var0;
   p.g1 = a->w.gamma1; p.m1 = a->w.mean1; p.v1 = a->w.var1;
+  p.packed = a->w.packed;
 
   int why = 0;
   const bool tc = a->engine != XB_GEMM_SIMT && tc_eligible(*a, &why);
@@ -180,4 +182,31 @@ extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
   dim3 grid(a->n_cand, a->requests);
   din_att_simt_kernel<<<grid, SIMT_THREADS, smem, stream>>>(p);
   return check_launch("din_att_simt_kernel");
+}
+
+extern "C" size_t xb_din_attention_packed_bytes(int32_t d, int32_t h0, int32_t h1) {
+  if (d <= 0 || h0 <= 0 || h1 <= 0) return 0;
+  xb_din_att_args a;
+  memset(&a, 0, sizeof(a));
+  a.d = d; a.h0 = h0; a.h1 = h1; a.T = 16;
+  if (!tc_eligible(a, nullptr)) return 0;
+  return att_packed_bytes(d, h0, h1);
+}
+
+extern "C" int xb_din_attention_pack(const xb_din_att_args* a, void* packed, size_t bytes, xb_stream_t stream) {
+  XB_REQUIRE(a && packed, XB_ERR_ARG, "xb_din_attention_pack: null argument");
+  XB_REQUIRE(a->w.W0 && a->w.W1 && a->w.W2, XB_ERR_ARG, "xb_din_attention_pack: missing weights");
+  XB_REQUIRE(a->act != XB_ACT_DICE || (a->w.gamma0 && a->w.mean0 && a->w.var0 && a->w.gamma1 && a->w.mean1 && a->w.var1),
+             XB_ERR_ARG, "xb_din_attention_pack: Dice needs gamma/mean/var for both layers");
+  const size_t need = xb_din_attention_packed_bytes(a->d, a->h0, a->h1);
+  XB_REQUIRE(need != 0, XB_ERR_UNSUPPORTED, "xb_din_attention_pack: shape outside the tcgen05 engine");
+  XB_REQUIRE(bytes >= need && ((uintptr_t)packed & 15) == 0, XB_ERR_ARG, "xb_din_attention_pack: buffer of %zu bytes, need %zu, 16-byte aligned", bytes, need);
+  AttParams p;
+  memset(&p, 0, sizeof(p));
+  p.T = 16; p.d = a->d; p.h0 = a->h0; p.h1 = a->h1; p.act = a->act;
+  p.W0 = (const __half*)a->w.W0; p.W1 = (const __half*)a->w.W1; p.W2 = a->w.W2;
+  p.b0 = a->w.b0; p.b1 = a->w.b1; p.b2 = a->w.b2;
+  p.g0 = a->w.gamma0; p.m0 = a->w.mean0; p.v0 = a->w.var0;
+  p.g1 = a->w.gamma1; p.m1 = a->w.mean1; p.v1 = a->w.var1;
+  return launch_att_pack(p, a->act, packed, (cudaStream_t)stream);
 }

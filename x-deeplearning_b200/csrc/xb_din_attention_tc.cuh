@@ -1,9 +1,12 @@
 // tcgen05 engine of the fused DIN attention unit (included by xb_din_attention.cu).
 //
 // One CTA owns 128 candidates of one request and walks the behaviour steps.
-// Two worker warpgroups (one candidate row per thread) take alternate steps; a
-// ninth warp issues every MMA, so the tensor pipe runs one warpgroup's step
-// while the other warpgroup does its activations:
+// Four worker warpgroups (one candidate row per thread each) split the work by
+// phase and step parity: warpgroup b (b = 0, 1) runs the layer-1 activations of
+// the steps of parity b, warpgroup 2+b builds A1 two steps ahead and runs the
+// layer-2 activations for parity b; two more warps issue the MMAs (one per layer).
+// Operands and accumulators are double-buffered by step parity, so in steady
+// state nobody waits: the tensor pipe, the SFU and the FP16 pipe overlap.
 //   worker: A1 = [q|k_t|q-k_t|q*k_t] (fp16, 128 x k1) into shared memory
 //   MMA   : acc1[128 x h0p] = A1 * W0^T                  (TMEM accumulator)
 //   worker: acc1 -> activation -> fp16 A2 in shared memory
@@ -29,7 +32,8 @@
 namespace xb {
 namespace {
 
-constexpr int TC_THREADS = 288;          // 2 worker warpgroups + 1 MMA warp
+constexpr int TC_THREADS = 576;          // 4 worker warpgroups + 2 MMA-issuing warps
+constexpr int MMA1_WARP = 16, MMA2_WARP = 17;
 constexpr int TMEM_COLS = 512;
 constexpr int ACC1_COL = 0, ACC2_COL = 128, ACC3_COL = 192, WG_COL = 256;
 
@@ -91,12 +95,80 @@ __device__ __forceinline__ __half2 act_pair_w(__half2 x, const uint4& c) {
   return act_pair<ACT>(x, c);
 }
 
+// Builds the weight operands the way the MMAs read them from shared memory: W0 [h0p rows, k1]
+// and W1 [h1p rows, k2] in core-matrix layout with the bias rows, and the per-column-pair
+// activation constants. `w0s..c2` may point to shared or global memory.
+template <int ACT>
+__device__ __forceinline__ void pack_weights(const AttParams& p, const TcGeom& G, __half* w0s, __half* w1s, uint4* c1,
+                                             uint4* c2, int tid, int nthreads) {
+  const int d = p.d, dp = G.dp, k1 = G.k1, h0p = G.h0p, k2 = G.k2, h1p = G.h1p;
+  const __half zero = __float2half(0.f);
+  for (int idx = tid; idx < h0p * k1; idx += nthreads) {
+    const int n = idx / k1, kk = idx - n * k1;
+    __half v = zero;
+    if (n < p.h0) {
+      if (kk == G.ones1) v = __float2half_rn(p.b0 ? p.b0[n] : 0.f);
+      else if (kk < 4 * dp) {
+        const int seg = kk / dp, i = kk - seg * dp;
+        if (i < d) v = p.W0[(int64_t)n * 4 * d + seg * d + i];
+      }
+    }
+    w0s[(kk >> 3) * (h0p * 8) + n * 8 + (kk & 7)] = v;
+  }
+  for (int idx = tid; idx < h1p * k2; idx += nthreads) {
+    const int n = idx / k2, kk = idx - n * k2;
+    __half v = zero;
+    if (n < p.h1) {
+      if (kk < p.h0) v = p.W1[(int64_t)n * p.h0 + kk];
+      else if (kk == h0p) v = __float2half_rn(p.b1 ? p.b1[n] : 0.f);
+    }
+    w1s[(kk >> 3) * (h1p * 8) + n * 8 + (kk & 7)] = v;
+  }
+  for (int j = tid; j < h0p / 2; j += nthreads) {
+    float A[2] = {0, 0}, B[2] = {0, 0}, C[2] = {0, 0}, D[2] = {0, 0};
+    for (int u = 0; u < 2; ++u) {
+      const int col = 2 * j + u;
+      if (col >= p.h0) continue;
+      if (ACT == XB_ACT_DICE) {
+        const float rs = dice_rstd(p.v0[col], 0), g = p.g0[col];
+        A[u] = 0.5f * rs; B[u] = -0.5f * p.m0[col] * rs; C[u] = 0.5f * (1.f + g); D[u] = 0.5f * (1.f - g);
+      } else if (ACT == XB_ACT_SIGMOID) { A[u] = 0.5f; C[u] = 0.5f; D[u] = 0.5f; }
+    }
+    c1[j] = make_uint4(h2_bits(__floats2half2_rn(A[0], A[1])), h2_bits(__floats2half2_rn(B[0], B[1])),
+                       h2_bits(__floats2half2_rn(C[0], C[1])), h2_bits(__floats2half2_rn(D[0], D[1])));
+  }
+  for (int j = tid; j < h1p / 2; j += nthreads) {
+    float A[2] = {0, 0}, B[2] = {0, 0}, C[2] = {0, 0}, D[2] = {0, 0};
+    for (int u = 0; u < 2; ++u) {
+      const int col = 2 * j + u;
+      if (col >= p.h1) continue;
+      const float w2 = p.W2[col];
+      if (ACT == XB_ACT_DICE) {
+        const float rs = dice_rstd(p.v1[col], 0), g = p.g1[col];
+        A[u] = 0.5f * rs; B[u] = -0.5f * p.m1[col] * rs; C[u] = 0.5f * (1.f + g) * w2; D[u] = 0.5f * (1.f - g) * w2;
+      } else if (ACT == XB_ACT_SIGMOID) { A[u] = 0.5f; C[u] = 0.5f * w2; D[u] = 0.5f * w2; }
+      else C[u] = w2;
+    }
+    c2[j] = make_uint4(h2_bits(__floats2half2_rn(A[0], A[1])), h2_bits(__floats2half2_rn(B[0], B[1])),
+                       h2_bits(__floats2half2_rn(C[0], C[1])), h2_bits(__floats2half2_rn(D[0], D[1])));
+  }
+}
+
+template <int ACT>
+__global__ void att_pack_kernel(const __grid_constant__ AttParams p, uint8_t* dst) {
+  const TcGeom G = tc_geom(p.d, p.h0, p.h1, p.T);
+  const int w0_bytes = G.h0p * G.k1 * 2, w1_bytes = G.h1p * G.k2 * 2;
+  pack_weights<ACT>(p, G, reinterpret_cast<__half*>(dst), reinterpret_cast<__half*>(dst + w0_bytes),
+                    reinterpret_cast<uint4*>(dst + w0_bytes + w1_bytes),
+                    reinterpret_cast<uint4*>(dst + w0_bytes + w1_bytes) + G.h0p / 2, threadIdx.x, blockDim.x);
+}
+
 template <int ACT>
 __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_constant__ AttParams p) {
   using namespace umma;
+  using umma::tanh_f16x2;
   extern __shared__ __align__(128) uint8_t smem[];
-  // [wg][a1_full, acc1_full, a2_full, acc2_full], then s_full, acc3_full
-  __shared__ __align__(8) uint64_t bars[10];
+  __shared__ __align__(8) uint64_t bars[12];
   __shared__ uint32_t tmem_base_s;
 
   const TcGeom G = tc_geom(p.d, p.h0, p.h1, p.T);
@@ -117,26 +189,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   const __half zero = __float2half(0.f), one = __float2half(1.f);
 
   // ---- prologue: operands that stay resident for the whole tile ----------------------------
-  for (int idx = threadIdx.x; idx < h0p * k1; idx += TC_THREADS) {
-    const int n = idx / k1, kk = idx - n * k1;
-    __half v = zero;
-    if (n < p.h0) {
-      if (kk == G.ones1) v = __float2half_rn(p.b0 ? p.b0[n] : 0.f);
-      else if (kk < 4 * dp) {
-        const int seg = kk / dp, i = kk - seg * dp;
-        if (i < d) v = p.W0[(int64_t)n * 4 * d + seg * d + i];
-      }
-    }
-    w0s[(kk >> 3) * (h0p * 8) + n * 8 + (kk & 7)] = v;
-  }
-  for (int idx = threadIdx.x; idx < h1p * k2; idx += TC_THREADS) {
-    const int n = idx / k2, kk = idx - n * k2;
-    __half v = zero;
-    if (n < p.h1) {
-      if (kk < p.h0) v = p.W1[(int64_t)n * p.h0 + kk];
-      else if (kk == h0p) v = __float2half_rn(p.b1 ? p.b1[n] : 0.f);
-    }
-    w1s[(kk >> 3) * (h1p * 8) + n * 8 + (kk & 7)] = v;
+  if (p.packed) {
+    // weight operands were laid out once by xb_din_attention_pack: straight 16-byte copies
+    const uint4* src = reinterpret_cast<const uint4*>(p.packed);
+    const int n01 = (h0p * k1 * 2 + h1p * k2 * 2) / 16;                 // W0 and W1 images are adjacent
+    for (int i = threadIdx.x; i < n01; i += TC_THREADS) reinterpret_cast<uint4*>(smem + L.w0)[i] = __ldg(src + i);
+    for (int i = threadIdx.x; i < h0p / 2 + h1p / 2; i += TC_THREADS) c1[i] = __ldg(src + n01 + i);   // c2 follows c1
+  } else {
+    pack_weights<ACT>(p, G, w0s, w1s, c1, c2, threadIdx.x, TC_THREADS);
   }
   for (int idx = threadIdx.x; idx < p.T * dp; idx += TC_THREADS) {
     const int t = idx / dp, i = idx - t * dp;
@@ -149,108 +209,171 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   }
   for (int idx = threadIdx.x; idx < 128 * tp / 8; idx += TC_THREADS)
     reinterpret_cast<uint4*>(ss)[idx] = make_uint4(0, 0, 0, 0);
-  for (int j = threadIdx.x; j < h0p / 2; j += TC_THREADS) {
-    float A[2] = {0, 0}, B[2] = {0, 0}, C[2] = {0, 0}, D[2] = {0, 0};
-    for (int u = 0; u < 2; ++u) {
-      const int col = 2 * j + u;
-      if (col >= p.h0) continue;
-      if (ACT == XB_ACT_DICE) {
-        const float rs = dice_rstd(p.v0[col], 0), g = p.g0[col];
-        A[u] = 0.5f * rs; B[u] = -0.5f * p.m0[col] * rs; C[u] = 0.5f * (1.f + g); D[u] = 0.5f * (1.f - g);
-      } else if (ACT == XB_ACT_SIGMOID) { A[u] = 0.5f; C[u] = 0.5f; D[u] = 0.5f; }
-    }
-    c1[j] = make_uint4(h2_bits(__floats2half2_rn(A[0], A[1])), h2_bits(__floats2half2_rn(B[0], B[1])),
-                       h2_bits(__floats2half2_rn(C[0], C[1])), h2_bits(__floats2half2_rn(D[0], D[1])));
-  }
-  for (int j = threadIdx.x; j < h1p / 2; j += TC_THREADS) {
-    float A[2] = {0, 0}, B[2] = {0, 0}, C[2] = {0, 0}, D[2] = {0, 0};
-    for (int u = 0; u < 2; ++u) {
-      const int col = 2 * j + u;
-      if (col >= p.h1) continue;
-      const float w2 = p.W2[col];
-      if (ACT == XB_ACT_DICE) {
-        const float rs = dice_rstd(p.v1[col], 0), g = p.g1[col];
-        A[u] = 0.5f * rs; B[u] = -0.5f * p.m1[col] * rs; C[u] = 0.5f * (1.f + g) * w2; D[u] = 0.5f * (1.f - g) * w2;
-      } else if (ACT == XB_ACT_SIGMOID) { A[u] = 0.5f; C[u] = 0.5f * w2; D[u] = 0.5f * w2; }
-      else C[u] = w2;
-    }
-    c2[j] = make_uint4(h2_bits(__floats2half2_rn(A[0], A[1])), h2_bits(__floats2half2_rn(B[0], B[1])),
-                       h2_bits(__floats2half2_rn(C[0], C[1])), h2_bits(__floats2half2_rn(D[0], D[1])));
-  }
+  // barriers, per accumulator/operand buffer b = step & 1:
+  //   a1_full[b]   4 builder warps       -> MMA warp: A1 of a step is in shared memory
+  //   acc1_full[b] tcgen05.commit        -> both warpgroups: layer-1 accumulator complete
+  //   a2_full[b]   4 layer-1 warps       -> MMA warp: A2 written and acc1[b] drained
+  //   acc2_full[b] tcgen05.commit        -> both warpgroups: layer-2 accumulator complete
+  //   acc2_free[b] 4 layer-2 warps       -> MMA warp: acc2[b] drained
+  //   s_full, acc3_full: the closing S*K product
+  uint64_t* a1_full = &bars[0];
+  uint64_t* acc1_full = &bars[2];
+  uint64_t* a2_full = &bars[4];
+  uint64_t* acc2_full = &bars[6];
+  uint64_t* acc2_free = &bars[8];
+  uint64_t* s_full = &bars[10];
+  uint64_t* acc3_full = &bars[11];
   if (threadIdx.x == 0) {
-    for (int g = 0; g < 2; ++g) {
-      mbar_init(smem_u32(&bars[4 * g + 0]), 128);
-      mbar_init(smem_u32(&bars[4 * g + 1]), 1);
-      mbar_init(smem_u32(&bars[4 * g + 2]), 128);
-      mbar_init(smem_u32(&bars[4 * g + 3]), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&a1_full[b]), 4);
+      mbar_init(smem_u32(&acc1_full[b]), 1);
+      mbar_init(smem_u32(&a2_full[b]), 4);
+      mbar_init(smem_u32(&acc2_full[b]), 1);
+      mbar_init(smem_u32(&acc2_free[b]), 4);
     }
-    mbar_init(smem_u32(&bars[8]), 256);
-    mbar_init(smem_u32(&bars[9]), 1);
+    mbar_init(smem_u32(s_full), 8);
+    mbar_init(smem_u32(acc3_full), 1);
     fence_barrier_init();
   }
-  if (warp == 8) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
+  if (warp == MMA1_WARP) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
   fence_proxy_async_smem();          // operands were written through the generic proxy
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem0 = tmem_base_s;
 
-  if (warp == 8) {
-    // ---- MMA issue --------------------------------------------------------------------------
+  if (warp == MMA1_WARP) {
+    // ---- layer-1 MMA issue: one thread, descriptors advanced by constant steps -----------------------
     if (lane == 0) {
-      const uint32_t w0a = smem_u32(w0s), w1a = smem_u32(w1s);
+      const uint64_t db0 = make_desc_interleaved(smem_u32(w0s), h0p * 16, 128);
+      const uint64_t db_step = (uint64_t)((2 * h0p * 16) >> 4), da_step = (uint64_t)((2 * 128 * 16) >> 4);
+      const int nks = k1 / 16;
+      for (int j = 0; j < tl; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        // A1 of step j is written; acc1[b] was drained before the layer-1 warps signalled a2_full(j-2)
+        if (!(mbar_wait(smem_u32(&a1_full[b]), ph, 10) && mbar_wait(smem_u32(&a2_full[b]), ph ^ 1u, 14))) break;
+        tc_fence_after_sync();
+        uint64_t da = make_desc_interleaved(smem_u32(smem + L.a1 + b * (128 * k1 * 2)), 128 * 16, 128);
+        uint64_t db = db0;
+        const uint32_t acc1 = tmem0 + b * WG_COL + ACC1_COL;
+        mma_f16_ss(acc1, da, db, p.idesc1, 0u);
+        for (int ks = 1; ks < nks; ++ks) {
+          da += da_step; db += db_step;
+          mma_f16_ss(acc1, da, db, p.idesc1, 1u);
+        }
+        mma_commit(smem_u32(&acc1_full[b]));
+      }
+    }
+  } else if (warp == MMA2_WARP) {
+    // ---- layer-2 MMA issue, then the closing S*K product -----------------------------------------------
+    if (lane == 0) {
+      const uint64_t db0 = make_desc_interleaved(smem_u32(w1s), h1p * 16, 128);
+      const uint64_t db_step = (uint64_t)((2 * h1p * 16) >> 4), da_step = (uint64_t)((2 * 128 * 16) >> 4);
+      const int nks = k2 / 16;
       bool ok = true;
-      for (int t = 0; t <= tl && ok; ++t) {
-        if (t < tl) {
-          const int g = t & 1, i = t >> 1;
-          ok = mbar_wait(smem_u32(&bars[4 * g + 0]), (uint32_t)i & 1u, 10);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t a1 = smem_u32(smem + L.a1 + g * (128 * k1 * 2));
-          const uint32_t acc1 = tmem0 + g * WG_COL + ACC1_COL;
-          for (int ks = 0; ks < k1 / 16; ++ks) {
-            const uint64_t da = make_desc_interleaved(a1 + ks * 2 * (128 * 16), 128 * 16, 128);
-            const uint64_t db = make_desc_interleaved(w0a + ks * 2 * (h0p * 16), h0p * 16, 128);
-            mma_f16_ss(acc1, da, db, p.idesc1, ks > 0 ? 1u : 0u);
-          }
-          mma_commit(smem_u32(&bars[4 * g + 1]));
+      for (int j = 0; j < tl; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        ok = mbar_wait(smem_u32(&a2_full[b]), ph, 11) && mbar_wait(smem_u32(&acc2_free[b]), ph ^ 1u, 13);
+        if (!ok) break;
+        tc_fence_after_sync();
+        uint64_t da = make_desc_interleaved(smem_u32(smem + L.a2 + b * (128 * k2 * 2)), 128 * 16, 128);
+        uint64_t db = db0;
+        const uint32_t acc2 = tmem0 + b * WG_COL + ACC2_COL;
+        mma_f16_ss(acc2, da, db, p.idesc2, 0u);
+        for (int ks = 1; ks < nks; ++ks) {
+          da += da_step; db += db_step;
+          mma_f16_ss(acc2, da, db, p.idesc2, 1u);
         }
-        if (t > 0) {
-          const int tt = t - 1, g = tt & 1, i = tt >> 1;
-          ok = mbar_wait(smem_u32(&bars[4 * g + 2]), (uint32_t)i & 1u, 11);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t a2 = smem_u32(smem + L.a2 + g * (128 * k2 * 2));
-          const uint32_t acc2 = tmem0 + g * WG_COL + ACC2_COL;
-          for (int ks = 0; ks < k2 / 16; ++ks) {
-            const uint64_t da = make_desc_interleaved(a2 + ks * 2 * (128 * 16), 128 * 16, 128);
-            const uint64_t db = make_desc_interleaved(w1a + ks * 2 * (h1p * 16), h1p * 16, 128);
-            mma_f16_ss(acc2, da, db, p.idesc2, ks > 0 ? 1u : 0u);
-          }
-          mma_commit(smem_u32(&bars[4 * g + 3]));
-        }
+        mma_commit(smem_u32(&acc2_full[b]));
       }
       // weighted sum over the steps: out = S * K
-      if (ok && mbar_wait(smem_u32(&bars[8]), 0, 12)) {
+      if (ok && mbar_wait(smem_u32(s_full), 0, 12)) {
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(ss), ka = smem_u32(kts);
+        uint64_t da = make_desc_interleaved(smem_u32(ss), 128 * 16, 128);
+        uint64_t db = make_desc_interleaved(smem_u32(kts), np * 16, 128);
+        const uint64_t db3 = (uint64_t)((2 * np * 16) >> 4);
         for (int ks = 0; ks < tp / 16; ++ks) {
-          const uint64_t da = make_desc_interleaved(sa + ks * 2 * (128 * 16), 128 * 16, 128);
-          const uint64_t db = make_desc_interleaved(ka + ks * 2 * (np * 16), np * 16, 128);
           mma_f16_ss(tmem0 + ACC3_COL, da, db, p.idesc3, ks > 0 ? 1u : 0u);
+          da += da_step; db += db3;
         }
       }
-      mma_commit(smem_u32(&bars[9]));
+      mma_commit(smem_u32(acc3_full));
+    }
+  } else if (warp < 8) {
+    // ---- layer-1 warpgroups: acc1 -> activation -> A2, for the steps of parity wb ---------------------
+    const int wb = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;                 // TMEM lane == candidate row of the tile
+    const uint32_t lane_addr = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint4 ones_chunk = make_uint4(0x00003C00u, 0, 0, 0);            // fp16 {1,0,0,0,0,0,0,0}
+    {
+      uint8_t* a2 = smem + L.a2 + wb * (128 * k2 * 2);
+      *reinterpret_cast<uint4*>(a2 + (h0p / 8) * (128 * 16) + row * 16) = ones_chunk;     // column h0p: bias b1
+      *reinterpret_cast<uint4*>(a2 + (h0p / 8 + 1) * (128 * 16) + row * 16) = make_uint4(0, 0, 0, 0);
+    }
+    bool ok = true;
+    for (int j = wb; j < tl; j += 2) {
+      const int b = wb;
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      uint8_t* a2 = smem + L.a2 + b * (128 * k2 * 2) + row * 16;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[b]), ph, 20) &&
+                                       mbar_wait(smem_u32(&acc2_full[b]), ph ^ 1u, 23));   // M2(j-2) has read A2[b]
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t acc1 = lane_addr + b * WG_COL + ACC1_COL;
+      for (int c = 0; c < h0p; c += 32) {
+        uint32_t v[32];
+        const bool full = h0p - c >= 32;
+        if (full) { tmem_ld32_nowait(acc1 + c, v); tmem_wait_ld(v); }
+        else {
+          uint32_t v16[16];
+          tmem_ld16_nowait(acc1 + c, v16);
+          tmem_wait_ld(v16);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = v16[e];
+        }
+        // all pairs of the block go through each stage together, so the SFU and FP16 pipes see
+        // sixteen independent operations back to back; the stores come last
+        const uint4* __restrict__ cc = c1 + (c >> 1);
+        uint8_t* __restrict__ dst = a2 + (c >> 3) * (128 * 16);
+        uint32_t y[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+          y[e] = h2_bits(__floats2half2_rn(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1])));
+        if (ACT != XB_ACT_NONE) {
+          uint32_t th[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            if (full || e < 8) th[e] = h2_bits(__hfma2(bits_h2(y[e]), bits_h2(cc[e].x), bits_h2(cc[e].y)));
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            if (full || e < 8) th[e] = tanh_f16x2(th[e]);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            if (full || e < 8) {
+              const __half2 g = __hfma2(bits_h2(th[e]), bits_h2(cc[e].w), bits_h2(cc[e].z));
+              y[e] = h2_bits(ACT == XB_ACT_DICE ? __hmul2(bits_h2(y[e]), g) : g);
+            }
+          }
+        }
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8)
+          if (full || q8 < 2)
+            *reinterpret_cast<uint4*>(dst + q8 * (128 * 16)) = make_uint4(y[4 * q8], y[4 * q8 + 1], y[4 * q8 + 2], y[4 * q8 + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&a2_full[b]));        // one arrival per warp
     }
   } else {
-    // ---- workers ----------------------------------------------------------------------------
-    const int g = warp >> 2;                 // warpgroup
-    const int row = (warp & 3) * 32 + lane;  // TMEM lane == candidate row of the tile
+    // ---- builder / layer-2 warpgroups: A1 two steps ahead, acc2 -> score -> S, steps of parity wb --
+    const int wb = (warp >> 2) & 1;
+    const int row = (warp & 3) * 32 + lane;
     const int n = tile * 128 + row;
     const bool valid = n < p.n_cand;
-    const uint32_t lane_addr = tmem0 + ((uint32_t)((warp & 3) * 32) << 16) + g * WG_COL;
-    uint8_t* a1 = smem + L.a1 + g * (128 * k1 * 2);
-    uint8_t* a2 = smem + L.a2 + g * (128 * k2 * 2);
+    const uint32_t lane_addr = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);
 
     // q row as 16-byte chunks (dp <= 64 -> at most 8), with the constant-1 column when it lives here
     uint4 qv[8];
@@ -269,19 +392,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       }
       qv[c] = *reinterpret_cast<uint4*>(h);
     }
-    // constant parts of both operands: the q segment (and the ones columns)
+    // constant part of this parity's A1 buffer: the q segment (and the ones column)
+    {
+      uint8_t* a1 = smem + L.a1 + wb * (128 * k1 * 2) + row * 16;
 #pragma unroll
-    for (int c = 0; c < 8; ++c)
-      if (c < nch) *reinterpret_cast<uint4*>(a1 + c * (128 * 16) + row * 16) = qv[c];
-    const uint4 ones_chunk = make_uint4(0x00003C00u, 0, 0, 0);          // fp16 {1,0,0,0,0,0,0,0}
-    if (G.ones1 == 4 * dp) {
-      *reinterpret_cast<uint4*>(a1 + (4 * nch) * (128 * 16) + row * 16) = ones_chunk;
-      *reinterpret_cast<uint4*>(a1 + (4 * nch + 1) * (128 * 16) + row * 16) = make_uint4(0, 0, 0, 0);
+      for (int c = 0; c < 8; ++c)
+        if (c < nch) *reinterpret_cast<uint4*>(a1 + c * (128 * 16)) = qv[c];
+      if (G.ones1 == 4 * dp) {
+        *reinterpret_cast<uint4*>(a1 + (4 * nch) * (128 * 16)) = make_uint4(0x00003C00u, 0, 0, 0);
+        *reinterpret_cast<uint4*>(a1 + (4 * nch + 1) * (128 * 16)) = make_uint4(0, 0, 0, 0);
+      }
     }
-    *reinterpret_cast<uint4*>(a2 + (h0p / 8) * (128 * 16) + row * 16) = ones_chunk;
-    *reinterpret_cast<uint4*>(a2 + (h0p / 8 + 1) * (128 * 16) + row * 16) = make_uint4(0, 0, 0, 0);
 
     auto build_a1 = [&](int t) {
+      uint8_t* a1 = smem + L.a1 + (t & 1) * (128 * k1 * 2) + row * 16;
       const uint4* kt = reinterpret_cast<const uint4*>(khs + t * dp);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -291,113 +415,101 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
           const __half2* qh = reinterpret_cast<const __half2*>(&qv[c]);
           uint4 df, pr;
           __half2* dh = reinterpret_cast<__half2*>(&df);
-          __half2* ph = reinterpret_cast<__half2*>(&pr);
+          __half2* ph2 = reinterpret_cast<__half2*>(&pr);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) { dh[e] = __hsub2(qh[e], kh[e]); ph[e] = __hmul2(qh[e], kh[e]); }
+          for (int e = 0; e < 4; ++e) { dh[e] = __hsub2(qh[e], kh[e]); ph2[e] = __hmul2(qh[e], kh[e]); }
           // q's padding column holding the constant 1 gives 1-0 in `df`; harmless, its W0 rows are zero
-          *reinterpret_cast<uint4*>(a1 + (nch + c) * (128 * 16) + row * 16) = kc;
-          *reinterpret_cast<uint4*>(a1 + (2 * nch + c) * (128 * 16) + row * 16) = df;
-          *reinterpret_cast<uint4*>(a1 + (3 * nch + c) * (128 * 16) + row * 16) = pr;
+          *reinterpret_cast<uint4*>(a1 + (nch + c) * (128 * 16)) = kc;
+          *reinterpret_cast<uint4*>(a1 + (2 * nch + c) * (128 * 16)) = df;
+          *reinterpret_cast<uint4*>(a1 + (3 * nch + c) * (128 * 16)) = pr;
         }
       }
       fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&bars[4 * g + 0]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&a1_full[t & 1]));
     };
 
     bool ok = true;
-    if (g < tl) build_a1(g);
-    int i = 0;
-    for (int t = g; t < tl; t += 2, ++i) {
-      // layer-1 accumulator -> activation -> A2
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars[4 * g + 1]), (uint32_t)i & 1u, 20));
+    if (tl > wb) build_a1(wb);
+    for (int j = wb; j < tl; j += 2) {
+      const int b = wb;
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      if (j + 2 < tl) {
+        // A1[b] is free once M1(j) has read it
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[b]), ph, 24));
+        if (!ok) break;
+        build_a1(j + 2);
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph, 21));
       if (!ok) break;
       tc_fence_after_sync();
-      for (int c = 0; c < h0p; c += 32) {
-        uint32_t v[32];
-        const bool full = h0p - c >= 32;
-        if (full) { tmem_ld32_nowait(lane_addr + ACC1_COL + c, v); tmem_wait_ld(v); }
-        else {
-          uint32_t v16[16];
-          tmem_ld16_nowait(lane_addr + ACC1_COL + c, v16);
-          tmem_wait_ld(v16);
+      const uint32_t acc2 = lane_addr + b * WG_COL + ACC2_COL;
+      __half2 part[4];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] = v16[e];
-        }
+      for (int e = 0; e < 4; ++e) part[e] = __floats2half2_rn(0.f, 0.f);
+      for (int c = 0; c < h1p; c += 16) {
+        uint32_t v[16];
+        tmem_ld16_nowait(acc2 + c, v);
+        tmem_wait_ld(v);
+        const uint4* __restrict__ cc = c2 + (c >> 1);
+        uint32_t x[8], th[8];
 #pragma unroll
-        for (int q8 = 0; q8 < 4; ++q8) {
-          if (full || q8 < 2) {
-            uint32_t y[4];
+        for (int e = 0; e < 8; ++e)
+          x[e] = h2_bits(__floats2half2_rn(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1])));
+        if (ACT == XB_ACT_NONE) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int col = q8 * 8 + 2 * e;
-              const __half2 x = __floats2half2_rn(__uint_as_float(v[col]), __uint_as_float(v[col + 1]));
-              y[e] = h2_bits(act_pair<ACT>(x, c1[(c + col) >> 1]));
-            }
-            *reinterpret_cast<uint4*>(a2 + ((c >> 3) + q8) * (128 * 16) + row * 16) = make_uint4(y[0], y[1], y[2], y[3]);
+          for (int e = 0; e < 8; ++e) part[e & 3] = __hfma2(bits_h2(x[e]), bits_h2(cc[e].z), part[e & 3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) th[e] = h2_bits(__hfma2(bits_h2(x[e]), bits_h2(cc[e].x), bits_h2(cc[e].y)));
+#pragma unroll
+          for (int e = 0; e < 8; ++e) th[e] = tanh_f16x2(th[e]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const __half2 g = __hfma2(bits_h2(th[e]), bits_h2(cc[e].w), bits_h2(cc[e].z));
+            part[e & 3] = ACT == XB_ACT_DICE ? __hfma2(bits_h2(x[e]), g, part[e & 3]) : __hadd2(part[e & 3], g);
           }
         }
       }
-      fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bars[4 * g + 2]));
-
-      // next step's A1 while the second MMA runs
-      if (t + 2 < tl) build_a1(t + 2);
-
-      // layer-2 accumulator -> activation -> score
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars[4 * g + 3]), (uint32_t)i & 1u, 21));
-      if (!ok) break;
-      tc_fence_after_sync();
-      float s = p.b2;
-      for (int c = 0; c < h1p; c += 16) {
-        uint32_t v[16];
-        tmem_ld16_nowait(lane_addr + ACC2_COL + c, v);
-        tmem_wait_ld(v);
-        float2 part = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const __half2 x = __floats2half2_rn(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
-          const float2 f = __half22float2(act_pair_w<ACT>(x, c2[(c >> 1) + e]));
-          part.x += f.x; part.y += f.y;
-        }
-        s += part.x + part.y;
-      }
-      tc_fence_before_sync();
-      if (p.scores && valid && !p.use_softmax) p.scores[((int64_t)r * p.n_cand + n) * p.T + t] = s;
-      ss[(t >> 3) * (128 * 8) + row * 8 + (t & 7)] = __float2half_rn(s);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc2_free[b]));
+      // short fp16 chains (h1p/8 terms each), combined in fp32
+      const float2 f0 = __half22float2(part[0]), f1 = __half22float2(part[1]);
+      const float2 f2 = __half22float2(part[2]), f3 = __half22float2(part[3]);
+      const float s = p.b2 + ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+      if (p.scores && valid && !p.use_softmax) p.scores[((int64_t)r * p.n_cand + n) * p.T + j] = s;
+      ss[(j >> 3) * (128 * 8) + row * 8 + (j & 7)] = __float2half_rn(s);
     }
 
-    if (p.use_softmax) {
+    if (p.use_softmax) asm volatile("bar.sync 1, 256;" ::: "memory");     // both parities' scores are in S
+    if (p.use_softmax && wb == 0) {
       // masked softmax over the steps, in place on this thread's row of S (steps >= tl are masked out)
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (g == 0) {
-        float m = -INFINITY;
-        for (int t = 0; t < tl; ++t) m = fmaxf(m, __half2float(ss[(t >> 3) * (128 * 8) + row * 8 + (t & 7)]));
-        float l = 0.f;
-        for (int t = 0; t < tl; ++t) l += __expf(__half2float(ss[(t >> 3) * (128 * 8) + row * 8 + (t & 7)]) - m);
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        for (int t = 0; t < tl; ++t) {
-          __half* e = &ss[(t >> 3) * (128 * 8) + row * 8 + (t & 7)];
-          *e = __float2half_rn(__expf(__half2float(*e) - m) * inv);
-        }
+      float m = -INFINITY;
+      for (int t = 0; t < tl; ++t) m = fmaxf(m, __half2float(ss[(t >> 3) * (128 * 8) + row * 8 + (t & 7)]));
+      float l = 0.f;
+      for (int t = 0; t < tl; ++t) l += __expf(__half2float(ss[(t >> 3) * (128 * 8) + row * 8 + (t & 7)]) - m);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      for (int t = 0; t < tl; ++t) {
+        __half* e = &ss[(t >> 3) * (128 * 8) + row * 8 + (t & 7)];
+        *e = __float2half_rn(__expf(__half2float(*e) - m) * inv);
       }
     }
     fence_proxy_async_smem();
-    mbar_arrive(smem_u32(&bars[8]));
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(s_full));
 
-    if (g == 0) {
-      ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(&bars[9]), 0, 22));
-      tc_fence_after_sync();
-      if (ok) {
-        __half* o = p.out + ((int64_t)r * p.n_cand + n) * p.ldo;
-        for (int c = 0; c < np; c += 16) {
-          float v[16];
-          tmem_ld16(tmem0 + ((uint32_t)((warp & 3) * 32) << 16) + ACC3_COL + c, v);
-          if (valid) {
+    if (wb == 0) ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(acc3_full), 0, 22));
+    tc_fence_after_sync();
+    if (ok && wb == 0) {
+      __half* o = p.out + ((int64_t)r * p.n_cand + n) * p.ldo;
+      for (int c = 0; c < np; c += 16) {
+        float v[16];
+        tmem_ld16(lane_addr + ACC3_COL + c, v);
+        if (valid) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e)
-              if (c + e < d) o[c + e] = __float2half_rn(v[e]);
-          }
+          for (int e = 0; e < 16; ++e)
+            if (c + e < d) o[c + e] = __float2half_rn(v[e]);
         }
       }
     }
@@ -405,7 +517,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == MMA1_WARP) {
     tc_fence_after_sync();
     tmem_dealloc(tmem0, TMEM_COLS);
   }
@@ -419,6 +531,18 @@ bool tc_eligible(const xb_din_att_args& a, int* why) {
   if (tc_layout(g, a.T).total > 220 * 1024) { if (why) *why = 3; return false; }
   if (a.use_softmax && a.scores) { if (why) *why = 4; return false; }   // normalised scores are not written out
   return true;
+}
+
+size_t att_packed_bytes(int d, int h0, int h1) {
+  const TcGeom g = tc_geom(d, h0, h1, 16);
+  return (size_t)g.h0p * g.k1 * 2 + (size_t)g.h1p * g.k2 * 2 + (size_t)(g.h0p / 2 + g.h1p / 2) * 16;
+}
+
+int launch_att_pack(const AttParams& p, int act, void* dst, cudaStream_t stream) {
+  if (act == XB_ACT_DICE) att_pack_kernel<XB_ACT_DICE><<<1, 256, 0, stream>>>(p, (uint8_t*)dst);
+  else if (act == XB_ACT_SIGMOID) att_pack_kernel<XB_ACT_SIGMOID><<<1, 256, 0, stream>>>(p, (uint8_t*)dst);
+  else att_pack_kernel<XB_ACT_NONE><<<1, 256, 0, stream>>>(p, (uint8_t*)dst);
+  return check_launch("att_pack_kernel");
 }
 
 int launch_att_tc(AttParams& p, const xb_din_att_args& a, cudaStream_t stream) {

@@ -104,7 +104,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&acc_full[s]), 1); mbar_init(smem_u32(&acc_empty[s]), EPI_WARPS * 32); }
+    for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&acc_full[s]), 1); mbar_init(smem_u32(&acc_empty[s]), EPI_WARPS); }
     fence_barrier_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -167,17 +167,23 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
     }
   } else {
-    // epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32); the two warpgroups split the columns
+    // epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32); the two warpgroups split the columns.
+    // Per-column operands (bias, activation parameters) are staged in shared memory once per (n tile,
+    // batch) - a persistent CTA walks m tiles first, so that is rare - and each thread loads all the
+    // accumulator chunks it owns before it waits, so one TMEM round trip is exposed per tile.
     const int ew = warp - 2;
     const int q = warp & 3;
     const int half_id = ew >> 2;
     const int row = q * 32 + lane;
-    // 16-column chunks [c_begin, c_end) of this warpgroup
     const int chunks = p.block_n / 16;
     const int c_begin = half_id ? (chunks + 1) / 2 : 0, c_end = half_id ? chunks : (chunks + 1) / 2;
     const bool vec_base = ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0) && ((p.ldy * sizeof(TOut)) % 16 == 0) &&
                           ((p.stride_y * sizeof(TOut)) % 16 == 0);
-    int it = 0;
+    float* s_bias = reinterpret_cast<float*>(smem + STAGES * (A_STAGE_BYTES + b_stage_bytes));   // [4][256]
+    float* s_a = s_bias + 256;
+    float* s_b = s_a + 256;
+    float* s_c = s_b + 256;
+    int it = 0, cur_n0 = -1, cur_b = -1;
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       const int b = (int)(tile / tiles_mn);
@@ -185,63 +191,74 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int m0 = (int)(rem % p.tiles_m) * BLOCK_M, n0 = (int)(rem / p.tiles_m) * p.block_n;
       const int as = it & 1;
       const int gm = m0 + row;
+      if (n0 != cur_n0 || b != cur_b) {
+        cur_n0 = n0; cur_b = b;
+        asm volatile("bar.sync 2, 256;" ::: "memory");                  // everyone is done with the old columns
+        const int e = ew * 32 + lane, gn = n0 + e;
+        if (e < p.block_n) {
+          const bool in = gn < p.N;
+          float bv = 0.f, pa = 0.f, pb = 0.f, pc = 0.f;
+          if (in && p.bias_kind == XB_BIAS_ROW) bv = p.beta * load_as_f32(p.bias, (int64_t)b * p.stride_bias + gn, p.bias_dtype);
+          if (in && p.epi.kind == XB_EPI_PRELU) pa = p.epi.a[(int64_t)b * p.stride_ep + (p.epi.count == 1 ? 0 : gn)];
+          if (in && p.epi.kind == XB_EPI_DICE) {
+            const float var = p.epi.c[(int64_t)b * p.stride_ep + gn];
+            pa = p.epi.a[(int64_t)b * p.stride_ep + gn];                            // gamma
+            pc = p.epi.nosqrt ? 1.f / var : rsqrtf(var + 1e-8f);                    // 1/std
+            pb = -p.epi.b[(int64_t)b * p.stride_ep + gn] * pc;                      // -mean/std
+          }
+          s_bias[e] = bv; s_a[e] = pa; s_b[e] = pb; s_c[e] = pc;
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_full[as]), (uint32_t)(it >> 1) & 1u, 3));
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + as * acc_stride + ((uint32_t)(q * 32) << 16);
-      const float* ea = p.epi.a ? p.epi.a + (int64_t)b * p.stride_ep : nullptr;
-      const float* eb = p.epi.b ? p.epi.b + (int64_t)b * p.stride_ep : nullptr;
-      const float* ec = p.epi.c ? p.epi.c + (int64_t)b * p.stride_ep : nullptr;
       TOut* yrow = reinterpret_cast<TOut*>(p.Y) + (int64_t)b * p.stride_y + (int64_t)gm * p.ldy;
-      for (int ci = c_begin; ci < c_end; ++ci) {
-        const int c = ci * 16;
-        float v[16];
-        tmem_ld16(tmem_acc + (uint32_t)c, v);             // whole warp, uniform
-        const int gn0 = n0 + c;
-        int valid = p.N - gn0;
-        valid = valid > 16 ? 16 : valid;
-        if (valid <= 0) continue;                          // uniform across the warp
-        float bias[16];
-        if (p.bias_kind == XB_BIAS_ROW && p.bias_dtype == XB_F32) {
-          load16(reinterpret_cast<const float*>(p.bias) + (int64_t)b * p.stride_bias + gn0, valid, bias);
-        } else if (p.bias_kind == XB_BIAS_NONE) {
+      for (int cg = c_begin; cg < c_end; cg += 4) {
+        uint32_t raw[4][16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) bias[i] = 0.f;
-        } else {
-          const int64_t base = (int64_t)b * p.stride_bias + (p.bias_kind == XB_BIAS_FULL ? (int64_t)gm * p.ldbias : 0) + gn0;
-          const bool row_ok = p.bias_kind == XB_BIAS_ROW || gm < p.M;
+        for (int u = 0; u < 4; ++u)
+          if (cg + u < c_end) tmem_ld16_nowait(tmem_acc + (uint32_t)((cg + u) * 16), raw[u]);   // uniform per warp
 #pragma unroll
-          for (int i = 0; i < 16; ++i) bias[i] = (row_ok && i < valid) ? load_as_f32(p.bias, base + i, p.bias_dtype) : 0.f;
-        }
+        for (int u = 0; u < 4; ++u)
+          if (cg + u < c_end) tmem_wait_ld(raw[u]);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = fmaf(p.alpha, v[i], p.beta * bias[i]);
-        if (p.epi.kind == XB_EPI_PRELU) {
-          if (p.epi.count == 1) {
-            const float w = __ldg(ea);
+        for (int u = 0; u < 4; ++u) {
+          const int c = (cg + u) * 16;
+          const int gn0 = n0 + c;
+          int valid = p.N - gn0;
+          valid = valid > 16 ? 16 : valid;
+          if (cg + u >= c_end || valid <= 0) continue;                   // uniform across the warp
+          float v[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = act_prelu(v[i], w);
-          } else {
-            float w[16];
-            load16(ea + gn0, valid, w);
+          for (int i = 0; i < 16; ++i) v[i] = fmaf(p.alpha, __uint_as_float(raw[u][i]), s_bias[c + i]);
+          if (p.bias_kind == XB_BIAS_FULL && gm < p.M) {
+            const int64_t base = (int64_t)b * p.stride_bias + (int64_t)gm * p.ldbias + gn0;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = act_prelu(v[i], w[i]);
+            for (int i = 0; i < 16; ++i)
+              if (i < valid) v[i] += p.beta * load_as_f32(p.bias, base + i, p.bias_dtype);
           }
-        } else if (p.epi.kind == XB_EPI_DICE) {
-          float g[16], mu[16], var[16];
-          load16(ea + gn0, valid, g);
-          load16(eb + gn0, valid, mu);
-          load16(ec + gn0, valid, var);
+          if (p.epi.kind == XB_EPI_PRELU) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            v[i] = act_dice(v[i], g[i], mu[i], p.epi.nosqrt ? __fdividef(1.f, var[i]) : rsqrtf(var[i] + 1e-8f));
-        } else if (p.epi.kind == XB_EPI_SIGMOID) {
+            for (int i = 0; i < 16; ++i) v[i] = act_prelu(v[i], s_a[c + i]);
+          } else if (p.epi.kind == XB_EPI_DICE) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = act_sigmoid(v[i]);
+            for (int i = 0; i < 16; ++i) {
+              const float g = s_a[c + i];
+              const float pr = __fdividef(1.f, 1.f + __expf(-fmaf(v[i], s_c[c + i], s_b[c + i])));
+              v[i] = v[i] * fmaf(pr, 1.f - g, g);
+            }
+          } else if (p.epi.kind == XB_EPI_SIGMOID) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = act_sigmoid(v[i]);
+          }
+          if (gm < p.M) store_row16<TOut>(yrow + gn0, v, valid, vec_base && ((gn0 * sizeof(TOut)) % 16 == 0));
         }
-        if (gm < p.M) store_row16<TOut>(yrow + gn0, v, valid, vec_base && ((gn0 * sizeof(TOut)) % 16 == 0));
       }
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&acc_empty[as]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[as]));              // one arrival per epilogue warp
     }
   }
 
@@ -341,7 +358,7 @@ int gemm_umma(const xb_gemm_args& a, cudaStream_t stream) {
   // persistent: one CTA per SM walks the tiles; the accumulator is double-buffered in TMEM so the
   // epilogue of one tile overlaps the loads and MMAs of the next
   dim3 grid((unsigned)std::min<int64_t>(total, sm_count()));
-  const size_t smem = (size_t)STAGES * (A_STAGE_BYTES + p.block_n * BLOCK_K * 2) + 1024;
+  const size_t smem = (size_t)STAGES * (A_STAGE_BYTES + p.block_n * BLOCK_K * 2) + 4 * 256 * sizeof(float) + 1024;
   switch (a.y_dtype) {
     case XB_F16: return launch_umma<__half>(ma, mb, p, grid, smem, stream);
     case XB_BF16: return launch_umma<__nv_bfloat16>(ma, mb, p, grid, smem, stream);

@@ -161,11 +161,13 @@ __global__ void pack_kmajor_kernel(const void* W, int wdt, int K, int N, int64_t
   }
 }
 
-// one CTA per (request, 32-candidate slab); his_sum is rebuilt per CTA from the T k rows
+// one CTA per (request, 64-candidate slab); his_sum is rebuilt per CTA from the T k rows. The row is
+// produced two columns (one 32-bit store) at a time when d and du are even; every feature segment then
+// starts on a 4-byte boundary in X and in q / att.
 __global__ void __launch_bounds__(256) din_tower_input_kernel(const __half* user, int64_t ldu, const __half* q,
                                                               int64_t ldq, const __half* k, int64_t ldk,
                                                               const __half* att, int64_t ldatt, __half* X, int64_t ldx,
-                                                              int n_cand, int T, int d, int du) {
+                                                              int n_cand, int T, int d, int du, int pairs_ok) {
   extern __shared__ float hs[];      // [d] his_sum, then [du] user row
   float* us = hs + d;
   const int r = blockIdx.y;
@@ -176,11 +178,33 @@ __global__ void __launch_bounds__(256) din_tower_input_kernel(const __half* user
   }
   for (int e = threadIdx.x; e < du; e += blockDim.x) us[e] = __half2float(user[(int64_t)r * ldu + e]);
   __syncthreads();
-  const int n0 = blockIdx.x * 32;
+  const int n0 = blockIdx.x * 64;
+  const int rows = min(64, n_cand - n0);
+  if (pairs_ok) {
+    const int wp = (int)(ldx >> 1);                    // half2 units per row
+    for (int idx = threadIdx.x; idx < rows * wp; idx += blockDim.x) {
+      const int n = n0 + idx / wp, c = (idx % wp) * 2;
+      const int64_t row = (int64_t)r * n_cand + n;
+      float2 v = make_float2(0.f, 0.f);
+      if (c < du) v = make_float2(us[c], us[c + 1]);
+      else if (c < du + 5 * d) {
+        const int seg = (c - du) / d, e = (c - du) - seg * d;
+        if (seg == 1) v = make_float2(hs[e], hs[e + 1]);
+        else if (seg == 3) v = __half22float2(*reinterpret_cast<const __half2*>(att + row * ldatt + e));
+        else {
+          const float2 qv = __half22float2(*reinterpret_cast<const __half2*>(q + row * ldq + e));
+          if (seg == 0) v = qv;
+          else if (seg == 2) v = make_float2(qv.x * hs[e], qv.y * hs[e + 1]);
+          else v = make_float2(qv.x - hs[e], qv.y - hs[e + 1]);
+        }
+      }
+      *reinterpret_cast<__half2*>(X + row * ldx + c) = __floats2half2_rn(v.x, v.y);
+    }
+    return;
+  }
   const int width = (int)ldx;
-  for (int idx = threadIdx.x; idx < 32 * width; idx += blockDim.x) {
+  for (int idx = threadIdx.x; idx < rows * width; idx += blockDim.x) {
     const int n = n0 + idx / width, c = idx % width;
-    if (n >= n_cand) break;
     const int64_t row = (int64_t)r * n_cand + n;
     float v = 0.f;
     if (c < du) v = us[c];
@@ -314,9 +338,12 @@ extern "C" int xb_din_tower_input(const void* user, int64_t ldu, const void* q, 
              "xb_din_tower_input: leading dimension too small");
   XB_REQUIRE(requests <= 65535 && ldx <= 65536, XB_ERR_LIMIT, "xb_din_tower_input: more than 65535 requests per call");
   if (requests == 0 || n_cand == 0) return 0;
-  dim3 grid((n_cand + 31) / 32, requests);
-  din_tower_input_kernel<<<grid, 256, sizeof(float) * (d + du), (cudaStream_t)s>>>(
+  dim3 grid((n_cand + 63) / 64, requests);
+  // 32-bit accesses need even segment widths and leading dimensions and 4-byte aligned bases
+  const int pairs_ok = d % 2 == 0 && du % 2 == 0 && ldx % 2 == 0 && ldq % 2 == 0 && ldatt % 2 == 0 &&
+                       (((uintptr_t)q | (uintptr_t)att | (uintptr_t)X) & 3) == 0;
+  din_tower_input_kernel<<<grid, 256, sizeof(float) * (d + du + 2), (cudaStream_t)s>>>(
       (const __half*)user, ldu, (const __half*)q, ldq, (const __half*)k, ldk, (const __half*)att, ldatt, (__half*)X,
-      ldx, n_cand, T, d, du);
+      ldx, n_cand, T, d, du, pairs_ok);
   return check_launch("din_tower_input_kernel");
 }

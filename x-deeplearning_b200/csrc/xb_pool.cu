@@ -55,23 +55,33 @@ __device__ __forceinline__ uint64_t mix64(uint64_t x) {
   x *= 0xc4ceb9fe1a85ec53ULL; x ^= x >> 33; return x;
 }
 
-// counts -> exclusive offsets, one CTA per group. 256 threads x 4 counts per pass.
-__global__ void __launch_bounds__(256) scan_counts_kernel(const __grid_constant__ ScanParams p) {
+// counts -> exclusive offsets, one CTA per group: 1024 threads x 8 counts per pass (8192 per pass).
+constexpr int SCAN_THREADS = 1024, SCAN_ITEMS = 8;
+__global__ void __launch_bounds__(SCAN_THREADS) scan_counts_kernel(const __grid_constant__ ScanParams p) {
   const int g = blockIdx.x;
   const int32_t* __restrict__ counts = p.counts[g];
   int32_t* __restrict__ offsets = p.offsets[g];
   const int64_t batch = p.batch[g];
-  __shared__ int32_t warp_sums[8];
+  __shared__ int32_t warp_sums[SCAN_THREADS / 32];
   __shared__ int32_t carry_s;
   if (threadIdx.x == 0) carry_s = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int64_t base = 0; base < batch; base += 1024) {
-    int64_t i0 = base + (int64_t)threadIdx.x * 4;
-    int32_t c[4];
+  const bool vec = (reinterpret_cast<uintptr_t>(counts) & 15) == 0;
+  for (int64_t base = 0; base < batch; base += SCAN_THREADS * SCAN_ITEMS) {
+    const int64_t i0 = base + (int64_t)threadIdx.x * SCAN_ITEMS;
+    int32_t c[SCAN_ITEMS];
+    if (vec && i0 + SCAN_ITEMS <= batch) {
+      const int4 a = __ldg(reinterpret_cast<const int4*>(counts + i0));
+      const int4 b = __ldg(reinterpret_cast<const int4*>(counts + i0) + 1);
+      c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+    } else {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) c[e] = (i0 + e < batch) ? counts[i0 + e] : 0;
-    int32_t tsum = c[0] + c[1] + c[2] + c[3];
+      for (int e = 0; e < SCAN_ITEMS; ++e) c[e] = (i0 + e < batch) ? counts[i0 + e] : 0;
+    }
+    int32_t tsum = 0;
+#pragma unroll
+    for (int e = 0; e < SCAN_ITEMS; ++e) tsum += c[e];
     int32_t incl = tsum;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -80,17 +90,26 @@ __global__ void __launch_bounds__(256) scan_counts_kernel(const __grid_constant_
     }
     if (lane == 31) warp_sums[warp] = incl;
     __syncthreads();
-    int32_t wbase = 0;
-    for (int w = 0; w < warp; ++w) wbase += warp_sums[w];
-    int32_t carry = carry_s;
-    int32_t excl = carry + wbase + incl - tsum;
+    // the first warp scans the 32 warp totals
+    if (warp == 0) {
+      int32_t w = warp_sums[lane], wi = w;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+      for (int off = 1; off < 32; off <<= 1) {
+        int32_t v = __shfl_up_sync(0xffffffffu, wi, off);
+        if (lane >= off) wi += v;
+      }
+      warp_sums[lane] = wi - w;          // exclusive
+    }
+    __syncthreads();
+    const int32_t carry = carry_s;
+    int32_t excl = carry + warp_sums[warp] + incl - tsum;
+#pragma unroll
+    for (int e = 0; e < SCAN_ITEMS; ++e) {
       if (i0 + e < batch) offsets[i0 + e] = excl;
       excl += c[e];
     }
     __syncthreads();
-    if (threadIdx.x == 255) carry_s = carry + wbase + incl;
+    if (threadIdx.x == SCAN_THREADS - 1) carry_s = excl;      // running total after this pass
     __syncthreads();
   }
   if (threadIdx.x == 0) offsets[batch] = carry_s;
@@ -445,7 +464,7 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
   if (p.n_groups == 0) return 0;
   p.total_warps = warps;
   if (sp.n) {
-    scan_counts_kernel<<<sp.n, 256, 0, stream>>>(sp);
+    scan_counts_kernel<<<sp.n, SCAN_THREADS, 0, stream>>>(sp);
     if (int rc = check_launch("scan_counts_kernel")) return rc;
   }
   const int64_t blocks = (warps + 7) / 8;

@@ -582,6 +582,19 @@ class DinAttentionOp final : public Operator<CUDAContext> {
     a.q = q->as<void>(); a.ldq = d; a.k = k->as<void>(); a.ldk = d; a.out = y->as<void>(); a.ldo = d;
     a.requests = R; a.n_cand = n_cand; a.T = T; a.d = d; a.h0 = h0; a.h1 = h1;
     a.act = act_; a.use_softmax = softmax_; a.engine = engine_;
+    if (!operands_) {
+      // all weights are constants (checked in HostScalar/Pack): lay the MMA operands out once
+      const size_t n = xb_din_attention_packed_bytes(d, h0, h1);
+      operands_.reset(new Blob(q->device_option()));
+      operands_->set_data_type(kFloat);
+      operands_->Reshape({(TIndex)((n + 3) / 4)});
+      has_operands_ = n != 0 && W0->is_constant && W1->is_constant && W2->is_constant;
+      if (has_operands_) {
+        XB_CHECK(xb_din_attention_pack(&a, operands_->as<void>(), n, s));
+        ++launches;
+      }
+    }
+    if (has_operands_) a.w.packed = operands_->as<void>();
     XB_CHECK(xb_din_attention(&a, s));
     ++launches;
     return true;
@@ -608,6 +621,8 @@ class DinAttentionOp final : public Operator<CUDAContext> {
   int act_, engine_;
   bool softmax_;
   PackedWeight pw0_, pw1_;
+  std::unique_ptr<Blob> operands_;
+  bool has_operands_ = false;
   Derived f_[9];
 };
 REGISTER_CUDA_OPERATOR(DinAttention, DinAttentionOp);

@@ -157,6 +157,8 @@ class DinAttention:
         self.dice1 = [f(t) for t in dice1] if dice1 else None
         self.act = act
         self.h0, self.h1 = W0.shape[1], W1.shape[1]
+        self.packed = None
+        self.d = W0.shape[0] // 4
 
     def __call__(self, q, k, requests, n_cand, T, out=None, seq_len=None, use_softmax=False, scores=None, engine=0):
         d = q.shape[1]
@@ -173,6 +175,16 @@ class DinAttention:
         if self.dice0:
             w.gamma0, w.mean0, w.var0 = [t.data_ptr() for t in self.dice0]
             w.gamma1, w.mean1, w.var1 = [t.data_ptr() for t in self.dice1]
+        if self.packed is None:
+            # weights are constants: lay the operands out once
+            n = int(lib().xb_din_attention_packed_bytes(d, self.h0, self.h1))
+            self.packed = False
+            if n:
+                buf = torch.empty(n, dtype=torch.uint8, device=q.device)
+                check(lib().xb_din_attention_pack(C.byref(a), ptr(buf), n, stream()))
+                self.packed = buf
+        if self.packed is not False:
+            w.packed = self.packed.data_ptr()
         check(lib().xb_din_attention(C.byref(a), stream()))
         return out
 
