@@ -160,6 +160,33 @@ size_t xb_embedding_pool_static_max_bytes(void);
 int xb_embedding_pool_static(const xb_pool_group* groups, int32_t n_groups, xb_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
+/* Row-sharded embedding tables (tables too large for one GPU). The reference has no
+ * multi-device path (Blaze is single-process, blaze/blaze/api/cpp_api/
+ * predictor_manager_impl.cc:142-177); these entry points are the device side of the
+ * exchange this project adds around xb_embedding_pool:
+ *   rule    owner = (uint64)id % shards, local row = (uint64)id / shards
+ *   step 1  xb_route_ids: bucket a rank's ids by owner with a stable counting sort;
+ *           out_rows / out_values / out_tags hold bucket 0, then bucket 1, ...;
+ *           out_tags[i] is the segment number (index into seg_offsets) the id belongs to;
+ *           owner_counts[w] = size of bucket w (device, int64)
+ *   step 2  (caller) all-to-all of the buckets
+ *   step 3  xb_tag_counts: segment lengths of what an owner received from one source rank
+ *           (tags arrive in ascending order), then xb_embedding_pool over the local shard
+ *           with identity keys -> partial sums [segments of every source, dim] fp32
+ *   step 4  (caller) all-to-all of the partial sums back to the sources
+ *   step 5  xb_shard_combine: out[sample, group*dim + e] = sum over owners 0..shards-1, in
+ *           that fixed order, of partial[owner][group*rows + sample][e]; with avg != 0 the
+ *           sum is multiplied by (float)(1.0 / seg_len) as kAvg does. */
+size_t xb_route_scratch_bytes(int64_t n_ids, int32_t shards);
+int xb_route_ids(const int64_t* ids, const float* values, const int32_t* seg_offsets, int64_t segments,
+                 int64_t n_ids, int32_t shards, int64_t* out_rows, float* out_values, int32_t* out_tags,
+                 int64_t* owner_counts, void* scratch, size_t scratch_bytes, xb_stream_t stream);
+int xb_tag_counts(const int32_t* tags, int64_t n, int32_t* counts, int64_t n_counts, xb_stream_t stream);
+int xb_shard_combine(const float* partial, int32_t shards, int64_t segments, int32_t dim, const int32_t* seg_len,
+                     int32_t avg, void* out, int64_t out_stride, int64_t groups, int32_t out_dtype,
+                     xb_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
 /* GEMM family with fused bias + activation epilogue.
  * Replaces GemmOp::RunOnDevice (blaze/blaze/operator/op/gemm_op.h:33-107),
  * FusedParallelGemmOp::RunOnDevice (blaze/blaze/operator/fused_op/

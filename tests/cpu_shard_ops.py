@@ -1,0 +1,41 @@
+"""CPU stand-in for the device side of the sharded pooling path (numpy + the CPU oracle).
+TEST INFRASTRUCTURE: lets the exchange logic of x-deeplearning_b200/sharded.py run under gloo."""
+import numpy as np
+import torch
+
+import orc
+
+
+class CpuShardOps:
+    def route(self, ids, values, seg_offsets, shards):
+        idn = ids.numpy()
+        owner, local = orc.route(idn, shards)
+        order = np.argsort(owner, kind="stable")
+        tags = np.searchsorted(seg_offsets.numpy(), np.arange(len(idn)), side="right") - 1
+        counts = np.bincount(owner, minlength=shards).astype(np.int64)
+        v = values.numpy() if values is not None else np.ones(len(idn), np.float32)
+        return (torch.from_numpy(local[order]), torch.from_numpy(v[order].astype(np.float32)),
+                torch.from_numpy(tags[order].astype(np.int32)), torch.from_numpy(counts))
+
+    def tag_counts(self, tags, n_segments):
+        return torch.from_numpy(np.bincount(tags.numpy(), minlength=n_segments).astype(np.int32))
+
+    def pool_partial(self, table, rows, vals, counts, dim):
+        out = np.zeros((counts.numel(), dim), np.float32)
+        orc.embedding_pool(table, rows.numpy(), vals.numpy(), counts.numpy(), [dict(udf=0, out=out, col=0)])
+        return torch.from_numpy(out)
+
+    def combine(self, partial, shards, segments, dim, groups, out, seg_len=None, avg=False):
+        p = partial.numpy().reshape(shards, segments, dim)
+        acc = np.zeros((segments, dim), np.float32)
+        for w in range(shards):
+            acc = acc + p[w]
+        if avg:
+            sl = seg_len.numpy()
+            scale = np.where(sl != 0, (1.0 / np.maximum(sl, 1)).astype(np.float32), np.float32(1))
+            acc = acc * scale[:, None]
+        rows = segments // groups
+        o = out.numpy()
+        for g in range(groups):
+            o[:, g * dim:(g + 1) * dim] = acc[g * rows:(g + 1) * rows]
+        return out

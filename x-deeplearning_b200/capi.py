@@ -70,6 +70,10 @@ SYMBOLS = {
     "xb_embedding_pool": (i32, [C.POINTER(PoolGroup), i32, vp, C.c_size_t, vp]),
     "xb_embedding_pool_static_max_bytes": (C.c_size_t, []),
     "xb_embedding_pool_static": (i32, [C.POINTER(PoolGroup), i32, vp]),
+    "xb_route_scratch_bytes": (C.c_size_t, [i64, i32]),
+    "xb_route_ids": (i32, [vp, vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, C.c_size_t, vp]),
+    "xb_tag_counts": (i32, [vp, i64, vp, i64, vp]),
+    "xb_shard_combine": (i32, [vp, i32, i64, i32, vp, i32, vp, i64, i64, i32, vp]),
     "xb_gemm": (i32, [C.POINTER(GemmArgs), vp]),
     "xb_gemm_uses_tcgen05": (i32, [C.POINTER(GemmArgs)]),
     "xb_pack_weight_kmajor": (i32, [vp, i32, i32, i32, i64, vp, i32, i64, i32, i64, i64, vp]),

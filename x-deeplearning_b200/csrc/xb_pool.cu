@@ -7,6 +7,7 @@
 // segment in order and accumulates in fp32; the NS partial sums are combined
 // with a fixed xor-butterfly, so a result does not depend on scheduling.
 // HBM-bound: per id the kernel moves 8 B id + 4 B value + one row.
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <vector>
@@ -502,4 +503,188 @@ extern "C" int xb_embedding_pool_static(const xb_pool_group* groups, int32_t n_g
              "(pass exclusive offsets instead of counts, split the call, or use xb_embedding_pool)",
              need, XB_POOL_STATIC_SCRATCH_BYTES);
   return xb_embedding_pool(groups, n_groups, dev_ptr[dev], XB_POOL_STATIC_SCRATCH_BYTES, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Row-sharded tables: routing of ids to their owner rank and the fixed-order
+// combine of the partial pooled vectors that come back.
+//
+// Rule (the CPU restatement is orc_route): owner = (uint64)id % shards,
+// local row = (uint64)id / shards. Ids are bucketed by owner with a STABLE
+// counting sort (original order kept inside a bucket), so that the ids of one
+// segment stay contiguous and ascending in segment number at the owner, and the
+// whole exchange is reproducible bit for bit.
+namespace xb {
+
+constexpr int ROUTE_CHUNK = 4096;     // ids per CTA
+constexpr int ROUTE_MAX_SHARDS = 16;
+
+// pass 1: per-CTA histogram of owners
+__global__ void __launch_bounds__(256) route_count_kernel(const int64_t* __restrict__ ids, int64_t n, int shards,
+                                                          int32_t* __restrict__ block_hist) {
+  __shared__ int32_t hist[ROUTE_MAX_SHARDS];
+  if (threadIdx.x < ROUTE_MAX_SHARDS) hist[threadIdx.x] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * ROUTE_CHUNK;
+  for (int i = threadIdx.x; i < ROUTE_CHUNK; i += 256) {
+    const int64_t idx = base + i;
+    if (idx < n) atomicAdd(&hist[(int)((uint64_t)ids[idx] % (uint64_t)shards)], 1);     // integer: order-free
+  }
+  __syncthreads();
+  if (threadIdx.x < shards) block_hist[(int64_t)blockIdx.x * shards + threadIdx.x] = hist[threadIdx.x];
+}
+
+// pass 2 (one CTA): exclusive scan in (owner, CTA) order -> first output slot of every (CTA, owner);
+// owner_counts[w] = ids routed to w, owner_offsets[w] = start of bucket w
+__global__ void __launch_bounds__(256) route_scan_kernel(int32_t* __restrict__ block_hist, int64_t blocks, int shards,
+                                                         int64_t* __restrict__ owner_counts) {
+  __shared__ int64_t total_s;
+  __shared__ int32_t part[256];
+  if (threadIdx.x == 0) total_s = 0;
+  __syncthreads();
+  for (int w = 0; w < shards; ++w) {
+    const int64_t start = total_s;
+    for (int64_t b0 = 0; b0 < blocks; b0 += 256) {
+      const int64_t b = b0 + threadIdx.x;
+      const int32_t v = b < blocks ? block_hist[b * shards + w] : 0;
+      part[threadIdx.x] = v;
+      __syncthreads();
+      // Hillis-Steele inclusive scan of the 256 partials
+      for (int off = 1; off < 256; off <<= 1) {
+        int32_t add = threadIdx.x >= off ? part[threadIdx.x - off] : 0;
+        __syncthreads();
+        part[threadIdx.x] += add;
+        __syncthreads();
+      }
+      if (b < blocks) block_hist[b * shards + w] = (int32_t)(total_s + part[threadIdx.x] - v);
+      __syncthreads();
+      if (threadIdx.x == 255) total_s += part[255];
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) owner_counts[w] = total_s - start;
+    __syncthreads();
+  }
+}
+
+// pass 3: stable scatter. tags[i] is the segment number of id i (expanded from the counts by the caller's
+// offsets: found here by binary search over the exclusive offsets).
+__global__ void __launch_bounds__(256) route_scatter_kernel(const int64_t* __restrict__ ids, const float* __restrict__ values,
+                                                            const int32_t* __restrict__ seg_offsets, int64_t segments,
+                                                            int64_t n, int shards, const int32_t* __restrict__ block_base,
+                                                            int64_t* __restrict__ out_rows, float* __restrict__ out_values,
+                                                            int32_t* __restrict__ out_tags) {
+  __shared__ int32_t running[ROUTE_MAX_SHARDS];
+  __shared__ int32_t warp_cnt[8][ROUTE_MAX_SHARDS];
+  if (threadIdx.x < shards) running[threadIdx.x] = block_base[(int64_t)blockIdx.x * shards + threadIdx.x];
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t base = (int64_t)blockIdx.x * ROUTE_CHUNK;
+  for (int i0 = 0; i0 < ROUTE_CHUNK; i0 += 256) {
+    const int64_t idx = base + i0 + threadIdx.x;
+    const bool live = idx < n;
+    uint64_t id = 0;
+    int owner = -1;
+    if (live) { id = (uint64_t)ids[idx]; owner = (int)(id % (uint64_t)shards); }
+    int rank_in_warp = 0;
+    for (int w = 0; w < shards; ++w) {
+      const unsigned m = __ballot_sync(0xffffffffu, owner == w);
+      if (owner == w) rank_in_warp = __popc(m & ((1u << lane) - 1));
+      if (lane == 0) warp_cnt[warp][w] = __popc(m);
+    }
+    __syncthreads();
+    if (live) {
+      int before = 0;
+      for (int ww = 0; ww < warp; ++ww) before += warp_cnt[ww][owner];
+      const int64_t pos = (int64_t)running[owner] + before + rank_in_warp;
+      // segment of this id: last offset <= idx
+      int64_t lo = 0, hi = segments;
+      while (hi - lo > 1) {
+        const int64_t mid = (lo + hi) >> 1;
+        if ((int64_t)seg_offsets[mid] <= idx) lo = mid; else hi = mid;
+      }
+      out_rows[pos] = (int64_t)(id / (uint64_t)shards);
+      if (out_values) out_values[pos] = values ? values[idx] : 1.f;
+      out_tags[pos] = (int32_t)lo;
+    }
+    __syncthreads();
+    if (threadIdx.x < shards) {
+      int add = 0;
+      for (int ww = 0; ww < 8; ++ww) add += warp_cnt[ww][threadIdx.x];
+      running[threadIdx.x] += add;
+    }
+    __syncthreads();
+  }
+}
+
+// segment lengths at the owner: tags arrive sorted per source rank; counts are integer atomics (exact)
+__global__ void tag_count_kernel(const int32_t* __restrict__ tags, int64_t n, int32_t* __restrict__ counts) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    atomicAdd(&counts[tags[i]], 1);
+}
+
+// out[s, col0 + e] = scale(s) * sum_{w=0..shards-1} partial[w][s][e], w ascending (fixed order)
+__global__ void shard_combine_kernel(const float* __restrict__ partial, int shards, int64_t segments, int dim,
+                                     const int32_t* __restrict__ seg_len, int avg, void* out, int64_t out_stride,
+                                     int64_t seg_per_row, int out_dtype) {
+  const int64_t total = segments * dim;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t s = i / dim;
+    const int e = (int)(i - s * dim);
+    float acc = 0.f;
+    for (int w = 0; w < shards; ++w) acc += partial[((int64_t)w * segments + s) * dim + e];
+    if (avg && seg_len && seg_len[s] != 0) acc = acc * (float)(1.0 / (double)seg_len[s]);
+    // segment s = group * rows + sample  ->  out[sample, group*dim + e]
+    const int64_t rows = segments / seg_per_row;
+    const int64_t grp = s / rows, sample = s - grp * rows;
+    store_out(out, sample * out_stride + grp * dim + e, out_dtype, acc);
+  }
+}
+
+}  // namespace xb
+
+extern "C" size_t xb_route_scratch_bytes(int64_t n_ids, int32_t shards) {
+  const int64_t blocks = (n_ids + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+  return (size_t)std::max<int64_t>(blocks, 1) * shards * sizeof(int32_t);
+}
+
+extern "C" int xb_route_ids(const int64_t* ids, const float* values, const int32_t* seg_offsets, int64_t segments,
+                            int64_t n_ids, int32_t shards, int64_t* out_rows, float* out_values, int32_t* out_tags,
+                            int64_t* owner_counts, void* scratch, size_t scratch_bytes, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(shards >= 1 && shards <= ROUTE_MAX_SHARDS, XB_ERR_LIMIT, "xb_route_ids: %d shards (1..%d)", shards, ROUTE_MAX_SHARDS);
+  XB_REQUIRE(n_ids >= 0 && segments >= 0 && owner_counts && out_rows && out_tags && seg_offsets, XB_ERR_ARG, "xb_route_ids: bad arguments");
+  XB_REQUIRE(n_ids == 0 || ids, XB_ERR_ARG, "xb_route_ids: ids missing");
+  XB_REQUIRE(n_ids < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_route_ids: more than 2^31 ids per call");
+  XB_REQUIRE(scratch_bytes >= xb_route_scratch_bytes(n_ids, shards) && scratch, XB_ERR_SCRATCH, "xb_route_ids: scratch too small");
+  const int64_t blocks = std::max<int64_t>((n_ids + ROUTE_CHUNK - 1) / ROUTE_CHUNK, 1);
+  int32_t* hist = reinterpret_cast<int32_t*>(scratch);
+  route_count_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, n_ids, shards, hist);
+  route_scan_kernel<<<1, 256, 0, stream>>>(hist, blocks, shards, owner_counts);
+  route_scatter_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, values, seg_offsets, segments, n_ids, shards, hist, out_rows,
+                                                             out_values, out_tags);
+  return check_launch("route kernels");
+}
+
+extern "C" int xb_tag_counts(const int32_t* tags, int64_t n, int32_t* counts, int64_t n_counts, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(counts && n >= 0 && n_counts >= 0 && (n == 0 || tags), XB_ERR_ARG, "xb_tag_counts: bad arguments");
+  XB_CUDA(cudaMemsetAsync(counts, 0, (size_t)n_counts * sizeof(int32_t), stream));
+  if (n == 0) return 0;
+  const int64_t blocks = std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 8);
+  tag_count_kernel<<<(unsigned)blocks, 256, 0, stream>>>(tags, n, counts);
+  return check_launch("tag_count_kernel");
+}
+
+extern "C" int xb_shard_combine(const float* partial, int32_t shards, int64_t segments, int32_t dim, const int32_t* seg_len,
+                                int32_t avg, void* out, int64_t out_stride, int64_t groups, int32_t out_dtype,
+                                xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(partial && out && shards >= 1 && segments >= 0 && dim >= 1 && groups >= 1, XB_ERR_ARG, "xb_shard_combine: bad arguments");
+  XB_REQUIRE(segments % groups == 0, XB_ERR_ARG, "xb_shard_combine: segments %lld not a multiple of groups %lld", (long long)segments, (long long)groups);
+  XB_REQUIRE(out_dtype == XB_F32 || out_dtype == XB_F16, XB_ERR_UNSUPPORTED, "xb_shard_combine: output dtype %d", out_dtype);
+  if (segments == 0) return 0;
+  const int64_t blocks = std::min<int64_t>((segments * dim + 255) / 256, (int64_t)sm_count() * 8);
+  shard_combine_kernel<<<(unsigned)blocks, 256, 0, stream>>>(partial, shards, segments, dim, seg_len, avg, out, out_stride, groups,
+                                                             out_dtype);
+  return check_launch("shard_combine_kernel");
 }
