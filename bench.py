@@ -371,6 +371,89 @@ def run_micro(args):
     print(json.dumps({"micro": args.micro, "launches": reps, "status": "ok", "ms_per_launch": t0.elapsed_time(t1) / reps}))
 
 
+def run_sharded(args):
+    """Row-sharded pooling + MLP (the large-table configuration): 4 tables x `--table-rows` rows x dim 32
+    fp16 sharded by id % world, batch 65536 x 40 feature groups split by sample, ids routed and pooled
+    vectors returned with NCCL all-to-all, then the MLP 1280-1024-512-256-1 (PReLU, sigmoid) data-parallel.
+    Launch under torch.distributed.run; prints one JSON line on rank 0."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import pkg
+    pkg.load()
+    from x_deeplearning_b200 import capi, ops, sharded, workloads
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    comm, gops = sharded.DistComm(), sharded.GpuShardOps()
+    n_tables, gpt, dim = 4, 10, 32
+    rows_total = args.table_rows
+    B = 65536 // world
+    rng = np.random.default_rng(100 + rank)
+    tables = []
+    for t in range(n_tables):
+        local_rows = (rows_total - rank + world - 1) // world
+        tb = ops.Table.__new__(ops.Table)
+        tb.rows, tb.dim, tb.dtype, tb.pitch = local_rows, dim, torch.float16, dim * 2
+        tb.buf = torch.empty((local_rows, dim), dtype=torch.float16, device="cuda")
+        for r0 in range(0, local_rows, 1 << 24):
+            tb.buf[r0:r0 + (1 << 24)].normal_(0, 0.01)
+        tb.desc = capi.TableDesc()
+        tb.desc.weights, tb.desc.rows, tb.desc.dim, tb.desc.dtype, tb.desc.row_pitch_bytes = tb.buf.data_ptr(), local_rows, dim, capi.XB_F16, dim * 2
+        tb.slot_keys = tb.slot_rows = None
+        tables.append(tb)
+    feeds = []
+    for t in range(n_tables):
+        counts = rng.integers(1, 31, gpt * B).astype(np.int32)
+        n = int(counts.sum())
+        ids = workloads.zipf_ids(rng, rows_total, n, 1.05)
+        off = np.zeros(len(counts) + 1, np.int32)
+        np.cumsum(counts, out=off[1:])
+        feeds.append((torch.from_numpy(ids).cuda(), torch.from_numpy(off).cuda(), n))
+    dims = [n_tables * gpt * dim, 1024, 512, 256, 1]
+    Ws = [torch.randn((dims[i + 1], dims[i]), device="cuda", dtype=torch.float16) / dims[i] ** 0.5 for i in range(4)]
+    bs = [torch.randn(dims[i + 1], device="cuda") * 0.01 for i in range(4)]
+    slope = torch.full((1,), 0.25, device="cuda")
+    pooled = torch.empty((B, dims[0]), dtype=torch.float16, device="cuda")
+    acts = [torch.empty((B, dims[i + 1]), dtype=torch.float16, device="cuda") for i in range(4)]
+
+    def step():
+        stats = []
+        for t in range(n_tables):
+            ids, off, _ = feeds[t]
+            stats.append(sharded.sharded_pool(comm, gops, tables[t], dim, ids, None, off, gpt, pooled[:, t * gpt * dim:(t + 1) * gpt * dim]))
+        x = pooled
+        for i in range(4):
+            last = i == 3
+            ops.gemm(x, Ws[i], Y=acts[i], bias=bs[i], trans_b=True, M=B, N=dims[i + 1], K=dims[i],
+                     epilogue=capi.XB_EPI_SIGMOID if last else capi.XB_EPI_PRELU, ep=(None if last else slope, None, None),
+                     ep_count=0 if last else 1)
+            x = acts[i]
+        return stats
+
+    for _ in range(args.warmup):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier(); torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        stats = step()
+    e1.record()
+    dist.barrier(); torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    assert ops.device_status() == 0
+    if rank == 0:
+        ms = float(t.item()) / args.steps
+        n_ids = sum(f[2] for f in feeds)
+        print(json.dumps({"micro": "sharded", "n_gpus": world, "ms_per_step": ms, "samples_per_s": 65536 / (ms * 1e-3),
+                          "table_rows": rows_total, "ids_per_rank_step": n_ids,
+                          "routed_bytes_per_rank_step": sum(s["routed_bytes"] for s in stats),
+                          "returned_bytes_per_rank_step": sum(s["returned_bytes"] for s in stats),
+                          "note": "max over ranks, CUDA events; MLP 1280-1024-512-256-1 included"}))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -381,9 +464,12 @@ def main():
     ap.add_argument("--batches", type=int, default=8, help="distinct pre-generated request batches that are cycled")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and pooling side measurements")
-    ap.add_argument("--micro", choices=["att", "pool", "gemm"], help="run --steps launches of one kernel on a small case "
+    ap.add_argument("--table-rows", type=int, default=200_000_000, help="rows per table of --micro sharded")
+    ap.add_argument("--micro", choices=["att", "pool", "gemm", "sharded"], help="run --steps launches of one kernel on a small case "
                     "(for profiler captures) instead of the benchmark")
     args = ap.parse_args()
+    if args.micro == "sharded":
+        return run_sharded(args)
     if args.micro:
         return run_micro(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
