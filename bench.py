@@ -193,7 +193,10 @@ def run_ours(args):
         "gpu_launches": din.DinModel.LAUNCHES_PER_FORWARD * K,
         "roofline": {"kernel": "din_att_tc_kernel", "bound": "tensor", "achieved": achieved_tf,
                      "peak": pk["tf_sustained"], "unit": "TFLOP/s", "frac": achieved_tf / pk["tf_sustained"],
-                     "traffic": None, "peak_source": pk["source"] + " (sustained bf16)", "ms_per_launch": att_ms,
+                     # DRAM bytes per launch: 440 KB measured by ncu on a 4-request launch (q, k and the result
+                     # only), scaled by the requests of one launch; see profiles/din_att_tc_kernel_4req.md
+                     "traffic": 110016 * R, "traffic_source": "ncu capture of 4 requests scaled by requests per launch",
+                     "peak_source": pk["source"] + " (sustained bf16)", "ms_per_launch": att_ms,
                      "pool_ms_per_step": pool_ms},
         "clocks": clocks,
     }
