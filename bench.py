@@ -194,7 +194,7 @@ def run_ours(args):
         "roofline": {"kernel": "din_att_tc_kernel", "bound": "tensor", "achieved": achieved_tf,
                      "peak": pk["tf_sustained"], "unit": "TFLOP/s", "frac": achieved_tf / pk["tf_sustained"],
                      # DRAM bytes per launch: 440 KB measured by ncu on a 4-request launch (q, k and the result
-                     # only), scaled by the requests of one launch; see profiles/din_att_tc_kernel_4req.md
+                     # only), scaled by the requests of one launch
                      "traffic": 110016 * R, "traffic_source": "ncu capture of 4 requests scaled by requests per launch",
                      "peak_source": pk["source"] + " (sustained bf16)", "ms_per_launch": att_ms,
                      "pool_ms_per_step": pool_ms},
@@ -463,7 +463,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--requests", type=int, default=64, help="requests per step (each 1 user x 1000 candidates)")
+    ap.add_argument("--requests", type=int, default=74,
+                    help="requests per step (each 1 user x 1000 candidates); 74 requests = 592 attention tiles = 4 x 148 SMs")
     ap.add_argument("--batches", type=int, default=8, help="distinct pre-generated request batches that are cycled")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and pooling side measurements")

@@ -171,12 +171,23 @@ __global__ void __launch_bounds__(256) din_tower_input_kernel(const __half* user
   extern __shared__ float hs[];      // [d] his_sum, then [du] user row
   float* us = hs + d;
   const int r = blockIdx.y;
-  for (int e = threadIdx.x; e < d; e += blockDim.x) {
+  // his_sum: the block's threads split the T steps (groups of d threads take every G-th step), partial
+  // sums meet in shared memory and are added in group order, so the result does not depend on timing
+  float* part = us + du;             // [G][d]
+  const int G = max(1, min((int)blockDim.x / d, 8));
+  if ((int)threadIdx.x < G * d) {
+    const int gi = threadIdx.x / d, e = threadIdx.x - gi * d;
     float s = 0.f;
-    for (int t = 0; t < T; ++t) s += __half2float(k[((int64_t)r * T + t) * ldk + e]);
-    hs[e] = s;
+    for (int t = gi; t < T; t += G) s += __half2float(k[((int64_t)r * T + t) * ldk + e]);
+    part[gi * d + e] = s;
   }
   for (int e = threadIdx.x; e < du; e += blockDim.x) us[e] = __half2float(user[(int64_t)r * ldu + e]);
+  __syncthreads();
+  for (int e = threadIdx.x; e < d; e += blockDim.x) {
+    float s = 0.f;
+    for (int gi = 0; gi < G; ++gi) s += part[gi * d + e];
+    hs[e] = s;
+  }
   __syncthreads();
   const int n0 = blockIdx.x * 64;
   const int rows = min(64, n_cand - n0);
@@ -334,6 +345,7 @@ extern "C" int xb_din_tower_input(const void* user, int64_t ldu, const void* q, 
                                   xb_stream_t s) {
   XB_REQUIRE(user && q && k && att && X, XB_ERR_ARG, "xb_din_tower_input: null tensor");
   XB_REQUIRE(requests >= 0 && n_cand >= 0 && T >= 0 && d > 0 && du >= 0, XB_ERR_ARG, "xb_din_tower_input: bad sizes");
+  XB_REQUIRE(d <= 256 && du <= 4096, XB_ERR_LIMIT, "xb_din_tower_input: d <= 256 and du <= 4096");
   XB_REQUIRE(ldx >= du + 5 * d && ldu >= du && ldq >= d && ldk >= d && ldatt >= d, XB_ERR_ARG,
              "xb_din_tower_input: leading dimension too small");
   XB_REQUIRE(requests <= 65535 && ldx <= 65536, XB_ERR_LIMIT, "xb_din_tower_input: more than 65535 requests per call");
@@ -342,7 +354,7 @@ extern "C" int xb_din_tower_input(const void* user, int64_t ldu, const void* q, 
   // 32-bit accesses need even segment widths and leading dimensions and 4-byte aligned bases
   const int pairs_ok = d % 2 == 0 && du % 2 == 0 && ldx % 2 == 0 && ldq % 2 == 0 && ldatt % 2 == 0 &&
                        (((uintptr_t)q | (uintptr_t)att | (uintptr_t)X) & 3) == 0;
-  din_tower_input_kernel<<<grid, 256, sizeof(float) * (d + du + 2), (cudaStream_t)s>>>(
+  din_tower_input_kernel<<<grid, 256, sizeof(float) * (9 * d + du + 2), (cudaStream_t)s>>>(
       (const __half*)user, ldu, (const __half*)q, ldq, (const __half*)k, ldk, (const __half*)att, ldatt, (__half*)X,
       ldx, n_cand, T, d, du, pairs_ok);
   return check_launch("din_tower_input_kernel");

@@ -271,10 +271,29 @@ __global__ void __launch_bounds__(256) pool_kernel(const __grid_constant__ PoolP
       float scale = 1.f;
       if (it.udf == XB_UDF_AVG && num != 0) scale = (float)(1.0 / (double)num);
       const int64_t o = seg * it.stride + col0;
-      for (int e = 0; e < epc; ++e) {
-        if (col0 + e < g.dim) {
-          float r = (it.udf == XB_UDF_AVG && num != 0) ? acc[e] * scale : acc[e];
-          store_out(it.out, o + e, g.out_dtype, r);
+      const bool avg = it.udf == XB_UDF_AVG && num != 0;
+      float r[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r[e] = avg ? acc[e] * scale : acc[e];
+      const int nvalid = min(epc, g.dim - col0);
+      if (g.out_dtype == XB_F32) {
+        float* dst = reinterpret_cast<float*>(it.out) + o;
+        if (nvalid == 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
+        } else {
+          for (int e = 0; e < nvalid; ++e) dst[e] = r[e];
+        }
+      } else {
+        __half* dst = reinterpret_cast<__half*>(it.out) + o;
+        if ((reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+          // 32-bit stores of column pairs; an odd tail column goes alone
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            if (e + 1 < nvalid) *reinterpret_cast<__half2*>(dst + e) = __floats2half2_rn(r[e], r[e + 1]);
+            else if (e < nvalid) dst[e] = __float2half_rn(r[e]);
+          }
+        } else {
+          for (int e = 0; e < nvalid; ++e) dst[e] = __float2half_rn(r[e]);
         }
       }
     }

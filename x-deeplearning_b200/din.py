@@ -54,8 +54,9 @@ class DinModel:
         p["hist_item"], p["hist_cate"] = i64(n_hist), i64(n_hist)
         p["cand_item"], p["cand_cate"] = i64(R * n_cand), i64(R * n_cand)
         p["seq_len"] = torch.empty(R, dtype=torch.int32, device=dev)
-        p["ones_R"] = torch.ones(R, dtype=torch.int32, device=dev)
-        p["ones_C"] = torch.ones(R * n_cand, dtype=torch.int32, device=dev)
+        # one id per user / candidate segment: their CSR offsets are 0, 1, 2, ... (no counts to scan)
+        p["ones_R"] = torch.arange(R + 1, dtype=torch.int32, device=dev)
+        p["ones_C"] = torch.arange(R * n_cand + 1, dtype=torch.int32, device=dev)
         h = lambda *s: torch.empty(s, dtype=torch.float16, device=dev)
         p["user_emb"], p["k"], p["q"] = h(R, G * e), h(R, T * d), h(R * n_cand, d)
         p["att"], p["X"] = h(R * n_cand, d), h(R * n_cand, self.ldx)
@@ -66,7 +67,8 @@ class DinModel:
         groups = []
         for g in range(G):
             groups.append(ops.make_group(self.user[g], p["user_ids"][g], None, p["ones_R"],
-                                         [dict(udf=S, out=p["user_emb"], col=g * e)], torch.float16))
+                                         [dict(udf=S, out=p["user_emb"], col=g * e)], torch.float16,
+                                         segments_are_offsets=True))
         # behaviour rows go straight into k [R, T, d]: item at column 0, category at column e of each step
         groups.append(ops.make_group(self.item, p["hist_item"], None, p["seq_len"],
                                      [dict(udf=A, trunc_num=T, trunc_dir=capi.XB_TRUNC_REVERSE, assign_stride=d,
@@ -75,9 +77,9 @@ class DinModel:
                                      [dict(udf=A, trunc_num=T, trunc_dir=capi.XB_TRUNC_REVERSE, assign_stride=d,
                                            out=p["k"], col=e)], torch.float16))
         groups.append(ops.make_group(self.item, p["cand_item"], None, p["ones_C"],
-                                     [dict(udf=S, out=p["q"], col=0)], torch.float16))
+                                     [dict(udf=S, out=p["q"], col=0)], torch.float16, segments_are_offsets=True))
         groups.append(ops.make_group(self.cate, p["cand_cate"], None, p["ones_C"],
-                                     [dict(udf=S, out=p["q"], col=e)], torch.float16))
+                                     [dict(udf=S, out=p["q"], col=e)], torch.float16, segments_are_offsets=True))
         p["pool"] = ops.PoolPlan(groups, device=dev)
         self._plans[key] = p
         return p
