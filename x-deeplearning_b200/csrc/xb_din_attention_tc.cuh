@@ -7,9 +7,9 @@
 // layer-2 activations for parity b; two more warps issue the MMAs (one per layer).
 // Operands and accumulators are double-buffered by step parity, so in steady
 // state nobody waits: the tensor pipe, the SFU and the FP16 pipe overlap.
-//   worker: A1 = [q|k_t|q-k_t|q*k_t] (fp16, 128 x k1) into shared memory
-//   MMA   : acc1[128 x h0p] = A1 * W0^T                  (TMEM accumulator)
-//   worker: acc1 -> activation -> fp16 A2 in shared memory
+//   worker: A1 = [q|k_t|q-k_t|q*k_t] (fp16, 128 x k1) into tensor memory (tcgen05.st)
+//   MMA   : acc1[128 x h0p] = A1 * W0^T                  (A from tensor memory, W0 from shared memory)
+//   worker: acc1 -> activation -> fp16 A2 in tensor memory
 //   MMA   : acc2[128 x h1p] = A2 * W1^T
 //   worker: acc2 -> activation, dot with W2 -> score s[n,t] -> fp16 column t of S
 // and, after the last step,
@@ -23,10 +23,12 @@
 //   sigmoid(z) = 1/2 + 1/2 tanh(z/2), so Dice(x) = x * (C + D*tanh(A*x + B)) with
 //   A = rstd/2, B = -mean*rstd/2, C = (1+gamma)/2, D = (1-gamma)/2 per column.
 //
-// Shared-memory operands use the un-swizzled K-major core-matrix layout: the
-// 16-byte chunk c (8 consecutive k) of row r sits at c*(rows*16) + r*16, so the
-// 32 rows a warp writes for one chunk are 512 contiguous bytes, the
-// descriptor's leading-dimension offset is rows*16 and its stride offset 128.
+// The A operands never touch shared memory: a thread owns one candidate row = one
+// tensor-memory lane and stores its fp16 pairs into that lane's columns (two
+// consecutive k per 32-bit column). Shared-memory operands (weights, S, K^T) use
+// the un-swizzled K-major core-matrix layout: the 16-byte chunk c (8 consecutive k)
+// of row r sits at c*(rows*16) + r*16, the descriptor's leading-dimension offset
+// is rows*16 and its stride offset 128.
 #pragma once
 
 namespace xb {
@@ -35,10 +37,12 @@ namespace {
 constexpr int TC_THREADS = 576;          // 4 worker warpgroups + 2 MMA-issuing warps
 constexpr int MMA1_WARP = 16, MMA2_WARP = 17;
 constexpr int TMEM_COLS = 512;
-constexpr int ACC1_COL = 0, ACC2_COL = 128, ACC3_COL = 192, WG_COL = 256;
 
+// Tensor-memory columns of one step parity: [acc1 | acc2 | A2 | A1]; the closing product's
+// accumulator reuses parity 0's A1 columns, which are idle by then.
 struct TcGeom {
   int dp, nch, k1, ones1, h0p, k2, h1p, tp, np;
+  int c_acc2, c_a2, c_a1, wg;
 };
 
 __host__ __device__ inline TcGeom tc_geom(int d, int h0, int h1, int T) {
@@ -52,19 +56,21 @@ __host__ __device__ inline TcGeom tc_geom(int d, int h0, int h1, int T) {
   g.h1p = (h1 + 15) / 16 * 16;
   g.tp = (T + 15) / 16 * 16;
   g.np = (g.dp + 15) / 16 * 16;
+  g.c_acc2 = g.h0p;
+  g.c_a2 = g.h0p + g.h1p;
+  g.c_a1 = g.c_a2 + g.k2 / 2;
+  g.wg = g.c_a1 + g.k1 / 2;
   return g;
 }
 
 struct TcSmemLayout {
-  int w0, w1, a1, a2, s, kt, kh, c1, c2, total;
+  int w0, w1, s, kt, kh, c1, c2, total;
 };
 __host__ __device__ inline TcSmemLayout tc_layout(const TcGeom& g, int T) {
   TcSmemLayout L;
   int off = 0;
   L.w0 = off; off += g.h0p * g.k1 * 2;          // W0 operand [h0p rows, k1]
   L.w1 = off; off += g.h1p * g.k2 * 2;          // W1 operand [h1p rows, k2]
-  L.a1 = off; off += 2 * 128 * g.k1 * 2;        // A1, one buffer per warpgroup
-  L.a2 = off; off += 2 * 128 * g.k2 * 2;        // A2, one buffer per warpgroup
   L.s = off; off += 128 * g.tp * 2;             // scores [128, tp]
   L.kt = off; off += g.np * g.tp * 2;           // K^T operand [np rows (feature), tp (step)]
   L.kh = off; off += T * g.dp * 2;              // k rows for building A1
@@ -246,7 +252,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     // ---- layer-1 MMA issue: one thread, descriptors advanced by constant steps -----------------------
     if (lane == 0) {
       const uint64_t db0 = make_desc_interleaved(smem_u32(w0s), h0p * 16, 128);
-      const uint64_t db_step = (uint64_t)((2 * h0p * 16) >> 4), da_step = (uint64_t)((2 * 128 * 16) >> 4);
+      const uint64_t db_step = (uint64_t)((2 * h0p * 16) >> 4);
       const int nks = k1 / 16;
       for (int j = 0; j < tl; ++j) {
         const int b = j & 1;
@@ -254,13 +260,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         // A1 of step j is written; acc1[b] was drained before the layer-1 warps signalled a2_full(j-2)
         if (!(mbar_wait(smem_u32(&a1_full[b]), ph, 10) && mbar_wait(smem_u32(&a2_full[b]), ph ^ 1u, 14))) break;
         tc_fence_after_sync();
-        uint64_t da = make_desc_interleaved(smem_u32(smem + L.a1 + b * (128 * k1 * 2)), 128 * 16, 128);
+        uint32_t ta = tmem0 + b * G.wg + G.c_a1;                // A1 lives in tensor memory
         uint64_t db = db0;
-        const uint32_t acc1 = tmem0 + b * WG_COL + ACC1_COL;
-        mma_f16_ss(acc1, da, db, p.idesc1, 0u);
+        const uint32_t acc1 = tmem0 + b * G.wg;
+        mma_f16_ts(acc1, ta, db, p.idesc1, 0u);
         for (int ks = 1; ks < nks; ++ks) {
-          da += da_step; db += db_step;
-          mma_f16_ss(acc1, da, db, p.idesc1, 1u);
+          ta += 8; db += db_step;
+          mma_f16_ts(acc1, ta, db, p.idesc1, 1u);
         }
         mma_commit(smem_u32(&acc1_full[b]));
       }
@@ -278,13 +284,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         ok = mbar_wait(smem_u32(&a2_full[b]), ph, 11) && mbar_wait(smem_u32(&acc2_free[b]), ph ^ 1u, 13);
         if (!ok) break;
         tc_fence_after_sync();
-        uint64_t da = make_desc_interleaved(smem_u32(smem + L.a2 + b * (128 * k2 * 2)), 128 * 16, 128);
+        uint32_t ta = tmem0 + b * G.wg + G.c_a2;                // A2 lives in tensor memory
         uint64_t db = db0;
-        const uint32_t acc2 = tmem0 + b * WG_COL + ACC2_COL;
-        mma_f16_ss(acc2, da, db, p.idesc2, 0u);
+        const uint32_t acc2 = tmem0 + b * G.wg + G.c_acc2;
+        mma_f16_ts(acc2, ta, db, p.idesc2, 0u);
         for (int ks = 1; ks < nks; ++ks) {
-          da += da_step; db += db_step;
-          mma_f16_ss(acc2, da, db, p.idesc2, 1u);
+          ta += 8; db += db_step;
+          mma_f16_ts(acc2, ta, db, p.idesc2, 1u);
         }
         mma_commit(smem_u32(&acc2_full[b]));
       }
@@ -295,7 +301,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         uint64_t db = make_desc_interleaved(smem_u32(kts), np * 16, 128);
         const uint64_t db3 = (uint64_t)((2 * np * 16) >> 4);
         for (int ks = 0; ks < tp / 16; ++ks) {
-          mma_f16_ss(tmem0 + ACC3_COL, da, db, p.idesc3, ks > 0 ? 1u : 0u);
+          mma_f16_ss(tmem0 + G.c_a1, da, db, p.idesc3, ks > 0 ? 1u : 0u);
           da += da_step; db += db3;
         }
       }
@@ -304,24 +310,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   } else if (warp < 8) {
     // ---- layer-1 warpgroups: acc1 -> activation -> A2, for the steps of parity wb ---------------------
     const int wb = warp >> 2;
-    const int row = (warp & 3) * 32 + lane;                 // TMEM lane == candidate row of the tile
-    const uint32_t lane_addr = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint4 ones_chunk = make_uint4(0x00003C00u, 0, 0, 0);            // fp16 {1,0,0,0,0,0,0,0}
+    const uint32_t lane_addr = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);   // TMEM lane == candidate row of the tile
     {
-      uint8_t* a2 = smem + L.a2 + wb * (128 * k2 * 2);
-      *reinterpret_cast<uint4*>(a2 + (h0p / 8) * (128 * 16) + row * 16) = ones_chunk;     // column h0p: bias b1
-      *reinterpret_cast<uint4*>(a2 + (h0p / 8 + 1) * (128 * 16) + row * 16) = make_uint4(0, 0, 0, 0);
+      // columns h0p.. of A2: the constant 1 that carries bias b1, then zeros (fp16 pairs per 32-bit column)
+      const uint32_t a2t = lane_addr + wb * G.wg + G.c_a2 + h0p / 2;
+      tmem_st4(a2t, 0x00003C00u, 0u, 0u, 0u);
+      tmem_st4(a2t + 4, 0u, 0u, 0u, 0u);
+      tmem_wait_st();
     }
     bool ok = true;
     for (int j = wb; j < tl; j += 2) {
       const int b = wb;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      uint8_t* a2 = smem + L.a2 + b * (128 * k2 * 2) + row * 16;
+      const uint32_t a2t = lane_addr + b * G.wg + G.c_a2;
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[b]), ph, 20) &&
                                        mbar_wait(smem_u32(&acc2_full[b]), ph ^ 1u, 23));   // M2(j-2) has read A2[b]
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t acc1 = lane_addr + b * WG_COL + ACC1_COL;
+      const uint32_t acc1 = lane_addr + b * G.wg;
       for (int c = 0; c < h0p; c += 32) {
         uint32_t v[32];
         const bool full = h0p - c >= 32;
@@ -336,7 +342,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         // all pairs of the block go through each stage together, so the SFU and FP16 pipes see
         // sixteen independent operations back to back; the stores come last
         const uint4* __restrict__ cc = c1 + (c >> 1);
-        uint8_t* __restrict__ dst = a2 + (c >> 3) * (128 * 16);
         uint32_t y[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e)
@@ -357,12 +362,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
             }
           }
         }
-#pragma unroll
-        for (int q8 = 0; q8 < 4; ++q8)
-          if (full || q8 < 2)
-            *reinterpret_cast<uint4*>(dst + q8 * (128 * 16)) = make_uint4(y[4 * q8], y[4 * q8 + 1], y[4 * q8 + 2], y[4 * q8 + 3]);
+        if (full) tmem_st16(a2t + (c >> 1), y);
+        else tmem_st8(a2t + (c >> 1), y);
       }
-      fence_proxy_async_smem();
+      tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&a2_full[b]));        // one arrival per warp
@@ -393,19 +396,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       qv[c] = *reinterpret_cast<uint4*>(h);
     }
     // constant part of this parity's A1 buffer: the q segment (and the ones column)
+    // (chunk c of 8 fp16 is 4 tensor-memory columns of this thread's lane)
     {
-      uint8_t* a1 = smem + L.a1 + wb * (128 * k1 * 2) + row * 16;
+      const uint32_t a1t = lane_addr + wb * G.wg + G.c_a1;
 #pragma unroll
       for (int c = 0; c < 8; ++c)
-        if (c < nch) *reinterpret_cast<uint4*>(a1 + c * (128 * 16)) = qv[c];
+        if (c < nch) tmem_st4(a1t + 4 * c, qv[c].x, qv[c].y, qv[c].z, qv[c].w);
       if (G.ones1 == 4 * dp) {
-        *reinterpret_cast<uint4*>(a1 + (4 * nch) * (128 * 16)) = make_uint4(0x00003C00u, 0, 0, 0);
-        *reinterpret_cast<uint4*>(a1 + (4 * nch + 1) * (128 * 16)) = make_uint4(0, 0, 0, 0);
+        tmem_st4(a1t + 16 * nch, 0x00003C00u, 0u, 0u, 0u);
+        tmem_st4(a1t + 16 * nch + 4, 0u, 0u, 0u, 0u);
       }
+      tmem_wait_st();
     }
 
     auto build_a1 = [&](int t) {
-      uint8_t* a1 = smem + L.a1 + (t & 1) * (128 * k1 * 2) + row * 16;
+      const uint32_t a1t = lane_addr + (t & 1) * G.wg + G.c_a1;
       const uint4* kt = reinterpret_cast<const uint4*>(khs + t * dp);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -419,17 +424,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
 #pragma unroll
           for (int e = 0; e < 4; ++e) { dh[e] = __hsub2(qh[e], kh[e]); ph2[e] = __hmul2(qh[e], kh[e]); }
           // q's padding column holding the constant 1 gives 1-0 in `df`; harmless, its W0 rows are zero
-          *reinterpret_cast<uint4*>(a1 + (nch + c) * (128 * 16)) = kc;
-          *reinterpret_cast<uint4*>(a1 + (2 * nch + c) * (128 * 16)) = df;
-          *reinterpret_cast<uint4*>(a1 + (3 * nch + c) * (128 * 16)) = pr;
+          tmem_st4(a1t + 4 * (nch + c), kc.x, kc.y, kc.z, kc.w);
+          tmem_st4(a1t + 4 * (2 * nch + c), df.x, df.y, df.z, df.w);
+          tmem_st4(a1t + 4 * (3 * nch + c), pr.x, pr.y, pr.z, pr.w);
         }
       }
-      fence_proxy_async_smem();
+      tmem_wait_st();
+      tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&a1_full[t & 1]));
     };
 
     bool ok = true;
+    const int npairs2 = (p.h1 + 1) / 2;
     if (tl > wb) build_a1(wb);
     for (int j = wb; j < tl; j += 2) {
       const int b = wb;
@@ -443,7 +450,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph, 21));
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t acc2 = lane_addr + b * WG_COL + ACC2_COL;
+      const uint32_t acc2 = lane_addr + b * G.wg + G.c_acc2;
       __half2 part[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) part[e] = __floats2half2_rn(0.f, 0.f);
@@ -460,14 +467,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
 #pragma unroll
           for (int e = 0; e < 8; ++e) part[e & 3] = __hfma2(bits_h2(x[e]), bits_h2(cc[e].z), part[e & 3]);
         } else {
+          const int live = npairs2 - (c >> 1);           // column pairs of this block that are not padding
 #pragma unroll
-          for (int e = 0; e < 8; ++e) th[e] = h2_bits(__hfma2(bits_h2(x[e]), bits_h2(cc[e].x), bits_h2(cc[e].y)));
+          for (int e = 0; e < 8; ++e)
+            if (e < live) th[e] = h2_bits(__hfma2(bits_h2(x[e]), bits_h2(cc[e].x), bits_h2(cc[e].y)));
 #pragma unroll
-          for (int e = 0; e < 8; ++e) th[e] = tanh_f16x2(th[e]);
+          for (int e = 0; e < 8; ++e)
+            if (e < live) th[e] = tanh_f16x2(th[e]);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const __half2 g = __hfma2(bits_h2(th[e]), bits_h2(cc[e].w), bits_h2(cc[e].z));
-            part[e & 3] = ACT == XB_ACT_DICE ? __hfma2(bits_h2(x[e]), g, part[e & 3]) : __hadd2(part[e & 3], g);
+            if (e < live) {
+              const __half2 g = __hfma2(bits_h2(th[e]), bits_h2(cc[e].w), bits_h2(cc[e].z));
+              part[e & 3] = ACT == XB_ACT_DICE ? __hfma2(bits_h2(x[e]), g, part[e & 3]) : __hadd2(part[e & 3], g);
+            }
           }
         }
       }
@@ -505,7 +517,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       __half* o = p.out + ((int64_t)r * p.n_cand + n) * p.ldo;
       for (int c = 0; c < np; c += 16) {
         float v[16];
-        tmem_ld16(lane_addr + ACC3_COL + c, v);
+        tmem_ld16(lane_addr + G.c_a1 + c, v);
         if (valid) {
 #pragma unroll
           for (int e = 0; e < 16; ++e)
@@ -528,6 +540,7 @@ bool tc_eligible(const xb_din_att_args& a, int* why) {
   if (g.dp > 64 || g.k1 > 272) { if (why) *why = 1; return false; }
   if (g.h0p > 128 || g.h1p > 64) { if (why) *why = 2; return false; }
   if (g.tp > 256) { if (why) *why = 5; return false; }
+  if (2 * g.wg > TMEM_COLS || g.np > g.k1 / 2) { if (why) *why = 6; return false; }
   if (tc_layout(g, a.T).total > 220 * 1024) { if (why) *why = 3; return false; }
   if (a.use_softmax && a.scores) { if (why) *why = 4; return false; }   // normalised scores are not written out
   return true;

@@ -62,21 +62,6 @@ __device__ __forceinline__ void store_row16(TOut* dst, const float (&v)[16], int
   }
 }
 
-// bias and per-column activation parameters of 16 consecutive columns, as fp32
-__device__ __forceinline__ void load16(const float* __restrict__ src, int n_valid, float (&dst)[16]) {
-  if (n_valid == 16 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-    const float4* s4 = reinterpret_cast<const float4*>(src);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 t = __ldg(s4 + i);
-      dst[4 * i] = t.x; dst[4 * i + 1] = t.y; dst[4 * i + 2] = t.z; dst[4 * i + 3] = t.w;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) dst[i] = i < n_valid ? __ldg(src + i) : 0.f;
-  }
-}
-
 constexpr int EPI_WARPS = 8;
 constexpr int GEMM_THREADS = 64 + EPI_WARPS * 32;
 
