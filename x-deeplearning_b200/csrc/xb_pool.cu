@@ -35,6 +35,7 @@ struct PoolGroupDev {
   int32_t lpr;                 // lanes per row
   int32_t tl;                  // lanes per segment (team)
   int32_t vhalf;               // per-id weights are fp16
+  int32_t segs;                // specialised kernel: rounds of segments per warp
   PoolItemDev items[XB_MAX_POOL_ITEMS];
 };
 
@@ -300,6 +301,211 @@ __global__ void __launch_bounds__(256) pool_kernel(const __grid_constant__ PoolP
   }
 }
 
+// Widest aligned store of `nvalid` (<= N) consecutive outputs starting at element index `o`.
+template <int N>
+__device__ __forceinline__ void store_vec(void* out, int64_t o, bool out16, const float (&r)[N], int nvalid) {
+  if (!out16) {
+    float* dst = reinterpret_cast<float*>(out) + o;
+    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+      for (int e = 0; e < N; e += 4) {
+        if (e + 4 <= nvalid) *reinterpret_cast<float4*>(dst + e) = make_float4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+        else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (e + u < nvalid) dst[e + u] = r[e + u];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < N; ++e)
+        if (e < nvalid) dst[e] = r[e];
+    }
+  } else {
+    __half* dst = reinterpret_cast<__half*>(out) + o;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(dst);
+    if (N == 8 && nvalid == 8 && (a & 15) == 0) {
+      uint4 v;
+      __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(r[2 * e], r[2 * e + 1]);
+      *reinterpret_cast<uint4*>(dst) = v;
+    } else if ((a & 3) == 0) {
+#pragma unroll
+      for (int e = 0; e < N; e += 2) {
+        if (e + 1 < nvalid) *reinterpret_cast<__half2*>(dst + e) = __floats2half2_rn(r[e], r[e + 1]);
+        else if (e < nvalid) dst[e] = __float2half_rn(r[e]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < N; ++e)
+        if (e < nvalid) dst[e] = __float2half_rn(r[e]);
+    }
+  }
+}
+
+// Single-item groups (one output per feature group: the usual case), specialised per table dtype
+// and lanes per row. Same team / sub-team geometry and the same summation order as pool_kernel
+// (sub-team s adds ids s, s+NS, s+2NS... in order, then the xor butterfly), so both kernels give
+// identical bits. What differs is the instruction count per id: a team loads TL ids, values and
+// row numbers with one coalesced load each (the index lookup runs once per id, not once per
+// lane), hands them to the sub-teams by shuffle and keeps up to four 16-byte row loads per lane
+// in flight.
+template <int TD, int LPR>
+__global__ void __launch_bounds__(256) pool_fast_kernel(const __grid_constant__ PoolParams p) {
+  constexpr int EPC = TD == XB_F32 ? 4 : 8;          // elements per 16-byte chunk
+  constexpr int RB = LPR < 4 ? LPR : 4;              // row loads in flight per lane
+  constexpr unsigned FULL = 0xffffffffu;
+  const int64_t warp_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp_id >= p.total_warps) return;              // whole warp leaves together
+  const int lane = threadIdx.x & 31;
+  int gi = 0;
+  while (gi + 1 < p.n_groups && p.g[gi + 1].warp_begin <= warp_id) ++gi;
+  const PoolGroupDev& g = p.g[gi];
+  const PoolItemDev& it = g.items[0];
+
+  const int tl = g.tl, ns = tl / LPR, spw = 32 / tl, segs = g.segs;
+  const int tlane = lane & (tl - 1), team0 = lane - tlane;
+  const int sub = tlane / LPR, chunk = tlane & (LPR - 1);
+  const int dim = g.dim, col0 = chunk * EPC;
+  const bool cvalid = col0 < dim;
+  const int nvalid = min(EPC, dim - col0);
+  const bool id64 = g.id_dtype == XB_I64, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
+  const int vmode = g.values ? (g.vhalf ? 2 : 1) : 0;
+  const bool assign = it.udf == XB_UDF_ASSIGN, avg = it.udf == XB_UDF_AVG;
+  const int tn = it.trunc_num, as = it.assign_stride ? it.assign_stride : dim;
+  const bool reverse = it.trunc_dir != XB_TRUNC_ORDER;
+  const char* wrow = g.weights + chunk * 16;
+  const int64_t pitch = g.pitch, batch = g.batch;
+  // this warp walks `segs` consecutive rounds of `spw` segments; the offsets of round i+2 and the ids of
+  // round i+1 are fetched while the rows of round i are in flight
+  const int64_t seg_first = (warp_id - g.warp_begin) * segs * spw + lane / tl;
+
+  auto load_span = [&](int i, int& st, int& nm) {
+    const int64_t sg = seg_first + (int64_t)i * spw;
+    st = 0; nm = 0;
+    if (i < segs && sg < batch) {
+      st = __ldg(g.offsets + sg);
+      nm = __ldg(g.offsets + sg + 1) - st;
+    }
+  };
+  // one id, value and table row number per lane: position base + tlane of the segment
+  auto load_ids = [&](int st, int nm, int base, int& row, float& v) {
+    const int idx = base + tlane;
+    row = -1; v = 1.f;
+    if (idx < nm) {
+      const int64_t at = (int64_t)st + idx;
+      const int64_t key = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + at)
+                               : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + at);
+      if (has_table) row = (int)lookup_row(g, key);
+      if (vmode == 1) v = __ldg(reinterpret_cast<const float*>(g.values) + at);
+      else if (vmode == 2) v = __half2float(reinterpret_cast<const __half*>(g.values)[at]);
+    }
+  };
+
+  int st0, nm0, st1, nm1, st2, nm2, row, row_next;
+  float v, v_next;
+  load_span(0, st0, nm0);
+  load_span(1, st1, nm1);
+  load_ids(st0, nm0, 0, row, v);
+  for (int i = 0; i < segs; ++i) {
+    const int64_t seg = seg_first + (int64_t)i * spw;
+    if (seg - lane / tl >= batch) break;               // uniform: this round starts past the last segment
+    load_span(i + 2, st2, nm2);
+    load_ids(st1, nm1, 0, row_next, v_next);
+    const bool active = seg < batch;
+    const int start = st0, num = nm0;
+    const int64_t obase = seg * it.stride + col0;
+    float acc[EPC];
+#pragma unroll
+    for (int e = 0; e < EPC; ++e) acc[e] = 0.f;
+
+    for (int base = 0; __any_sync(FULL, base < num); base += tl) {
+      if (base > 0) load_ids(start, num, base, row, v);
+#pragma unroll
+      for (int r0 = 0; r0 < LPR; r0 += RB) {
+        if (r0 > 0 && !__any_sync(FULL, base + r0 * ns < num)) break;      // no team has ids left in this batch
+        int rr[RB];
+        float vv[RB];
+        uint4 raw[RB];
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+          const int src = team0 + (r0 + u) * ns + sub;
+          rr[u] = __shfl_sync(FULL, row, src);
+          vv[u] = __shfl_sync(FULL, v, src);
+        }
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+          raw[u] = make_uint4(0, 0, 0, 0);
+          if (rr[u] >= 0 && cvalid) raw[u] = __ldg(reinterpret_cast<const uint4*>(wrow + (int64_t)rr[u] * pitch));
+        }
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+          float w[8];
+          unpack_chunk(raw[u], TD, w);
+          if (!assign) {
+            if (rr[u] >= 0) {                       // a missing key contributes nothing
+#pragma unroll
+              for (int e = 0; e < EPC; ++e) acc[e] = acc[e] + vv[u] * w[e];
+            }
+          } else {
+            // kAssign: the id at position jj of the segment owns one output slot; a missing key leaves zeros
+            const int jj = base + (r0 + u) * ns + sub;
+            if (jj < num && cvalid) {
+              int slot = -1;
+              if (!reverse) { if (jj < tn) slot = jj; }
+              else if (num - jj <= tn) slot = tn - (num - jj);
+              if (slot >= 0) {
+                float o[EPC];
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) o[e] = rr[u] >= 0 ? vv[u] * w[e] : 0.f;
+                store_vec<EPC>(it.out, obase + (int64_t)slot * as, out16, o, nvalid);
+              }
+            }
+          }
+        }
+      }
+    }
+
+    if (assign) {
+      // slots no id maps to are cleared (the reference memsets the whole span first)
+      if (active) {
+        const int used = min(num, tn), nz = tn - used, z0 = reverse ? 0 : used;
+        for (int k = tlane; k < nz * dim; k += tl) {
+          const int t = k / dim, e = k - t * dim;
+          store_out(it.out, seg * it.stride + (int64_t)(z0 + t) * as + e, g.out_dtype, 0.f);
+        }
+      }
+    } else {
+      // fixed-order combine of the sub-team partial sums
+      for (int off = LPR; off < tl; off <<= 1) {
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) acc[e] += __shfl_xor_sync(FULL, acc[e], off);
+      }
+      if (active && sub == 0 && cvalid) {
+        if (avg && num != 0) {
+          const float scale = (float)(1.0 / (double)num);
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) acc[e] = acc[e] * scale;
+        }
+        store_vec<EPC>(it.out, obase, out16, acc, nvalid);
+      }
+    }
+    st0 = st1; nm0 = nm1; st1 = st2; nm1 = nm2; row = row_next; v = v_next;
+  }
+}
+
+template <int TD>
+static int launch_pool_fast(const PoolParams& p, int lpr, unsigned blocks, cudaStream_t stream) {
+  switch (lpr) {
+    case 1: case 2: pool_fast_kernel<TD, 2><<<blocks, 256, 0, stream>>>(p); break;
+    case 4: pool_fast_kernel<TD, 4><<<blocks, 256, 0, stream>>>(p); break;
+    case 8: pool_fast_kernel<TD, 8><<<blocks, 256, 0, stream>>>(p); break;
+    default: pool_fast_kernel<TD, 16><<<blocks, 256, 0, stream>>>(p); break;
+  }
+  return check_launch("pool_fast_kernel");
+}
+
 static int next_pow2(int v) { int p = 1; while (p < v) p <<= 1; return p; }
 
 }  // namespace xb
@@ -404,12 +610,17 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
   XB_REQUIRE(xb_embedding_pool_scratch_bytes(groups, n_groups) <= scratch_bytes, XB_ERR_SCRATCH,
              "xb_embedding_pool: scratch %zu bytes, need %zu", scratch_bytes,
              xb_embedding_pool_scratch_bytes(groups, n_groups));
+  // p: groups for the general kernel; fp[b]: single-item groups for the specialised kernel, one launch
+  // per (table dtype, lanes per row) bucket
+  constexpr int kBuckets = 8;
   static thread_local PoolParams p;
+  static thread_local PoolParams fp[kBuckets];
   static thread_local ScanParams sp;
   p.n_groups = 0;
+  p.total_warps = 0;
+  for (int b = 0; b < kBuckets; ++b) { fp[b].n_groups = 0; fp[b].total_warps = 0; }
   sp.n = 0;
   size_t soff = 0;
-  int64_t warps = 0;
   for (int i = 0; i < n_groups; ++i) {
     const xb_pool_group& h = groups[i];
     XB_REQUIRE(h.batch >= 0 && h.n_ids >= 0, XB_ERR_ARG, "xb_embedding_pool: group %d negative size", i);
@@ -424,7 +635,7 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
                "xb_embedding_pool: group %d output dtype %d", i, h.out_dtype);
     XB_REQUIRE(h.batch < ((int64_t)1 << 31) && h.n_ids < ((int64_t)1 << 31), XB_ERR_LIMIT,
                "xb_embedding_pool: group %d beyond int32 offsets", i);
-    PoolGroupDev& d = p.g[p.n_groups];
+    PoolGroupDev d;
     memset(&d, 0, sizeof(d));
     d.has_table = h.table != nullptr;
     XB_REQUIRE(h.dim >= 1 && h.dim <= 256, XB_ERR_LIMIT, "xb_embedding_pool: group %d dim %d (1..256)", i, h.dim);
@@ -449,6 +660,8 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     const int epc = d.tdtype == XB_F32 ? 4 : 8;
     d.lpr = next_pow2((dim + epc - 1) / epc);
     if (d.lpr > 32) return fail(XB_ERR_LIMIT, "xb_embedding_pool: row too wide");
+    const bool fast = h.n_items == 1 && d.lpr <= 16;
+    if (fast && d.lpr < 2) d.lpr = 2;
     const double avg = (double)h.n_ids / (double)h.batch;
     int ns = 1;
     while (ns < 32 / d.lpr && ns < avg) ns <<= 1;
@@ -476,18 +689,33 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
       sp.counts[sp.n] = h.segments; sp.offsets[sp.n] = off; sp.batch[sp.n] = h.batch; ++sp.n;
       d.offsets = off;
     }
-    d.warp_begin = warps;
+    int lg = 0;
+    while ((2 << lg) < d.lpr) ++lg;                 // lanes per row 2, 4, 8, 16 -> 0..3
+    PoolParams& dst = fast ? fp[(d.tdtype == XB_F32 ? 0 : 4) + lg] : p;
+    d.warp_begin = dst.total_warps;
     const int spw = 32 / d.tl;
-    warps += (h.batch + spw - 1) / spw;
-    ++p.n_groups;
+    const int64_t rounds = (h.batch + spw - 1) / spw;
+    // the specialised kernel gives a warp several rounds, as long as every SM still gets dozens of warps
+    d.segs = 1;
+    if (fast) d.segs = (int)std::max<int64_t>(1, std::min<int64_t>(8, rounds / ((int64_t)sm_count() * 48)));
+    dst.total_warps += (rounds + d.segs - 1) / d.segs;
+    dst.g[dst.n_groups++] = d;
   }
-  if (p.n_groups == 0) return 0;
-  p.total_warps = warps;
   if (sp.n) {
     scan_counts_kernel<<<sp.n, SCAN_THREADS, 0, stream>>>(sp);
     if (int rc = check_launch("scan_counts_kernel")) return rc;
   }
-  const int64_t blocks = (warps + 7) / 8;
+  for (int b = 0; b < kBuckets; ++b) {
+    if (fp[b].n_groups == 0) continue;
+    const int64_t blocks = (fp[b].total_warps + 7) / 8;
+    XB_REQUIRE(blocks < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_embedding_pool: too many segments");
+    const int lpr = 2 << (b & 3);
+    const int rc = b < 4 ? launch_pool_fast<XB_F32>(fp[b], lpr, (unsigned)blocks, stream)
+                         : launch_pool_fast<XB_F16>(fp[b], lpr, (unsigned)blocks, stream);
+    if (rc) return rc;
+  }
+  if (p.n_groups == 0) return 0;
+  const int64_t blocks = (p.total_warps + 7) / 8;
   XB_REQUIRE(blocks < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_embedding_pool: too many segments");
   pool_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
   return check_launch("pool_kernel");
