@@ -352,7 +352,7 @@ __device__ __forceinline__ void store_vec(void* out, int64_t o, bool out16, cons
 // lane), hands them to the sub-teams by shuffle and keeps up to four 16-byte row loads per lane
 // in flight.
 template <int TD, int LPR>
-__global__ void __launch_bounds__(256) pool_fast_kernel(const __grid_constant__ PoolParams p) {
+__global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant__ PoolParams p) {
   constexpr int EPC = TD == XB_F32 ? 4 : 8;          // elements per 16-byte chunk
   constexpr int RB = LPR < 4 ? LPR : 4;              // row loads in flight per lane
   constexpr unsigned FULL = 0xffffffffu;
@@ -376,7 +376,8 @@ __global__ void __launch_bounds__(256) pool_fast_kernel(const __grid_constant__ 
   const int tn = it.trunc_num, as = it.assign_stride ? it.assign_stride : dim;
   const bool reverse = it.trunc_dir != XB_TRUNC_ORDER;
   const char* wrow = g.weights + chunk * 16;
-  const int64_t pitch = g.pitch, batch = g.batch;
+  const int pitch = (int)g.pitch;                    // a row is at most 256 bytes here: 32 x 32 -> 64-bit multiply
+  const int64_t batch = g.batch;
   // this warp walks `segs` consecutive rounds of `spw` segments; the offsets of round i+2 and the ids of
   // round i+1 are fetched while the rows of round i are in flight
   const int64_t seg_first = (warp_id - g.warp_begin) * segs * spw + lane / tl;
@@ -664,7 +665,14 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     if (fast && d.lpr < 2) d.lpr = 2;
     const double avg = (double)h.n_ids / (double)h.batch;
     int ns = 1;
-    while (ns < 32 / d.lpr && ns < avg) ns <<= 1;
+    if (fast) {
+      // one sub-team per segment gives the fewest instructions per id (no cross-lane combine, whole rows
+      // per lane group); teams only grow while the launch would otherwise leave SMs without warps
+      const int64_t want_warps = (int64_t)sm_count() * 16;
+      while (ns < 32 / d.lpr && ns < avg && h.batch * (int64_t)(d.lpr * ns) / 32 < want_warps) ns <<= 1;
+    } else {
+      while (ns < 32 / d.lpr && ns < avg) ns <<= 1;
+    }
     d.tl = d.lpr * ns;
     XB_REQUIRE(h.values_dtype == 0 || h.values_dtype == XB_F32 || h.values_dtype == XB_F16, XB_ERR_UNSUPPORTED,
                "xb_embedding_pool: group %d values dtype %d", i, h.values_dtype);
