@@ -87,6 +87,81 @@ def test_pool_missing_table_zero_fills():
     _run_case(rng, 100, 18, 65, 5, torch.float16, torch.float32, hashed=False, use_offsets=False, missing_table=True)
 
 
+def _run_single_item(rng, rows, dim, batch, max_len, tdtype, out_dtype, udf, trunc_dir=0, hashed=False, id32=False,
+                     with_values=True, use_offsets=True, min_len=0):
+    """One item per feature group: the case the specialised kernels (static teams for small batches and
+    kAssign, a per-warp segment queue for large sum / average batches) take."""
+    pkg.load()
+    from x_deeplearning_b200 import ops
+    w = rng.normal(0, 0.5, (rows, dim)).astype(np.float32)
+    if tdtype == torch.float16:
+        w = w.astype(np.float16).astype(np.float32)
+    tkeys = rng.choice(1 << 30 if id32 else 1 << 40, size=rows, replace=False).astype(np.int64) if hashed else None
+    counts = rng.integers(min_len, max_len + 1, batch).astype(np.int32)
+    n = int(counts.sum())
+    base = tkeys if hashed else np.arange(rows, dtype=np.int64)
+    ids = base[rng.integers(0, rows, n)]
+    bad = rng.random(n) < 0.05
+    ids[bad] = (1 << 30) + 12345 if id32 else rng.integers(1 << 41, 1 << 42, int(bad.sum()))
+    values = rng.normal(1, 0.5, n).astype(np.float32) if with_values else np.ones(n, np.float32)
+    tn = 5
+    span = dim * (tn if udf == 2 else 1)
+    width = span + 3
+
+    def items(out):
+        return [dict(udf=udf, trunc_dir=trunc_dir, trunc_num=tn, out=out, col=1)]
+    want = np.full((batch, width), 3.0, np.float32)
+    scale = np.full((batch, width), 3.0, np.float32)
+    orc.embedding_pool(w, ids, values, counts, items(want), table_keys=tkeys)
+    orc.embedding_pool(np.abs(w), ids, np.abs(values), counts, items(scale), table_keys=tkeys)
+    table = ops.Table(torch.from_numpy(w), tdtype, keys=None if tkeys is None else torch.from_numpy(tkeys))
+    got = torch.full((batch, width), 3.0, dtype=out_dtype, device="cuda")
+    d_ids = torch.from_numpy(ids.astype(np.int32) if id32 else ids).cuda()
+    d_val = torch.from_numpy(values).cuda() if with_values else None
+    if use_offsets:
+        off = np.zeros(batch + 1, np.int32)
+        np.cumsum(counts, out=off[1:])
+        seg = torch.from_numpy(off).cuda()
+    else:
+        seg = torch.from_numpy(counts).cuda()
+    g = ops.make_group(table, d_ids, d_val, seg, items(got), out_dtype, segments_are_offsets=use_offsets, dim=dim)
+    ops.embedding_pool([g])
+    torch.cuda.synchronize()
+    got = got.float().cpu().numpy()
+    tol = 1e-5 if out_dtype == torch.float32 else 1.5e-3
+    err = np.abs(got - want)
+    assert (err <= tol * np.maximum(scale, 1e-3) + 1e-7).all(), float((err / np.maximum(scale, 1e-3)).max())
+    assert (got[:, 0] == 3.0).all() and (got[:, -1] == 3.0).all()
+
+
+@pytest.mark.parametrize("udf,trunc_dir", [(0, 0), (1, 0), (2, 0), (2, 1)])
+@pytest.mark.parametrize("dim,tdtype,out_dtype", [(16, torch.float32, torch.float32), (18, torch.float16, torch.float16),
+                                                  (36, torch.float16, torch.float32), (5, torch.float32, torch.float16),
+                                                  (100, torch.float16, torch.float32)])
+def test_pool_single_item_small_batch(udf, trunc_dir, dim, tdtype, out_dtype):
+    rng = np.random.default_rng(1000 + 10 * dim + udf + trunc_dir)
+    _run_single_item(rng, 3000, dim, 333, 11, tdtype, out_dtype, udf, trunc_dir, hashed=dim % 2 == 0)
+
+
+@pytest.mark.parametrize("udf", [0, 1])
+@pytest.mark.parametrize("dim,tdtype,out_dtype,max_len", [(16, torch.float32, torch.float32, 50),
+                                                          (18, torch.float16, torch.float16, 7),
+                                                          (36, torch.float16, torch.float32, 20),
+                                                          (3, torch.float32, torch.float32, 9),
+                                                          (72, torch.float32, torch.float32, 12)])
+def test_pool_single_item_large_batch_segment_queue(udf, dim, tdtype, out_dtype, max_len):
+    """Batches large enough for the segment-queue kernel, empty segments and missing keys included."""
+    rng = np.random.default_rng(2000 + 10 * dim + udf)
+    _run_single_item(rng, 5000, dim, 60001, max_len, tdtype, out_dtype, udf, hashed=dim == 36, use_offsets=dim != 18,
+                     with_values=dim != 3, id32=dim == 3)
+
+
+def test_pool_single_item_long_segments_few_samples():
+    rng = np.random.default_rng(3000)
+    _run_single_item(rng, 4000, 16, 9, 700, torch.float32, torch.float32, 0, min_len=300)
+    _run_single_item(rng, 4000, 18, 5, 300, torch.float16, torch.float32, 2, trunc_dir=1, min_len=1)
+
+
 def test_pool_rejects_bad_arguments():
     m = pkg.load()
     from x_deeplearning_b200 import ops, capi

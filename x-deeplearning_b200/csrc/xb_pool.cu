@@ -1,12 +1,15 @@
 // Embedding pooling over variable-length id lists, and the HBM table image.
 //
-// Kernel shape: a warp is split into teams of TL lanes, one team per
-// (sample, feature-group) segment; a team is split into sub-teams of LPR lanes
-// that each fetch one table row with 128-bit loads (lane c reads bytes
-// [16c,16c+16) of the row). Sub-team s walks ids s, s+NS, s+2NS... of the
-// segment in order and accumulates in fp32; the NS partial sums are combined
-// with a fixed xor-butterfly, so a result does not depend on scheduling.
-// HBM-bound: per id the kernel moves 8 B id + 4 B value + one row.
+// Three kernels share one geometry: a table row is fetched by LPR lanes with 128-bit loads (lane c
+// reads bytes [16c,16c+16) of the row) and accumulated in fp32.
+//   pool_queue_kernel  sum / average, one output per feature group, large batches: one sub-team of LPR
+//                      lanes per segment, 32 segments per warp handed out as sub-teams finish.
+//   pool_fast_kernel   one output per feature group (kAssign included), any batch: teams of TL lanes
+//                      per segment, TL/LPR sub-teams that walk the ids s, s+NS, s+2NS..., combined
+//                      with a fixed xor butterfly.
+//   pool_kernel        several outputs per feature group (the general case), same team layout.
+// In every kernel the order in which a segment's rows are added is fixed by the geometry alone, so a
+// result does not depend on scheduling. Per id the kernels move 8 B id + 4 B value + one row.
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -496,6 +499,138 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
   }
 }
 
+// Sum / average pooling with one sub-team (LPR lanes) per segment and a per-warp segment queue: a warp
+// owns 32 consecutive segments, its 32/LPR sub-teams each take the next unclaimed one as soon as they
+// finish theirs, so lanes stay busy whatever the spread of segment lengths. A sub-team adds the ids of its
+// segment strictly in order (no cross-lane combine). The ids of the batch after the current one are
+// requested before the rows of the current one, so both latencies overlap.
+template <int TD, int LPR>
+__global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constant__ PoolParams p) {
+  constexpr int EPC = TD == XB_F32 ? 4 : 8;
+  constexpr unsigned FULL = 0xffffffffu;
+  constexpr int NT = 32 / LPR;                       // sub-teams per warp
+  const int64_t warp_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp_id >= p.total_warps) return;
+  const int lane = threadIdx.x & 31;
+  int gi = 0;
+  while (gi + 1 < p.n_groups && p.g[gi + 1].warp_begin <= warp_id) ++gi;
+  const PoolGroupDev& g = p.g[gi];
+  const PoolItemDev& it = g.items[0];
+
+  const int tlane = lane & (LPR - 1), team0 = lane - tlane, team = lane / LPR;
+  const int dim = g.dim, col0 = tlane * EPC;
+  const bool cvalid = col0 < dim;
+  const int nvalid = min(EPC, dim - col0);
+  const bool id64 = g.id_dtype == XB_I64, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
+  const int vmode = g.values ? (g.vhalf ? 2 : 1) : 0;
+  const bool avg = it.udf == XB_UDF_AVG;
+  const char* wrow = g.weights + tlane * 16;
+  const int pitch = (int)g.pitch;
+  const int64_t s0 = (warp_id - g.warp_begin) * 32;
+  const int nseg = (int)min((int64_t)32, g.batch - s0);
+
+  // lane l keeps the span of segment s0 + l
+  int my_start = 0, my_num = 0;
+  if (lane < nseg) {
+    my_start = __ldg(g.offsets + s0 + lane);
+    my_num = __ldg(g.offsets + s0 + lane + 1) - my_start;
+  }
+  auto load_ids = [&](int st, int nm, int pos, int& row, float& v) {
+    const int idx = pos + tlane;
+    row = -1; v = 1.f;
+    if (idx < nm) {
+      const int64_t at = (int64_t)st + idx;
+      const int64_t key = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + at)
+                               : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + at);
+      if (has_table) row = (int)lookup_row(g, key);
+      if (vmode == 1) v = __ldg(reinterpret_cast<const float*>(g.values) + at);
+      else if (vmode == 2) v = __half2float(reinterpret_cast<const __half*>(g.values)[at]);
+    }
+  };
+
+  int m = team, next = NT;                           // my segment (relative), first unclaimed one
+  int start = __shfl_sync(FULL, my_start, m & 31), num = __shfl_sync(FULL, my_num, m & 31);
+  if (m >= nseg) num = 0;
+  int pos = 0, row;
+  float v;
+  load_ids(start, num, 0, row, v);
+  float acc[EPC];
+#pragma unroll
+  for (int e = 0; e < EPC; ++e) acc[e] = 0.f;
+
+  while (__any_sync(FULL, m < nseg)) {
+    // where this sub-team goes after the current batch: on in its segment, or to the next unclaimed one
+    const bool live = m < nseg;
+    const bool finishing = live && pos + LPR >= num;
+    const unsigned fmask = __ballot_sync(FULL, finishing && tlane == 0);
+    int m2 = m, pos2 = pos + LPR, start2 = start, num2 = num;
+    if (fmask) {
+      const int cand = next + __popc(fmask & ((1u << team0) - 1u));
+      const int cs = __shfl_sync(FULL, my_start, cand & 31), cn = __shfl_sync(FULL, my_num, cand & 31);
+      if (finishing) {
+        m2 = cand; pos2 = 0; start2 = cs;
+        num2 = cand < nseg ? cn : 0;
+      }
+      next += __popc(fmask);
+    }
+    int row2;
+    float v2;
+    load_ids(start2, m2 < nseg ? num2 : 0, pos2, row2, v2);
+
+    // rows of the current batch: id r of the batch sits in lane team0 + r
+    int rr[LPR];
+    float vv[LPR];
+#pragma unroll
+    for (int r = 0; r < LPR; ++r) {
+      rr[r] = __shfl_sync(FULL, row, team0 + r);
+      vv[r] = __shfl_sync(FULL, v, team0 + r);
+    }
+#pragma unroll
+    for (int r0 = 0; r0 < LPR; r0 += 4) {
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        raw[u] = make_uint4(0, 0, 0, 0);
+        if (r0 + u < LPR && rr[r0 + u] >= 0 && cvalid)
+          raw[u] = __ldg(reinterpret_cast<const uint4*>(wrow + (int64_t)rr[r0 + u] * pitch));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (r0 + u < LPR && rr[r0 + u] >= 0) {             // a missing key contributes nothing
+          float w[8];
+          unpack_chunk(raw[u], TD, w);
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) acc[e] = acc[e] + vv[r0 + u] * w[e];
+        }
+      }
+    }
+    if (finishing) {
+      if (cvalid) {
+        if (avg && num != 0) {
+          const float scale = (float)(1.0 / (double)num);
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) acc[e] = acc[e] * scale;
+        }
+        store_vec<EPC>(it.out, (s0 + m) * it.stride + col0, out16, acc, nvalid);
+      }
+#pragma unroll
+      for (int e = 0; e < EPC; ++e) acc[e] = 0.f;
+    }
+    m = m2; pos = pos2; start = start2; num = num2; row = row2; v = v2;
+  }
+}
+
+template <int TD>
+static int launch_pool_queue(const PoolParams& p, int lpr, unsigned blocks, cudaStream_t stream) {
+  switch (lpr) {
+    case 1: case 2: pool_queue_kernel<TD, 2><<<blocks, 256, 0, stream>>>(p); break;
+    case 4: pool_queue_kernel<TD, 4><<<blocks, 256, 0, stream>>>(p); break;
+    case 8: pool_queue_kernel<TD, 8><<<blocks, 256, 0, stream>>>(p); break;
+    default: pool_queue_kernel<TD, 16><<<blocks, 256, 0, stream>>>(p); break;
+  }
+  return check_launch("pool_queue_kernel");
+}
+
 template <int TD>
 static int launch_pool_fast(const PoolParams& p, int lpr, unsigned blocks, cudaStream_t stream) {
   switch (lpr) {
@@ -616,10 +751,11 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
   constexpr int kBuckets = 8;
   static thread_local PoolParams p;
   static thread_local PoolParams fp[kBuckets];
+  static thread_local PoolParams qp[kBuckets];       // segment-queue kernel (sum / average, large batches)
   static thread_local ScanParams sp;
   p.n_groups = 0;
   p.total_warps = 0;
-  for (int b = 0; b < kBuckets; ++b) { fp[b].n_groups = 0; fp[b].total_warps = 0; }
+  for (int b = 0; b < kBuckets; ++b) { fp[b].n_groups = 0; fp[b].total_warps = 0; qp[b].n_groups = 0; qp[b].total_warps = 0; }
   sp.n = 0;
   size_t soff = 0;
   for (int i = 0; i < n_groups; ++i) {
@@ -699,14 +835,18 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     }
     int lg = 0;
     while ((2 << lg) < d.lpr) ++lg;                 // lanes per row 2, 4, 8, 16 -> 0..3
-    PoolParams& dst = fast ? fp[(d.tdtype == XB_F32 ? 0 : 4) + lg] : p;
+    const int bucket = (d.tdtype == XB_F32 ? 0 : 4) + lg;
+    // sum / average groups with plenty of segments go to the segment-queue kernel: 32 segments per warp
+    const bool queue = fast && d.tl == d.lpr && h.items[0].udf != XB_UDF_ASSIGN && avg >= 3.0 &&
+                       (h.batch + 31) / 32 >= (int64_t)sm_count() * 8;
+    PoolParams& dst = queue ? qp[bucket] : fast ? fp[bucket] : p;
     d.warp_begin = dst.total_warps;
     const int spw = 32 / d.tl;
     const int64_t rounds = (h.batch + spw - 1) / spw;
     // the specialised kernel gives a warp several rounds, as long as every SM still gets dozens of warps
     d.segs = 1;
     if (fast) d.segs = (int)std::max<int64_t>(1, std::min<int64_t>(8, rounds / ((int64_t)sm_count() * 48)));
-    dst.total_warps += (rounds + d.segs - 1) / d.segs;
+    dst.total_warps += queue ? (h.batch + 31) / 32 : (rounds + d.segs - 1) / d.segs;
     dst.g[dst.n_groups++] = d;
   }
   if (sp.n) {
@@ -720,6 +860,15 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     const int lpr = 2 << (b & 3);
     const int rc = b < 4 ? launch_pool_fast<XB_F32>(fp[b], lpr, (unsigned)blocks, stream)
                          : launch_pool_fast<XB_F16>(fp[b], lpr, (unsigned)blocks, stream);
+    if (rc) return rc;
+  }
+  for (int b = 0; b < kBuckets; ++b) {
+    if (qp[b].n_groups == 0) continue;
+    const int64_t blocks = (qp[b].total_warps + 7) / 8;
+    XB_REQUIRE(blocks < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_embedding_pool: too many segments");
+    const int lpr = 2 << (b & 3);
+    const int rc = b < 4 ? launch_pool_queue<XB_F32>(qp[b], lpr, (unsigned)blocks, stream)
+                         : launch_pool_queue<XB_F16>(qp[b], lpr, (unsigned)blocks, stream);
     if (rc) return rc;
   }
   if (p.n_groups == 0) return 0;
