@@ -223,6 +223,11 @@ typedef struct xb_gemm_args {
   int32_t dice_nosqrt;
   int64_t stride_ep;       /* per-batch stride of ep_a/b/c, elements (0 = shared) */
   int32_t engine;          /* XB_GEMM_AUTO picks tcgen05 when the layout allows */
+  int64_t bias_row_group;  /* XB_BIAS_FULL only: rows of Y that share one bias row (output row m reads bias
+                              row m / bias_row_group); 0 or 1 = one bias row per output row. This is the
+                              broadcast add of PrunedGemmOp (blaze/blaze/operator/op/pruned_gemm_op.h:106-152:
+                              the one-row partial product added to every row), applied per group of rows so
+                              that several requests share a launch. */
 } xb_gemm_args;
 
 int xb_gemm(const xb_gemm_args* args, xb_stream_t stream);
@@ -289,6 +294,47 @@ int xb_din_tower_input(const void* user, int64_t ldu, const void* q, int64_t ldq
                        int64_t ldk, const void* att, int64_t ldatt, void* X, int64_t ldx,
                        int32_t requests, int32_t n_cand, int32_t T, int32_t d, int32_t du,
                        xb_stream_t stream);
+/* The same features split the way PrunedGemmOp wants its two operands
+ * (blaze/blaze/operator/op/pruned_gemm_op.h:1-10: [A|B] x [C;D] = A x C + B x D): the columns that are
+ * equal for every candidate of a request go once per request into
+ *   Xu[r]           = [user[r] (du) | his_sum[r] (d) | 0...]            [requests, ldxu]
+ * and the per-candidate columns into
+ *   Xc[r*n_cand+n]  = [q | q*his_sum[r] | att | q-his_sum[r] | 0...]    [requests*n_cand, ldxc]. */
+int xb_din_tower_input_split(const void* user, int64_t ldu, const void* q, int64_t ldq, const void* k,
+                             int64_t ldk, const void* att, int64_t ldatt, void* Xu, int64_t ldxu, void* Xc,
+                             int64_t ldxc, int32_t requests, int32_t n_cand, int32_t T, int32_t d, int32_t du,
+                             xb_stream_t stream);
+
+/* Fused DIN tower: the assembly above, the tower MLP du+5d -> n1 -> n2 -> n3 with Dice after the first
+ * two layers, and the final softmax, in one tcgen05 kernel (plus a small per-request kernel). Replaces
+ * rows 17-29 of the shipped DIN graph: the Concat / Fuse rows above, three Gemm rows with bias
+ * (blaze/blaze/operator/op/gemm_op.h:33-107), two Dice rows (dice_op.cu:11-21) and Softmax
+ * (softmax_op.cc:21-78). The first layer is computed as PrunedGemmOp does
+ * (blaze/blaze/operator/op/pruned_gemm_op.h:1-163): the [user | his_sum] columns once per request.
+ * Weights are the model's fp16 constants in Blaze's [K, N] layout; biases and Dice parameters fp32.
+ * prob [requests*n_cand, n3] fp32: softmax over n3 (softmax != 0) or the fp16-rounded logits. */
+typedef struct xb_din_tower_args {
+  const void* user; int64_t ldu;        /* [requests, du] fp16 */
+  const void* q; int64_t ldq;           /* [requests*n_cand, d] fp16 */
+  const void* k; int64_t ldk;           /* [requests*T, d] fp16 */
+  const void* att; int64_t ldatt;       /* [requests*n_cand, d] fp16 */
+  float* prob;
+  int32_t requests, n_cand, T, d, du, n1, n2, n3;
+  const void* W1; const float* b1; const float* gamma1; const float* mean1; const float* var1;   /* [du+5d, n1] */
+  const void* W2; const float* b2; const float* gamma2; const float* mean2; const float* var2;   /* [n1, n2] */
+  const void* W3; const float* b3;                                                              /* [n2, n3] */
+  int32_t softmax;
+  const void* packed;                   /* image written by xb_din_tower_pack */
+} xb_din_tower_args;
+
+/* 0 for shapes the kernel does not take (d <= 64, n1 <= 256, n2 <= 128, n3 <= 8). */
+size_t xb_din_tower_packed_bytes(int32_t d, int32_t n1, int32_t n2, int32_t n3);
+/* Lays the weights out once in the form the kernel keeps in shared memory (needs d, du, n1..n3, W*, b2, b3,
+ * gamma*, mean*, var*). */
+int xb_din_tower_pack(const xb_din_tower_args* args, void* packed, size_t bytes, xb_stream_t stream);
+/* Per-launch scratch: his_sum [requests, d] and the per-request product [requests, n1], fp32. */
+size_t xb_din_tower_workspace_bytes(int32_t requests, int32_t d, int32_t n1);
+int xb_din_tower(const xb_din_tower_args* args, void* workspace, size_t workspace_bytes, xb_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
 /* Recurrent layers of the DIEN-style model. x, y [batch, T, H] in `dtype` (XB_F32 or

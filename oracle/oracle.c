@@ -181,6 +181,26 @@ void orc_gemm_op(int transa, int transb, int64_t M, int64_t N, int64_t K, float 
   orc_gemm(transa, transb, M, N, K, alpha, A, B, beta, Y);
 }
 
+/* PrunedGemm: [X1|X2] x [W1;W2] = X1 x W1 + X2 x W2, blaze/blaze/operator/op/pruned_gemm_op.h:40-160.
+ * Y <- broadcast(bias) (:69-77), then for operands with different row counts the long product
+ * goes into Y with `beta` and the one-row product into a scratch row that is added to every
+ * row of Y (:106-152, DimEqualBroadcastFMA). The reference allows a short operand of exactly
+ * one row; `group` = rows of Y per row of the short product (M for the reference's case)
+ * restates that per request when several requests are stacked. With equal row counts (:82-105)
+ * the intended sum of both products is formed (the reference passes X2 twice there).
+ * x_short [M/group, ks], w_short [ks, N], x_long [M, kl], w_long [kl, N], bias [N] or NULL. */
+void orc_pruned_gemm(int64_t M, int64_t N, int64_t group, int64_t ks, int64_t kl, float alpha, float beta,
+                     const float* x_short, const float* w_short, const float* x_long, const float* w_long,
+                     const float* bias, float* Y) {
+  int64_t m = M / group;
+  float* part = (float*)malloc(sizeof(float) * (size_t)(m * N));
+  orc_gemm_op(0, 0, M, N, kl, alpha, x_long, w_long, beta, bias, 1, Y);
+  orc_gemm(0, 0, m, N, ks, alpha, x_short, w_short, 0.f, part);
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) Y[i * N + j] += part[(i / group) * N + j];
+  free(part);
+}
+
 /* FusedParallelGemm, 2-D input: P GEMMs sharing A; W stacked [P*K,N] (or
  * [P*N,K] with transB); bias [P*N] (bias_rows 1) or [P*M,N] (bias_rows M);
  * Y [P*M,N]. blaze/blaze/operator/fused_op/fused_parallel_gemm_op.h:43-133. */

@@ -123,6 +123,7 @@ HOT_PATH_DIRS = [
     "fused_op/fused_parallel_gemm", "fused_op/fused_parallel_matmul",
     "fused_op/fused_parallel_mul", "fused_op/fused_parallel_mul_reducesum",
     "fused_op/fused_slice_concat",
+    "op/pruned_gemm",
 ]
 # GRU: the reference ships 19 shapes; the small ones are enough to pin the gate math.
 GRU_KEEP = re.compile(r"gru_test_(\d+)_(\d+)_(\d+)_cpu\.conf$")

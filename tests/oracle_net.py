@@ -61,6 +61,9 @@ def run_op(op, env):
             ys = [orc.gemm_op(a[i], x[1], bias, ta, tb, alpha, beta) for i in range(a.shape[0])]
             return [np.stack(ys)]
         return [orc.gemm_op(a, x[1], bias, ta, tb, alpha, beta)]
+    if t == "PrunedGemm":
+        return [orc.pruned_gemm(x[0], x[1], x[2], x[3], x[4] if len(x) > 4 else None,
+                                _arg(op, "alpha", 1.0, "f"), _arg(op, "beta", 1.0, "f"))]
     if t == "FusedParallelGemm":
         return [orc.fused_parallel_gemm(x[0], x[1], x[2] if len(x) > 2 else None, _arg(op, "parallel_num"),
                                         bool(_arg(op, "transA", 0)), bool(_arg(op, "transB", 0)),

@@ -97,6 +97,24 @@ def gemm_op(A, B, bias=None, transa=False, transb=False, alpha=1.0, beta=1.0):
     return Y
 
 
+def pruned_gemm(x1, x2, w1, w2, bias=None, alpha=1.0, beta=1.0):
+    """PrunedGemm with the shorter of x1 / x2 broadcast over row groups of the longer one."""
+    x1, x2, w1, w2 = f32(x1), f32(x2), f32(w1), f32(w2)
+    if x1.shape[0] <= x2.shape[0]:
+        xs, ws, xl, wl = x1, w1, x2, w2
+    else:
+        xs, ws, xl, wl = x2, w2, x1, w1
+    M, N = xl.shape[0], wl.shape[1]
+    assert M % xs.shape[0] == 0
+    Y = np.empty((M, N), np.float32)
+    if bias is not None:
+        bias = f32(bias).ravel()
+    lib().orc_pruned_gemm(C.c_int64(M), C.c_int64(N), C.c_int64(M // xs.shape[0]), C.c_int64(xs.shape[1]),
+                          C.c_int64(xl.shape[1]), C.c_float(alpha), C.c_float(beta), _p(xs, _f), _p(ws, _f),
+                          _p(xl, _f), _p(wl, _f), _p(bias, _f), _p(Y, _f))
+    return Y
+
+
 def gemm_strided_batched(A, sa, B, sb, M, N, K, batch, transa=False, transb=False, alpha=1.0):
     A, B = f32(A).ravel(), f32(B).ravel()
     Cm = np.zeros((batch, M, N), np.float32)

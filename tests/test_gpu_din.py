@@ -30,6 +30,11 @@ def test_din_probabilities_match_oracle(emb_sigma, seq):
     got = prob.cpu().numpy()
     assert np.abs(got - want).max() <= 2e-3, np.abs(got - want).max()
     assert np.abs(got.sum(1) - 1).max() < 1e-5
+    # the first tower layer as one Gemm over the full concat (no pruned product) stays within the same bound
+    for pruned in (False, True):
+        got_ops = net.forward_device(p, pruned=pruned, fused_tower=False).cpu().numpy()
+        assert np.abs(got_ops - want).max() <= 2e-3, (pruned, np.abs(got_ops - want).max())
+    prob = net.forward_device(p)
     # end to end from pinned host buffers gives the same answer
     got2 = net.forward(staged).numpy()
     np.testing.assert_array_equal(got, got2)

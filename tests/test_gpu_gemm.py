@@ -112,6 +112,46 @@ def test_tcgen05_engine_fp32_output_full_bias_and_padded_lda():
     _tc_case(260, 48, 100, "none", np.random.default_rng(3), out_dtype=torch.float32, lda=104, bias_full=True)
 
 
+@pytest.mark.parametrize("engine", ["tcgen05", "simt"])
+@pytest.mark.parametrize("M,group,N,ks,kl,epi", [(600, 200, 200, 184, 144, "dice"), (96, 96, 80, 40, 72, "none"),
+                                                 (1000, 1, 64, 16, 64, "prelu")])
+def test_pruned_product_with_grouped_bias(engine, M, group, N, ks, kl, epi):
+    """X1 x W1 computed once per row group (fp32), added in the epilogue of X2 x W2: the PrunedGemm form."""
+    ops, capi = _ops()
+    rng = np.random.default_rng(M + N + ks)
+    m = M // group
+    xs = rng.normal(0, 1, (m, ks)).astype(np.float16)
+    xl = rng.normal(0, 1, (M, kl)).astype(np.float16)
+    ws = rng.normal(0, 1 / np.sqrt(ks), (ks, N)).astype(np.float16)
+    wl = rng.normal(0, 1 / np.sqrt(kl), (kl, N)).astype(np.float16)
+    b = rng.normal(0, 0.3, N).astype(np.float32)
+    f = lambda a: a.astype(np.float32)
+    want = orc.pruned_gemm(f(xs), f(xl), f(ws), f(wl), b)
+    c = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    kw = {}
+    if epi == "dice":
+        g, mu, var = rng.uniform(0, 0.5, N).astype(np.float32), rng.normal(0, 0.1, N).astype(np.float32), rng.uniform(0.5, 1.5, N).astype(np.float32)
+        want = orc.dice(want, g, mu, var)
+        kw = dict(epilogue=capi.XB_EPI_DICE, ep=(c(g), c(mu), c(var)))
+    elif epi == "prelu":
+        sl = rng.uniform(0.1, 0.4, N).astype(np.float32)
+        want = orc.prelu(want, sl)
+        kw = dict(epilogue=capi.XB_EPI_PRELU, ep=(c(sl), None, None), ep_count=N)
+    eng = capi.XB_GEMM_TCGEN05 if engine == "tcgen05" else capi.XB_GEMM_SIMT
+    part = torch.empty((m, N), dtype=torch.float32, device="cuda")
+    Y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    dxs, dxl = c(xs), c(xl)
+    ops.gemm(dxs, ops.pack_weight_kmajor(c(ws), torch.float16), Y=part, bias=c(b), trans_b=True, M=m, N=N, K=ks, engine=eng)
+    ops.gemm(dxl, ops.pack_weight_kmajor(c(wl), torch.float16), Y=Y, bias=part, bias_kind=capi.XB_BIAS_FULL, ldbias=N,
+             bias_row_group=group, trans_b=True, M=M, N=N, K=kl, engine=eng, **kw)
+    _status_ok(ops)
+    got = Y.float().cpu().numpy()
+    scale = np.abs(f(xs)) @ np.abs(f(ws))
+    scale = np.repeat(scale, group, axis=0) + np.abs(f(xl)) @ np.abs(f(wl)) + np.abs(b)
+    err = np.abs(got - want)
+    assert (err <= 2e-3 * (1 + scale)).all(), float(err.max())
+
+
 def test_parallel_gemm_benchmark_config():
     """8 branches of [4096,256]x[256,128] + bias + PReLU(0.25), fp16, concatenated to [4096,1024]."""
     ops, capi = _ops()

@@ -94,6 +94,40 @@ def test_fed_inputs_gemm_activation_fusion_and_shared_constants():
         mgr.close()
 
 
+@pytest.mark.parametrize("m1,m2", [(1, 300), (5, 1000), (260, 260), (400, 2)])
+def test_pruned_gemm_operator_fp16_with_fused_dice(m1, m2):
+    """PrunedGemm (blaze/blaze/operator/op/pruned_gemm_op.h): one-row broadcast as in the reference, row groups,
+    equal row counts; with LoadModel's fusion pass folding the following Dice into the product."""
+    api = _api()
+    import orc
+    rng = np.random.default_rng(m1 + m2)
+    k1, k2, N = 184, 144, 200
+    h = lambda a: a.astype(np.float16)
+    W1, W2 = h(rng.normal(0, 1 / 14, (k1, N))), h(rng.normal(0, 1 / 12, (k2, N)))
+    b = h(rng.normal(0, 0.1, N))
+    g, mu, var = h(rng.uniform(0, 0.5, N)), h(rng.normal(0, 0.1, N)), h(rng.uniform(0.5, 1.5, N))
+    ops = [api.constant_text("W1", W1, 12), api.constant_text("W2", W2, 12), api.constant_text("b", b, 12),
+           api.constant_text("g", g, 12), api.constant_text("mu", mu, 12), api.constant_text("var", var, 12),
+           api.op_text("PrunedGemm", ["x1", "x2", "W1", "W2", "b"], ["h"]), api.op_text("Dice", ["h", "g", "mu", "var"], ["y"])]
+    text = api.netdef_text(ops, [("x1", 12), ("x2", 12)], [("y", 12)])
+    f32 = lambda a: a.astype(np.float32)
+    x1, x2 = h(rng.normal(0, 1, (m1, k1))), h(rng.normal(0, 1, (m2, k2)))
+    want = orc.dice(orc.pruned_gemm(f32(x1), f32(x2), f32(W1), f32(W2), f32(b)), f32(g), f32(mu), f32(var))
+    for optimize in (False, True):
+        mgr = api.PredictorManager()
+        mgr.load_model_text(text, optimize=optimize)
+        p = mgr.create_predictor()
+        keep = [p.feed("x1", x1), p.feed("x2", x2)]
+        p.forward()
+        got = p.output("y")
+        assert got.shape == (max(m1, m2), N)
+        np.testing.assert_allclose(got.astype(np.float32), want, rtol=4e-3, atol=4e-3)
+        p.forward()
+        assert p.launches() == (2 if optimize else 3), p.launches()      # short product + long product (+ Dice)
+        p.close()
+        mgr.close()
+
+
 def test_binary_netdef_file(tmp_path):
     """LoadModel reads the protobuf wire format of blaze.NetDef (hand-encoded here)."""
     api = _api()

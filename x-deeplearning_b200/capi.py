@@ -42,7 +42,8 @@ class GemmArgs(C.Structure):
                 ("stride_b", i64), ("bias", vp), ("ldbias", i64), ("stride_bias", i64), ("bias_kind", i32),
                 ("Y", vp), ("ldy", i64), ("stride_y", i64), ("batch", i32), ("ab_dtype", i32),
                 ("bias_dtype", i32), ("y_dtype", i32), ("epilogue", i32), ("ep_a", vp), ("ep_b", vp),
-                ("ep_c", vp), ("ep_count", i32), ("dice_nosqrt", i32), ("stride_ep", i64), ("engine", i32)]
+                ("ep_c", vp), ("ep_count", i32), ("dice_nosqrt", i32), ("stride_ep", i64), ("engine", i32),
+                ("bias_row_group", i64)]
 
 
 class DinAttWeights(C.Structure):
@@ -54,6 +55,14 @@ class DinAttArgs(C.Structure):
     _fields_ = [("q", vp), ("ldq", i64), ("k", vp), ("ldk", i64), ("seq_len", vp), ("out", vp), ("ldo", i64),
                 ("scores", vp), ("requests", i32), ("n_cand", i32), ("T", i32), ("d", i32), ("h0", i32),
                 ("h1", i32), ("act", i32), ("use_softmax", i32), ("engine", i32), ("w", DinAttWeights)]
+
+
+class DinTowerArgs(C.Structure):
+    _fields_ = [("user", vp), ("ldu", i64), ("q", vp), ("ldq", i64), ("k", vp), ("ldk", i64), ("att", vp), ("ldatt", i64),
+                ("prob", vp), ("requests", i32), ("n_cand", i32), ("T", i32), ("d", i32), ("du", i32), ("n1", i32),
+                ("n2", i32), ("n3", i32), ("W1", vp), ("b1", vp), ("gamma1", vp), ("mean1", vp), ("var1", vp),
+                ("W2", vp), ("b2", vp), ("gamma2", vp), ("mean2", vp), ("var2", vp), ("W3", vp), ("b3", vp),
+                ("softmax", i32), ("packed", vp)]
 
 
 # every symbol include/xdlb200.h declares: (restype, argtypes)
@@ -80,7 +89,12 @@ SYMBOLS = {
     "xb_din_attention": (i32, [C.POINTER(DinAttArgs), vp]),
     "xb_din_attention_packed_bytes": (C.c_size_t, [i32, i32, i32]),
     "xb_din_attention_pack": (i32, [C.POINTER(DinAttArgs), vp, C.c_size_t, vp]),
+    "xb_din_tower_packed_bytes": (C.c_size_t, [i32, i32, i32, i32]),
+    "xb_din_tower_pack": (i32, [C.POINTER(DinTowerArgs), vp, C.c_size_t, vp]),
+    "xb_din_tower_workspace_bytes": (C.c_size_t, [i32, i32, i32]),
+    "xb_din_tower": (i32, [C.POINTER(DinTowerArgs), vp, C.c_size_t, vp]),
     "xb_din_tower_input": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, vp]),
+    "xb_din_tower_input_split": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, vp]),
     "xb_gru": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp, i32, vp]),
     "xb_augru": (i32, [vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, i32, vp]),
     "xb_dice": (i32, [vp, vp, i64, i32, vp, vp, vp, i32, i32, vp]),

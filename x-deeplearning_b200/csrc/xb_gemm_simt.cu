@@ -14,7 +14,7 @@ struct SimtGemmParams {
   float alpha, beta;
   const void* A; int64_t lda, stride_a;
   const void* B; int64_t ldb, stride_b;
-  const void* bias; int64_t ldbias, stride_bias; int bias_kind, bias_dtype;
+  const void* bias; int64_t ldbias, stride_bias, bias_group; int bias_kind, bias_dtype;
   void* Y; int64_t ldy, stride_y;
   EpiParams epi; int64_t stride_ep;
 };
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const __grid_constant__ 
       if (p.bias_kind == XB_BIAS_ROW)
         v += p.beta * load_as_f32(p.bias, (int64_t)b * p.stride_bias + gn, p.bias_dtype);
       else if (p.bias_kind == XB_BIAS_FULL)
-        v += p.beta * load_as_f32(p.bias, (int64_t)b * p.stride_bias + (int64_t)gm * p.ldbias + gn, p.bias_dtype);
+        v += p.beta * load_as_f32(p.bias, (int64_t)b * p.stride_bias + (int64_t)(gm / p.bias_group) * p.ldbias + gn, p.bias_dtype);
       v = apply_epilogue(epi, v, gn);
       Y[(int64_t)gm * p.ldy + gn] = from_f32<TOut>(v);
     }
@@ -113,6 +113,7 @@ int gemm_simt(const xb_gemm_args& a, cudaStream_t stream) {
   p.A = a.A; p.lda = a.lda; p.stride_a = a.stride_a;
   p.B = a.B; p.ldb = a.ldb; p.stride_b = a.stride_b;
   p.bias = a.bias; p.ldbias = a.ldbias; p.stride_bias = a.stride_bias;
+  p.bias_group = a.bias_row_group > 1 ? a.bias_row_group : 1;
   p.bias_kind = a.bias ? a.bias_kind : XB_BIAS_NONE; p.bias_dtype = a.bias_dtype;
   p.Y = a.Y; p.ldy = a.ldy; p.stride_y = a.stride_y;
   p.epi.kind = a.epilogue; p.epi.a = a.ep_a; p.epi.b = a.ep_b; p.epi.c = a.ep_c;

@@ -35,7 +35,7 @@ struct UmmaGemmParams {
   int M, N, K, block_n, tmem_cols, tiles_m, tiles_n, batch;
   float alpha, beta;
   int a_batched, b_batched;
-  const void* bias; int64_t ldbias, stride_bias; int bias_kind, bias_dtype;
+  const void* bias; int64_t ldbias, stride_bias; int bias_kind, bias_dtype, bias_group;
   void* Y; int64_t ldy, stride_y; int y_dtype;
   EpiParams epi; int64_t stride_ep;
   uint32_t idesc;
@@ -176,6 +176,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int m0 = (int)(rem % p.tiles_m) * BLOCK_M, n0 = (int)(rem / p.tiles_m) * p.block_n;
       const int as = it & 1;
       const int gm = m0 + row;
+      const int brow = p.bias_group > 1 ? gm / p.bias_group : gm;      // bias row of this output row
       if (n0 != cur_n0 || b != cur_b) {
         cur_n0 = n0; cur_b = b;
         asm volatile("bar.sync 2, 256;" ::: "memory");                  // everyone is done with the old columns
@@ -219,10 +220,22 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = fmaf(p.alpha, __uint_as_float(raw[u][i]), s_bias[c + i]);
           if (p.bias_kind == XB_BIAS_FULL && gm < p.M) {
-            const int64_t base = (int64_t)b * p.stride_bias + (int64_t)gm * p.ldbias + gn0;
+            const int64_t base = (int64_t)b * p.stride_bias + (int64_t)brow * p.ldbias + gn0;
+            const float* bf = reinterpret_cast<const float*>(p.bias) + base;
+            if (p.bias_dtype == XB_F32 && valid == 16 && (reinterpret_cast<uintptr_t>(bf) & 15) == 0) {
+              // fp32 rows (the per-group partial product of a pruned GEMM): four 16-byte loads, mostly one
+              // address per warp since consecutive output rows share the bias row
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (i < valid) v[i] += p.beta * load_as_f32(p.bias, base + i, p.bias_dtype);
+              for (int i = 0; i < 4; ++i) {
+                const float4 t = __ldg(reinterpret_cast<const float4*>(bf) + i);
+                v[4 * i] += p.beta * t.x; v[4 * i + 1] += p.beta * t.y;
+                v[4 * i + 2] += p.beta * t.z; v[4 * i + 3] += p.beta * t.w;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (i < valid) v[i] += p.beta * load_as_f32(p.bias, base + i, p.bias_dtype);
+            }
           }
           if (p.epi.kind == XB_EPI_PRELU) {
 #pragma unroll
@@ -327,6 +340,7 @@ int gemm_umma(const xb_gemm_args& a, cudaStream_t stream) {
   p.alpha = a.alpha; p.beta = a.beta;
   p.a_batched = a.stride_a != 0; p.b_batched = a.stride_b != 0;
   p.bias = a.bias; p.ldbias = a.ldbias; p.stride_bias = a.stride_bias;
+  p.bias_group = a.bias_row_group > 1 ? (int)a.bias_row_group : 1;
   p.bias_kind = a.bias ? a.bias_kind : XB_BIAS_NONE; p.bias_dtype = a.bias_dtype;
   p.Y = a.Y; p.ldy = a.ldy; p.stride_y = a.stride_y; p.y_dtype = a.y_dtype;
   p.epi.kind = a.epilogue; p.epi.a = a.ep_a; p.epi.b = a.ep_b; p.epi.c = a.ep_c;
@@ -363,18 +377,22 @@ using namespace xb;
 namespace xb {
 int att_status(int* out);
 int att_clear_status();
+int tower_status(int* out);
+int tower_clear_status();
 }  // namespace xb
 
 extern "C" int xb_device_status(int* status) {
   XB_REQUIRE(status, XB_ERR_ARG, "xb_device_status: null pointer");
-  int a = 0, b = 0;
-  XB_REQUIRE(gemm_umma_status(&a) == 0 && att_status(&b) == 0, XB_ERR_CUDA, "xb_device_status: read failed");
-  *status = a ? a : b;
+  int a = 0, b = 0, c = 0;
+  XB_REQUIRE(gemm_umma_status(&a) == 0 && att_status(&b) == 0 && tower_status(&c) == 0, XB_ERR_CUDA,
+             "xb_device_status: read failed");
+  *status = a ? a : (b ? b : c);
   return 0;
 }
 
 extern "C" int xb_device_status_clear(void) {
-  XB_REQUIRE(gemm_umma_clear_status() == 0 && att_clear_status() == 0, XB_ERR_CUDA, "xb_device_status_clear failed");
+  XB_REQUIRE(gemm_umma_clear_status() == 0 && att_clear_status() == 0 && tower_clear_status() == 0, XB_ERR_CUDA,
+             "xb_device_status_clear failed");
   return 0;
 }
 
@@ -395,6 +413,8 @@ static int validate_gemm(const xb_gemm_args* a) {
   XB_REQUIRE(!a->bias || a->bias_kind == XB_BIAS_ROW || a->bias_kind == XB_BIAS_FULL, XB_ERR_ARG,
              "xb_gemm: bias kind %d", a->bias_kind);
   XB_REQUIRE(!a->bias || dtype_size(a->bias_dtype) != 0, XB_ERR_UNSUPPORTED, "xb_gemm: bias dtype %d", a->bias_dtype);
+  XB_REQUIRE(a->bias_row_group >= 0 && (a->bias_row_group <= 1 || (a->bias && a->bias_kind == XB_BIAS_FULL)), XB_ERR_ARG,
+             "xb_gemm: bias_row_group needs a full [rows, N] bias");
   const int64_t a_cols = a->trans_a ? a->M : a->K, b_cols = a->trans_b ? a->K : a->N;
   XB_REQUIRE(a->lda >= a_cols && a->ldb >= b_cols && a->ldy >= a->N, XB_ERR_ARG,
              "xb_gemm: leading dimension smaller than the row (lda=%lld ldb=%lld ldy=%lld)", (long long)a->lda,

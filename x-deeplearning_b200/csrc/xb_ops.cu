@@ -232,6 +232,77 @@ __global__ void __launch_bounds__(256) din_tower_input_kernel(const __half* user
   }
 }
 
+// Split form: per-request columns [user | his_sum] once per request, per-candidate columns
+// [q | q*his_sum | att | q-his_sum] per candidate. Same CTA shape as above.
+__global__ void __launch_bounds__(256) din_tower_split_kernel(const __half* user, int64_t ldu, const __half* q,
+                                                              int64_t ldq, const __half* k, int64_t ldk,
+                                                              const __half* att, int64_t ldatt, __half* Xu, int64_t ldxu,
+                                                              __half* Xc, int64_t ldxc, int n_cand, int T, int d, int du,
+                                                              int pairs_ok) {
+  extern __shared__ float hs[];      // [d] his_sum, then [G][d] partial sums
+  float* part = hs + d;
+  const int r = blockIdx.y;
+  const int G = max(1, min((int)blockDim.x / d, 8));
+  if ((int)threadIdx.x < G * d) {
+    const int gi = threadIdx.x / d, e = threadIdx.x - gi * d;
+    float s = 0.f;
+    for (int t = gi; t < T; t += G) s += __half2float(k[((int64_t)r * T + t) * ldk + e]);
+    part[gi * d + e] = s;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < d; e += blockDim.x) {
+    float s = 0.f;
+    for (int gi = 0; gi < G; ++gi) s += part[gi * d + e];
+    hs[e] = s;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int c = threadIdx.x; c < (int)ldxu; c += blockDim.x) {
+      __half v = __float2half(0.f);
+      if (c < du) v = user[(int64_t)r * ldu + c];
+      else if (c < du + d) v = __float2half_rn(hs[c - du]);
+      Xu[(int64_t)r * ldxu + c] = v;
+    }
+  }
+  const int n0 = blockIdx.x * 64;
+  const int rows = min(64, n_cand - n0);
+  if (pairs_ok) {
+    const int wp = (int)(ldxc >> 1);                   // half2 units per row
+    for (int idx = threadIdx.x; idx < rows * wp; idx += blockDim.x) {
+      const int n = n0 + idx / wp, c = (idx % wp) * 2;
+      const int64_t row = (int64_t)r * n_cand + n;
+      float2 v = make_float2(0.f, 0.f);
+      if (c < 4 * d) {
+        const int seg = c / d, e = c - seg * d;
+        if (seg == 2) v = __half22float2(*reinterpret_cast<const __half2*>(att + row * ldatt + e));
+        else {
+          const float2 qv = __half22float2(*reinterpret_cast<const __half2*>(q + row * ldq + e));
+          if (seg == 0) v = qv;
+          else if (seg == 1) v = make_float2(qv.x * hs[e], qv.y * hs[e + 1]);
+          else v = make_float2(qv.x - hs[e], qv.y - hs[e + 1]);
+        }
+      }
+      *reinterpret_cast<__half2*>(Xc + row * ldxc + c) = __floats2half2_rn(v.x, v.y);
+    }
+    return;
+  }
+  const int width = (int)ldxc;
+  for (int idx = threadIdx.x; idx < rows * width; idx += blockDim.x) {
+    const int n = n0 + idx / width, c = idx % width;
+    const int64_t row = (int64_t)r * n_cand + n;
+    float v = 0.f;
+    if (c < 4 * d) {
+      const int seg = c / d, e = c % d;
+      if (seg == 2) v = __half2float(att[row * ldatt + e]);
+      else {
+        const float qv = __half2float(q[row * ldq + e]);
+        v = seg == 0 ? qv : (seg == 1 ? qv * hs[e] : qv - hs[e]);
+      }
+    }
+    Xc[row * ldxc + c] = __float2half_rn(v);
+  }
+}
+
 static bool float_dtype(int dt) { return dt == XB_F32 || dt == XB_F16 || dt == XB_BF16; }
 
 }  // namespace xb
@@ -358,4 +429,25 @@ extern "C" int xb_din_tower_input(const void* user, int64_t ldu, const void* q, 
       (const __half*)user, ldu, (const __half*)q, ldq, (const __half*)k, ldk, (const __half*)att, ldatt, (__half*)X,
       ldx, n_cand, T, d, du, pairs_ok);
   return check_launch("din_tower_input_kernel");
+}
+
+extern "C" int xb_din_tower_input_split(const void* user, int64_t ldu, const void* q, int64_t ldq, const void* k,
+                                        int64_t ldk, const void* att, int64_t ldatt, void* Xu, int64_t ldxu, void* Xc,
+                                        int64_t ldxc, int32_t requests, int32_t n_cand, int32_t T, int32_t d, int32_t du,
+                                        xb_stream_t s) {
+  XB_REQUIRE(user && q && k && att && Xu && Xc, XB_ERR_ARG, "xb_din_tower_input_split: null tensor");
+  XB_REQUIRE(requests >= 0 && n_cand >= 0 && T >= 0 && d > 0 && du >= 0, XB_ERR_ARG, "xb_din_tower_input_split: bad sizes");
+  XB_REQUIRE(d <= 256 && du <= 4096, XB_ERR_LIMIT, "xb_din_tower_input_split: d <= 256 and du <= 4096");
+  XB_REQUIRE(ldxu >= du + d && ldxc >= 4 * d && ldu >= du && ldq >= d && ldk >= d && ldatt >= d, XB_ERR_ARG,
+             "xb_din_tower_input_split: leading dimension too small");
+  XB_REQUIRE(requests <= 65535 && ldxc <= 65536 && ldxu <= 65536, XB_ERR_LIMIT,
+             "xb_din_tower_input_split: more than 65535 requests per call");
+  if (requests == 0) return 0;
+  dim3 grid(n_cand > 0 ? (n_cand + 63) / 64 : 1, requests);
+  const int pairs_ok = d % 2 == 0 && ldxc % 2 == 0 && ldq % 2 == 0 && ldatt % 2 == 0 &&
+                       (((uintptr_t)q | (uintptr_t)att | (uintptr_t)Xc) & 3) == 0;
+  din_tower_split_kernel<<<grid, 256, sizeof(float) * (9 * d + 2), (cudaStream_t)s>>>(
+      (const __half*)user, ldu, (const __half*)q, ldq, (const __half*)k, ldk, (const __half*)att, ldatt, (__half*)Xu,
+      ldxu, (__half*)Xc, ldxc, n_cand, T, d, du, pairs_ok);
+  return check_launch("din_tower_split_kernel");
 }

@@ -14,6 +14,15 @@ from . import capi, ops
 from .capi import check, lib
 
 
+def split_tower_rows(du, d):
+    """Row indices of the first tower weight [du + 5d, N] that meet the per-request columns
+    [user | his_sum] and the per-candidate columns [q | q*his_sum | att | q-his_sum]."""
+    r = np.arange
+    rows_u = np.concatenate([r(0, du), r(du + d, du + 2 * d)])
+    rows_c = np.concatenate([r(du, du + d), r(du + 2 * d, du + 5 * d)])
+    return rows_u, rows_c
+
+
 class DinModel:
     def __init__(self, model, device="cuda", engine=capi.XB_GEMM_AUTO):
         self.dev = device
@@ -34,11 +43,22 @@ class DinModel:
         f32 = lambda x: t(np.ascontiguousarray(x)).to(device=device, dtype=torch.float32)
         # weights are constants: pack once to the K-major layout the tcgen05 engine reads
         self.W1 = ops.pack_weight_kmajor(t(tw["W1"]).to(device), torch.float16, ldk=self.ldx)
+        # the same layer split for the pruned product: rows of W1 that meet the per-request columns
+        # [user | his_sum] and rows that meet the per-candidate columns [q | q*his_sum | att | q-his_sum]
+        du, d = D["user_groups"] * D["emb"], D["d"]
+        self.du = du
+        rows_u, rows_c = split_tower_rows(du, d)
+        self.ldxu, self.ldxc = (du + d + 7) // 8 * 8, (4 * d + 7) // 8 * 8
+        self.W1u = ops.pack_weight_kmajor(t(np.ascontiguousarray(tw["W1"][rows_u])).to(device), torch.float16, ldk=self.ldxu)
+        self.W1c = ops.pack_weight_kmajor(t(np.ascontiguousarray(tw["W1"][rows_c])).to(device), torch.float16, ldk=self.ldxc)
         self.W2 = ops.pack_weight_kmajor(t(tw["W2"]).to(device), torch.float16)
         self.W3 = ops.pack_weight_kmajor(t(tw["W3"]).to(device), torch.float16)
         self.b1, self.b2, self.b3 = f32(tw["b1"]), f32(tw["b2"]), f32(tw["b3"])
         self.dice1 = [f32(x) for x in tw["dice1"]]
         self.dice2 = [f32(x) for x in tw["dice2"]]
+        # the whole tower (assembly, three layers, softmax) as one tcgen05 kernel
+        self.tower = ops.DinTower(d, du, t(tw["W1"]), t(tw["b1"]), [t(x) for x in tw["dice1"]], t(tw["W2"]), t(tw["b2"]),
+                                  [t(x) for x in tw["dice2"]], t(tw["W3"]), t(tw["b3"]), device=device)
         self._plans = {}
 
     # -- per-shape buffers and the pooling plan ------------------------------------------------
@@ -60,6 +80,8 @@ class DinModel:
         h = lambda *s: torch.empty(s, dtype=torch.float16, device=dev)
         p["user_emb"], p["k"], p["q"] = h(R, G * e), h(R, T * d), h(R * n_cand, d)
         p["att"], p["X"] = h(R * n_cand, d), h(R * n_cand, self.ldx)
+        p["Xu"], p["Xc"] = h(R, self.ldxu), h(R * n_cand, self.ldxc)
+        p["partial"] = torch.empty((R, D["tower"][0]), dtype=torch.float32, device=dev)
         p["y1"], p["y2"] = h(R * n_cand, D["tower"][0]), h(R * n_cand, D["tower"][1])
         p["logit"] = torch.empty((R * n_cand, D["tower"][2]), dtype=torch.float32, device=dev)
         p["prob"] = torch.empty_like(p["logit"])
@@ -103,10 +125,12 @@ class DinModel:
             p[name].copy_(staged[name], non_blocking=True)
         return p
 
-    def forward_device(self, p, att_engine=None, marks=None):
+    def forward_device(self, p, att_engine=None, marks=None, pruned=True, fused_tower=True):
         """The hot path on inputs already resident in HBM. Returns probabilities [R*n_cand, 2] fp32.
         `marks`, when given, is a list of four CUDA events recorded on the current stream around the
-        pooling launches (0,1) and the attention kernel (2,3) for per-kernel timing."""
+        pooling launches (0,1) and the attention kernel (2,3) for per-kernel timing. With `pruned` the
+        first tower layer runs as Blaze's PrunedGemm does: the per-request columns are multiplied once per
+        request and added to every candidate row of that request in the epilogue."""
         D = self.D
         R, n_cand, T, d = p["R"], p["n_cand"], D["T"], D["d"]
         s = ops.stream()
@@ -121,12 +145,24 @@ class DinModel:
                  engine=self.engine if att_engine is None else att_engine)
         if marks:
             marks[3].record()
-        check(lib().xb_din_tower_input(ops.ptr(p["user_emb"]), p["user_emb"].stride(0), ops.ptr(p["q"]), d,
-                                       ops.ptr(p["k"]), d, ops.ptr(p["att"]), d, ops.ptr(p["X"]), self.ldx, R,
-                                       n_cand, T, d, D["user_groups"] * D["emb"], s))
         E = capi
-        ops.gemm(p["X"], self.W1, Y=p["y1"], bias=self.b1, trans_b=True, epilogue=E.XB_EPI_DICE, ep=self.dice1,
-                 engine=self.engine, K=self.ldx, M=R * n_cand, N=D["tower"][0])
+        if fused_tower:
+            return self.tower(p["user_emb"], p["q"], p["k"].view(R * T, d), p["att"], R, n_cand, T, out=p["prob"])
+        if pruned:
+            check(lib().xb_din_tower_input_split(ops.ptr(p["user_emb"]), p["user_emb"].stride(0), ops.ptr(p["q"]), d,
+                                                 ops.ptr(p["k"]), d, ops.ptr(p["att"]), d, ops.ptr(p["Xu"]), self.ldxu,
+                                                 ops.ptr(p["Xc"]), self.ldxc, R, n_cand, T, d, self.du, s))
+            ops.gemm(p["Xu"], self.W1u, Y=p["partial"], bias=self.b1, trans_b=True, engine=self.engine,
+                     K=self.ldxu, M=R, N=D["tower"][0])
+            ops.gemm(p["Xc"], self.W1c, Y=p["y1"], bias=p["partial"], bias_kind=E.XB_BIAS_FULL, ldbias=D["tower"][0],
+                     bias_row_group=n_cand, trans_b=True, epilogue=E.XB_EPI_DICE, ep=self.dice1, engine=self.engine,
+                     K=self.ldxc, M=R * n_cand, N=D["tower"][0])
+        else:
+            check(lib().xb_din_tower_input(ops.ptr(p["user_emb"]), p["user_emb"].stride(0), ops.ptr(p["q"]), d,
+                                           ops.ptr(p["k"]), d, ops.ptr(p["att"]), d, ops.ptr(p["X"]), self.ldx, R,
+                                           n_cand, T, d, self.du, s))
+            ops.gemm(p["X"], self.W1, Y=p["y1"], bias=self.b1, trans_b=True, epilogue=E.XB_EPI_DICE, ep=self.dice1,
+                     engine=self.engine, K=self.ldx, M=R * n_cand, N=D["tower"][0])
         ops.gemm(p["y1"], self.W2, Y=p["y2"], bias=self.b2, trans_b=True, epilogue=E.XB_EPI_DICE, ep=self.dice2,
                  engine=self.engine, K=D["tower"][0], M=R * n_cand, N=D["tower"][1])
         ops.gemm(p["y2"], self.W3, Y=p["logit"], bias=self.b3, trans_b=True, engine=self.engine,
@@ -134,8 +170,8 @@ class DinModel:
         check(lib().xb_softmax(ops.ptr(p["logit"]), ops.ptr(p["prob"]), R * n_cand, D["tower"][2], 1, capi.XB_F32, s))
         return p["prob"]
 
-    # kernels launched by one forward_device call (pool scan + pool + attention + assemble + 3 GEMM + softmax)
-    LAUNCHES_PER_FORWARD = 8
+    # kernels launched by one forward_device call (pool scan + pool + attention + the two tower kernels)
+    LAUNCHES_PER_FORWARD = 5
 
     def forward(self, staged):
         """End to end: host ids -> device -> probabilities back on the host."""

@@ -50,18 +50,25 @@ def build(model):
         ops.append(api.constant_text("att_" + n, a[n], F16))
         names.append("att_" + n)
     ops.append(api.op_text("DinAttention", ["ad_emb", "his_emb"] + names, ["att"], {"act": 2}))
-    ops.append(api.op_text("DinTowerInput", ["uid_emb", "ad_emb", "his_emb", "att"], ["tower_in"]))
+    # first tower layer as a PrunedGemm: the columns that are equal for all candidates of a request
+    # ([user | his_sum]) are one operand, the per-candidate columns the other
+    ops.append(api.op_text("DinTowerInput", ["uid_emb", "ad_emb", "his_emb", "att"], ["tower_user", "tower_cand"]))
     tw = model["tower"]
-    tin = G * e + 5 * d
-    ld = (tin + 7) // 8 * 8
-    W1 = np.zeros((ld, tw["W1"].shape[1]), np.float32)        # rows of the zero padding columns of tower_in
-    W1[:tin] = tw["W1"]
-    for name, arr in (("W1", W1), ("b1", tw["b1"]), ("W2", tw["W2"]), ("b2", tw["b2"]), ("W3", tw["W3"]), ("b3", tw["b3"])):
+    from .din import split_tower_rows
+    rows_u, rows_c = split_tower_rows(G * e, d)
+
+    def padded(rows):
+        ld = (len(rows) + 7) // 8 * 8                         # rows of the zero padding columns of the operand
+        W = np.zeros((ld, tw["W1"].shape[1]), np.float32)
+        W[:len(rows)] = tw["W1"][rows]
+        return W
+    for name, arr in (("W1u", padded(rows_u)), ("W1c", padded(rows_c)), ("b1", tw["b1"]), ("W2", tw["W2"]), ("b2", tw["b2"]),
+                      ("W3", tw["W3"]), ("b3", tw["b3"])):
         ops.append(api.constant_text("t_" + name, arr, F16))
     for i, key in ((1, "dice1"), (2, "dice2")):
         for n, arr in zip(("g", "m", "v"), tw[key]):
             ops.append(api.constant_text("t_%s%d" % (n, i), arr, F16))
-    ops.append(api.op_text("Gemm", ["tower_in", "t_W1", "t_b1"], ["h1"]))
+    ops.append(api.op_text("PrunedGemm", ["tower_user", "tower_cand", "t_W1u", "t_W1c", "t_b1"], ["h1"]))
     ops.append(api.op_text("Dice", ["h1", "t_g1", "t_m1", "t_v1"], ["y1"]))
     ops.append(api.op_text("Gemm", ["y1", "t_W2", "t_b2"], ["h2"]))
     ops.append(api.op_text("Dice", ["h2", "t_g2", "t_m2", "t_v2"], ["y2"]))

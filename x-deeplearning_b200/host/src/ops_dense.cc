@@ -223,6 +223,108 @@ class GemmOp final : public Operator<CUDAContext> {
 REGISTER_CUDA_OPERATOR(Gemm, GemmOp);
 OPERATOR_SCHEMA(Gemm).NumInputs(2, 6).NumOutputs(1);
 
+// PrunedGemm: [X1 | X2] x [W1 ; W2] = X1 x W1 + X2 x W2 (+ bias), the "common features computed once"
+// product (blaze/blaze/operator/op/pruned_gemm_op.h:1-163). The reference takes operands with equal
+// row counts or one of them with a single row that is broadcast; here the short operand may also have
+// m rows with the long one a multiple of m: row i of the long operand pairs with row i / (M/m) of the
+// short one, which is the one-row case applied to m requests in one launch. The short product (with the
+// bias) is kept in fp32 and added in the epilogue of the long one, before the optional fused activation
+// and the single rounding to the output type. (In the equal-rows branch the reference passes X2 for both
+// operands of its second Gemm, pruned_gemm_op.h:95-105; the product computed here is X2 x W2.)
+class PrunedGemmOp final : public Operator<CUDAContext> {
+ public:
+  PrunedGemmOp(const OperatorDef& def, Workspace* ws) : Operator<CUDAContext>(def, ws) {
+    c_.transa = GetSingleArgument<bool>("transA", false);
+    c_.transb = GetSingleArgument<bool>("transB", false);
+    c_.alpha = GetSingleArgument<float>("alpha", 1.0f);
+    c_.beta = GetSingleArgument<float>("beta", 1.0f);
+    epilogue_ = GetSingleArgument<int>("epilogue", XB_EPI_NONE);
+    nosqrt_ = GetSingleArgument<bool>("nosqrt", false);
+    BLAZE_CONDITION_THROW(!c_.transa, "PrunedGemm: transA is not supported");
+  }
+
+  bool RunOnDevice() override {
+    const size_t n_epi = epilogue_ == XB_EPI_DICE ? 3 : (epilogue_ == XB_EPI_PRELU ? 1 : 0);
+    const size_t n_plain = InputSize() - n_epi;
+    BLAZE_CONDITION_THROW(n_plain == 4 || n_plain == 5, "PrunedGemm takes x1, x2, w1, w2 and an optional bias");
+    Blob *x1 = Input(0), *x2 = Input(1), *w1 = Input(2), *w2 = Input(3);
+    Blob* bias = n_plain > 4 ? Input(4) : nullptr;
+    Blob* y = Output(0);
+    for (Blob* b : {x1, x2, w1, w2})
+      BLAZE_CONDITION_THROW(b->shape().size() == 2, "PrunedGemm: only 2-D operands, got rank ", b->shape().size());
+    BLAZE_CONDITION_THROW(x1->data_type() == x2->data_type() && x1->data_type() == w1->data_type() &&
+                          w1->data_type() == w2->data_type(), "PrunedGemm: operand data types differ");
+    const TIndex m1 = x1->shape()[0], k1 = x1->shape()[1], m2 = x2->shape()[0], k2 = x2->shape()[1];
+    const TIndex n1 = c_.transb ? w1->shape()[0] : w1->shape()[1], n2 = c_.transb ? w2->shape()[0] : w2->shape()[1];
+    BLAZE_CONDITION_THROW((c_.transb ? w1->shape()[1] : w1->shape()[0]) == k1, "x1_k=", k1, " does not match w1");
+    BLAZE_CONDITION_THROW((c_.transb ? w2->shape()[1] : w2->shape()[0]) == k2, "x2_k=", k2, " does not match w2");
+    BLAZE_CONDITION_THROW(n1 == n2, "w1_n=", n1, " w2_n=", n2);
+    const TIndex M = std::max(m1, m2), m = std::min(m1, m2), N = n1;
+    BLAZE_CONDITION_THROW(m > 0 && M % m == 0, "PrunedGemm: row counts ", m1, " and ", m2, " do not broadcast");
+    if (bias) BLAZE_CONDITION_THROW(bias->size() == (size_t)N, "PrunedGemm: bias of ", bias->size(), " for N=", N);
+    const bool first_short = m1 <= m2;
+    Blob* xs = first_short ? x1 : x2;          // short operand: computed once per row group
+    Blob* ws = first_short ? w1 : w2;
+    Blob* xl = first_short ? x2 : x1;
+    Blob* wl = first_short ? w2 : w1;
+    const TIndex ks = first_short ? k1 : k2, kl = first_short ? k2 : k1;
+    y->set_data_type(x1->data_type());
+    y->Reshape({M, N});
+    cudaStream_t s = context_.cuda_stream();
+    if (!partial_) partial_.reset(new Blob(device_option_));
+    partial_->set_data_type(kFloat);
+    partial_->Reshape({m, N});
+
+    xb_gemm_args g;
+    memset(&g, 0, sizeof(g));
+    bool tb; int64_t ldb, sb;
+    // short product: partial = alpha * xs x ws + beta * bias, fp32
+    g.M = (int)m; g.N = (int)N; g.K = (int)ks; g.alpha = c_.alpha; g.beta = bias ? c_.beta : 0.f;
+    g.A = xs->as<void>(); g.lda = ks;
+    g.B = PackIfUseful(ws, c_.transb, (int)ks, (int)N, 1, &packed_[0], s, &launches, &tb, &ldb, &sb);
+    g.trans_b = tb; g.ldb = ldb;
+    if (bias) { g.bias = bias->as<void>(); g.bias_dtype = bias->data_type(); g.bias_kind = XB_BIAS_ROW; }
+    g.Y = partial_->as<void>(); g.ldy = N; g.batch = 1;
+    g.ab_dtype = xs->data_type(); g.y_dtype = kFloat;
+    XB_CHECK(xb_gemm(&g, s));
+    ++launches;
+    // long product with the short one added per row group, then the activation
+    memset(&g, 0, sizeof(g));
+    g.M = (int)M; g.N = (int)N; g.K = (int)kl; g.alpha = c_.alpha; g.beta = 1.f;
+    g.A = xl->as<void>(); g.lda = kl;
+    g.B = PackIfUseful(wl, c_.transb, (int)kl, (int)N, 1, &packed_[1], s, &launches, &tb, &ldb, &sb);
+    g.trans_b = tb; g.ldb = ldb;
+    g.bias = partial_->as<void>(); g.bias_dtype = kFloat; g.bias_kind = XB_BIAS_FULL; g.ldbias = N;
+    g.bias_row_group = M / m;
+    g.Y = y->as<void>(); g.ldy = N; g.batch = 1;
+    g.ab_dtype = xl->data_type(); g.y_dtype = y->data_type();
+    g.epilogue = epilogue_; g.dice_nosqrt = nosqrt_;
+    if (epilogue_ == XB_EPI_PRELU) {
+      Blob* w = Input(n_plain);
+      g.ep_a = AsF32(w, &ep_[0], s, &launches);
+      g.ep_count = (int)w->size();
+      BLAZE_CONDITION_THROW(g.ep_count == 1 || g.ep_count == (int)N, "PRelu slopes ", g.ep_count, " for N=", N);
+    } else if (epilogue_ == XB_EPI_DICE) {
+      g.ep_a = AsF32(Input(n_plain), &ep_[0], s, &launches);
+      g.ep_b = AsF32(Input(n_plain + 1), &ep_[1], s, &launches);
+      g.ep_c = AsF32(Input(n_plain + 2), &ep_[2], s, &launches);
+    }
+    XB_CHECK(xb_gemm(&g, s));
+    ++launches;
+    return true;
+  }
+
+ private:
+  GemmCommon c_;
+  int epilogue_;
+  bool nosqrt_;
+  PackedWeight packed_[2];
+  Derived ep_[3];
+  std::unique_ptr<Blob> partial_;
+};
+REGISTER_CUDA_OPERATOR(PrunedGemm, PrunedGemmOp);
+OPERATOR_SCHEMA(PrunedGemm).NumInputs(4, 8).NumOutputs(1);
+
 class FusedParallelGemmOp final : public Operator<CUDAContext> {
  public:
   FusedParallelGemmOp(const OperatorDef& def, Workspace* ws) : Operator<CUDAContext>(def, ws) {
@@ -637,6 +739,7 @@ class DinTowerInputOp final : public Operator<CUDAContext> {
   }
   bool RunOnDevice() override {
     Blob *u = Input(0), *q = Input(1), *k = Input(2), *att = Input(3), *x = Output(0);
+    if (OutputSize() == 2) return RunSplit(u, q, k, att);
     for (int i = 0; i < 4; ++i) BLAZE_CONDITION_THROW(Input(i)->data_type() == kFloat16, "DinTowerInput needs fp16 inputs");
     BLAZE_CONDITION_THROW(k->shape().size() == 3 && u->shape().size() == 2, "DinTowerInput: k [R,T,d], user [R,du]");
     const int R = (int)k->shape()[0], T = (int)k->shape()[1], d = (int)k->shape()[2], du = (int)u->shape()[1];
@@ -649,10 +752,29 @@ class DinTowerInputOp final : public Operator<CUDAContext> {
     ++launches;
     return true;
   }
+  // two outputs: [user | his_sum] per request and [q | q*his_sum | att | q-his_sum] per candidate, the two
+  // operands of a PrunedGemm
+  bool RunSplit(Blob* u, Blob* q, Blob* k, Blob* att) {
+    for (int i = 0; i < 4; ++i) BLAZE_CONDITION_THROW(Input(i)->data_type() == kFloat16, "DinTowerInput needs fp16 inputs");
+    BLAZE_CONDITION_THROW(k->shape().size() == 3 && u->shape().size() == 2, "DinTowerInput: k [R,T,d], user [R,du]");
+    const int R = (int)k->shape()[0], T = (int)k->shape()[1], d = (int)k->shape()[2], du = (int)u->shape()[1];
+    const int n_cand = (int)(q->size() / ((size_t)R * d));
+    const int ldu = (du + d + 7) / 8 * 8, ldc = (4 * d + 7) / 8 * 8;
+    Blob *xu = Output(0), *xc = Output(1);
+    xu->set_data_type(kFloat16);
+    xu->Reshape({(TIndex)R, (TIndex)ldu});
+    xc->set_data_type(kFloat16);
+    xc->Reshape({(TIndex)R * n_cand, (TIndex)ldc});
+    XB_CHECK(xb_din_tower_input_split(u->as<void>(), du, q->as<void>(), d, k->as<void>(), d, att->as<void>(), d,
+                                      xu->as<void>(), ldu, xc->as<void>(), ldc, R, n_cand, T, d, du,
+                                      context_.cuda_stream()));
+    ++launches;
+    return true;
+  }
   int ld_;
 };
 REGISTER_CUDA_OPERATOR(DinTowerInput, DinTowerInputOp);
-OPERATOR_SCHEMA(DinTowerInput).NumInputs(4).NumOutputs(1);
+OPERATOR_SCHEMA(DinTowerInput).NumInputs(4).NumOutputs(1, 2);
 
 }  // namespace
 }  // namespace blaze

@@ -346,7 +346,8 @@ void FuseGemmActivation(NetDef* def) {
     for (const auto& v : def->external_output) ext_out.insert(v.name);
     for (size_t i = 0; i < def->op.size() && !changed; ++i) {
       OperatorDef& g = def->op[i];
-      if (g.type != "Gemm" || g.FindArg("epilogue") || g.output.size() != 1 || g.input.size() != 3) continue;
+      const bool gemm = g.type == "Gemm" && g.input.size() == 3, pruned = g.type == "PrunedGemm" && g.input.size() == 5;
+      if (!(gemm || pruned) || g.FindArg("epilogue") || g.output.size() != 1) continue;
       const std::string& y = g.output[0];
       if (consumers[y] != 1 || ext_out.count(y)) continue;
       for (size_t j = i + 1; j < def->op.size(); ++j) {

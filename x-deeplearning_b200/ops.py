@@ -107,7 +107,7 @@ def embedding_pool(groups):
 
 def gemm(A, B, Y=None, bias=None, trans_a=False, trans_b=False, alpha=1.0, beta=1.0, epilogue=0, ep=(None, None, None),
          ep_count=0, nosqrt=False, engine=0, out_dtype=None, batch=1, strides=(0, 0, 0, 0), M=None, N=None, K=None,
-         lda=None, ldb=None, ldy=None, bias_kind=None, stride_ep=0, ldbias=None):
+         lda=None, ldb=None, ldy=None, bias_kind=None, stride_ep=0, ldbias=None, bias_row_group=0):
     """2-D (or explicitly strided batched) GEMM through xb_gemm. Returns Y."""
     a = GemmArgs()
     if M is None:
@@ -124,6 +124,7 @@ def gemm(A, B, Y=None, bias=None, trans_a=False, trans_b=False, alpha=1.0, beta=
         a.bias_kind = bias_kind if bias_kind is not None else (capi.XB_BIAS_ROW if bias.dim() == 1 else capi.XB_BIAS_FULL)
         a.ldbias = ldbias if ldbias is not None else (bias.stride(-2) if bias.dim() > 1 else 0)
         a.stride_bias = strides[2]
+        a.bias_row_group = bias_row_group
     a.Y, a.ldy, a.stride_y = Y.data_ptr(), ldy if ldy is not None else Y.stride(-2), strides[3]
     a.batch, a.ab_dtype, a.y_dtype = batch, dt(A), dt(Y)
     a.epilogue = epilogue
@@ -193,3 +194,49 @@ def device_status():
     s = C.c_int32(0)
     check(lib().xb_device_status(C.byref(s)))
     return s.value
+
+
+class DinTower:
+    """Weights of the DIN tower (du+5d -> n1 -> n2 -> n3, Dice after the first two layers) packed for
+    xb_din_tower. W1 [du+5d, n1], W2 [n1, n2], W3 [n2, n3] are float32 CPU tensors in Blaze's [K, N] layout."""
+
+    def __init__(self, d, du, W1, b1, dice1, W2, b2, dice2, W3, b3, softmax=True, device="cuda"):
+        h = lambda x: x.to(device=device, dtype=torch.float16).contiguous()
+        f = lambda x: x.to(device=device, dtype=torch.float32).contiguous()
+        self.d, self.du = d, du
+        self.n1, self.n2, self.n3 = W1.shape[1], W2.shape[1], W3.shape[1]
+        assert W1.shape[0] == du + 5 * d and W2.shape[0] == self.n1 and W3.shape[0] == self.n2
+        self.keep = [h(W1), f(b1), f(dice1[0]), f(dice1[1]), f(dice1[2]), h(W2), f(b2), f(dice2[0]), f(dice2[1]),
+                     f(dice2[2]), h(W3), f(b3)]
+        self.softmax = softmax
+        nbytes = lib().xb_din_tower_packed_bytes(d, self.n1, self.n2, self.n3)
+        if nbytes == 0:
+            raise capi.XbError("DinTower: shape outside the fused tower kernel")
+        self.packed = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        a = self._args()
+        check(lib().xb_din_tower_pack(C.byref(a), ptr(self.packed), nbytes, stream()))
+        self._ws = None
+
+    def _args(self):
+        a = capi.DinTowerArgs()
+        a.d, a.du, a.n1, a.n2, a.n3, a.softmax = self.d, self.du, self.n1, self.n2, self.n3, int(self.softmax)
+        k = self.keep
+        a.W1, a.b1, a.gamma1, a.mean1, a.var1 = k[0].data_ptr(), k[1].data_ptr(), k[2].data_ptr(), k[3].data_ptr(), k[4].data_ptr()
+        a.W2, a.b2, a.gamma2, a.mean2, a.var2 = k[5].data_ptr(), k[6].data_ptr(), k[7].data_ptr(), k[8].data_ptr(), k[9].data_ptr()
+        a.W3, a.b3 = k[10].data_ptr(), k[11].data_ptr()
+        a.packed = self.packed.data_ptr()
+        return a
+
+    def __call__(self, user, q, k, att, requests, n_cand, T, out=None):
+        """user [R, du], q / att [R*n_cand, d], k [R*T, d] fp16 -> probabilities [R*n_cand, n3] fp32."""
+        if out is None:
+            out = torch.empty((requests * n_cand, self.n3), dtype=torch.float32, device=q.device)
+        need = lib().xb_din_tower_workspace_bytes(requests, self.d, self.n1)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+        a = self._args()
+        a.user, a.ldu, a.q, a.ldq = user.data_ptr(), user.stride(0), q.data_ptr(), q.stride(0)
+        a.k, a.ldk, a.att, a.ldatt = k.data_ptr(), k.stride(0), att.data_ptr(), att.stride(0)
+        a.prob, a.requests, a.n_cand, a.T = out.data_ptr(), requests, n_cand, T
+        check(lib().xb_din_tower(C.byref(a), ptr(self._ws), self._ws.numel(), stream()))
+        return out
