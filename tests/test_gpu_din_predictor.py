@@ -9,14 +9,15 @@ import pkg
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("fused_tower", [True, False])
 @pytest.mark.parametrize("emb_sigma,seq", [(0.5, None), (0.5, [100, 17, 0]), (0.01, None)])
-def test_predictor_din_matches_oracle(emb_sigma, seq):
+def test_predictor_din_matches_oracle(emb_sigma, seq, fused_tower):
     pkg.load()
     from x_deeplearning_b200 import blaze_api as api, din_netdef, workloads
     model = workloads.din_model(0, item_rows=20000, cate_rows=500, user_rows=3000, emb_sigma=emb_sigma)
     req = workloads.din_requests(model, 2, requests=3, n_cand=200, seq_len=seq)
     want = din_oracle.forward(model, req)
-    text, feed_names = din_netdef.build(model)
+    text, feed_names = din_netdef.build(model, fused_tower=fused_tower)
     mgr = api.PredictorManager()
     din_netdef.register_tables(mgr, model)
     mgr.load_model_text(text, optimize=True)
@@ -34,8 +35,9 @@ def test_predictor_din_matches_oracle(emb_sigma, seq):
     p.forward()
     got2 = p.output("output").astype(np.float32)
     assert np.abs(got2 - din_oracle.forward(model, req2)).max() <= 2e-3
-    # pooling (scan + pool) x2, 2 concat copies, attention, tower input, 3 gemm, softmax
-    assert p.launches() == 13, p.launches()
+    # pooling (scan + pool) x2, 2 concat copies, attention, then the two tower kernels or, op by op,
+    # tower input, pruned product (2 launches), 2 gemm, softmax
+    assert p.launches() == (9 if fused_tower else 13), p.launches()
     p.close()
     mgr.close()
 

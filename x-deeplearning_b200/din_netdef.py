@@ -23,8 +23,10 @@ def _item(fg, udf, trunc_num=None):
     return '  embedding_block_config_item { feature_group: "%s" udf_type: %d%s }\n' % (fg, udf, extra)
 
 
-def build(model):
-    """Returns (netdef_text, input_names) for `model` (workloads.din_model)."""
+def build(model, fused_tower=True):
+    """Returns (netdef_text, input_names) for `model` (workloads.din_model). With `fused_tower` the tower is
+    the single DinTower operator (output fp32); without it the tower stays a chain of reference operators
+    (DinTowerInput, PrunedGemm, Dice, Gemm, Dice, Gemm, Softmax; output fp16)."""
     D = model["dims"]
     e, d, T, G = D["emb"], D["d"], D["T"], D["user_groups"]
     users = ["u%d" % g for g in range(G)]
@@ -50,10 +52,24 @@ def build(model):
         ops.append(api.constant_text("att_" + n, a[n], F16))
         names.append("att_" + n)
     ops.append(api.op_text("DinAttention", ["ad_emb", "his_emb"] + names, ["att"], {"act": 2}))
+    tw = model["tower"]
+    feeds = []
+    for n in users + ["mid_list", "cat_list", "mid", "cat"]:
+        feeds += [(n + ".ids", I64), (n + ".values", F16), (n + ".segments", I32)]
+    if fused_tower:
+        consts = []
+        for i, key in ((1, "dice1"), (2, "dice2"), (3, None)):
+            group = [("W%d" % i, tw["W%d" % i]), ("b%d" % i, tw["b%d" % i])]
+            if key:
+                group += [("%s%d" % (n, i), arr) for n, arr in zip(("g", "m", "v"), tw[key])]
+            for name, arr in group:
+                ops.append(api.constant_text("t_" + name, arr, F16))
+                consts.append("t_" + name)
+        ops.append(api.op_text("DinTower", ["uid_emb", "ad_emb", "his_emb", "att"] + consts, ["output"]))
+        return api.netdef_text(ops, feeds, [("output", F32)], name="din"), [n for n, _ in feeds]
     # first tower layer as a PrunedGemm: the columns that are equal for all candidates of a request
     # ([user | his_sum]) are one operand, the per-candidate columns the other
     ops.append(api.op_text("DinTowerInput", ["uid_emb", "ad_emb", "his_emb", "att"], ["tower_user", "tower_cand"]))
-    tw = model["tower"]
     from .din import split_tower_rows
     rows_u, rows_c = split_tower_rows(G * e, d)
 
@@ -74,9 +90,6 @@ def build(model):
     ops.append(api.op_text("Dice", ["h2", "t_g2", "t_m2", "t_v2"], ["y2"]))
     ops.append(api.op_text("Gemm", ["y2", "t_W3", "t_b3"], ["logit"]))
     ops.append(api.op_text("Softmax", ["logit"], ["output"], {"axis": 1}))
-    feeds = []
-    for n in users + ["mid_list", "cat_list", "mid", "cat"]:
-        feeds += [(n + ".ids", I64), (n + ".values", F16), (n + ".segments", I32)]
     return api.netdef_text(ops, feeds, [("output", F16)], name="din"), [n for n, _ in feeds]
 
 

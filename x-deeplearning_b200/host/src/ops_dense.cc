@@ -773,6 +773,73 @@ class DinTowerInputOp final : public Operator<CUDAContext> {
   }
   int ld_;
 };
+// DinTower: the whole tower of the DIN-style model as one operator - feature assembly, Gemm + Dice twice,
+// the output Gemm and Softmax - computed by the fused tcgen05 tower kernel.
+// Inputs: uid_emb [R, du], ad_emb [R*n, d], his_emb [R, T, d], att [R*n, d], then the constants
+// W1 [du+5d, n1], b1, gamma1, mean1, var1, W2 [n1, n2], b2, gamma2, mean2, var2, W3 [n2, n3], b3.
+class DinTowerOp final : public Operator<CUDAContext> {
+ public:
+  DinTowerOp(const OperatorDef& def, Workspace* ws) : Operator<CUDAContext>(def, ws) {
+    softmax_ = GetSingleArgument<bool>("softmax", true);
+  }
+  bool RunOnDevice() override {
+    Blob *u = Input(0), *q = Input(1), *k = Input(2), *att = Input(3), *y = Output(0);
+    for (int i = 0; i < 4; ++i) BLAZE_CONDITION_THROW(Input(i)->data_type() == kFloat16, "DinTower needs fp16 inputs");
+    BLAZE_CONDITION_THROW(k->shape().size() == 3 && u->shape().size() == 2, "DinTower: his_emb [R,T,d], uid_emb [R,du]");
+    const int R = (int)k->shape()[0], T = (int)k->shape()[1], d = (int)k->shape()[2], du = (int)u->shape()[1];
+    const int n_cand = (int)(q->size() / ((size_t)R * d));
+    Blob *W1 = Input(4), *W2 = Input(9), *W3 = Input(14);
+    for (Blob* w : {W1, W2, W3})
+      BLAZE_CONDITION_THROW(w->shape().size() == 2 && w->data_type() == kFloat16 && w->is_constant,
+                            "DinTower: weights must be fp16 rank-2 constants");
+    const int n1 = (int)W1->shape()[1], n2 = (int)W2->shape()[1], n3 = (int)W3->shape()[1];
+    BLAZE_CONDITION_THROW(W1->shape()[0] == (TIndex)(du + 5 * d) && W2->shape()[0] == (TIndex)n1 && W3->shape()[0] == (TIndex)n2,
+                          "DinTower: weight shapes do not chain: ", W1->shape()[0], "x", n1, ", ", W2->shape()[0], "x", n2,
+                          ", ", W3->shape()[0], "x", n3);
+    cudaStream_t s = context_.cuda_stream();
+    xb_din_tower_args a;
+    memset(&a, 0, sizeof(a));
+    a.d = d; a.du = du; a.n1 = n1; a.n2 = n2; a.n3 = n3; a.softmax = softmax_;
+    a.W1 = W1->as<void>(); a.W2 = W2->as<void>(); a.W3 = W3->as<void>();
+    a.b1 = AsF32(Input(5), &f_[0], s, &launches);
+    a.gamma1 = AsF32(Input(6), &f_[1], s, &launches); a.mean1 = AsF32(Input(7), &f_[2], s, &launches);
+    a.var1 = AsF32(Input(8), &f_[3], s, &launches);
+    a.b2 = AsF32(Input(10), &f_[4], s, &launches);
+    a.gamma2 = AsF32(Input(11), &f_[5], s, &launches); a.mean2 = AsF32(Input(12), &f_[6], s, &launches);
+    a.var2 = AsF32(Input(13), &f_[7], s, &launches);
+    a.b3 = AsF32(Input(15), &f_[8], s, &launches);
+    if (!image_) {
+      const size_t n = xb_din_tower_packed_bytes(d, n1, n2, n3);
+      BLAZE_CONDITION_THROW(n != 0, "DinTower: d=", d, " n1=", n1, " n2=", n2, " n3=", n3, " is outside the fused tower kernel");
+      image_.reset(new Blob(device_option_));
+      image_->set_data_type(kFloat);
+      image_->Reshape({(TIndex)((n + 3) / 4)});
+      XB_CHECK(xb_din_tower_pack(&a, image_->as<void>(), n, s));
+      ++launches;
+    }
+    a.packed = image_->as<void>();
+    const size_t wbytes = xb_din_tower_workspace_bytes(R, d, n1);
+    if (!scratch_) scratch_.reset(new Blob(device_option_));
+    scratch_->set_data_type(kFloat);
+    scratch_->Reshape({(TIndex)((wbytes + 3) / 4)});
+    y->set_data_type(kFloat);
+    y->Reshape({(TIndex)R * n_cand, (TIndex)n3});
+    a.user = u->as<void>(); a.ldu = du; a.q = q->as<void>(); a.ldq = d; a.k = k->as<void>(); a.ldk = d;
+    a.att = att->as<void>(); a.ldatt = d; a.prob = y->as<float>();
+    a.requests = R; a.n_cand = n_cand; a.T = T;
+    XB_CHECK(xb_din_tower(&a, scratch_->as<void>(), wbytes, s));
+    launches += 2;
+    return true;
+  }
+
+ private:
+  bool softmax_;
+  Derived f_[9];
+  std::unique_ptr<Blob> image_, scratch_;
+};
+REGISTER_CUDA_OPERATOR(DinTower, DinTowerOp);
+OPERATOR_SCHEMA(DinTower).NumInputs(16).NumOutputs(1);
+
 REGISTER_CUDA_OPERATOR(DinTowerInput, DinTowerInputOp);
 OPERATOR_SCHEMA(DinTowerInput).NumInputs(4).NumOutputs(1, 2);
 
