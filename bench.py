@@ -392,6 +392,15 @@ def run_micro(args):
         t0.record()
         for _ in range(reps):
             net.att(p["q"], p["k"].view(-1, 36), p["R"], N_CAND, T_STEPS, out=p["att"])
+    elif args.micro == "tower":
+        model = workloads.din_model(seed=0, item_rows=200_000, cate_rows=10_000, user_rows=10_000, emb_sigma=0.5)
+        net = din.DinModel(model)
+        p = net.upload(net.stage(workloads.din_requests(model, 3, args.requests, N_CAND)))
+        net.forward_device(p)
+        torch.cuda.synchronize()
+        t0.record()
+        for _ in range(reps):
+            net.tower(p["user_emb"], p["q"], p["k"].view(-1, 36), p["att"], p["R"], N_CAND, T_STEPS, out=p["prob"])
     elif args.micro == "pool":
         cfg = workloads.embedding_config(seed=0, batch=65536)
         table = ops.Table(torch.from_numpy(cfg["table"]), torch.float32)
@@ -523,7 +532,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and pooling side measurements")
     ap.add_argument("--table-rows", type=int, default=200_000_000, help="rows per table of --micro sharded")
-    ap.add_argument("--micro", choices=["att", "pool", "gemm", "sharded"], help="run --steps launches of one kernel on a small case "
+    ap.add_argument("--micro", choices=["att", "pool", "gemm", "tower", "sharded"], help="run --steps launches of one kernel on a small case "
                     "(for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     if args.micro == "sharded":

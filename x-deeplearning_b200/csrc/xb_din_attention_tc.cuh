@@ -64,7 +64,7 @@ __host__ __device__ inline TcGeom tc_geom(int d, int h0, int h1, int T) {
 }
 
 struct TcSmemLayout {
-  int w0, w1, s, kt, kh, c1, c2, total;
+  int w0, w1, s, kt, kh, q, c1, c2, total;
 };
 __host__ __device__ inline TcSmemLayout tc_layout(const TcGeom& g, int T) {
   TcSmemLayout L;
@@ -74,6 +74,8 @@ __host__ __device__ inline TcSmemLayout tc_layout(const TcGeom& g, int T) {
   L.s = off; off += 128 * g.tp * 2;             // scores [128, tp]
   L.kt = off; off += g.np * g.tp * 2;           // K^T operand [np rows (feature), tp (step)]
   L.kh = off; off += T * g.dp * 2;              // k rows for building A1
+  off = (off + 15) / 16 * 16;
+  L.q = off; off += 128 * g.dp * 2;             // q rows of the tile, chunk-major
   off = (off + 15) / 16 * 16;
   L.c1 = off; off += (g.h0p / 2) * 16;          // per column pair: A, B, C, D as half2
   L.c2 = off; off += (g.h1p / 2) * 16;
@@ -190,31 +192,63 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   __half* ss = reinterpret_cast<__half*>(smem + L.s);
   __half* kts = reinterpret_cast<__half*>(smem + L.kt);
   __half* khs = reinterpret_cast<__half*>(smem + L.kh);
+  __half* qs = reinterpret_cast<__half*>(smem + L.q);
   uint4* c1 = reinterpret_cast<uint4*>(smem + L.c1);
   uint4* c2 = reinterpret_cast<uint4*>(smem + L.c2);
   const __half zero = __float2half(0.f), one = __float2half(1.f);
 
   // ---- prologue: operands that stay resident for the whole tile ----------------------------
+  // Everything that comes from global memory is requested with asynchronous copies first (weight image,
+  // k rows of the request, q rows of the tile), so the latencies overlap instead of adding up.
+  const bool async8 = (d % 4 == 0) && (p.ldq % 4 == 0) && (p.ldk % 4 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k)) & 7) == 0;
   if (p.packed) {
-    // weight operands were laid out once by xb_din_attention_pack: straight 16-byte copies
-    const uint4* src = reinterpret_cast<const uint4*>(p.packed);
-    const int n01 = (h0p * k1 * 2 + h1p * k2 * 2) / 16;                 // W0 and W1 images are adjacent
-    for (int i = threadIdx.x; i < n01; i += TC_THREADS) reinterpret_cast<uint4*>(smem + L.w0)[i] = __ldg(src + i);
-    for (int i = threadIdx.x; i < h0p / 2 + h1p / 2; i += TC_THREADS) c1[i] = __ldg(src + n01 + i);   // c2 follows c1
+    // weight operands were laid out once by xb_din_attention_pack: W0, W1, c1, c2 are adjacent
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.packed);
+    const int n01 = (h0p * k1 * 2 + h1p * k2 * 2) / 16;
+    for (int i = threadIdx.x; i < n01; i += TC_THREADS) cp_async16(smem + L.w0 + 16 * i, src + 16 * i);
+    for (int i = threadIdx.x; i < h0p / 2 + h1p / 2; i += TC_THREADS) cp_async16(c1 + i, src + 16 * (n01 + i));
   } else {
     pack_weights<ACT>(p, G, w0s, w1s, c1, c2, threadIdx.x, TC_THREADS);
   }
+  if (async8) {
+    const int ppr = d / 4;                                   // 8-byte pieces per row
+    const __half* kreq = p.k + (int64_t)r * p.T * p.ldk;
+    for (int idx = threadIdx.x; idx < p.T * ppr; idx += TC_THREADS) {
+      const int t = idx / ppr, pc = idx - t * ppr;
+      cp_async8(khs + t * dp + pc * 4, kreq + (int64_t)t * p.ldk + pc * 4);
+    }
+    const int rows = min(128, p.n_cand - tile * 128);
+    const __half* qreq = p.q + ((int64_t)r * p.n_cand + tile * 128) * p.ldq;
+    for (int idx = threadIdx.x; idx < rows * ppr; idx += TC_THREADS) {
+      const int row = idx / ppr, pc = idx - row * ppr;
+      cp_async8(qs + ((pc >> 1) * 128 + row) * 8 + (pc & 1) * 4, qreq + (int64_t)row * p.ldq + pc * 4);
+    }
+  }
+  cp_async_commit();
+  // what no copy writes: padding columns, rows past the last candidate, the constant-1 column, S
+  for (int idx = threadIdx.x; idx < 128 * dp; idx += TC_THREADS) {
+    const int row = idx / dp, i = idx - row * dp;
+    const bool have = i < d && tile * 128 + row < p.n_cand;
+    __half* dst = &qs[(i >> 3) * (128 * 8) + row * 8 + (i & 7)];
+    if (!async8) *dst = have ? p.q[((int64_t)r * p.n_cand + tile * 128 + row) * p.ldq + i] : (i == G.ones1 ? one : zero);
+    else if (!have) *dst = (i == G.ones1) ? one : zero;
+  }
   for (int idx = threadIdx.x; idx < p.T * dp; idx += TC_THREADS) {
     const int t = idx / dp, i = idx - t * dp;
-    khs[idx] = (i < d) ? p.k[((int64_t)r * p.T + t) * p.ldk + i] : zero;
-  }
-  for (int idx = threadIdx.x; idx < np * tp; idx += TC_THREADS) {
-    const int e = idx / tp, t = idx - e * tp;
-    const __half v = (e < d && t < tl) ? p.k[((int64_t)r * p.T + t) * p.ldk + e] : zero;
-    kts[(t >> 3) * (np * 8) + e * 8 + (t & 7)] = v;
+    if (!async8) khs[idx] = (i < d) ? p.k[((int64_t)r * p.T + t) * p.ldk + i] : zero;
+    else if (i >= d) khs[idx] = zero;
   }
   for (int idx = threadIdx.x; idx < 128 * tp / 8; idx += TC_THREADS)
     reinterpret_cast<uint4*>(ss)[idx] = make_uint4(0, 0, 0, 0);
+  cp_async_wait_all();
+  __syncthreads();
+  // K^T operand of the closing product, from the k rows now in shared memory
+  for (int idx = threadIdx.x; idx < np * tp; idx += TC_THREADS) {
+    const int t = idx / np, e = idx - t * np;
+    const __half v = (e < d && t < tl) ? khs[t * dp + e] : zero;
+    kts[(t >> 3) * (np * 8) + e * 8 + (t & 7)] = v;
+  }
   // barriers, per accumulator/operand buffer b = step & 1:
   //   a1_full[b]   4 builder warps       -> MMA warp: A1 of a step is in shared memory
   //   acc1_full[b] tcgen05.commit        -> both warpgroups: layer-1 accumulator complete
@@ -381,20 +415,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     // q row as 16-byte chunks (dp <= 64 -> at most 8), with the constant-1 column when it lives here
     uint4 qv[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      __half h[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int i = c * 8 + e;
-        __half v = zero;
-        if (c < nch) {
-          if (i < d) v = valid ? p.q[((int64_t)r * p.n_cand + n) * p.ldq + i] : zero;
-          else if (i == G.ones1) v = one;
-        }
-        h[e] = v;
-      }
-      qv[c] = *reinterpret_cast<uint4*>(h);
-    }
+    for (int c = 0; c < 8; ++c)
+      qv[c] = c < nch ? *reinterpret_cast<const uint4*>(qs + (c * 128 + row) * 8) : make_uint4(0, 0, 0, 0);
     // constant part of this parity's A1 buffer: the q segment (and the ones column)
     // (chunk c of 8 fp16 is 4 tensor-memory columns of this thread's lane)
     {

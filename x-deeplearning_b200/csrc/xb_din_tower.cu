@@ -90,14 +90,11 @@ struct TowerParams {
 __device__ __forceinline__ uint32_t h2u(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __half2 u2h(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
 
-__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(umma::smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(umma::smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+using umma::cp_async16;
+using umma::cp_async4;
+using umma::cp_async8;
+using umma::cp_async_commit;
+using umma::cp_async_wait_all;
 
 // ---- once per model: weight operands, activation constants ---------------------------------------
 __global__ void tower_pack_kernel(const __grid_constant__ TowerParams p, uint8_t* dst) {
@@ -201,12 +198,13 @@ __global__ void __launch_bounds__(TW_THREADS, 1) din_tower_tc_kernel(const __gri
   const int d = p.d, dp = G.dp, nch = G.nch, n1p = G.n1p, n2p = G.n2p, n3 = p.n3;
   const int64_t total_tiles = (int64_t)p.requests * p.tiles_per_req;
 
-  // weight image: straight 16-byte copies
+  // weight image: asynchronous 16-byte copies, all in flight at once
   {
-    const uint4* src = reinterpret_cast<const uint4*>(p.packed);
-    for (int i = threadIdx.x; i < G.image_bytes / 16; i += TW_THREADS) reinterpret_cast<uint4*>(smem)[i] = __ldg(src + i);
+    for (int i = threadIdx.x; i < G.image_bytes / 16; i += TW_THREADS) cp_async16(smem + 16 * i, p.packed + 16 * i);
+    cp_async_commit();
     for (int i = threadIdx.x; i < (G.total - G.image_bytes) / 16; i += TW_THREADS)
       reinterpret_cast<uint4*>(smem + G.image_bytes)[i] = make_uint4(0, 0, 0, 0);     // padding columns stay zero
+    cp_async_wait_all();
   }
   uint64_t* a1_full = &bars[0];
   uint64_t* acc1_full = &bars[1];
