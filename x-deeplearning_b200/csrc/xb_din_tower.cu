@@ -154,14 +154,18 @@ __global__ void tower_pack_kernel(const __grid_constant__ TowerParams p, uint8_t
 
 // ---- once per launch: his_sum and the per-request product of layer 1 -------------------------------
 // partial[r][n] = b1[n] + sum_c user[r][c] * W1[c][n] + sum_e fp16(his_sum[r][e]) * W1[du+d+e][n]
-// One CTA per request; the T steps are split over groups of d threads and added in group order.
-__global__ void __launch_bounds__(256) din_tower_partial_kernel(const __grid_constant__ TowerParams p) {
-  extern __shared__ float sm[];            // [d] his_sum, [du] user row, [G][d] partial sums
+// One CTA per (request, 64 output columns): 4 groups of 64 threads split the du + d weight rows, sixteen
+// independent loads in flight per thread; the group sums are added in group order. his_sum: the T steps
+// are split over groups of d threads and added in group order.
+constexpr int PT_COLS = 64, PT_SLICES = 4;
+__global__ void __launch_bounds__(PT_COLS * PT_SLICES) din_tower_partial_kernel(const __grid_constant__ TowerParams p) {
+  extern __shared__ float sm[];            // [d] his_sum, [du] user row, [G][d] step sums, [PT_SLICES][PT_COLS]
   const int r = blockIdx.x, d = p.d, du = p.du;
   float* hs = sm;
   float* us = hs + d;
   float* part = us + du;
   const int G = max(1, min((int)blockDim.x / d, 8));
+  float* colsum = part + 8 * d;
   if ((int)threadIdx.x < G * d) {
     const int gi = threadIdx.x / d, e = threadIdx.x - gi * d;
     float s = 0.f;
@@ -176,14 +180,37 @@ __global__ void __launch_bounds__(256) din_tower_partial_kernel(const __grid_con
     // his_sum is an fp16 tensor in the model's graph: every use sees the rounded value
     s = __half2float(__float2half_rn(s));
     hs[e] = s;
-    p.hs[(int64_t)r * d + e] = s;
+    if (blockIdx.y == 0) p.hs[(int64_t)r * d + e] = s;
   }
   __syncthreads();
-  for (int n = threadIdx.x; n < p.n1; n += blockDim.x) {
-    float acc = p.b1 ? p.b1[n] : 0.f;
-    for (int c = 0; c < du; ++c) acc = fmaf(us[c], __half2float(p.W1[(int64_t)c * p.n1 + n]), acc);
-    for (int e = 0; e < d; ++e) acc = fmaf(hs[e], __half2float(p.W1[(int64_t)(du + d + e) * p.n1 + n]), acc);
-    p.partial[(int64_t)r * p.n1 + n] = acc;
+  // weight rows 0..du-1 meet the user row, rows du+d..du+2d-1 meet his_sum; x(c) is the matching input
+  const int col = threadIdx.x % PT_COLS, slice = threadIdx.x / PT_COLS;
+  const int n = blockIdx.y * PT_COLS + col;
+  const int rows = du + d, per = (rows + PT_SLICES - 1) / PT_SLICES;
+  const int c_begin = slice * per, c_end = min(rows, c_begin + per);
+  float acc = 0.f;
+  if (n < p.n1) {
+    for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+      __half w[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int c = c0 + u;
+        const int wr = c < du ? c : c + d;               // skip the q rows of W1
+        w[u] = c < c_end ? p.W1[(int64_t)wr * p.n1 + n] : __float2half(0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int c = c0 + u;
+        if (c < c_end) acc = fmaf(c < du ? us[c] : hs[c - du], __half2float(w[u]), acc);
+      }
+    }
+  }
+  colsum[slice * PT_COLS + col] = acc;
+  __syncthreads();
+  if (slice == 0 && n < p.n1) {
+    float s = p.b1 ? p.b1[n] : 0.f;
+    for (int g = 0; g < PT_SLICES; ++g) s += colsum[g * PT_COLS + col];
+    p.partial[(int64_t)r * p.n1 + n] = s;
   }
 }
 
@@ -556,7 +583,9 @@ extern "C" int xb_din_tower(const xb_din_tower_args* a, void* workspace, size_t 
   const TowerGeom g = tower_geom(a->d, a->n1, a->n2, a->n3);
   p.idesc1 = umma::make_idesc(128, g.n1p, 0);
   p.idesc2 = umma::make_idesc(128, g.n2p, 0);
-  din_tower_partial_kernel<<<a->requests, 256, sizeof(float) * (9 * a->d + a->du + 2), stream>>>(p);
+  XB_REQUIRE(a->requests <= 65535 * 32, XB_ERR_LIMIT, "xb_din_tower: too many requests per call");
+  din_tower_partial_kernel<<<dim3(a->requests, (a->n1 + PT_COLS - 1) / PT_COLS), PT_COLS * PT_SLICES,
+                             sizeof(float) * (9 * a->d + a->du + PT_COLS * PT_SLICES + 2), stream>>>(p);
   if (int rc = check_launch("din_tower_partial_kernel")) return rc;
   static bool attr_set = false;
   if (!attr_set) {
