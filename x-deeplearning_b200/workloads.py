@@ -100,6 +100,29 @@ def din_model(seed=0, item_rows=5_000_000, cate_rows=10_000, user_rows=100_000, 
     return m
 
 
+def dien_model(seed=0, **kw):
+    """Random-init DIEN-style model: the DIN tables, a GRU over the behaviour rows (hidden 36), an attention
+    MLP 144-80-40-1 with sigmoid activations scoring every GRU state against the candidate, an AUGRU gated
+    by those scores, and a final MLP [user | q | his_sum | q*his_sum | final state] -> 200 -> 80 -> 2 with PReLU."""
+    m = din_model(seed, **kw)
+    rng = np.random.default_rng(seed + 7)
+    D = m["dims"]
+    H = D["d"]
+
+    def w(k, n, scale=1.0):
+        return fp16_round(rng.normal(0, scale / np.sqrt(k), (k, n)))
+    m["gru"] = dict(i2h=w(H, 3 * H), h2h=w(H, 3 * H), i2h_bias=fp16_round(rng.normal(0, 0.05, 3 * H)),
+                    h2h_bias=fp16_round(rng.normal(0, 0.05, 3 * H)))
+    m["augru"] = dict(Wg=w(2 * H, 2 * H), bg=fp16_round(rng.normal(0, 0.05, 2 * H)), Wc=w(2 * H, H),
+                      bc=fp16_round(rng.normal(0, 0.05, H)))
+    tin = D["user_groups"] * D["emb"] + 4 * H
+    t1, t2, t3 = D["tower"]
+    m["dien_tower"] = dict(W1=w(tin, t1), b1=fp16_round(rng.normal(0, 0.01, t1)), W2=w(t1, t2),
+                           b2=fp16_round(rng.normal(0, 0.01, t2)), W3=w(t2, t3), b3=fp16_round(rng.normal(0, 0.01, t3)),
+                           slope1=fp16_round(rng.uniform(0.1, 0.4, t1)), slope2=fp16_round(rng.uniform(0.1, 0.4, t2)))
+    return m
+
+
 def din_requests(model, seed, requests, n_cand=1000, s=1.1, seq_len=None):
     """`requests` requests of one user and n_cand candidate items each."""
     rng = np.random.default_rng(seed)
