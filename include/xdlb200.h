@@ -253,6 +253,9 @@ int xb_pack_weight_kmajor(const void* W, int32_t w_dtype, int32_t K, int32_t N, 
  *   out[n] = sum_t s[n,t] * k[t]     (optionally masked softmax over t first).
  * The 4d-wide concat is built in shared memory and never written to HBM. */
 enum { XB_ACT_NONE = 0, XB_ACT_SIGMOID = 1, XB_ACT_DICE = 2 };
+/* `engine` of xb_din_att_args takes XB_GEMM_AUTO / XB_GEMM_SIMT / XB_GEMM_TCGEN05 or this value: the tcgen05
+ * engine that regroups layer 1 as q x (Wq + Wd + diag(k_t) Wp) and runs two steps per MMA (needs `packed`). */
+enum { XB_ATT_ENGINE_PAIR = 3 };
 
 typedef struct xb_din_att_weights {
   /* K-major packed fp16 weights: W0 [h0, 4d], W1 [h1, h0]; W2 fp32 [h1] */

@@ -130,6 +130,7 @@ __global__ void __launch_bounds__(SIMT_THREADS) din_att_simt_kernel(const __grid
 }  // namespace xb
 
 #include "xb_din_attention_tc.cuh"
+#include "xb_din_attention_pair.cuh"
 
 namespace xb {
 
@@ -167,6 +168,16 @@ extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
   p.packed = a->w.packed;
 
   int why = 0;
+  // The packed image holds the per-step engine's operands first and, when the shape allows, the step-pair
+  // engine's after them. The step-pair engine runs on request only: it halves the tensor-pipe time but both
+  // engines end up bound by the activation math, and it rounds in different places.
+  if (a->engine == XB_ATT_ENGINE_PAIR) {
+    XB_REQUIRE(a->w.packed && pair_image_wanted(a->d, a->h0, a->h1) && pair_eligible(*a, &why), XB_ERR_UNSUPPORTED,
+               "xb_din_attention: shape outside the step-pair engine (reason %d; it needs packed weights)", why);
+    const size_t first = tc_eligible_shape(a->d, a->h0, a->h1) ? att_packed_bytes(a->d, a->h0, a->h1) : 0;
+    p.packed = (const char*)a->w.packed + (first + 15) / 16 * 16;
+    return launch_att_pair(p, *a, stream);
+  }
   const bool tc = a->engine != XB_GEMM_SIMT && tc_eligible(*a, &why);
   XB_REQUIRE(tc || a->engine != XB_GEMM_TCGEN05, XB_ERR_UNSUPPORTED,
              "xb_din_attention: shape outside the tcgen05 engine (reason %d)", why);
@@ -186,11 +197,10 @@ extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
 
 extern "C" size_t xb_din_attention_packed_bytes(int32_t d, int32_t h0, int32_t h1) {
   if (d <= 0 || h0 <= 0 || h1 <= 0) return 0;
-  xb_din_att_args a;
-  memset(&a, 0, sizeof(a));
-  a.d = d; a.h0 = h0; a.h1 = h1; a.T = 16;
-  if (!tc_eligible(a, nullptr)) return 0;
-  return att_packed_bytes(d, h0, h1);
+  size_t n = 0;
+  if (tc_eligible_shape(d, h0, h1)) n += (att_packed_bytes(d, h0, h1) + 15) / 16 * 16;
+  if (pair_image_wanted(d, h0, h1)) n += att_pair_packed_bytes(d, h0, h1);
+  return n;
 }
 
 extern "C" int xb_din_attention_pack(const xb_din_att_args* a, void* packed, size_t bytes, xb_stream_t stream) {
@@ -208,5 +218,18 @@ extern "C" int xb_din_attention_pack(const xb_din_att_args* a, void* packed, siz
   p.b0 = a->w.b0; p.b1 = a->w.b1; p.b2 = a->w.b2;
   p.g0 = a->w.gamma0; p.m0 = a->w.mean0; p.v0 = a->w.var0;
   p.g1 = a->w.gamma1; p.m1 = a->w.mean1; p.v1 = a->w.var1;
-  return launch_att_pack(p, a->act, packed, (cudaStream_t)stream);
+  size_t first = 0;
+  if (tc_eligible_shape(a->d, a->h0, a->h1)) {
+    if (int rc = launch_att_pack(p, a->act, packed, (cudaStream_t)stream)) return rc;
+    first = (att_packed_bytes(a->d, a->h0, a->h1) + 15) / 16 * 16;
+  }
+  if (pair_image_wanted(a->d, a->h0, a->h1))
+    return launch_att_pair_pack(p, a->act, (char*)packed + first, (cudaStream_t)stream);
+  return 0;
 }
+
+#ifdef XB_ATT_TRACE
+extern "C" int xb_debug_att_trace(long long* dst) {
+  return (int)cudaMemcpyFromSymbol(dst, xb::g_att_trace, sizeof(long long) * 6 * 128 * 12);
+}
+#endif

@@ -568,6 +568,14 @@ bool tc_eligible(const xb_din_att_args& a, int* why) {
   return true;
 }
 
+// the part of tc_eligible that depends on the weights' shape only
+bool tc_eligible_shape(int d, int h0, int h1) {
+  xb_din_att_args a;
+  memset(&a, 0, sizeof(a));
+  a.d = d; a.h0 = h0; a.h1 = h1; a.T = 16;
+  return tc_eligible(a, nullptr);
+}
+
 size_t att_packed_bytes(int d, int h0, int h1) {
   const TcGeom g = tc_geom(d, h0, h1, 16);
   return (size_t)g.h0p * g.k1 * 2 + (size_t)g.h1p * g.k2 * 2 + (size_t)(g.h0p / 2 + g.h1p / 2) * 16;
