@@ -71,3 +71,4 @@ def test_ragged_and_empty_sequences(engine):
 def test_other_dims(engine):
     _case(engine, R=1, n_cand=129, T=33, d=16, h0=32, h1=16, act=0, softmax=False, seed=3)
     _case(engine, R=1, n_cand=5, T=3, d=20, h0=48, h1=24, act=2, softmax=False, seed=4)
+    _case(engine, R=2, n_cand=140, T=11, d=18, h0=32, h1=16, act=1, softmax=False, seed=5)    # d not a multiple of 4

@@ -507,11 +507,18 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
       __half2 part[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) part[e] = __floats2half2_rn(0.f, 0.f);
-      for (int c = 0; c < h1p; c += 16) {
-        uint32_t v[16];
-        tmem_ld16_nowait(acc2 + c, v);
+      // blocks of 16 columns; the next block's load is in flight while this one is activated
+      const int nblk2 = h1p / 16;
+      uint32_t va[16], vb[16];
+      auto block2 = [&](int blk, uint32_t (&v)[16], uint32_t (&nxt)[16]) {
         tmem_wait_ld(v);
-        const uint4* __restrict__ cc = c2 + (c >> 1);
+        if (blk + 1 < nblk2) tmem_ld16_nowait(acc2 + 16 * (blk + 1), nxt);
+        else {
+          tc_fence_before_sync();                  // the accumulator is in registers
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&acc2_free[b]));
+        }
+        const uint4* __restrict__ cc = c2 + 8 * blk;
         uint32_t x[8], th[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e)
@@ -520,13 +527,10 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
 #pragma unroll
           for (int e = 0; e < 8; ++e) part[e & 3] = __hfma2(bits_h2(x[e]), bits_h2(cc[e].z), part[e & 3]);
         } else {
-          const int live = npairs2 - (c >> 1);           // column pairs of this block that are not padding
+          const int live = npairs2 - 8 * blk;            // column pairs of this block that are not padding
 #pragma unroll
           for (int e = 0; e < 8; ++e)
-            if (e < live) th[e] = h2_bits(__hfma2(bits_h2(x[e]), bits_h2(cc[e].x), bits_h2(cc[e].y)));
-#pragma unroll
-          for (int e = 0; e < 8; ++e)
-            if (e < live) th[e] = tanh_f16x2(th[e]);
+            if (e < live) th[e] = tanh_f16x2(h2_bits(__hfma2(bits_h2(x[e]), bits_h2(cc[e].x), bits_h2(cc[e].y))));
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             if (e < live) {
@@ -535,10 +539,12 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
             }
           }
         }
+      };
+      tmem_ld16_nowait(acc2, va);
+      for (int blk = 0; blk < nblk2; blk += 2) {
+        block2(blk, va, vb);
+        if (blk + 1 < nblk2) block2(blk + 1, vb, va);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&acc2_free[b]));
       if ((warp & 3) == 0) ATT_TRACE(2 + wb, j, 11);
       const float2 f0 = __half22float2(part[0]), f1 = __half22float2(part[1]);
       const float2 f2 = __half22float2(part[2]), f3 = __half22float2(part[3]);

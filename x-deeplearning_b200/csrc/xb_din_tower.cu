@@ -566,7 +566,8 @@ extern "C" int xb_din_tower_pack(const xb_din_tower_args* a, void* packed, size_
 extern "C" int xb_din_tower(const xb_din_tower_args* a, void* workspace, size_t workspace_bytes, xb_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (int rc = validate_tower(a, "xb_din_tower")) return rc;
-  XB_REQUIRE(a->user && a->q && a->k && a->att && a->prob && a->packed, XB_ERR_ARG, "xb_din_tower: null tensor");
+  XB_REQUIRE((a->user || a->du == 0) && a->q && a->k && a->att && a->prob && a->packed, XB_ERR_ARG,
+             "xb_din_tower: null tensor");
   XB_REQUIRE(a->requests >= 0 && a->n_cand >= 0 && a->T >= 0, XB_ERR_ARG, "xb_din_tower: negative size");
   XB_REQUIRE(a->ldu >= a->du && a->ldq >= a->d && a->ldk >= a->d && a->ldatt >= a->d, XB_ERR_ARG,
              "xb_din_tower: leading dimension too small");

@@ -53,6 +53,9 @@ struct ScanParams {
   const int32_t* counts[XB_MAX_POOL_GROUPS];
   int32_t* offsets[XB_MAX_POOL_GROUPS];
   int64_t batch[XB_MAX_POOL_GROUPS];
+  // multi-CTA form: chunks of SCAN_THREADS * SCAN_ITEMS counts, numbered across the groups
+  int32_t* chunk_sums[XB_MAX_POOL_GROUPS];
+  int32_t chunk_begin[XB_MAX_POOL_GROUPS + 1];
 };
 
 __device__ __forceinline__ uint64_t mix64(uint64_t x) {
@@ -118,6 +121,93 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_counts_kernel(const __grid_
     __syncthreads();
   }
   if (threadIdx.x == 0) offsets[batch] = carry_s;
+}
+
+// Multi-CTA form for long count arrays, two launches: every CTA sums its chunk; then every CTA adds up the
+// sums of the chunks before it (same group) and scans its own chunk from that base.
+__device__ __forceinline__ int scan_find_group(const ScanParams& p, int chunk) {
+  int g = 0;
+  while (g + 1 < p.n && p.chunk_begin[g + 1] <= chunk) ++g;
+  return g;
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS) scan_sums_kernel(const __grid_constant__ ScanParams p) {
+  const int g = scan_find_group(p, blockIdx.x), lc = blockIdx.x - p.chunk_begin[g];
+  const int32_t* __restrict__ counts = p.counts[g];
+  const int64_t batch = p.batch[g], i0 = (int64_t)lc * SCAN_THREADS * SCAN_ITEMS + (int64_t)threadIdx.x * SCAN_ITEMS;
+  __shared__ int32_t warp_sums[SCAN_THREADS / 32];
+  int32_t s = 0;
+#pragma unroll
+  for (int e = 0; e < SCAN_ITEMS; ++e) s += (i0 + e < batch) ? counts[i0 + e] : 0;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    int32_t w = warp_sums[threadIdx.x];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) w += __shfl_xor_sync(0xffffffffu, w, off);
+    if (threadIdx.x == 0) p.chunk_sums[g][lc] = w;
+  }
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS) scan_apply_kernel(const __grid_constant__ ScanParams p) {
+  const int g = scan_find_group(p, blockIdx.x), lc = blockIdx.x - p.chunk_begin[g];
+  const int32_t* __restrict__ counts = p.counts[g];
+  int32_t* __restrict__ offsets = p.offsets[g];
+  const int64_t batch = p.batch[g];
+  __shared__ int32_t warp_sums[SCAN_THREADS / 32];
+  __shared__ int32_t base_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // base = sum of the chunk sums before this chunk (integer sums: any order gives the same value)
+  int32_t b = 0;
+  for (int c = threadIdx.x; c < lc; c += SCAN_THREADS) b += p.chunk_sums[g][c];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) b += __shfl_xor_sync(0xffffffffu, b, off);
+  if (lane == 0) warp_sums[warp] = b;
+  __syncthreads();
+  if (warp == 0) {
+    int32_t w = warp_sums[lane];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) w += __shfl_xor_sync(0xffffffffu, w, off);
+    if (lane == 0) base_s = w;
+  }
+  __syncthreads();
+  const int32_t base = base_s;
+  const int64_t i0 = (int64_t)lc * SCAN_THREADS * SCAN_ITEMS + (int64_t)threadIdx.x * SCAN_ITEMS;
+  int32_t c[SCAN_ITEMS];
+#pragma unroll
+  for (int e = 0; e < SCAN_ITEMS; ++e) c[e] = (i0 + e < batch) ? counts[i0 + e] : 0;
+  int32_t tsum = 0;
+#pragma unroll
+  for (int e = 0; e < SCAN_ITEMS; ++e) tsum += c[e];
+  int32_t incl = tsum;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    int32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += v;
+  }
+  __syncthreads();                       // warp_sums is reused
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int32_t w = warp_sums[lane], wi = w;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      int32_t v = __shfl_up_sync(0xffffffffu, wi, off);
+      if (lane >= off) wi += v;
+    }
+    warp_sums[lane] = wi - w;            // exclusive
+  }
+  __syncthreads();
+  int32_t excl = base + warp_sums[warp] + incl - tsum;
+#pragma unroll
+  for (int e = 0; e < SCAN_ITEMS; ++e) {
+    if (i0 + e < batch) offsets[i0 + e] = excl;
+    excl += c[e];
+  }
+  // the thread that holds the last count of the group also writes the total
+  if (i0 < batch && i0 + SCAN_ITEMS >= batch) offsets[batch] = excl;
 }
 
 __device__ __forceinline__ int64_t lookup_row(const PoolGroupDev& g, int64_t key) {
@@ -729,11 +819,15 @@ extern "C" void xb_table_destroy(xb_table_desc* t) {
 }
 
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+static size_t scan_chunks(int64_t batch) {
+  return (size_t)((batch + SCAN_THREADS * SCAN_ITEMS - 1) / (SCAN_THREADS * SCAN_ITEMS));
+}
 
 extern "C" size_t xb_embedding_pool_scratch_bytes(const xb_pool_group* groups, int32_t n_groups) {
   size_t total = 0;
   for (int i = 0; i < n_groups; ++i)
-    if (!groups[i].segments_are_offsets) total += align256(((size_t)groups[i].batch + 1) * 4);
+    if (!groups[i].segments_are_offsets)
+      total += align256(((size_t)groups[i].batch + 1) * 4) + align256(scan_chunks(groups[i].batch) * 4);
   return total;
 }
 
@@ -757,6 +851,7 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
   p.total_warps = 0;
   for (int b = 0; b < kBuckets; ++b) { fp[b].n_groups = 0; fp[b].total_warps = 0; qp[b].n_groups = 0; qp[b].total_warps = 0; }
   sp.n = 0;
+  sp.chunk_begin[0] = 0;
   size_t soff = 0;
   for (int i = 0; i < n_groups; ++i) {
     const xb_pool_group& h = groups[i];
@@ -830,6 +925,9 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     } else {
       int32_t* off = reinterpret_cast<int32_t*>((char*)scratch + soff);
       soff += align256(((size_t)h.batch + 1) * 4);
+      sp.chunk_sums[sp.n] = reinterpret_cast<int32_t*>((char*)scratch + soff);
+      soff += align256(scan_chunks(h.batch) * 4);
+      sp.chunk_begin[sp.n + 1] = sp.chunk_begin[sp.n] + (int32_t)scan_chunks(h.batch);
       sp.counts[sp.n] = h.segments; sp.offsets[sp.n] = off; sp.batch[sp.n] = h.batch; ++sp.n;
       d.offsets = off;
     }
@@ -850,8 +948,16 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     dst.g[dst.n_groups++] = d;
   }
   if (sp.n) {
-    scan_counts_kernel<<<sp.n, SCAN_THREADS, 0, stream>>>(sp);
-    if (int rc = check_launch("scan_counts_kernel")) return rc;
+    if (sp.chunk_begin[sp.n] > sp.n) {
+      // some count array is longer than one chunk: all chunks in parallel, two launches
+      scan_sums_kernel<<<sp.chunk_begin[sp.n], SCAN_THREADS, 0, stream>>>(sp);
+      if (int rc = check_launch("scan_sums_kernel")) return rc;
+      scan_apply_kernel<<<sp.chunk_begin[sp.n], SCAN_THREADS, 0, stream>>>(sp);
+      if (int rc = check_launch("scan_apply_kernel")) return rc;
+    } else {
+      scan_counts_kernel<<<sp.n, SCAN_THREADS, 0, stream>>>(sp);
+      if (int rc = check_launch("scan_counts_kernel")) return rc;
+    }
   }
   for (int b = 0; b < kBuckets; ++b) {
     if (fp[b].n_groups == 0) continue;
