@@ -174,25 +174,6 @@ __global__ void att_pair_pack_kernel(const __grid_constant__ AttParams p, uint8_
   }
 }
 
-// 16 accumulator columns of layer 1 (fp32, already in registers) -> activation -> 8 fp16 pairs of A2
-template <int ACT>
-__device__ __forceinline__ void pair_l1_block(const uint32_t (&cur)[16], const uint4* __restrict__ cc, uint32_t (&y)[8]) {
-#pragma unroll
-  for (int e = 0; e < 8; ++e)
-    y[e] = h2_bits(__floats2half2_rn(__uint_as_float(cur[2 * e]), __uint_as_float(cur[2 * e + 1])));
-  if (ACT != XB_ACT_NONE) {
-    uint32_t th[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e)
-      th[e] = umma::tanh_f16x2(h2_bits(__hfma2(bits_h2(y[e]), bits_h2(cc[e].x), bits_h2(cc[e].y))));
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const __half2 g = __hfma2(bits_h2(th[e]), bits_h2(cc[e].w), bits_h2(cc[e].z));
-      y[e] = h2_bits(ACT == XB_ACT_DICE ? __hmul2(bits_h2(y[e]), g) : g);
-    }
-  }
-}
-
 template <int ACT>
 __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __grid_constant__ AttParams p) {
   using namespace umma;

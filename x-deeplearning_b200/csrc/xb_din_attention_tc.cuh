@@ -162,6 +162,25 @@ __device__ __forceinline__ void pack_weights(const AttParams& p, const TcGeom& G
   }
 }
 
+// 16 accumulator columns of layer 1 (fp32, already in registers) -> activation -> 8 fp16 pairs of A2
+template <int ACT>
+__device__ __forceinline__ void pair_l1_block(const uint32_t (&cur)[16], const uint4* __restrict__ cc, uint32_t (&y)[8]) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    y[e] = h2_bits(__floats2half2_rn(__uint_as_float(cur[2 * e]), __uint_as_float(cur[2 * e + 1])));
+  if (ACT != XB_ACT_NONE) {
+    uint32_t th[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      th[e] = umma::tanh_f16x2(h2_bits(__hfma2(bits_h2(y[e]), bits_h2(cc[e].x), bits_h2(cc[e].y))));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const __half2 g = __hfma2(bits_h2(th[e]), bits_h2(cc[e].w), bits_h2(cc[e].z));
+      y[e] = h2_bits(ACT == XB_ACT_DICE ? __hmul2(bits_h2(y[e]), g) : g);
+    }
+  }
+}
+
 template <int ACT>
 __global__ void att_pack_kernel(const __grid_constant__ AttParams p, uint8_t* dst) {
   const TcGeom G = tc_geom(p.d, p.h0, p.h1, p.T);
@@ -357,48 +376,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       const int b = wb;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
       const uint32_t a2t = lane_addr + b * G.wg + G.c_a2;
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[b]), ph, 20) &&
-                                       mbar_wait(smem_u32(&acc2_full[b]), ph ^ 1u, 23));   // M2(j-2) has read A2[b]
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[b]), ph, 20));
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t acc1 = lane_addr + b * G.wg;
-      for (int c = 0; c < h0p; c += 32) {
-        uint32_t v[32];
-        const bool full = h0p - c >= 32;
-        if (full) { tmem_ld32_nowait(acc1 + c, v); tmem_wait_ld(v); }
-        else {
-          uint32_t v16[16];
-          tmem_ld16_nowait(acc1 + c, v16);
-          tmem_wait_ld(v16);
-#pragma unroll
-          for (int e = 0; e < 16; ++e) v[e] = v16[e];
+      // blocks of 16 columns (8 fp16 pairs): the load of the next block is in flight while this one is
+      // converted, activated and stored
+      const int nblk = h0p / 16;
+      uint32_t va[16], vb[16];
+      auto block = [&](int blk, uint32_t (&cur)[16], uint32_t (&nxt)[16]) {
+        tmem_wait_ld(cur);
+        if (blk + 1 < nblk) tmem_ld16_nowait(acc1 + 16 * (blk + 1), nxt);
+        uint32_t y[8];
+        pair_l1_block<ACT>(cur, c1 + 8 * blk, y);
+        if (blk == 0) {
+          // A2[b] is free once the layer-2 MMA of step j-2 has read it: waited for after the first block's
+          // arithmetic, so that that MMA overlaps the start of this step
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph ^ 1u, 23));
+          if (ok) tc_fence_after_sync();
         }
-        // all pairs of the block go through each stage together, so the SFU and FP16 pipes see
-        // sixteen independent operations back to back; the stores come last
-        const uint4* __restrict__ cc = c1 + (c >> 1);
-        uint32_t y[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e)
-          y[e] = h2_bits(__floats2half2_rn(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1])));
-        if (ACT != XB_ACT_NONE) {
-          uint32_t th[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e)
-            if (full || e < 8) th[e] = h2_bits(__hfma2(bits_h2(y[e]), bits_h2(cc[e].x), bits_h2(cc[e].y)));
-#pragma unroll
-          for (int e = 0; e < 16; ++e)
-            if (full || e < 8) th[e] = tanh_f16x2(th[e]);
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            if (full || e < 8) {
-              const __half2 g = __hfma2(bits_h2(th[e]), bits_h2(cc[e].w), bits_h2(cc[e].z));
-              y[e] = h2_bits(ACT == XB_ACT_DICE ? __hmul2(bits_h2(y[e]), g) : g);
-            }
-          }
-        }
-        if (full) tmem_st16(a2t + (c >> 1), y);
-        else tmem_st8(a2t + (c >> 1), y);
+        if (ok) tmem_st8(a2t + 8 * blk, y);
+      };
+      tmem_ld16_nowait(acc1, va);
+      for (int blk = 0; blk < nblk && ok; blk += 2) {
+        block(blk, va, vb);
+        if (blk + 1 < nblk && ok) block(blk + 1, vb, va);
       }
+      if (!ok) break;
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
