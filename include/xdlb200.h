@@ -186,6 +186,11 @@ int xb_shard_combine(const float* partial, int32_t shards, int64_t segments, int
                      int32_t avg, void* out, int64_t out_stride, int64_t groups, int32_t out_dtype,
                      xb_stream_t stream);
 
+/* Self-test of the bounded waits (no counterpart in the reference): launches one warp that waits on a barrier
+ * nothing will ever signal and gives up after `limit_cycles`. Afterwards xb_device_status reports a non-zero
+ * word (site 99) until xb_device_status_clear, and every other entry point keeps working. */
+int xb_selftest_wait_timeout(int64_t limit_cycles, xb_stream_t stream);
+
 /* ------------------------------------------------------------------------- */
 /* GEMM family with fused bias + activation epilogue.
  * Replaces GemmOp::RunOnDevice (blaze/blaze/operator/op/gemm_op.h:33-107),

@@ -381,6 +381,30 @@ int tower_status(int* out);
 int tower_clear_status();
 }  // namespace xb
 
+// A wait that nothing will ever satisfy, with its own short limit: shows that a bounded wait gives up,
+// records where, and leaves the context usable. Site code 99.
+__global__ void wait_selftest_kernel(long long limit_cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    umma::mbar_init(umma::smem_u32(&bar), 1);
+    umma::fence_barrier_init();
+  }
+  __syncthreads();
+  const long long t0 = clock64();
+  bool done = false;
+  while (!(done = umma::mbar_try_wait(umma::smem_u32(&bar), 0))) {
+    if (clock64() - t0 > limit_cycles) break;
+  }
+  if (!done && threadIdx.x == 0) umma::wait_gave_up(99);
+}
+
+extern "C" int xb_selftest_wait_timeout(int64_t limit_cycles, xb_stream_t stream) {
+  XB_REQUIRE(limit_cycles > 0 && limit_cycles <= ((int64_t)1 << 31), XB_ERR_ARG,
+             "xb_selftest_wait_timeout: limit of %lld cycles (1 .. 2^31)", (long long)limit_cycles);
+  wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((long long)limit_cycles);
+  return check_launch("wait_selftest_kernel");
+}
+
 extern "C" int xb_device_status(int* status) {
   XB_REQUIRE(status, XB_ERR_ARG, "xb_device_status: null pointer");
   int a = 0, b = 0, c = 0;
