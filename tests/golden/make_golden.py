@@ -3,7 +3,7 @@
 
 Run once, in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <reference checkout>
 
 The reference's operator tests are text-proto NetDefs whose inputs are
 ConstantFill ops and whose expected outputs are NetDef-level args
