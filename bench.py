@@ -475,6 +475,81 @@ def run_micro(args):
     print(json.dumps({"micro": args.micro, "launches": reps, "status": "ok", "ms_per_launch": t0.elapsed_time(t1) / reps}))
 
 
+def run_batching(args):
+    """Request batching through the Predictor API: `--requests` predictors of the DIN-style model, each holding one
+    request (1 user x 1000 candidates) in host buffers; every round feeds all of them, runs them and reads the
+    outputs back. Arm "alone": each predictor runs Forward() in turn. Arm "batched": with InitScheduler(enable_batching)
+    the Forward(cb) calls are stacked by the batch thread into one run. Wall clock, host to host."""
+    import threading
+    import time
+    import numpy as np
+    import pkg
+    pkg.load()
+    from x_deeplearning_b200 import blaze_api as api, din_netdef, workloads
+    model = workloads.din_model(seed=0, item_rows=200_000, cate_rows=10_000, user_rows=10_000, emb_sigma=0.5)
+    text, _ = din_netdef.build(model)
+    P = args.requests
+    feeds = [din_netdef.feeds_of(model, workloads.din_requests(model, 100 + i, 1, N_CAND)) for i in range(P)]
+    outs = [np.empty((N_CAND, 2), np.float32) for _ in range(P)]
+
+    def arm(batched):
+        api.init_scheduler(batched, max_batch_size=P, batch_timeout_micros=200)
+        mgr = api.PredictorManager()
+        din_netdef.register_tables(mgr, model)
+        mgr.load_model_text(text, optimize=True)
+        preds = [mgr.create_predictor() for _ in range(P)]
+        done = [threading.Event() for _ in range(P)]
+
+        phase = {"feed": 0.0, "forward": 0.0, "output": 0.0}
+
+        def round_():
+            t_a = time.perf_counter()
+            for p, f in zip(preds, feeds):
+                for n, a in f.items():
+                    p.feed(n, a)
+            t_b = time.perf_counter()
+            if batched:
+                for p, ev in zip(preds, done):
+                    ev.clear()
+                    p.forward_async(ev.set)
+                for ev in done:
+                    assert ev.wait(60)
+            else:
+                for p in preds:
+                    p.forward()
+            t_c = time.perf_counter()
+            for p, o in zip(preds, outs):
+                p.output("output", into=o)
+            t_d = time.perf_counter()
+            phase["feed"] += t_b - t_a
+            phase["forward"] += t_c - t_b
+            phase["output"] += t_d - t_c
+        for _ in range(max(args.warmup, 3)):
+            round_()
+        phase = {k: 0.0 for k in phase}
+        t = time.perf_counter()
+        for _ in range(args.steps):
+            round_()
+        dt = (time.perf_counter() - t) / args.steps
+        for p in preds:
+            p.close()
+        mgr.close()
+        api.init_scheduler(False)
+        return dt, {k: v / args.steps * 1e3 for k, v in phase.items()}, outs[0].copy()
+    b0, t0 = api.batching_stats()
+    dt_alone, ph_alone, first_alone = arm(False)
+    dt_batched, ph_batched, first_batched = arm(True)
+    b1, t1 = api.batching_stats()
+    assert np.array_equal(first_alone, first_batched)
+    print(json.dumps({"micro": "batching", "predictors": P, "candidates_per_request": N_CAND, "rounds": args.steps,
+                      "alone": {"ms_per_round": dt_alone * 1e3, "predictions_per_s": P * N_CAND / dt_alone,
+                                "phase_ms": ph_alone},
+                      "batched": {"ms_per_round": dt_batched * 1e3, "predictions_per_s": P * N_CAND / dt_batched,
+                                  "phase_ms": ph_batched, "requests_per_merged_run": (t1 - t0) / max(b1 - b0, 1)},
+                      "note": "wall clock, host buffers in and out, one submitting thread; phase_ms.forward is "
+                              "Forward() of every predictor in turn (alone) or Forward(cb) of all until the last callback (batched)"}))
+
+
 def run_sharded(args):
     """Row-sharded pooling + MLP (the large-table configuration): 4 tables x `--table-rows` rows x dim 32
     fp16 sharded by id % world, batch 65536 x 40 feature groups split by sample, ids routed and pooled
@@ -522,10 +597,9 @@ def run_sharded(args):
     acts = [torch.empty((B, dims[i + 1]), dtype=torch.float16, device="cuda") for i in range(4)]
 
     def step():
-        stats = []
-        for t in range(n_tables):
-            ids, off, _ = feeds[t]
-            stats.append(sharded.sharded_pool(comm, gops, tables[t], dim, ids, None, off, gpt, pooled[:, t * gpt * dim:(t + 1) * gpt * dim]))
+        # the four tables share the ownership rule: one routing pass and one pair of exchanges for all of them
+        stats = [sharded.sharded_pool_tables(comm, gops, tables, dim, [f[0] for f in feeds], [None] * n_tables,
+                                             [f[1] for f in feeds], [gpt] * n_tables, pooled)]
         x = pooled
         for i in range(4):
             last = i == 3
@@ -572,11 +646,13 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and pooling side measurements")
     ap.add_argument("--table-rows", type=int, default=200_000_000, help="rows per table of --micro sharded")
-    ap.add_argument("--micro", choices=["att", "pool", "gemm", "tower", "sharded"], help="run --steps launches of one kernel on a small case "
+    ap.add_argument("--micro", choices=["att", "pool", "gemm", "tower", "sharded", "batching"], help="run --steps launches of one kernel on a small case "
                     "(for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     if args.micro == "sharded":
         return run_sharded(args)
+    if args.micro == "batching":
+        return run_batching(args)
     if args.micro:
         return run_micro(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -114,8 +114,10 @@ typedef struct xb_pool_group {
   const xb_table_desc* table;  /* HOST pointer; NULL = table-name miss: outputs are zero-filled */
   const void* ids;             /* [n_ids] */
   const void* values;          /* [n_ids] per-id weights (values_dtype), NULL = all 1.0 */
-  const int32_t* segments;     /* [batch] counts, or [batch+1] exclusive offsets */
-  int64_t n_ids;
+  const int32_t* segments;     /* [batch] counts, or [batch+1] exclusive offsets into ids (they need not start
+                                  at 0: several groups may share one id buffer) */
+  int64_t n_ids;               /* ids the group's segments cover; with offsets it only sizes the work split,
+                                  so an estimate is enough when the exact number is not known on the host */
   int64_t batch;
   int32_t dim;                 /* the group's configured dim (EmbeddingFeatureGroupConfig.dim); must
                                   equal table->dim when the table exists */

@@ -25,6 +25,23 @@ class CpuShardOps:
         orc.embedding_pool(table, rows.numpy(), vals.numpy(), counts.numpy(), [dict(udf=0, out=out, col=0)])
         return torch.from_numpy(out)
 
+    def pool_partial_tables(self, tables, rows, vals, offsets, sources, table_segments, dim):
+        S = sum(table_segments)
+        off = offsets.numpy()
+        out = np.zeros((sources * S, dim), np.float32)
+        r = rows.numpy()
+        v = vals.numpy() if vals is not None else np.ones(len(r), np.float32)
+        for s in range(sources):
+            lo = s * S
+            for table, n in zip(tables, table_segments):
+                a, b = int(off[lo]), int(off[lo + n])
+                counts = (off[lo + 1:lo + n + 1] - off[lo:lo + n]).astype(np.int32)
+                part = np.zeros((n, dim), np.float32)
+                orc.embedding_pool(table, r[a:b], v[a:b], counts, [dict(udf=0, out=part, col=0)])
+                out[lo:lo + n] = part
+                lo += n
+        return torch.from_numpy(out)
+
     def combine(self, partial, shards, segments, dim, groups, out, seg_len=None, avg=False):
         p = partial.numpy().reshape(shards, segments, dim)
         acc = np.zeros((segments, dim), np.float32)

@@ -70,3 +70,63 @@ def test_route_large_stream_is_a_stable_partition():
     c = CpuShardOps().route(torch.from_numpy(ids), None, torch.from_numpy(off), world)
     for a, b in zip(g, c):
         assert torch.equal(a.cpu(), b)
+
+
+class _SelfComm:
+    """A world of one rank: both exchanges hand the buffers back."""
+    world, rank = 1, 0
+
+    def exchange_counts(self, counts):
+        return counts.clone()
+
+    def all_to_all_v(self, send, send_counts, recv_counts):
+        return send.clone()
+
+    def all_to_all_equal(self, send):
+        return send.clone()
+
+
+@pytest.mark.parametrize("with_values", [True, False])
+def test_several_tables_through_one_routing_pass(with_values):
+    pkg.load()
+    from x_deeplearning_b200 import ops, sharded
+    dim, per_rank, groups = 8, 5, [3, 2, 4]
+    cases = [_case(11 + t, 1, rows_total=r, groups=g) for t, (r, g) in enumerate(zip([4000, 777, 50], groups))]
+    tables = [ops.Table(torch.from_numpy(table), torch.float32) for table, _ in cases]
+    mine = [data[0] for _, data in cases]
+    out = torch.zeros((per_rank, sum(groups) * dim), device="cuda")
+    sharded.sharded_pool_tables(_SelfComm(), sharded.GpuShardOps(), tables, dim, [torch.from_numpy(m[0]).cuda() for m in mine],
+                                [torch.from_numpy(m[1]).cuda() if with_values else None for m in mine],
+                                [torch.from_numpy(m[2]).cuda() for m in mine], groups, out)
+    want = []
+    for (table, _), (ids, vals, off, counts), g in zip(cases, mine, groups):
+        w = np.zeros((g * per_rank, dim), np.float32)
+        orc.embedding_pool(table, ids, vals if with_values else np.ones(len(ids), np.float32), counts, [dict(udf=0, out=w, col=0)])
+        want.append(w.reshape(g, per_rank, dim).transpose(1, 0, 2).reshape(per_rank, g * dim))
+    np.testing.assert_allclose(out.cpu().numpy(), np.concatenate(want, axis=1), rtol=1e-5, atol=1e-5)
+
+
+def test_owner_side_pooling_of_several_sources_and_tables_matches_the_cpu_restatement():
+    pkg.load()
+    from x_deeplearning_b200 import ops, sharded
+    rng = np.random.default_rng(5)
+    dim, sources, table_segments = 8, 3, [6, 4]
+    S = sum(table_segments)
+    shards_np = [rng.normal(0, 0.5, (300, dim)).astype(np.float32), rng.normal(0, 0.5, (40, dim)).astype(np.float32)]
+    counts = rng.integers(0, 5, sources * S).astype(np.int32)
+    off = np.zeros(len(counts) + 1, np.int32)
+    np.cumsum(counts, out=off[1:])
+    rows = np.zeros(int(off[-1]), np.int64)
+    for s in range(sources):
+        lo = s * S
+        for shard, n in zip(shards_np, table_segments):
+            a, b = off[lo], off[lo + n]
+            rows[a:b] = rng.integers(0, len(shard), b - a)
+            lo += n
+    vals = rng.normal(1, 0.3, len(rows)).astype(np.float32)
+    want = CpuShardOps().pool_partial_tables(shards_np, torch.from_numpy(rows), torch.from_numpy(vals), torch.from_numpy(off),
+                                             sources, table_segments, dim)
+    tables = [ops.Table(torch.from_numpy(t), torch.float32) for t in shards_np]
+    got = sharded.GpuShardOps().pool_partial_tables(tables, torch.from_numpy(rows).cuda(), torch.from_numpy(vals).cuda(),
+                                                    torch.from_numpy(off).cuda(), sources, table_segments, dim)
+    np.testing.assert_allclose(got.cpu().numpy(), want.numpy(), rtol=1e-5, atol=1e-5)

@@ -58,6 +58,35 @@ def _worker(rank, world, port, seed, avg, ret):
     dist.destroy_process_group()
 
 
+def _worker_tables(rank, world, port, seed, with_values, ret):
+    """Two tables of different sizes and group counts through one routing pass and one pair of exchanges."""
+    sys.path.insert(0, HERE)
+    import torch.distributed as dist
+    import pkg
+    pkg.load()
+    from x_deeplearning_b200 import sharded
+    import orc
+    from cpu_shard_ops import CpuShardOps
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    dim, per_rank = 8, 5
+    cases = [_case(seed, world, rows_total=4000, groups=3), _case(seed + 50, world, rows_total=777, groups=2)]
+    groups = [3, 2]
+    shards = [np.ascontiguousarray(table[rank::world]) for table, _ in cases]
+    mine = [data[rank] for _, data in cases]
+    out = torch.zeros((per_rank, sum(groups) * dim), dtype=torch.float32)
+    stats = sharded.sharded_pool_tables(
+        sharded.DistComm(), CpuShardOps(), shards, dim, [torch.from_numpy(m[0]) for m in mine],
+        [torch.from_numpy(m[1]) if with_values else None for m in mine], [torch.from_numpy(m[2]) for m in mine], groups, out)
+    want = []
+    for (table, _), (ids, vals, off, counts), g in zip(cases, mine, groups):
+        w = np.zeros((g * per_rank, dim), np.float32)
+        orc.embedding_pool(table, ids, vals if with_values else np.ones(len(ids), np.float32), counts, [dict(udf=0, out=w, col=0)])
+        want.append(w.reshape(g, per_rank, dim).transpose(1, 0, 2).reshape(per_rank, g * dim))
+    err = float(np.abs(out.numpy() - np.concatenate(want, axis=1)).max())
+    ret[rank] = (err, stats["routed_bytes"])
+    dist.destroy_process_group()
+
+
 def _run(world, seed, avg):
     port = _free_port()
     mgr = mp.Manager()
@@ -79,6 +108,29 @@ def test_two_ranks_avg():
 
 def test_three_ranks_sum():
     _run(3, 2, False)
+
+
+def _run_tables(world, seed, with_values):
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker_tables, args=(world, port, seed, with_values, ret), nprocs=world, join=True)
+    got = dict(ret)
+    assert len(got) == world
+    for r in range(world):
+        assert got[r][0] <= 1e-5, got[r]
+    return got
+
+
+def test_two_tables_one_exchange():
+    _run_tables(2, 5, True)
+
+
+def test_two_tables_without_values_route_fewer_bytes():
+    a = _run_tables(2, 6, False)
+    b = _run_tables(2, 6, True)
+    for r in range(2):
+        assert a[r][1] * 16 == b[r][1] * 12            # 12 bytes per routed id instead of 16
 
 
 def test_routing_rule_is_bit_exact():

@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(HERE, "lib", "libblaze_b200.so")
 
 _lib = None
 vp, cp = C.c_void_p, C.c_char_p
+FORWARD_CB = C.CFUNCTYPE(None, C.c_void_p)
 
 
 def lib():
@@ -41,6 +42,10 @@ def lib():
         L.Blaze_B200_PredictorLastLaunchCount.argtypes = [vp, C.POINTER(C.c_int)]
         L.Blaze_PredictorListInputNames.argtypes = [vp, C.POINTER(C.c_size_t), C.POINTER(C.POINTER(cp))]
         L.Blaze_PredictorListOutputNames.argtypes = [vp, C.POINTER(C.c_size_t), C.POINTER(C.POINTER(cp))]
+        L.Blaze_InitScheduler.argtypes = [C.c_int] * 6
+        L.Blaze_B200_PredictorForwardAsync.argtypes = [vp, FORWARD_CB, vp]
+        L.Blaze_B200_PlanBatch.argtypes = [vp, C.c_int, C.c_int, C.c_int, vp]
+        L.Blaze_B200_BatchingStats.argtypes = [C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         _lib = L
     return _lib
 
@@ -55,6 +60,32 @@ def _ck(rc):
 
 
 NP_DTYPE = {1: np.float32, 2: np.int32, 10: np.int64, 12: np.float16}
+
+
+def init_scheduler(enable_batching, max_batch_size=100, batch_timeout_micros=100, num_threads_for_cpu=4,
+                   num_threads_for_cuda=4, num_threads_for_pipe=2):
+    """InitScheduler of the predictor API; batching applies to predictors created afterwards."""
+    _ck(lib().Blaze_InitScheduler(int(enable_batching), max_batch_size, batch_timeout_micros, num_threads_for_cpu,
+                                  num_threads_for_cuda, num_threads_for_pipe))
+
+
+def plan_batch(rows, max_tasks):
+    """Positions of the waiting requests that would run together with request 0; rows[t][j] is the first
+    dimension of request t's j-th per-sample input."""
+    r = np.ascontiguousarray(rows, np.int64)
+    r = r.reshape(len(rows), -1) if len(rows) else np.zeros((0, 1), np.int64)
+    picked = np.zeros(max(len(rows), 1), np.int32)
+    n = lib().Blaze_B200_PlanBatch(r.ctypes.data, r.shape[0], r.shape[1], max_tasks, picked.ctypes.data)
+    if n < 0:
+        _ck(n)
+    return picked[:n].tolist()
+
+
+def batching_stats():
+    """(merged runs, requests they carried) since the process started."""
+    b, t = C.c_int64(), C.c_int64()
+    _ck(lib().Blaze_B200_BatchingStats(C.byref(b), C.byref(t)))
+    return b.value, t.value
 
 
 class PredictorManager:
@@ -112,6 +143,11 @@ class Predictor:
 
     def forward(self):
         _ck(lib().Blaze_PredictorForward(self.h))
+
+    def forward_async(self, callback):
+        """Forward(cb): `callback()` runs when the outputs are ready (on the batch thread when batching is on)."""
+        self._cb = FORWARD_CB(lambda _arg: callback())       # kept alive until the next call
+        _ck(lib().Blaze_B200_PredictorForwardAsync(self.h, self._cb, None))
 
     def output_shape(self, name):
         nd, sh = C.c_size_t(), C.POINTER(C.c_size_t)()

@@ -61,6 +61,17 @@ int Blaze_B200_PredictorFeedDevice(PredictorHandle handle, const char* name, con
 int Blaze_B200_PredictorOutputDevice(PredictorHandle handle, const char* name, void** device_data, size_t* len);
 /* Number of kernel-library calls issued by the last Forward. */
 int Blaze_B200_PredictorLastLaunchCount(PredictorHandle handle, int* count);
+/* Predictor::Forward(cb): with batching switched on by Blaze_InitScheduler the call returns at once and
+ * cb(arg) runs on the batch thread when this predictor's outputs are ready (requests of several
+ * predictors of one model are stacked into one run); without batching the net runs before the call
+ * returns and cb(arg) is called from it. */
+int Blaze_B200_PredictorForwardAsync(PredictorHandle handle, void (*cb)(void*), void* arg);
+/* The batch the queue would close on `n_tasks` waiting requests, without running anything: rows[t * n_inputs + j]
+ * is the first dimension of request t's j-th per-sample input. Writes the positions that run together with
+ * request 0 (at most max_tasks, request 0 included) and returns how many; -1 on bad arguments. */
+int Blaze_B200_PlanBatch(const int64_t* rows, int n_tasks, int n_inputs, int max_tasks, int* picked);
+/* Merged runs so far and the requests they carried (process-wide). */
+int Blaze_B200_BatchingStats(int64_t* batches, int64_t* tasks);
 
 #ifdef __cplusplus
 }

@@ -7,6 +7,7 @@
 
 #include "blaze/api/c_api/c_api_predictor.h"
 #include "blaze/api/cpp_api/predictor.h"
+#include "batching.h"
 #include "runtime.h"
 
 namespace blaze {
@@ -46,6 +47,10 @@ class PredictorImpl {
   std::vector<char> staging_;
   std::vector<size_t> scratch_shape_;
   bool profile_ = false;
+  // request batching (InitScheduler(enable_batching = true)): the queue of this model and device, and
+  // what the last batched Forward reported
+  std::shared_ptr<BatchQueue> queue_;
+  std::string async_error_;
 };
 
 class PredictorManagerImpl {
@@ -100,6 +105,7 @@ class PredictorManagerImpl {
   std::shared_ptr<store::SparsePuller> puller_;
   std::mutex mu_;
   std::map<int, std::shared_ptr<ConstantStore>> constants_;      // per device
+  std::map<int, std::shared_ptr<BatchQueue>> queues_;            // per device, as the reference keeps one per NetDef
 };
 
 struct ManagerAccess {
@@ -123,7 +129,13 @@ Predictor* PredictorManagerImpl::Create(PredictDeviceType type, int device_id) {
     if (!run_mode_.empty()) def.run_mode = run_mode_;
     auto& store = constants_[device_id];
     if (!store) store.reset(new ConstantStore());
-    return new Predictor(new PredictorImpl(def, puller_, store));
+    std::unique_ptr<PredictorImpl> impl(new PredictorImpl(def, puller_, store));
+    if (GlobalSchedulerOptions().enable_batching) {
+      auto& queue = queues_[device_id];
+      if (!queue) queue.reset(new BatchQueue(def, puller_, store, GlobalSchedulerOptions()));
+      impl->queue_ = queue;
+    }
+    return new Predictor(impl.release());
   } catch (const std::exception& e) {
     SetError(MakeString("create predictor failed: ", e.what()));
     return nullptr;
@@ -200,6 +212,30 @@ const std::vector<std::string>& Predictor::ListInputName() const { return impl_-
 bool Predictor::Forward(const PredictorCallback&& cb) {
   try {
     CUDA_CHECK(cudaSetDevice(impl_->net_->device_id()));
+    impl_->async_error_.clear();
+    if (cb && impl_->queue_) {
+      // asynchronous: the batch thread stacks this request with others of the same model, runs them
+      // as one net and calls cb once this predictor's outputs are in place
+      BatchQueue::Task task;
+      task.ws = &impl_->ws_;
+      BatchQueue::Describe(impl_->net_->net_def(), &task);
+      CUDA_CHECK(cudaEventCreateWithFlags(&task.ready, cudaEventDisableTiming));
+      CUDA_CHECK(cudaEventRecord(task.ready, impl_->net_->stream()));
+      PredictorImpl* impl = impl_;
+      PredictorCallback user_cb = cb;
+      task.done = [impl, user_cb](const std::string& error) {
+        impl->async_error_ = error;
+        user_cb();
+      };
+      cudaEvent_t ready = task.ready;
+      std::string why;
+      if (!impl_->queue_->Schedule(&task, &why)) {
+        cudaEventDestroy(ready);
+        SetError(MakeString("forward failed: ", why));
+        return false;
+      }
+      return true;
+    }
     impl_->net_->profile = impl_->profile_;
     if (!impl_->net_->Run()) return false;
     CUDA_CHECK(cudaStreamSynchronize(impl_->net_->stream()));
@@ -213,6 +249,7 @@ bool Predictor::Forward(const PredictorCallback&& cb) {
 
 bool Predictor::Output(const char* name, void** data, size_t* len) {
   try {
+    BLAZE_CONDITION_THROW(impl_->async_error_.empty(), impl_->async_error_);
     Blob* b = impl_->ws_.GetBlob(name);
     BLAZE_CONDITION_THROW(b != nullptr, "output ", name, " does not exist");
     impl_->staging_.resize(std::max<size_t>(b->bytes(), 1));
@@ -289,9 +326,17 @@ bool PredictorManager::LoadModel(const char* conf_file, const char*, ModelType m
 }
 Predictor* PredictorManager::CreatePredictor(PredictDeviceType type, int device_id) { return impl_->Create(type, device_id); }
 
-bool InitScheduler(bool, int, int, int, int, int) {
-  // Every operator runs in stream order on the predictor's own stream; there are no scheduler
-  // threads to configure. Accepting the call keeps start-up code written for Blaze unchanged.
+bool InitScheduler(bool enable_batching, int max_batch_size, int batch_timeout_micros, int, int, int) {
+  // Every operator runs in stream order on the predictor's own stream, so the thread counts have
+  // nothing to size. Batching applies to predictors created after this call: their Forward(cb) goes
+  // through the model's batch queue (one batch thread per model and device).
+  if (enable_batching && max_batch_size < 1) { SetError("InitScheduler: max_batch_size must be at least 1"); return false; }
+  SchedulerOptions& o = GlobalSchedulerOptions();
+  o.enable_batching = enable_batching;
+  if (enable_batching) {
+    o.max_batch_size = max_batch_size;
+    o.batch_timeout_micros = batch_timeout_micros < 0 ? 0 : batch_timeout_micros;
+  }
   return true;
 }
 
@@ -478,6 +523,24 @@ int Blaze_B200_PredictorLastLaunchCount(PredictorHandle h, int* count) {
   PredictorImpl* impl = PredictorManagerImpl::ImplOf(static_cast<CPredictor*>(h)->p);
   *count = impl->net_->last_launches;
   API_END();
+}
+int Blaze_B200_PredictorForwardAsync(PredictorHandle h, void (*cb)(void*), void* arg) {
+  if (cb == nullptr) { SetError("Blaze_B200_PredictorForwardAsync needs a callback"); return -1; }
+  return Ret(static_cast<CPredictor*>(h)->p->Forward([cb, arg] { cb(arg); }));
+}
+int Blaze_B200_PlanBatch(const int64_t* rows, int n_tasks, int n_inputs, int max_tasks, int* picked) {
+  if (!rows || !picked || n_tasks < 0 || n_inputs < 0) { SetError("Blaze_B200_PlanBatch: bad arguments"); return -1; }
+  std::deque<BatchQueue::Task> queue((size_t)n_tasks);
+  for (int t = 0; t < n_tasks; ++t)
+    for (int j = 0; j < n_inputs; ++j) queue[t].rows.push_back((TIndex)rows[(size_t)t * n_inputs + j]);
+  const std::vector<size_t> got = BatchQueue::PickBatch(queue, (size_t)std::max(max_tasks, 0));
+  for (size_t i = 0; i < got.size(); ++i) picked[i] = (int)got[i];
+  return (int)got.size();
+}
+int Blaze_B200_BatchingStats(int64_t* batches, int64_t* tasks) {
+  if (batches) *batches = GlobalBatchingStats().batches.load();
+  if (tasks) *tasks = GlobalBatchingStats().tasks.load();
+  return 0;
 }
 
 }  // extern "C"

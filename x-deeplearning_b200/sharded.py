@@ -70,34 +70,84 @@ class GpuShardOps:
         xops.embedding_pool([g])
         return out
 
+    def pool_partial_tables(self, tables, rows, vals, offsets, sources, table_segments, dim):
+        """rows/vals: everything this owner received (source-major, and table-major inside a source);
+        offsets [sources * S + 1] int32: where each (source, segment) starts in `rows`, S = sum(table_segments).
+        Table t pools the segments [sum(table_segments[:t]), +table_segments[t]) of every source: one pooling
+        group per (source, table), all over the same id buffer. Returns [sources * S, dim] fp32."""
+        S = sum(table_segments)
+        out = torch.empty((sources * S, dim), dtype=torch.float32, device=rows.device)
+        groups = []
+        for s in range(sources):
+            lo = s * S
+            for table, n in zip(tables, table_segments):
+                g = xops.make_group(table, rows, vals, offsets[lo:lo + n + 1],
+                                    [dict(udf=capi.XB_UDF_SUM, out=out[lo:lo + n], col=0)], torch.float32,
+                                    segments_are_offsets=True)
+                # the exact share of this (source, table) is only known on the device: the group's ids are
+                # taken as proportional to its segments (the number sizes the work split, nothing else)
+                g.n_ids = rows.numel() * n // max(sources * S, 1)
+                groups.append(g)
+                lo += n
+        for i in range(0, len(groups), capi.XB_MAX_POOL_GROUPS):
+            xops.embedding_pool(groups[i:i + capi.XB_MAX_POOL_GROUPS])
+        return out
+
     def combine(self, partial, shards, segments, dim, groups, out, seg_len=None, avg=False):
         check(lib().xb_shard_combine(xops.ptr(partial), shards, segments, dim, xops.ptr(seg_len), int(avg), xops.ptr(out),
                                      out.stride(0), groups, xops.dt(out), xops.stream()))
         return out
 
 
-def sharded_pool(comm, ops, table_shard, dim, ids, values, seg_offsets, groups, out, avg=False):
-    """ids/values/seg_offsets: this rank's ids of `groups` feature groups over one row-sharded table,
-    laid out group-major (segment = group * rows + sample, rows = samples of this rank);
-    out [rows, >= groups*dim] receives the pooled vectors of this rank's samples.
-    Returns the per-step byte counts of the two exchanges."""
+def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, groups, out, avg=False):
+    """Pooling over several row-sharded tables of one `dim` with ONE routing pass and one pair of exchanges.
+
+    ids[t] / values[t] / seg_offsets[t]: this rank's ids of the `groups[t]` feature groups of table t, laid out
+    group-major (segment = group * rows + sample, rows = samples of this rank, the same for every table);
+    values[t] may be None (all 1.0) only if it is None for every table. out [rows, >= sum(groups) * dim]
+    receives the pooled vectors, table after table. All tables follow the same ownership rule, so their ids
+    form one routing problem whose segments are numbered table after table; the owner pools each table's
+    segment range against that table's shard. Returns the per-step byte counts of the two exchanges."""
     W = comm.world
-    segments = seg_offsets.numel() - 1
-    rows, vals, tags, owner_counts = ops.route(ids, values, seg_offsets, W)
-    send_counts = [int(c) for c in owner_counts.cpu()]                       # bucket sizes drive the exchange
-    recv_counts = [int(c) for c in comm.exchange_counts(owner_counts).cpu()]
+    T = len(table_shards)
+    table_segments = [int(o.numel()) - 1 for o in seg_offsets]
+    segments = sum(table_segments)
+    if T == 1:
+        all_ids, all_vals, all_off = ids[0], values[0], seg_offsets[0]
+    else:
+        all_ids = torch.cat(list(ids))
+        assert all(v is None for v in values) or all(v is not None for v in values)
+        all_vals = None if values[0] is None else torch.cat(list(values))
+        parts, base = [], 0
+        for t in range(T):
+            parts.append(seg_offsets[t][:-1] + base if base else seg_offsets[t][:-1])
+            base += int(ids[t].numel())
+        parts.append(torch.full((1,), base, dtype=seg_offsets[0].dtype, device=seg_offsets[0].device))
+        all_off = torch.cat(parts)
+    rows, vals, tags, owner_counts = ops.route(all_ids, all_vals, all_off, W)
+    both = torch.stack([owner_counts, comm.exchange_counts(owner_counts)]).cpu()   # bucket sizes drive the exchange
+    send_counts, recv_counts = [int(c) for c in both[0]], [int(c) for c in both[1]]
     r_rows = comm.all_to_all_v(rows, send_counts, recv_counts)
-    r_vals = comm.all_to_all_v(vals, send_counts, recv_counts)
+    r_vals = comm.all_to_all_v(vals, send_counts, recv_counts) if all_vals is not None else None
     r_tags = comm.all_to_all_v(tags, send_counts, recv_counts)
-    # segment lengths of every source rank's slice (every rank has the same number of segments)
+    # segment lengths of every source rank's slice (every rank has the same number of segments), then where
+    # every (source, segment) starts in the received buffer
+    offsets = torch.zeros(W * segments + 1, dtype=torch.int32, device=r_tags.device)
     counts = []
     pos = 0
     for s in range(W):
         counts.append(ops.tag_counts(r_tags[pos:pos + recv_counts[s]], segments))
         pos += recv_counts[s]
-    counts = torch.cat(counts)
-    partial = ops.pool_partial(table_shard, r_rows, r_vals, counts, dim)    # [W*segments, dim] fp32
+    torch.cumsum(torch.cat(counts), 0, dtype=torch.int32, out=offsets[1:])
+    partial = ops.pool_partial_tables(table_shards, r_rows, r_vals, offsets, W, table_segments, dim)   # [W*segments, dim] fp32
     back = comm.all_to_all_equal(partial)                                    # slice w: from owner w
-    seg_len = (seg_offsets[1:] - seg_offsets[:-1]).to(torch.int32) if avg else None
-    ops.combine(back, W, segments, dim, groups, out, seg_len, avg)
-    return {"routed_bytes": sum(send_counts) * (8 + 4 + 4), "returned_bytes": partial.numel() * 4}
+    seg_len = (all_off[1:] - all_off[:-1]).to(torch.int32) if avg else None
+    ops.combine(back, W, segments, dim, sum(groups), out, seg_len, avg)
+    per_id = 8 + 4 + (4 if all_vals is not None else 0)
+    return {"routed_bytes": sum(send_counts) * per_id, "returned_bytes": partial.numel() * 4}
+
+
+def sharded_pool(comm, ops, table_shard, dim, ids, values, seg_offsets, groups, out, avg=False):
+    """One table: ids/values/seg_offsets are this rank's ids of `groups` feature groups (group-major segments),
+    out [rows, >= groups*dim] receives the pooled vectors of this rank's samples."""
+    return sharded_pool_tables(comm, ops, [table_shard], dim, [ids], [values], [seg_offsets], [groups], out, avg)
