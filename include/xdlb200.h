@@ -391,6 +391,17 @@ int xb_elementwise(int32_t op, const void* a, const int64_t* a_strides, const vo
  * fused_op/fused_slice_concat_op.cu:24-140). src row stride 0 broadcasts one row. */
 int xb_copy2d(const void* src, int64_t src_ld, int32_t src_dtype, void* dst, int64_t dst_ld,
               int32_t dst_dtype, int64_t rows, int64_t cols, xb_stream_t stream);
+/* Many flat device-to-device copies in one launch: the merge and split steps of request batching
+ * (Batching::CopyDataToMergedNet, blaze/blaze/scheduler/batching.cc:117-129, issues one cudaMemcpyAsync per input
+ * blob and request; stacking 32 requests of a 39-input net is 1248 of them). `items` is a DEVICE array of n_items
+ * descriptors (the caller copies it there, e.g. from pinned memory on the same stream); max_bytes is the largest
+ * `bytes` among them (it sizes the grid). Source and destination ranges must not overlap. */
+typedef struct xb_copy_item {
+  const void* src;
+  void* dst;
+  int64_t bytes;
+} xb_copy_item;
+int xb_copy_segments(const xb_copy_item* items, int32_t n_items, int64_t max_bytes, xb_stream_t stream);
 /* ReduceSum over the middle axis of [outer, r, inner], blaze/blaze/math/reduce.cu:12-113 */
 int xb_reduce_sum(const void* x, void* y, int64_t outer, int64_t r, int64_t inner, int32_t dtype,
                   xb_stream_t stream);

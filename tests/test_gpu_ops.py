@@ -76,3 +76,29 @@ def test_elementwise_broadcast():
         capi.check(L.xb_elementwise(op, ops.ptr(da), arr([0, 3, 1, 0]), ops.ptr(db), arr([0, 0, 0, 1]), None, None,
                                     ops.ptr(y), arr([1, 2, 3, 2]), capi.XB_F32, ops.stream()))
         np.testing.assert_array_equal(y.cpu().numpy(), f(a, b))
+
+
+def test_copy_segments_moves_every_range_in_one_launch():
+    """Flat copies of odd lengths and alignments (id lists, counts, fp16 rows) against numpy slicing."""
+    pkg.load()
+    from x_deeplearning_b200 import capi, ops
+    rng = np.random.default_rng(9)
+    src = torch.from_numpy(rng.integers(0, 256, 3_000_000, dtype=np.uint8)).cuda()
+    dst = torch.zeros(3_200_000, dtype=torch.uint8, device="cuda")
+    want = np.zeros(3_200_000, np.uint8)
+    host = src.cpu().numpy()
+    lengths = [0, 1, 7, 16, 33, 800, 4096, 32 * 1024, 32 * 1024 + 1, 100_003, 1_000_000]
+    items, so, do = [], 5, 3                                       # odd starts: the byte path
+    for i, n in enumerate(lengths):
+        if i % 2:                                                  # every other copy 16-byte aligned at both ends
+            so, do = (so + 15) // 16 * 16, (do + 15) // 16 * 16
+        items.append((src.data_ptr() + so, dst.data_ptr() + do, n))
+        want[do:do + n] = host[so:so + n]
+        so += n + 3
+        do += n + 5
+    table = torch.tensor([[a, b, n] for a, b, n in items], dtype=torch.int64).cuda()
+    capi.check(capi.lib().xb_copy_segments(table.data_ptr(), len(items), max(lengths), ops.stream()))
+    torch.cuda.synchronize()
+    assert np.array_equal(dst.cpu().numpy(), want)
+    # nothing to do
+    capi.check(capi.lib().xb_copy_segments(None, 0, 0, ops.stream()))

@@ -77,6 +77,7 @@ SYMBOLS = {
     "xb_table_create": (i32, [C.POINTER(C.POINTER(TableDesc)), i64, i32, i32, vp, vp]),
     "xb_table_destroy": (None, [C.POINTER(TableDesc)]),
     "xb_table_build_index_host": (i32, [vp, i64, i64, vp, vp]),
+    "xb_copy_segments": (i32, [vp, i32, i64, vp]),
     "xb_embedding_pool_scratch_bytes": (C.c_size_t, [C.POINTER(PoolGroup), i32]),
     "xb_embedding_pool": (i32, [C.POINTER(PoolGroup), i32, vp, C.c_size_t, vp]),
     "xb_embedding_pool_static_max_bytes": (C.c_size_t, []),

@@ -389,6 +389,36 @@ extern "C" int xb_copy2d(const void* src, int64_t src_ld, int32_t sdt, void* dst
   return check_launch("copy2d_kernel");
 }
 
+// One CTA column per descriptor, blockIdx.y walks the copy in 32 KB pieces; 16-byte vectors when both ends
+// and the length allow it, single bytes otherwise (id lists and segment counts of odd lengths).
+constexpr int64_t COPY_PIECE = 32 * 1024;
+__global__ void copy_segments_kernel(const xb_copy_item* __restrict__ items) {
+  const xb_copy_item it = items[blockIdx.x];
+  const int64_t begin = (int64_t)blockIdx.y * COPY_PIECE;
+  if (begin >= it.bytes) return;
+  const int64_t n = min(COPY_PIECE, it.bytes - begin);
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(it.src) + begin;
+  uint8_t* dst = reinterpret_cast<uint8_t*>(it.dst) + begin;
+  if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+    const int64_t nv = n / 16;
+    for (int64_t i = threadIdx.x; i < nv; i += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+    for (int64_t i = nv * 16 + threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+  } else {
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+extern "C" int xb_copy_segments(const xb_copy_item* items, int32_t n_items, int64_t max_bytes, xb_stream_t s) {
+  XB_REQUIRE(n_items >= 0 && max_bytes >= 0 && (n_items == 0 || items), XB_ERR_ARG, "xb_copy_segments: bad arguments");
+  if (n_items == 0 || max_bytes == 0) return 0;
+  const int64_t pieces = (max_bytes + COPY_PIECE - 1) / COPY_PIECE;
+  XB_REQUIRE(pieces <= 65535, XB_ERR_LIMIT, "xb_copy_segments: a copy of %lld bytes is too long for one call", (long long)max_bytes);
+  dim3 grid((unsigned)n_items, (unsigned)pieces);
+  copy_segments_kernel<<<grid, 256, 0, (cudaStream_t)s>>>(items);
+  return check_launch("copy_segments_kernel");
+}
+
 extern "C" int xb_reduce_sum(const void* x, void* y, int64_t outer, int64_t r, int64_t inner, int32_t dtype,
                              xb_stream_t s) {
   XB_REQUIRE(x && y && outer >= 0 && r >= 0 && inner >= 0, XB_ERR_ARG, "xb_reduce_sum: bad arguments");

@@ -65,9 +65,59 @@ std::vector<size_t> BatchQueue::PickBatch(const std::deque<Task>& queue, size_t 
   return picked;
 }
 
+// Descriptor table of one merge or split step: filled in pinned host memory, copied to the device on the
+// batch stream, consumed by one kernel. The two halves alternate so that the split step's table does not
+// overwrite the merge step's while its copy may still be in flight.
+struct BatchQueue::CopyTable {
+  std::vector<xb_copy_item> items;
+  xb_copy_item* host[2] = {nullptr, nullptr};
+  xb_copy_item* device[2] = {nullptr, nullptr};
+  size_t capacity[2] = {0, 0};
+  int turn = 0;
+  int64_t max_bytes = 0;
+  ~CopyTable() {
+    for (int i = 0; i < 2; ++i) {
+      if (host[i]) cudaFreeHost(host[i]);
+      if (device[i]) cudaFree(device[i]);
+    }
+  }
+};
+
+void BatchQueue::AddCopy(const void* src, void* dst, size_t bytes) {
+  if (bytes == 0) return;
+  xb_copy_item it;
+  it.src = src; it.dst = dst; it.bytes = (int64_t)bytes;
+  copies_->items.push_back(it);
+  copies_->max_bytes = std::max<int64_t>(copies_->max_bytes, (int64_t)bytes);
+}
+
+void BatchQueue::FlushCopies(cudaStream_t stream) {
+  CopyTable& c = *copies_;
+  const size_t n = c.items.size();
+  if (n == 0) return;
+  const int h = c.turn;
+  c.turn ^= 1;
+  if (c.capacity[h] < n) {
+    // the stream is idle or only runs work of this batch that does not read the old table any more
+    CUDA_CHECK(cudaStreamSynchronize(stream));
+    if (c.host[h]) cudaFreeHost(c.host[h]);
+    if (c.device[h]) cudaFree(c.device[h]);
+    c.host[h] = nullptr; c.device[h] = nullptr; c.capacity[h] = 0;
+    const size_t cap = std::max<size_t>(2 * n, 256);
+    CUDA_CHECK(cudaMallocHost(reinterpret_cast<void**>(&c.host[h]), cap * sizeof(xb_copy_item)));
+    CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&c.device[h]), cap * sizeof(xb_copy_item)));
+    c.capacity[h] = cap;
+  }
+  memcpy(c.host[h], c.items.data(), n * sizeof(xb_copy_item));
+  CUDA_CHECK(cudaMemcpyAsync(c.device[h], c.host[h], n * sizeof(xb_copy_item), cudaMemcpyHostToDevice, stream));
+  BLAZE_CONDITION_THROW(xb_copy_segments(c.device[h], (int32_t)n, c.max_bytes, stream) == 0, xb_last_error());
+  c.items.clear();
+  c.max_bytes = 0;
+}
+
 BatchQueue::BatchQueue(const NetDef& def, std::shared_ptr<store::SparsePuller> puller,
                        std::shared_ptr<ConstantStore> constants, const SchedulerOptions& options)
-    : def_(def), puller_(puller), constants_(constants), options_(options) {
+    : def_(def), puller_(puller), constants_(constants), options_(options), copies_(new CopyTable()) {
   if (options_.max_batch_size < 1) options_.max_batch_size = 1;
   if (options_.batch_timeout_micros < 0) options_.batch_timeout_micros = 0;
   if (options_.max_enqueued_batches < 1) options_.max_enqueued_batches = 1;
@@ -116,6 +166,7 @@ void BatchQueue::Loop() {
   // the merged net's operators and blobs belong to this thread's stream: release them here
   net_.reset();
   ws_.reset();
+  copies_.reset();
 }
 
 void BatchQueue::MergeInputs(const std::vector<Task>& batch, cudaStream_t stream) {
@@ -127,8 +178,7 @@ void BatchQueue::MergeInputs(const std::vector<Task>& batch, cudaStream_t stream
     dst->set_data_type(first->data_type());
     if (shape.empty()) {                               // a scalar cannot be stacked: the head's value stands
       dst->Reshape(shape);
-      if (first->bytes())
-        CUDA_CHECK(cudaMemcpyAsync(dst->as<void>(), first->as<void>(), first->bytes(), cudaMemcpyDeviceToDevice, stream));
+      AddCopy(first->as<void>(), dst->as<void>(), first->bytes());
       continue;
     }
     TIndex total = 0;
@@ -138,11 +188,11 @@ void BatchQueue::MergeInputs(const std::vector<Task>& batch, cudaStream_t stream
     size_t offset = 0;
     for (const auto& t : batch) {
       const Blob* src = t.ws->GetBlob(v.name);
-      if (src->bytes())
-        CUDA_CHECK(cudaMemcpyAsync(dst->as<char>() + offset, src->as<void>(), src->bytes(), cudaMemcpyDeviceToDevice, stream));
+      AddCopy(src->as<void>(), dst->as<char>() + offset, src->bytes());
       offset += src->bytes();
     }
   }
+  FlushCopies(stream);
 }
 
 void BatchQueue::SplitOutputs(const std::vector<Task>& batch, cudaStream_t stream) {
@@ -178,10 +228,11 @@ void BatchQueue::SplitOutputs(const std::vector<Task>& batch, cudaStream_t strea
       dst->set_data_type(src->data_type());
       dst->Reshape(shape);
       const size_t n = row_bytes * shape[0];
-      if (n) CUDA_CHECK(cudaMemcpyAsync(dst->as<void>(), src->as<char>() + offset, n, cudaMemcpyDeviceToDevice, stream));
+      AddCopy(src->as<char>() + offset, dst->as<void>(), n);
       offset += n;
     }
   }
+  FlushCopies(stream);
 }
 
 void BatchQueue::RunBatch(std::vector<Task>* batch) {
@@ -208,6 +259,7 @@ void BatchQueue::RunBatch(std::vector<Task>* batch) {
     error = MakeString("batched forward failed: ", e.what());
     LOG_ERROR(error);
     if (stream) cudaStreamSynchronize(stream);
+    if (copies_) { copies_->items.clear(); copies_->max_bytes = 0; }
   }
   for (auto& t : *batch) {
     if (t.ready) cudaEventDestroy(t.ready);

@@ -78,11 +78,17 @@ class BatchQueue {
   void RunBatch(std::vector<Task>* batch);
   void MergeInputs(const std::vector<Task>& batch, cudaStream_t stream);
   void SplitOutputs(const std::vector<Task>& batch, cudaStream_t stream);
+  // All copies of a merge (or split) step go out as one descriptor table and one kernel launch
+  // (xb_copy_segments) instead of one cudaMemcpyAsync per blob and request.
+  void AddCopy(const void* src, void* dst, size_t bytes);
+  void FlushCopies(cudaStream_t stream);
+  struct CopyTable;
 
   NetDef def_;
   std::shared_ptr<store::SparsePuller> puller_;
   std::shared_ptr<ConstantStore> constants_;
   SchedulerOptions options_;
+  std::unique_ptr<CopyTable> copies_;
   std::unique_ptr<Workspace> ws_;       // created and destroyed on the batch thread
   std::unique_ptr<Net> net_;
   std::mutex mu_;
