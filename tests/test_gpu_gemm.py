@@ -181,6 +181,31 @@ def test_parallel_gemm_benchmark_config():
     np.testing.assert_allclose(Y0.float().cpu().numpy(), want0, rtol=2e-3, atol=2e-3)
 
 
+def test_tcgen05_engine_resident_weight_tile_runs():
+    """Many m tiles per weight tile and several tiles per CTA: the weight tile stays in shared memory while a
+    CTA walks a contiguous run of tiles, and is replaced when the run crosses into the next n tile or batch
+    entry. Ragged in every direction: last m tile 77 rows, last n tile 64 columns, last k block 8 wide."""
+    ops, capi = _ops()
+    rng = np.random.default_rng(12)
+    P, M, N, K = 3, 5197, 320, 200
+    A = rng.normal(0, 1, (P, M, K)).astype(np.float16)
+    W = (rng.normal(0, 1, (P, K, N)) / np.sqrt(K)).astype(np.float16)
+    bias = rng.normal(0, 0.1, (P, N)).astype(np.float32)
+    c = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    Wk = ops.pack_weight_kmajor(c(W), torch.float16, batch=P)
+    ldk = Wk.shape[-1]
+    slope = torch.full((1,), 0.25, device="cuda")
+    Y = torch.zeros((P, M, N), dtype=torch.float16, device="cuda")
+    ops.gemm(c(A), Wk, Y=Y, bias=c(bias), trans_b=True, batch=P, M=M, N=N, K=K, lda=K, ldb=ldk, ldy=N,
+             strides=(M * K, N * ldk, N, M * N), bias_kind=capi.XB_BIAS_ROW, epilogue=capi.XB_EPI_PRELU,
+             ep=(slope, None, None), ep_count=1, engine=capi.XB_GEMM_TCGEN05)
+    _status_ok(ops)
+    got = Y.float().cpu().numpy()
+    for p in range(P):
+        want = orc.prelu(orc.gemm_op(A[p].astype(np.float32), W[p].astype(np.float32), bias[p]), np.array([0.25], np.float32))
+        np.testing.assert_allclose(got[p], want, rtol=2e-3, atol=2e-3)
+
+
 def test_auto_engine_falls_back_for_layouts_tma_cannot_take():
     ops, capi = _ops()
     rng = np.random.default_rng(5)

@@ -5,15 +5,18 @@
 //   A [M,K] row-major (K-major), B [N,K] row-major (K-major), fp16 or bf16,
 //   fp32 accumulation in tensor memory.
 //
-// One CTA computes one 128 x BLOCK_N output tile. Warp 0 streams 128x64 A
-// tiles and BLOCK_Nx64 B tiles through a 4-stage shared-memory ring with TMA
-// (128-byte swizzle, out-of-range rows/columns zero-filled by the TMA unit,
-// so M, N and K tails need no padding in HBM). Warp 1 issues tcgen05.mma
-// (128 x BLOCK_N x 16 per instruction) into a TMEM accumulator and releases
-// ring slots with tcgen05.commit. Warps 2-5 read the accumulator with
-// tcgen05.ld (one output row per thread), apply bias and activation and store
-// with an arbitrary row stride, which is what lets parallel branches write
-// side by side into one wide output (axis-1 concat) or stacked (axis 0).
+// Persistent kernel, one CTA per SM, 128 x BLOCK_N output tiles. Warp 0 streams
+// 128x64 A tiles (and BLOCK_Nx64 B tiles) through a shared-memory ring with TMA
+// (as many stages as fit; 128-byte swizzle, out-of-range rows/columns zero-filled
+// by the TMA unit, so M, N and K tails need no padding in HBM). When the whole
+// B tile (all of K) is small and many m tiles share it, it is loaded once and stays
+// resident while the CTA walks a contiguous run of tiles. Warp 1 issues
+// tcgen05.mma (128 x BLOCK_N x 16 per instruction) into one of two TMEM
+// accumulators and releases ring slots with tcgen05.commit. Warps 2-17 read the
+// accumulator with tcgen05.ld (one output row per thread, a quarter of the
+// columns per warpgroup), apply bias and activation and store with an arbitrary
+// row stride, which is what lets parallel branches write side by side into one
+// wide output (axis-1 concat) or stacked (axis 0).
 #include <algorithm>
 #include <cstring>
 
@@ -28,11 +31,14 @@ namespace {
 
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;
-constexpr int STAGES = 4;
+constexpr int MAX_STAGES = 8;       // the launch picks as many as fit in shared memory (at least 2)
+constexpr int SMEM_BUDGET = 220 * 1024;
 constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;
 
 struct UmmaGemmParams {
-  int M, N, K, block_n, tmem_cols, tiles_m, tiles_n, batch;
+  int M, N, K, block_n, tmem_cols, tiles_m, tiles_n, batch, stages;
+  int b_resident;        // the B tile (all of K) stays in shared memory while consecutive tiles share it
+  uint32_t tiles_per_cta;
   float alpha, beta;
   int a_batched, b_batched;
   const void* bias; int64_t ldbias, stride_bias; int bias_kind, bias_dtype, bias_group;
@@ -62,8 +68,115 @@ __device__ __forceinline__ void store_row16(TOut* dst, const float (&v)[16], int
   }
 }
 
-constexpr int EPI_WARPS = 8;
+// 16 epilogue warps: four per TMEM lane quarter, each owning a quarter of the tile's columns, so every
+// scheduler has four of them to hide the TMEM round trip and the store latency behind one another
+constexpr int EPI_WARPS = 16;
 constexpr int GEMM_THREADS = 64 + EPI_WARPS * 32;
+
+// 16 results of one output row as one (fp32: four) 16-byte store(s)
+template <typename TOut>
+__device__ __forceinline__ void store16_vec(TOut* dst, const float (&v)[16]);
+template <>
+__device__ __forceinline__ void store16_vec<float>(float* dst, const float (&v)[16]) {
+  float4* d = reinterpret_cast<float4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+template <>
+__device__ __forceinline__ void store16_vec<__half>(__half* dst, const float (&v)[16]) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  d[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  d[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+template <>
+__device__ __forceinline__ void store16_vec<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[16]) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  d[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  d[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// Activation of 16 adjacent columns of one row; the per-column parameters sit in shared memory and are
+// read as 16-byte vectors (all lanes read the same address: a broadcast).
+template <int KIND>
+__device__ __forceinline__ void epi_apply16(float (&v)[16], const float* s_a, const float* s_b, const float* s_c) {
+  if constexpr (KIND != XB_EPI_NONE) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (KIND == XB_EPI_PRELU) {
+      const float4 a = reinterpret_cast<const float4*>(s_a)[j];
+      // x * (x < 0 ? w : 1): the same value as act_prelu for every x, signed zeros and NaN included
+      v[4 * j] *= v[4 * j] < 0.f ? a.x : 1.f;
+      v[4 * j + 1] *= v[4 * j + 1] < 0.f ? a.y : 1.f;
+      v[4 * j + 2] *= v[4 * j + 2] < 0.f ? a.z : 1.f;
+      v[4 * j + 3] *= v[4 * j + 3] < 0.f ? a.w : 1.f;
+    } else if (KIND == XB_EPI_DICE) {
+      const float4 g = reinterpret_cast<const float4*>(s_a)[j];
+      const float4 b = reinterpret_cast<const float4*>(s_b)[j];
+      const float4 c = reinterpret_cast<const float4*>(s_c)[j];
+      const float gg[4] = {g.x, g.y, g.z, g.w}, bb[4] = {b.x, b.y, b.z, b.w}, cc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float x = v[4 * j + i];
+        const float pr = __fdividef(1.f, 1.f + __expf(-fmaf(x, cc[i], bb[i])));
+        v[4 * j + i] = x * fmaf(pr, 1.f - gg[i], gg[i]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[4 * j + i] = act_sigmoid(v[4 * j + i]);
+    }
+  }
+  }
+}
+
+// Epilogue of a tile that lies fully inside the output, with a per-column bias (or none) and 16-byte
+// aligned rows: this thread's row, columns [16 * c_begin, 16 * c_end) of the tile.
+template <typename TOut, int KIND>
+__device__ __forceinline__ void epi_tile_fast(uint32_t tmem_row, int c_begin, int c_end, float alpha,
+                                              const float* s_bias, const float* s_a, const float* s_b,
+                                              const float* s_c, TOut* yrow) {
+  using namespace umma;
+  for (int cg = c_begin; cg < c_end; cg += 2) {
+    // two chunks per TMEM round trip when the thread owns two more
+    uint32_t raw[32];
+    const bool two = cg + 1 < c_end;                                    // uniform across the CTA
+    if (two) {
+      tmem_ld32_nowait(tmem_row + (uint32_t)(cg * 16), raw);
+    } else {
+#pragma unroll
+      for (int i = 16; i < 32; ++i) raw[i] = 0u;
+      tmem_ld16_lo_nowait(tmem_row + (uint32_t)(cg * 16), raw);
+    }
+    tmem_wait_ld(raw);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (u == 1 && !two) break;
+      const int c = (cg + u) * 16;
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 b = reinterpret_cast<const float4*>(s_bias + c)[j];
+        v[4 * j] = fmaf(alpha, __uint_as_float(raw[16 * u + 4 * j]), b.x);
+        v[4 * j + 1] = fmaf(alpha, __uint_as_float(raw[16 * u + 4 * j + 1]), b.y);
+        v[4 * j + 2] = fmaf(alpha, __uint_as_float(raw[16 * u + 4 * j + 2]), b.z);
+        v[4 * j + 3] = fmaf(alpha, __uint_as_float(raw[16 * u + 4 * j + 3]), b.w);
+      }
+      epi_apply16<KIND>(v, s_a + c, s_b + c, s_c + c);
+      store16_vec<TOut>(yrow + c, v);
+    }
+  }
+}
 
 template <typename TOut>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -74,20 +187,33 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int b_stage_bytes = p.block_n * BLOCK_K * 2;
   uint8_t* smem_a = smem;
-  uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
-  __shared__ __align__(8) uint64_t full_bar[STAGES];
-  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  const int STAGES = p.stages;
+  uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;      // per-stage B tiles, or the resident B tile (all k blocks)
+  __shared__ __align__(8) uint64_t b_full, b_free;
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
-  const int64_t tiles_mn = (int64_t)p.tiles_m * p.tiles_n;
-  const int64_t total_tiles = tiles_mn * p.batch;
+  // tile numbers fit 31 bits (checked by the host): 32-bit divisions, a few per tile and thread
+  const uint32_t tiles_mn = (uint32_t)p.tiles_m * (uint32_t)p.tiles_n;
+  const uint32_t total_tiles = tiles_mn * (uint32_t)p.batch;
   const uint32_t acc_stride = (uint32_t)p.tmem_cols / 2;
+  // Tile sequence of this CTA, the same for every role. With a resident B tile each CTA takes a contiguous
+  // run (m fastest), so that B changes once or twice per CTA; otherwise CTAs interleave, so that the CTAs
+  // running at the same time read the same B tile from L2.
+  const bool bres = p.b_resident != 0;
+  const uint32_t tile_first = bres ? blockIdx.x * p.tiles_per_cta : blockIdx.x;
+  const uint32_t tile_step = bres ? 1u : gridDim.x;
+  const uint32_t tile_end = bres ? min(total_tiles, tile_first + p.tiles_per_cta) : total_tiles;
+  const int b_bytes_per_load = bres ? 0 : b_stage_bytes;
 
   if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&b_full), 1);
+    mbar_init(smem_u32(&b_free), 1);
     for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&acc_full[s]), 1); mbar_init(smem_u32(&acc_empty[s]), EPI_WARPS); }
     fence_barrier_init();
@@ -100,46 +226,65 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
 
-  // every role walks the same tile sequence: m fastest, so concurrent CTAs share the B tile in L2
   if (warp == 0) {
     if (lane == 0) {
-      int kbg = 0;
+      int s = 0;
+      uint32_t ph = 0;                 // stage and its phase: the stage counter wraps, the phase flips
+      uint32_t b_loads = 0;
+      int cur_n0 = -1, cur_b = -1;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (uint32_t tile = tile_first; tile < tile_end && ok; tile += tile_step) {
         const int b = (int)(tile / tiles_mn);
-        const int64_t rem = tile - (int64_t)b * tiles_mn;
-        const int m0 = (int)(rem % p.tiles_m) * BLOCK_M, n0 = (int)(rem / p.tiles_m) * p.block_n;
-        for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
-          const int s = kbg % STAGES;
-          const uint32_t ph = (uint32_t)(kbg / STAGES) & 1u;
+        const uint32_t rem = tile - (uint32_t)b * tiles_mn, nt = rem / (uint32_t)p.tiles_m;
+        const int m0 = (int)(rem - nt * (uint32_t)p.tiles_m) * BLOCK_M, n0 = (int)nt * p.block_n;
+        if (bres && (n0 != cur_n0 || b != cur_b)) {
+          cur_n0 = n0; cur_b = b;
+          // the MMAs that read the previous B tile have completed (signalled after the last tile that used it)
+          if (b_loads > 0) ok = mbar_wait(smem_u32(&b_free), (b_loads - 1) & 1u, 5);
+          if (!ok) break;
+          mbar_arrive_expect_tx(smem_u32(&b_full), (uint32_t)(num_kb * b_stage_bytes));
+          for (int kb = 0; kb < num_kb; ++kb)
+            tma_load_3d(smem_u32(smem_b + kb * b_stage_bytes), &map_b, smem_u32(&b_full), kb * BLOCK_K, n0,
+                        p.b_batched ? b : 0);
+          ++b_loads;
+        }
+        for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
           ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, 1);
           if (!ok) break;
-          mbar_arrive_expect_tx(smem_u32(&full_bar[s]), (uint32_t)(A_STAGE_BYTES + b_stage_bytes));
+          mbar_arrive_expect_tx(smem_u32(&full_bar[s]), (uint32_t)(A_STAGE_BYTES + b_bytes_per_load));
           tma_load_3d(smem_u32(smem_a + s * A_STAGE_BYTES), &map_a, smem_u32(&full_bar[s]), kb * BLOCK_K, m0,
                       p.a_batched ? b : 0);
-          tma_load_3d(smem_u32(smem_b + s * b_stage_bytes), &map_b, smem_u32(&full_bar[s]), kb * BLOCK_K, n0,
-                      p.b_batched ? b : 0);
+          if (!bres)
+            tma_load_3d(smem_u32(smem_b + s * b_stage_bytes), &map_b, smem_u32(&full_bar[s]), kb * BLOCK_K, n0,
+                        p.b_batched ? b : 0);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      int kbg = 0, it = 0;
+      int s = 0, it = 0;
+      uint32_t ph = 0;
+      uint32_t b_loads = 0;
+      uint32_t cur_bn = 0xffffffffu;             // (batch, n tile) of the resident B tile
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      for (uint32_t tile = tile_first; tile < tile_end && ok; tile += tile_step, ++it) {
         const int as = it & 1;
         ok = mbar_wait(smem_u32(&acc_empty[as]), ((uint32_t)(it >> 1) & 1u) ^ 1u, 4);   // epilogue drained it
         if (!ok) break;
+        if (bres && tile / (uint32_t)p.tiles_m != cur_bn) {
+          cur_bn = tile / (uint32_t)p.tiles_m;
+          ok = mbar_wait(smem_u32(&b_full), b_loads & 1u, 6);
+          if (!ok) break;
+          ++b_loads;
+        }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + as * acc_stride;
-        for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
-          const int s = kbg % STAGES;
-          const uint32_t ph = (uint32_t)(kbg / STAGES) & 1u;
+        for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
           ok = mbar_wait(smem_u32(&full_bar[s]), ph, 2);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem_a + s * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(smem_b + s * b_stage_bytes);
+          const uint32_t b_addr = smem_u32(smem_b + (bres ? kb : s) * b_stage_bytes);
 #pragma unroll
           for (int k = 0; k < BLOCK_K / 16; ++k) {
             const uint64_t da = make_desc_sw128(a_addr + k * 32, 1024);
@@ -149,37 +294,41 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           mma_commit(smem_u32(&empty_bar[s]));     // slot free once these MMAs have read it
         }
         mma_commit(smem_u32(&acc_full[as]));       // accumulator complete
+        // the next tile of this CTA needs another B tile: tell the producer when these MMAs are done with this one
+        if (bres && ok && tile + tile_step < tile_end && (tile + tile_step) / (uint32_t)p.tiles_m != cur_bn)
+          mma_commit(smem_u32(&b_free));
       }
     }
   } else {
-    // epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32); the two warpgroups split the columns.
+    // epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32); the four warpgroups split the columns.
     // Per-column operands (bias, activation parameters) are staged in shared memory once per (n tile,
     // batch) - a persistent CTA walks m tiles first, so that is rare - and each thread loads all the
     // accumulator chunks it owns before it waits, so one TMEM round trip is exposed per tile.
     const int ew = warp - 2;
     const int q = warp & 3;
-    const int half_id = ew >> 2;
+    const int part = ew >> 2;
     const int row = q * 32 + lane;
     const int chunks = p.block_n / 16;
-    const int c_begin = half_id ? (chunks + 1) / 2 : 0, c_end = half_id ? chunks : (chunks + 1) / 2;
+    const int c_begin = chunks * part / 4, c_end = chunks * (part + 1) / 4;
     const bool vec_base = ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0) && ((p.ldy * sizeof(TOut)) % 16 == 0) &&
                           ((p.stride_y * sizeof(TOut)) % 16 == 0);
-    float* s_bias = reinterpret_cast<float*>(smem + STAGES * (A_STAGE_BYTES + b_stage_bytes));   // [4][256]
+    float* s_bias = reinterpret_cast<float*>(smem + STAGES * A_STAGE_BYTES +
+                                             (bres ? num_kb : STAGES) * b_stage_bytes);           // [4][256]
     float* s_a = s_bias + 256;
     float* s_b = s_a + 256;
     float* s_c = s_b + 256;
     int it = 0, cur_n0 = -1, cur_b = -1;
     bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+    for (uint32_t tile = tile_first; tile < tile_end && ok; tile += tile_step, ++it) {
       const int b = (int)(tile / tiles_mn);
-      const int64_t rem = tile - (int64_t)b * tiles_mn;
-      const int m0 = (int)(rem % p.tiles_m) * BLOCK_M, n0 = (int)(rem / p.tiles_m) * p.block_n;
+      const uint32_t rem = tile - (uint32_t)b * tiles_mn, nt = rem / (uint32_t)p.tiles_m;
+      const int m0 = (int)(rem - nt * (uint32_t)p.tiles_m) * BLOCK_M, n0 = (int)nt * p.block_n;
       const int as = it & 1;
       const int gm = m0 + row;
-      const int brow = p.bias_group > 1 ? gm / p.bias_group : gm;      // bias row of this output row
+      const int brow = p.bias_group > 1 ? (int)((uint32_t)gm / (uint32_t)p.bias_group) : gm;   // bias row of this output row
       if (n0 != cur_n0 || b != cur_b) {
         cur_n0 = n0; cur_b = b;
-        asm volatile("bar.sync 2, 256;" ::: "memory");                  // everyone is done with the old columns
+        asm volatile("bar.sync 2, 512;" ::: "memory");                  // everyone is done with the old columns
         const int e = ew * 32 + lane, gn = n0 + e;
         if (e < p.block_n) {
           const bool in = gn < p.N;
@@ -194,23 +343,36 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           s_bias[e] = bv; s_a[e] = pa; s_b[e] = pb; s_c[e] = pc;
         }
-        asm volatile("bar.sync 2, 256;" ::: "memory");
+        asm volatile("bar.sync 2, 512;" ::: "memory");
       }
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_full[as]), (uint32_t)(it >> 1) & 1u, 3));
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + as * acc_stride + ((uint32_t)(q * 32) << 16);
       TOut* yrow = reinterpret_cast<TOut*>(p.Y) + (int64_t)b * p.stride_y + (int64_t)gm * p.ldy;
-      for (int cg = c_begin; cg < c_end; cg += 4) {
-        uint32_t raw[4][16];
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (cg + u < c_end) tmem_ld16_nowait(tmem_acc + (uint32_t)((cg + u) * 16), raw[u]);   // uniform per warp
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (cg + u < c_end) tmem_wait_ld(raw[u]);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
+      if (vec_base && p.bias_kind != XB_BIAS_FULL && m0 + BLOCK_M <= p.M && n0 + p.block_n <= p.N &&
+          (n0 * sizeof(TOut)) % 16 == 0) {
+        // the common case, without the per-chunk edge and bias-matrix handling of the loop below
+        switch (p.epi.kind) {
+          case XB_EPI_PRELU:
+            epi_tile_fast<TOut, XB_EPI_PRELU>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0); break;
+          case XB_EPI_DICE:
+            epi_tile_fast<TOut, XB_EPI_DICE>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0); break;
+          case XB_EPI_SIGMOID:
+            epi_tile_fast<TOut, XB_EPI_SIGMOID>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0); break;
+          default:
+            epi_tile_fast<TOut, XB_EPI_NONE>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0); break;
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&acc_empty[as]));
+        continue;
+      }
+      for (int cg = c_begin; cg < c_end; ++cg) {
+        uint32_t raw[1][16];
+        tmem_ld16_nowait(tmem_acc + (uint32_t)(cg * 16), raw[0]);
+        tmem_wait_ld(raw[0]);
+        for (int u = 0; u < 1; ++u) {
           const int c = (cg + u) * 16;
           const int gn0 = n0 + c;
           int valid = p.N - gn0;
@@ -323,7 +485,7 @@ int launch_umma(const CUtensorMap& ma, const CUtensorMap& mb, const UmmaGemmPara
                 cudaStream_t s) {
   static bool attr_set = false;   // per instantiation
   if (!attr_set) {
-    XB_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    XB_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 6 * 1024));
     attr_set = true;
   }
   gemm_umma_kernel<TOut><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, p);
@@ -354,10 +516,28 @@ int gemm_umma(const xb_gemm_args& a, cudaStream_t stream) {
   p.tiles_n = (a.N + p.block_n - 1) / p.block_n;
   p.batch = a.batch;
   const int64_t total = (int64_t)p.tiles_m * p.tiles_n * p.batch;
+  XB_REQUIRE(total < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_gemm: %lld output tiles are too many for one call", (long long)total);
   // persistent: one CTA per SM walks the tiles; the accumulator is double-buffered in TMEM so the
   // epilogue of one tile overlaps the loads and MMAs of the next
   dim3 grid((unsigned)std::min<int64_t>(total, sm_count()));
-  const size_t smem = (size_t)STAGES * (A_STAGE_BYTES + p.block_n * BLOCK_K * 2) + 4 * 256 * sizeof(float) + 1024;
+  // When the whole B tile (all of K) is small and several m tiles share it, it is loaded once and stays in
+  // shared memory: re-reading it from L2 for every tile doubles the L2-to-SM traffic of a thin GEMM, which
+  // then bounds the kernel below the HBM rate.
+  const int b_stage_bytes = p.block_n * BLOCK_K * 2;
+  const int num_kb = (a.K + BLOCK_K - 1) / BLOCK_K;
+  const int grid_ctas = (int)std::min<int64_t>(total, sm_count());
+  p.tiles_per_cta = (uint32_t)((total + grid_ctas - 1) / grid_ctas);
+  p.b_resident = (int64_t)num_kb * b_stage_bytes <= 96 * 1024 && p.tiles_m >= 4 && p.tiles_per_cta >= 2;
+  size_t smem;
+  if (p.b_resident) {
+    const int b_bytes = num_kb * b_stage_bytes;
+    p.stages = std::max(2, std::min(MAX_STAGES, (SMEM_BUDGET - b_bytes) / A_STAGE_BYTES));
+    smem = (size_t)p.stages * A_STAGE_BYTES + b_bytes + 4 * 256 * sizeof(float) + 1024;
+  } else {
+    const int stage_bytes = A_STAGE_BYTES + b_stage_bytes;
+    p.stages = std::max(2, std::min(MAX_STAGES, SMEM_BUDGET / stage_bytes));
+    smem = (size_t)p.stages * stage_bytes + 4 * 256 * sizeof(float) + 1024;
+  }
   switch (a.y_dtype) {
     case XB_F16: return launch_umma<__half>(ma, mb, p, grid, smem, stream);
     case XB_BF16: return launch_umma<__nv_bfloat16>(ma, mb, p, grid, smem, stream);
