@@ -140,12 +140,45 @@ __device__ __forceinline__ void epi_apply16(float (&v)[16], const float* s_a, co
   }
 }
 
+// 8 results as one 16-byte piece of 2-byte elements
+template <typename TOut>
+__device__ __forceinline__ uint4 pack8(const float* v);
+template <>
+__device__ __forceinline__ uint4 pack8<__half>(const float* v) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+__device__ __forceinline__ uint4 pack8<__nv_bfloat16>(const float* v) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+__device__ __forceinline__ uint4 pack8<float>(const float*) { return make_uint4(0, 0, 0, 0); }   // not used
+
+constexpr int EPI_STAGE_BYTES = 32 * 64;      // per epilogue warp: 32 rows x 32 two-byte results
+
 // Epilogue of a tile that lies fully inside the output, with a per-column bias (or none) and 16-byte
 // aligned rows: this thread's row, columns [16 * c_begin, 16 * c_end) of the tile.
+// Two-byte outputs go through a 2 KB staging area of the warp: a thread holds 64 contiguous bytes of its
+// own row, and a store instruction of one piece per lane would touch 32 different lines; after the
+// exchange the 32 lanes of an instruction write 8 rows x 64 contiguous bytes. Piece j of row l is kept at
+// position j ^ ((l >> 1) & 3) of the row, which makes both the writes (lane = row) and the reads (four
+// lanes per row) free of bank conflicts.
 template <typename TOut, int KIND>
 __device__ __forceinline__ void epi_tile_fast(uint32_t tmem_row, int c_begin, int c_end, float alpha,
                                               const float* s_bias, const float* s_a, const float* s_b,
-                                              const float* s_c, TOut* yrow) {
+                                              const float* s_c, TOut* yrow, int64_t ldy, uint4* stage, int lane) {
   using namespace umma;
   for (int cg = c_begin; cg < c_end; cg += 2) {
     // two chunks per TMEM round trip when the thread owns two more
@@ -173,7 +206,24 @@ __device__ __forceinline__ void epi_tile_fast(uint32_t tmem_row, int c_begin, in
         v[4 * j + 3] = fmaf(alpha, __uint_as_float(raw[16 * u + 4 * j + 3]), b.w);
       }
       epi_apply16<KIND>(v, s_a + c, s_b + c, s_c + c);
-      store16_vec<TOut>(yrow + c, v);
+      if (sizeof(TOut) == 2 && two) {
+        const int sw = (lane >> 1) & 3;
+        stage[lane * 4 + ((2 * u) ^ sw)] = pack8<TOut>(v);
+        stage[lane * 4 + ((2 * u + 1) ^ sw)] = pack8<TOut>(v + 8);
+      } else {
+        store16_vec<TOut>(yrow + c, v);
+      }
+    }
+    if (sizeof(TOut) == 2 && two) {
+      __syncwarp();
+      TOut* base = yrow + cg * 16 + (lane & 3) * 8;          // this lane's 16-byte column slot, in its own row
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = 8 * i + (lane >> 2);
+        const uint4 x = stage[r * 4 + ((lane & 3) ^ ((r >> 1) & 3))];
+        *reinterpret_cast<uint4*>(base + (int64_t)(r - lane) * ldy) = x;
+      }
+      __syncwarp();                                          // the next round overwrites the staging area
     }
   }
 }
@@ -314,6 +364,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                           ((p.stride_y * sizeof(TOut)) % 16 == 0);
     float* s_bias = reinterpret_cast<float*>(smem + STAGES * A_STAGE_BYTES +
                                              (bres ? num_kb : STAGES) * b_stage_bytes);           // [4][256]
+    uint4* stage = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(s_bias + 4 * 256) + ew * EPI_STAGE_BYTES);
     float* s_a = s_bias + 256;
     float* s_b = s_a + 256;
     float* s_c = s_b + 256;
@@ -355,13 +406,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // the common case, without the per-chunk edge and bias-matrix handling of the loop below
         switch (p.epi.kind) {
           case XB_EPI_PRELU:
-            epi_tile_fast<TOut, XB_EPI_PRELU>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0); break;
+            epi_tile_fast<TOut, XB_EPI_PRELU>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0, p.ldy, stage, lane); break;
           case XB_EPI_DICE:
-            epi_tile_fast<TOut, XB_EPI_DICE>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0); break;
+            epi_tile_fast<TOut, XB_EPI_DICE>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0, p.ldy, stage, lane); break;
           case XB_EPI_SIGMOID:
-            epi_tile_fast<TOut, XB_EPI_SIGMOID>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0); break;
+            epi_tile_fast<TOut, XB_EPI_SIGMOID>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0, p.ldy, stage, lane); break;
           default:
-            epi_tile_fast<TOut, XB_EPI_NONE>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0); break;
+            epi_tile_fast<TOut, XB_EPI_NONE>(tmem_acc, c_begin, c_end, p.alpha, s_bias, s_a, s_b, s_c, yrow + n0, p.ldy, stage, lane); break;
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -528,15 +579,17 @@ int gemm_umma(const xb_gemm_args& a, cudaStream_t stream) {
   const int grid_ctas = (int)std::min<int64_t>(total, sm_count());
   p.tiles_per_cta = (uint32_t)((total + grid_ctas - 1) / grid_ctas);
   p.b_resident = (int64_t)num_kb * b_stage_bytes <= 96 * 1024 && p.tiles_m >= 4 && p.tiles_per_cta >= 2;
+  // after the ring: per-column epilogue parameters [4][256] fp32, then the epilogue warps' staging areas
+  const int tail = 4 * 256 * (int)sizeof(float) + (a.y_dtype == XB_F32 ? 0 : EPI_WARPS * EPI_STAGE_BYTES);
   size_t smem;
   if (p.b_resident) {
     const int b_bytes = num_kb * b_stage_bytes;
-    p.stages = std::max(2, std::min(MAX_STAGES, (SMEM_BUDGET - b_bytes) / A_STAGE_BYTES));
-    smem = (size_t)p.stages * A_STAGE_BYTES + b_bytes + 4 * 256 * sizeof(float) + 1024;
+    p.stages = std::max(2, std::min(MAX_STAGES, (SMEM_BUDGET - tail - b_bytes) / A_STAGE_BYTES));
+    smem = (size_t)p.stages * A_STAGE_BYTES + b_bytes + tail + 1024;
   } else {
     const int stage_bytes = A_STAGE_BYTES + b_stage_bytes;
-    p.stages = std::max(2, std::min(MAX_STAGES, SMEM_BUDGET / stage_bytes));
-    smem = (size_t)p.stages * stage_bytes + 4 * 256 * sizeof(float) + 1024;
+    p.stages = std::max(2, std::min(MAX_STAGES, (SMEM_BUDGET - tail) / stage_bytes));
+    smem = (size_t)p.stages * stage_bytes + tail + 1024;
   }
   switch (a.y_dtype) {
     case XB_F16: return launch_umma<__half>(ma, mb, p, grid, smem, stream);
