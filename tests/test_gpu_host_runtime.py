@@ -164,3 +164,55 @@ def test_binary_netdef_file(tmp_path):
     np.testing.assert_allclose(p.output("y"), 1 / (1 + np.exp(-x)), rtol=1e-6)
     p.close()
     mgr.close()
+
+
+@pytest.mark.parametrize("bn_first,trans_b,dtype", [(True, False, 12), (False, False, 12), (True, True, 1), (False, False, 1)])
+def test_batchnorm_folds_into_the_neighbouring_gemm(bn_first, trans_b, dtype):
+    """LoadModel's optimisation pass folds a BatchNormalization with constant parameters into the Gemm it feeds
+    (the shape of the reference DIN graph: bn_layer -> inner_product_layer) or follows; the folded graph is one
+    kernel-library call (with the Dice behind it fused as well) and gives the un-folded graph's values."""
+    api = _api()
+    import orc
+    rng = np.random.default_rng(7 + 2 * bn_first + trans_b)
+    M, K, N = 260, 72, 80
+    npdt = np.float16 if dtype == 12 else np.float32
+    cast = lambda a: a.astype(npdt)
+    W, b = cast(rng.normal(0, 1 / 8, (K, N))), cast(rng.normal(0, 0.1, N))
+    c = K if bn_first else N
+    gamma, beta = cast(rng.uniform(0.5, 1.5, c)), cast(rng.normal(0, 0.2, c))
+    mean, var = cast(rng.normal(0, 0.3, c)), cast(rng.uniform(0.5, 2.0, c))
+    g, mu, dv = cast(rng.uniform(0, 0.5, N)), cast(rng.normal(0, 0.1, N)), cast(rng.uniform(0.5, 1.5, N))
+    consts = [api.constant_text("W", W.T if trans_b else W, dtype), api.constant_text("b", b, dtype)]
+    consts += [api.constant_text(n, a, dtype) for n, a in (("gamma", gamma), ("beta", beta), ("mean", mean), ("var", var),
+                                                           ("g", g), ("mu", mu), ("dv", dv))]
+    gemm_args = {"transB": 1} if trans_b else None
+    if bn_first:
+        body = [api.op_text("BatchNormalization", ["x", "gamma", "beta", "mean", "var"], ["xn"], {"eps": 0.001}),
+                api.op_text("Gemm", ["xn", "W", "b"], ["h"], gemm_args)]
+    else:
+        body = [api.op_text("Gemm", ["x", "W", "b"], ["h0"], gemm_args),
+                api.op_text("BatchNormalization", ["h0", "gamma", "beta", "mean", "var"], ["h"], {"eps": 0.001})]
+    body.append(api.op_text("Dice", ["h", "g", "mu", "dv"], ["y"]))
+    text = api.netdef_text(consts + body, [("x", dtype)], [("y", dtype)])
+    f32 = lambda a: a.astype(np.float32)
+    x = cast(rng.normal(0, 1, (M, K)))
+    if bn_first:
+        h = orc.gemm_op(orc.batchnorm(f32(x), f32(gamma), f32(beta), f32(mean), f32(var), 0.001), f32(W), f32(b))
+    else:
+        h = orc.batchnorm(orc.gemm_op(f32(x), f32(W), f32(b)), f32(gamma), f32(beta), f32(mean), f32(var), 0.001)
+    want = orc.dice(h, f32(g), f32(mu), f32(dv))
+    got = {}
+    for optimize in (False, True):
+        mgr = api.PredictorManager()
+        mgr.load_model_text(text, optimize=optimize)
+        p = mgr.create_predictor()
+        keep = p.feed("x", x)
+        p.forward()
+        p.forward()
+        assert p.launches() == (1 if optimize else 3), p.launches()
+        got[optimize] = p.output("y").astype(np.float32)
+        p.close()
+        mgr.close()
+    tol = 5e-3 if dtype == 12 else 2e-4
+    np.testing.assert_allclose(got[False], want, rtol=tol, atol=tol)
+    np.testing.assert_allclose(got[True], want, rtol=tol, atol=tol)

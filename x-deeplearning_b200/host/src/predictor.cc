@@ -69,7 +69,10 @@ class PredictorManagerImpl {
 
   bool SetNet(const NetDef& def, bool optimize) {
     net_def_ = def;
-    if (optimize) FuseGemmActivation(&net_def_);
+    if (optimize) {
+      FoldBatchNorm(&net_def_);
+      FuseGemmActivation(&net_def_);
+    }
     loaded_ = true;
     return true;
   }

@@ -334,6 +334,164 @@ bool Net::Run() {
   return true;
 }
 
+// ---- BatchNormalization folding ---------------------------------------------------------------------
+namespace {
+// Values of a ConstantFill operator as fp32 (what the operator itself would upload), or false.
+bool ConstantValues(const OperatorDef& op, std::vector<float>* out, std::vector<int64_t>* shape, int* dtype) {
+  if (op.type != "ConstantFill" || op.output.size() != 1) return false;
+  const Argument* v = op.FindArg("value");
+  const Argument* sh = op.FindArg("shape");
+  const Argument* dt = op.FindArg("dtype");
+  if (!v || !sh) return false;
+  *dtype = dt && dt->has_i ? (int)dt->i : kFloat;
+  if (*dtype != kFloat && *dtype != kFloat16) return false;
+  *shape = sh->ints;
+  size_t n = 1;
+  for (int64_t d : *shape) n *= (size_t)d;
+  *out = v->floats;
+  if (out->empty() && !v->ints.empty()) out->assign(v->ints.begin(), v->ints.end());
+  if (out->empty() && v->has_f) out->assign(1, v->f);
+  if (out->size() != n) return false;
+  if (*dtype == kFloat16)                                   // the operator rounds to fp16 when it uploads
+    for (float& f : *out) f = HalfBitsToFloat(FloatToHalfBits(f));
+  return true;
+}
+
+OperatorDef MakeConstant(const std::string& name, const std::vector<float>& values, const std::vector<int64_t>& shape, int dtype) {
+  OperatorDef op;
+  op.type = "ConstantFill";
+  op.name = name;
+  op.output.push_back(name);
+  Argument a;
+  a.name = "shape"; a.ints = shape;
+  op.arg.push_back(a);
+  Argument d;
+  d.name = "dtype"; d.has_i = true; d.i = dtype;
+  op.arg.push_back(d);
+  Argument v;
+  v.name = "value"; v.floats = values;
+  op.arg.push_back(v);
+  return op;
+}
+}  // namespace
+
+// A BatchNormalization with constant parameters next to a Gemm with a constant weight is an affine map of the
+// Gemm's K (BN before) or N (BN after) axis: it folds into the weight and bias, computed here in fp32 from
+// the constants' values, and the BN node disappears. The reference DIN graph has this shape (bn_layer feeding
+// the first inner_product_layer, blaze/tools/example_model/din/model/graph_ulf.txt).
+void FoldBatchNorm(NetDef* def) {
+  bool changed = true;
+  int serial = 0;
+  while (changed) {
+    changed = false;
+    std::map<std::string, int> consumers, producer;
+    for (size_t i = 0; i < def->op.size(); ++i) {
+      for (const auto& in : def->op[i].input) ++consumers[in];
+      for (const auto& out : def->op[i].output) producer[out] = (int)i;
+    }
+    std::set<std::string> ext_out;
+    for (const auto& v : def->external_output) ext_out.insert(v.name);
+    auto constant = [&](const std::string& name, std::vector<float>* v, std::vector<int64_t>* sh, int* dt) {
+      auto it = producer.find(name);
+      return it != producer.end() && ConstantValues(def->op[it->second], v, sh, dt);
+    };
+    for (size_t bi = 0; bi < def->op.size() && !changed; ++bi) {
+      const OperatorDef bn = def->op[bi];
+      if (bn.type != "BatchNormalization" || bn.input.size() != 5 || bn.output.size() != 1) continue;
+      std::vector<float> gamma, beta, mean, var;
+      std::vector<int64_t> sh;
+      int dt = 0;
+      if (!constant(bn.input[1], &gamma, &sh, &dt) || !constant(bn.input[2], &beta, &sh, &dt) ||
+          !constant(bn.input[3], &mean, &sh, &dt) || !constant(bn.input[4], &var, &sh, &dt)) continue;
+      const size_t c = gamma.size();
+      if (beta.size() != c || mean.size() != c || var.size() != c) continue;
+      const Argument* ns = bn.FindArg("nosqrt");
+      const Argument* ep = bn.FindArg("eps");
+      const bool nosqrt = ns && (ns->has_i ? ns->i != 0 : ns->f != 0.f);
+      const float eps = ep && ep->has_f ? ep->f : 0.001f;
+      std::vector<float> scale(c), shift(c);               // y = x * scale + shift
+      for (size_t i = 0; i < c; ++i) {
+        scale[i] = gamma[i] / (nosqrt ? var[i] : sqrtf(var[i] + eps));
+        shift[i] = beta[i] - mean[i] * scale[i];
+      }
+      // the Gemm on the other side of the BN: its only consumer (BN first) or its producer (Gemm first)
+      int gi = -1;
+      bool bn_first = false;
+      const std::string& x = bn.input[0];
+      const std::string& y = bn.output[0];
+      if (consumers[y] == 1 && !ext_out.count(y)) {
+        for (size_t j = 0; j < def->op.size(); ++j)
+          if (def->op[j].type == "Gemm" && !def->op[j].input.empty() && def->op[j].input[0] == y) { gi = (int)j; bn_first = true; }
+      }
+      if (gi < 0 && consumers[x] == 1 && !ext_out.count(x) && producer.count(x) && def->op[producer[x]].type == "Gemm" &&
+          !def->op[producer[x]].FindArg("epilogue"))
+        gi = producer[x];
+      if (gi < 0) continue;
+      OperatorDef& g = def->op[gi];
+      if (g.input.size() < 2 || g.input.size() > 3 || g.output.size() != 1) continue;
+      auto flag = [&](const char* name) {
+        const Argument* a = g.FindArg(name);
+        return a && (a->has_i ? a->i != 0 : a->f != 0.f);
+      };
+      auto scalar = [&](const char* name) {
+        const Argument* a = g.FindArg(name);
+        return a ? (a->has_f ? a->f : (a->has_i ? (float)a->i : 1.f)) : 1.f;
+      };
+      if (flag("transA") || scalar("alpha") != 1.f || scalar("beta") != 1.f) continue;
+      const bool tb = flag("transB");
+      std::vector<float> W, bias;
+      std::vector<int64_t> wsh, bsh;
+      int wdt = 0, bdt = 0;
+      if (!constant(g.input[1], &W, &wsh, &wdt) || wsh.size() != 2) continue;
+      const size_t K = (size_t)(tb ? wsh[1] : wsh[0]), N = (size_t)(tb ? wsh[0] : wsh[1]);
+      const bool has_bias = g.input.size() == 3;
+      if (has_bias && (!constant(g.input[2], &bias, &bsh, &bdt) || bias.size() != N)) continue;
+      if (!has_bias) { bias.assign(N, 0.f); bdt = wdt; }
+      if (c != (bn_first ? K : N)) continue;
+      auto w = [&](size_t k, size_t n) -> float& { return tb ? W[n * K + k] : W[k * N + n]; };
+      if (bn_first) {
+        // (x * scale + shift) W + b = x (diag(scale) W) + (shift W + b)
+        for (size_t n = 0; n < N; ++n) {
+          double acc = bias[n];
+          for (size_t k = 0; k < K; ++k) acc += (double)shift[k] * w(k, n);
+          bias[n] = (float)acc;
+        }
+        for (size_t k = 0; k < K; ++k)
+          for (size_t n = 0; n < N; ++n) w(k, n) *= scale[k];
+      } else {
+        // (x W + b) * scale + shift = x (W diag(scale)) + (b * scale + shift)
+        for (size_t k = 0; k < K; ++k)
+          for (size_t n = 0; n < N; ++n) w(k, n) *= scale[n];
+        for (size_t n = 0; n < N; ++n) bias[n] = bias[n] * scale[n] + shift[n];
+      }
+      const std::string tag = "__bn" + std::to_string(serial++);
+      OperatorDef cw = MakeConstant(g.input[1] + tag, W, wsh, wdt);
+      OperatorDef cb = MakeConstant((has_bias ? g.input[2] : g.output[0] + "_bias") + tag, bias, {(int64_t)N}, bdt);
+      g.input.resize(3);
+      g.input[1] = cw.output[0];
+      g.input[2] = cb.output[0];
+      if (bn_first) g.input[0] = x; else g.output[0] = y;
+      // the BN node goes; the new constants are placed before every operator
+      def->op.erase(def->op.begin() + bi);
+      def->op.insert(def->op.begin(), cb);
+      def->op.insert(def->op.begin(), cw);
+      changed = true;
+    }
+  }
+  if (serial == 0) return;
+  // constants that only the folded nodes read (old weights, the BN parameters) would still be uploaded
+  std::map<std::string, int> consumers;
+  for (const auto& op : def->op)
+    for (const auto& in : op.input) ++consumers[in];
+  std::set<std::string> ext_out;
+  for (const auto& v : def->external_output) ext_out.insert(v.name);
+  for (size_t i = def->op.size(); i-- > 0;) {
+    const OperatorDef& op = def->op[i];
+    if (op.type == "ConstantFill" && op.output.size() == 1 && consumers[op.output[0]] == 0 && !ext_out.count(op.output[0]))
+      def->op.erase(def->op.begin() + i);
+  }
+}
+
 // ---- Gemm + activation fusion -----------------------------------------------------------------------
 void FuseGemmActivation(NetDef* def) {
   bool changed = true;

@@ -378,6 +378,9 @@ class Net {
 // Graph rewrite run by LoadModel(optimization_pass = true): folds Dice / PRelu / Sigmoid nodes
 // into the producing Gemm's epilogue when the Gemm output has no other consumer.
 void FuseGemmActivation(NetDef* def);
+// Run before it: folds a BatchNormalization with constant parameters into the weight and bias of the Gemm it
+// feeds or follows (constants re-computed in fp32), so the node disappears from the graph.
+void FoldBatchNorm(NetDef* def);
 
 // fp32 <-> fp16 on the host (round to nearest even)
 uint16_t FloatToHalfBits(float f);
