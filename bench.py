@@ -469,10 +469,29 @@ def run_micro(args):
             ops.gemm(A, Wk, Y=Y, bias=bias, trans_b=True, batch=P, M=M, N=N, K=K, lda=K, ldb=K, ldy=P * N,
                      strides=(M * K, N * K, N, N), bias_kind=capi.XB_BIAS_ROW, epilogue=capi.XB_EPI_PRELU,
                      ep=(slope, None, None), ep_count=1, engine=capi.XB_GEMM_TCGEN05)
+    elif args.micro == "gemm_mlp":
+        # first layer of the large-table configuration's MLP at 8x its per-GPU batch: compute-bound (512 flop/B)
+        M, K, N = 65536, 1280, 1024
+        A = torch.randn((M, K), device="cuda", dtype=torch.float16)
+        Wk = torch.randn((N, K), device="cuda", dtype=torch.float16) / K ** 0.5
+        bias = torch.randn(N, device="cuda") * 0.01
+        slope = torch.full((1,), 0.25, device="cuda")
+        Y = torch.empty((M, N), device="cuda", dtype=torch.float16)
+        run = lambda: ops.gemm(A, Wk, Y=Y, bias=bias, trans_b=True, M=M, N=N, K=K, epilogue=capi.XB_EPI_PRELU,
+                               ep=(slope, None, None), ep_count=1, engine=capi.XB_GEMM_TCGEN05)
+        run()
+        t0.record()
+        for _ in range(reps):
+            run()
+        extra = {"tflops": 2.0 * M * N * K / 1e12}
     t1.record()
     torch.cuda.synchronize()
     assert ops.device_status() == 0
-    print(json.dumps({"micro": args.micro, "launches": reps, "status": "ok", "ms_per_launch": t0.elapsed_time(t1) / reps}))
+    ms = t0.elapsed_time(t1) / reps
+    line = {"micro": args.micro, "launches": reps, "status": "ok", "ms_per_launch": ms}
+    if args.micro == "gemm_mlp":
+        line["tflop_per_s"] = extra["tflops"] / (ms * 1e-3)
+    print(json.dumps(line))
 
 
 def run_batching(args):
@@ -646,7 +665,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and pooling side measurements")
     ap.add_argument("--table-rows", type=int, default=200_000_000, help="rows per table of --micro sharded")
-    ap.add_argument("--micro", choices=["att", "pool", "gemm", "tower", "sharded", "batching"], help="run --steps launches of one kernel on a small case "
+    ap.add_argument("--micro", choices=["att", "pool", "gemm", "gemm_mlp", "tower", "sharded", "batching"], help="run --steps launches of one kernel on a small case "
                     "(for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     if args.micro == "sharded":
