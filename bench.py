@@ -615,10 +615,20 @@ def run_sharded(args):
     pooled = torch.empty((B, dims[0]), dtype=torch.float16, device="cuda")
     acts = [torch.empty((B, dims[i + 1]), dtype=torch.float16, device="cuda") for i in range(4)]
 
-    def step():
+    phases = []
+
+    def step(timed=False):
         # the four tables share the ownership rule: one routing pass and one pair of exchanges for all of them
+        events = []
+
+        def mark(name):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            events.append((name, e))
+        if timed:
+            mark("start")
         stats = [sharded.sharded_pool_tables(comm, gops, tables, dim, [f[0] for f in feeds], [None] * n_tables,
-                                             [f[1] for f in feeds], [gpt] * n_tables, pooled)]
+                                             [f[1] for f in feeds], [gpt] * n_tables, pooled, mark=mark if timed else None)]
         x = pooled
         for i in range(4):
             last = i == 3
@@ -626,6 +636,9 @@ def run_sharded(args):
                      epilogue=capi.XB_EPI_SIGMOID if last else capi.XB_EPI_PRELU, ep=(None if last else slope, None, None),
                      ep_count=0 if last else 1)
             x = acts[i]
+        if timed:
+            mark("mlp")
+            phases.append(events)
         return stats
 
     for _ in range(args.warmup):
@@ -639,6 +652,15 @@ def run_sharded(args):
     dist.barrier(); torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    # where a step spends its time on this rank: a few more steps with an event after every phase (outside the
+    # timed region; the events themselves cost nothing but the host gaps between phases show up here too)
+    for _ in range(5):
+        step(timed=True)
+    torch.cuda.synchronize()
+    phase_ms = {}
+    for events in phases:
+        for (_, a), (name, b) in zip(events[:-1], events[1:]):
+            phase_ms[name] = phase_ms.get(name, 0.0) + a.elapsed_time(b) / len(phases)
     assert ops.device_status() == 0
     if rank == 0:
         ms = float(t.item()) / args.steps
@@ -647,6 +669,7 @@ def run_sharded(args):
                           "table_rows": rows_total, "ids_per_rank_step": n_ids,
                           "routed_bytes_per_rank_step": sum(s["routed_bytes"] for s in stats),
                           "returned_bytes_per_rank_step": sum(s["returned_bytes"] for s in stats),
+                          "phase_ms_rank0": {k: round(v, 4) for k, v in phase_ms.items()},
                           "note": "max over ranks, CUDA events; MLP 1280-1024-512-256-1 included"}))
     dist.destroy_process_group()
 

@@ -130,3 +130,25 @@ def test_owner_side_pooling_of_several_sources_and_tables_matches_the_cpu_restat
     got = sharded.GpuShardOps().pool_partial_tables(tables, torch.from_numpy(rows).cuda(), torch.from_numpy(vals).cuda(),
                                                     torch.from_numpy(off).cuda(), sources, table_segments, dim)
     np.testing.assert_allclose(got.cpu().numpy(), want.numpy(), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("world,dim,out_dtype,avg", [(8, 32, torch.float16, False), (3, 8, torch.float32, True),
+                                                     (2, 6, torch.float32, False), (4, 12, torch.float16, True)])
+def test_combine_matches_the_cpu_restatement(world, dim, out_dtype, avg):
+    """Owner-ordered sum of the returned partial vectors: the 16-byte path (dim % 4 == 0) and the element path."""
+    pkg.load()
+    from x_deeplearning_b200 import sharded
+    rng = np.random.default_rng(world * 100 + dim)
+    groups, rows = 5, 37
+    segments = groups * rows
+    partial = rng.normal(0, 1, (world * segments, dim)).astype(np.float32)
+    seg_len = rng.integers(0, 9, segments).astype(np.int32)
+    want = torch.zeros((rows, groups * dim), dtype=torch.float32)
+    CpuShardOps().combine(torch.from_numpy(partial), world, segments, dim, groups, want, torch.from_numpy(seg_len), avg)
+    out = torch.zeros((rows, groups * dim), dtype=out_dtype, device="cuda")
+    sharded.GpuShardOps().combine(torch.from_numpy(partial).cuda(), world, segments, dim, groups, out,
+                                  torch.from_numpy(seg_len).cuda() if avg else None, avg)
+    if out_dtype == torch.float32:
+        assert torch.equal(out.cpu(), want)                      # same adds in the same order
+    else:
+        assert torch.equal(out.cpu(), want.to(torch.float16))

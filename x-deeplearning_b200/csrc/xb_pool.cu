@@ -1029,6 +1029,22 @@ namespace xb {
 constexpr int ROUTE_CHUNK = 4096;     // ids per CTA
 constexpr int ROUTE_MAX_SHARDS = 16;
 
+// owner = id % shards and local row = id / shards; a mask and a shift when shards is a power of two
+__device__ __forceinline__ int route_owner(uint64_t id, int shards) {
+  return (shards & (shards - 1)) == 0 ? (int)(id & (uint64_t)(shards - 1)) : (int)(id % (uint64_t)shards);
+}
+__device__ __forceinline__ uint64_t route_row(uint64_t id, int shards) {
+  return (shards & (shards - 1)) == 0 ? id >> (31 - __clz(shards)) : id / (uint64_t)shards;
+}
+// last segment whose exclusive offset is <= idx, searched in [lo, hi)
+__device__ __forceinline__ int64_t route_segment(const int32_t* __restrict__ seg_offsets, int64_t lo, int64_t hi, int64_t idx) {
+  while (hi - lo > 1) {
+    const int64_t mid = (lo + hi) >> 1;
+    if ((int64_t)__ldg(seg_offsets + mid) <= idx) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
 // pass 1: per-CTA histogram of owners
 __global__ void __launch_bounds__(256) route_count_kernel(const int64_t* __restrict__ ids, int64_t n, int shards,
                                                           int32_t* __restrict__ block_hist) {
@@ -1038,7 +1054,7 @@ __global__ void __launch_bounds__(256) route_count_kernel(const int64_t* __restr
   const int64_t base = (int64_t)blockIdx.x * ROUTE_CHUNK;
   for (int i = threadIdx.x; i < ROUTE_CHUNK; i += 256) {
     const int64_t idx = base + i;
-    if (idx < n) atomicAdd(&hist[(int)((uint64_t)ids[idx] % (uint64_t)shards)], 1);     // integer: order-free
+    if (idx < n) atomicAdd(&hist[route_owner((uint64_t)ids[idx], shards)], 1);           // integer: order-free
   }
   __syncthreads();
   if (threadIdx.x < shards) block_hist[(int64_t)blockIdx.x * shards + threadIdx.x] = hist[threadIdx.x];
@@ -1085,16 +1101,24 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int64_t* __res
                                                             int32_t* __restrict__ out_tags) {
   __shared__ int32_t running[ROUTE_MAX_SHARDS];
   __shared__ int32_t warp_cnt[8][ROUTE_MAX_SHARDS];
-  if (threadIdx.x < shards) running[threadIdx.x] = block_base[(int64_t)blockIdx.x * shards + threadIdx.x];
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __shared__ int64_t window[2];
   const int64_t base = (int64_t)blockIdx.x * ROUTE_CHUNK;
+  if (threadIdx.x < shards) running[threadIdx.x] = block_base[(int64_t)blockIdx.x * shards + threadIdx.x];
+  // the ids of this CTA are consecutive, so their segments lie between those of its first and last id:
+  // two searches over all segments per CTA, then each id searches that window only (its offsets stay in L1)
+  if (threadIdx.x < 2 && base < n) {
+    const int64_t idx = threadIdx.x == 0 ? base : min(base + ROUTE_CHUNK, n) - 1;
+    window[threadIdx.x] = route_segment(seg_offsets, 0, segments, idx);
+  }
+  __syncthreads();
+  const int64_t win_lo = window[0], win_hi = window[1] + 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i0 = 0; i0 < ROUTE_CHUNK; i0 += 256) {
     const int64_t idx = base + i0 + threadIdx.x;
     const bool live = idx < n;
     uint64_t id = 0;
     int owner = -1;
-    if (live) { id = (uint64_t)ids[idx]; owner = (int)(id % (uint64_t)shards); }
+    if (live) { id = (uint64_t)ids[idx]; owner = route_owner(id, shards); }
     int rank_in_warp = 0;
     for (int w = 0; w < shards; ++w) {
       const unsigned m = __ballot_sync(0xffffffffu, owner == w);
@@ -1107,12 +1131,8 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int64_t* __res
       for (int ww = 0; ww < warp; ++ww) before += warp_cnt[ww][owner];
       const int64_t pos = (int64_t)running[owner] + before + rank_in_warp;
       // segment of this id: last offset <= idx
-      int64_t lo = 0, hi = segments;
-      while (hi - lo > 1) {
-        const int64_t mid = (lo + hi) >> 1;
-        if ((int64_t)seg_offsets[mid] <= idx) lo = mid; else hi = mid;
-      }
-      out_rows[pos] = (int64_t)(id / (uint64_t)shards);
+      const int64_t lo = route_segment(seg_offsets, win_lo, win_hi, idx);
+      out_rows[pos] = (int64_t)route_row(id, shards);
       if (out_values) out_values[pos] = values ? values[idx] : 1.f;
       out_tags[pos] = (int32_t)lo;
     }
@@ -1147,6 +1167,50 @@ __global__ void shard_combine_kernel(const float* __restrict__ partial, int shar
     const int64_t rows = segments / seg_per_row;
     const int64_t grp = s / rows, sample = s - grp * rows;
     store_out(out, sample * out_stride + grp * dim + e, out_dtype, acc);
+  }
+}
+
+// The same sum, four adjacent elements per thread (dim and the output row stride multiples of 4, aligned
+// bases): 16-byte loads of all owners' partials are issued before the first add, the adds keep the owner order.
+template <int SHARDS>
+__global__ void __launch_bounds__(256) shard_combine4_kernel(const float4* __restrict__ partial, int shards, int64_t segments,
+                                                             int dim4, const int32_t* __restrict__ seg_len, int avg,
+                                                             void* out, int64_t out_stride, int64_t rows, int out_dtype) {
+  const int64_t total = segments * dim4;
+  const int n_sh = SHARDS ? SHARDS : shards;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t s = i / dim4;
+    const int e4 = (int)(i - s * dim4);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (SHARDS) {
+      float4 v[SHARDS ? SHARDS : 1];
+#pragma unroll
+      for (int w = 0; w < SHARDS; ++w) v[w] = __ldcs(partial + ((int64_t)w * segments + s) * dim4 + e4);
+#pragma unroll
+      for (int w = 0; w < SHARDS; ++w) { acc.x += v[w].x; acc.y += v[w].y; acc.z += v[w].z; acc.w += v[w].w; }
+    } else {
+      for (int w = 0; w < n_sh; ++w) {
+        const float4 v = __ldcs(partial + ((int64_t)w * segments + s) * dim4 + e4);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    if (avg && seg_len) {
+      const int32_t len = seg_len[s];
+      if (len != 0) {
+        const float sc = (float)(1.0 / (double)len);
+        acc.x *= sc; acc.y *= sc; acc.z *= sc; acc.w *= sc;
+      }
+    }
+    // segment s = group * rows + sample  ->  out[sample, group*dim + e]
+    const int64_t grp = s / rows, sample = s - grp * rows;
+    const int64_t o = sample * out_stride + (grp * dim4 + e4) * 4;
+    if (out_dtype == XB_F32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + o) = acc;
+    } else {
+      const __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + o) =
+          make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
   }
 }
 
@@ -1193,6 +1257,21 @@ extern "C" int xb_shard_combine(const float* partial, int32_t shards, int64_t se
   XB_REQUIRE(segments % groups == 0, XB_ERR_ARG, "xb_shard_combine: segments %lld not a multiple of groups %lld", (long long)segments, (long long)groups);
   XB_REQUIRE(out_dtype == XB_F32 || out_dtype == XB_F16, XB_ERR_UNSUPPORTED, "xb_shard_combine: output dtype %d", out_dtype);
   if (segments == 0) return 0;
+  const size_t esz = out_dtype == XB_F32 ? 4 : 2;
+  if (dim % 4 == 0 && out_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(partial) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & (4 * esz - 1)) == 0) {
+    const int dim4 = dim / 4;
+    const int64_t rows = segments / groups;
+    const int64_t blocks4 = std::min<int64_t>((segments * dim4 + 255) / 256, (int64_t)sm_count() * 16);
+    const float4* p4 = reinterpret_cast<const float4*>(partial);
+    switch (shards) {
+      case 2: shard_combine4_kernel<2><<<(unsigned)blocks4, 256, 0, stream>>>(p4, shards, segments, dim4, seg_len, avg, out, out_stride, rows, out_dtype); break;
+      case 4: shard_combine4_kernel<4><<<(unsigned)blocks4, 256, 0, stream>>>(p4, shards, segments, dim4, seg_len, avg, out, out_stride, rows, out_dtype); break;
+      case 8: shard_combine4_kernel<8><<<(unsigned)blocks4, 256, 0, stream>>>(p4, shards, segments, dim4, seg_len, avg, out, out_stride, rows, out_dtype); break;
+      default: shard_combine4_kernel<0><<<(unsigned)blocks4, 256, 0, stream>>>(p4, shards, segments, dim4, seg_len, avg, out, out_stride, rows, out_dtype); break;
+    }
+    return check_launch("shard_combine4_kernel");
+  }
   const int64_t blocks = std::min<int64_t>((segments * dim + 255) / 256, (int64_t)sm_count() * 8);
   shard_combine_kernel<<<(unsigned)blocks, 256, 0, stream>>>(partial, shards, segments, dim, seg_len, avg, out, out_stride, groups,
                                                              out_dtype);

@@ -99,7 +99,7 @@ class GpuShardOps:
         return out
 
 
-def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, groups, out, avg=False):
+def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, groups, out, avg=False, mark=None):
     """Pooling over several row-sharded tables of one `dim` with ONE routing pass and one pair of exchanges.
 
     ids[t] / values[t] / seg_offsets[t]: this rank's ids of the `groups[t]` feature groups of table t, laid out
@@ -107,7 +107,9 @@ def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, 
     values[t] may be None (all 1.0) only if it is None for every table. out [rows, >= sum(groups) * dim]
     receives the pooled vectors, table after table. All tables follow the same ownership rule, so their ids
     form one routing problem whose segments are numbered table after table; the owner pools each table's
-    segment range against that table's shard. Returns the per-step byte counts of the two exchanges."""
+    segment range against that table's shard. Returns the per-step byte counts of the two exchanges.
+    `mark(name)`, when given, is called after each phase (bench.py records a CUDA event there)."""
+    mark = mark or (lambda name: None)
     W = comm.world
     T = len(table_shards)
     table_segments = [int(o.numel()) - 1 for o in seg_offsets]
@@ -124,12 +126,16 @@ def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, 
             base += int(ids[t].numel())
         parts.append(torch.full((1,), base, dtype=seg_offsets[0].dtype, device=seg_offsets[0].device))
         all_off = torch.cat(parts)
+    mark("concat")
     rows, vals, tags, owner_counts = ops.route(all_ids, all_vals, all_off, W)
+    mark("route")
     both = torch.stack([owner_counts, comm.exchange_counts(owner_counts)]).cpu()   # bucket sizes drive the exchange
     send_counts, recv_counts = [int(c) for c in both[0]], [int(c) for c in both[1]]
+    mark("counts")
     r_rows = comm.all_to_all_v(rows, send_counts, recv_counts)
     r_vals = comm.all_to_all_v(vals, send_counts, recv_counts) if all_vals is not None else None
     r_tags = comm.all_to_all_v(tags, send_counts, recv_counts)
+    mark("exchange_ids")
     # segment lengths of every source rank's slice (every rank has the same number of segments), then where
     # every (source, segment) starts in the received buffer
     offsets = torch.zeros(W * segments + 1, dtype=torch.int32, device=r_tags.device)
@@ -139,10 +145,14 @@ def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, 
         counts.append(ops.tag_counts(r_tags[pos:pos + recv_counts[s]], segments))
         pos += recv_counts[s]
     torch.cumsum(torch.cat(counts), 0, dtype=torch.int32, out=offsets[1:])
+    mark("offsets")
     partial = ops.pool_partial_tables(table_shards, r_rows, r_vals, offsets, W, table_segments, dim)   # [W*segments, dim] fp32
+    mark("pool")
     back = comm.all_to_all_equal(partial)                                    # slice w: from owner w
+    mark("exchange_partials")
     seg_len = (all_off[1:] - all_off[:-1]).to(torch.int32) if avg else None
     ops.combine(back, W, segments, dim, sum(groups), out, seg_len, avg)
+    mark("combine")
     per_id = 8 + 4 + (4 if all_vals is not None else 0)
     return {"routed_bytes": sum(send_counts) * per_id, "returned_bytes": partial.numel() * 4}
 
