@@ -170,7 +170,10 @@ int xb_embedding_pool_static(const xb_pool_group* groups, int32_t n_groups, xb_s
  *   step 1  xb_route_ids: bucket a rank's ids by owner with a stable counting sort;
  *           out_rows / out_values / out_tags hold bucket 0, then bucket 1, ...;
  *           out_tags[i] is the segment number (index into seg_offsets) the id belongs to;
- *           owner_counts[w] = size of bucket w (device, int64)
+ *           owner_counts[w] = size of bucket w (device, int64).
+ *           With out_tags == NULL, out_rows receives packed records instead, (segment << 32) | local row
+ *           (8 bytes per id on the wire instead of 12; local rows and segment numbers below 2^31), which
+ *           xb_unpack_routed splits at the owner into int32 rows (xb_embedding_pool takes XB_I32 ids) and tags
  *   step 2  (caller) all-to-all of the buckets
  *   step 3  xb_tag_counts: segment lengths of what an owner received from one source rank
  *           (tags arrive in ascending order), then xb_embedding_pool over the local shard
@@ -183,6 +186,7 @@ size_t xb_route_scratch_bytes(int64_t n_ids, int32_t shards);
 int xb_route_ids(const int64_t* ids, const float* values, const int32_t* seg_offsets, int64_t segments,
                  int64_t n_ids, int32_t shards, int64_t* out_rows, float* out_values, int32_t* out_tags,
                  int64_t* owner_counts, void* scratch, size_t scratch_bytes, xb_stream_t stream);
+int xb_unpack_routed(const int64_t* packed, int64_t n, int32_t* rows, int32_t* tags, xb_stream_t stream);
 int xb_tag_counts(const int32_t* tags, int64_t n, int32_t* counts, int64_t n_counts, xb_stream_t stream);
 int xb_shard_combine(const float* partial, int32_t shards, int64_t segments, int32_t dim, const int32_t* seg_len,
                      int32_t avg, void* out, int64_t out_stride, int64_t groups, int32_t out_dtype,

@@ -17,6 +17,21 @@ class CpuShardOps:
         return (torch.from_numpy(local[order]), torch.from_numpy(v[order].astype(np.float32)),
                 torch.from_numpy(tags[order].astype(np.int32)), torch.from_numpy(counts))
 
+    def route_packed(self, ids, values, seg_offsets, shards):
+        rows, vals, tags, counts = self.route(ids, values, seg_offsets, shards)
+        r = np.minimum(rows.numpy().astype(np.uint64), np.uint64(0x7fffffff))
+        packed = (tags.numpy().astype(np.uint64) << np.uint64(32)) | r
+        return torch.from_numpy(packed.astype(np.int64)), (vals if values is not None else None), counts
+
+    def unpack(self, packed):
+        v = packed.numpy().astype(np.uint64)
+        return (torch.from_numpy((v & np.uint64(0xffffffff)).astype(np.int32)),
+                torch.from_numpy((v >> np.uint64(32)).astype(np.int32)))
+
+    @staticmethod
+    def shard_rows(table):
+        return len(table)
+
     def tag_counts(self, tags, n_segments):
         return torch.from_numpy(np.bincount(tags.numpy(), minlength=n_segments).astype(np.int32))
 

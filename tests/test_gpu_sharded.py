@@ -152,3 +152,35 @@ def test_combine_matches_the_cpu_restatement(world, dim, out_dtype, avg):
         assert torch.equal(out.cpu(), want)                      # same adds in the same order
     else:
         assert torch.equal(out.cpu(), want.to(torch.float16))
+
+
+@pytest.mark.parametrize("world", [8, 5])
+def test_packed_records_carry_the_same_routing(world):
+    """(segment << 32) | local row per id: the same buckets as rows and tags apart, bit for bit, with and
+    without per-id values; a local row beyond 31 bits travels as 0x7fffffff (a row no shard holds)."""
+    pkg.load()
+    from x_deeplearning_b200 import sharded
+    rng = np.random.default_rng(30 + world)
+    counts = rng.integers(0, 40, 9000).astype(np.int32)
+    n = int(counts.sum())
+    ids = rng.integers(0, 1 << 33, n).astype(np.int64)
+    ids[:5] = [(1 << 50) + 3, -1, 0, (1 << 31) * world - 1, (1 << 31) * world]
+    vals = rng.normal(1, 0.3, n).astype(np.float32)
+    off = np.zeros(len(counts) + 1, np.int32)
+    np.cumsum(counts, out=off[1:])
+    gops, cops = sharded.GpuShardOps(), CpuShardOps()
+    for v in (vals, None):
+        g = gops.route_packed(torch.from_numpy(ids).cuda(), None if v is None else torch.from_numpy(v).cuda(),
+                              torch.from_numpy(off).cuda(), world)
+        c = cops.route_packed(torch.from_numpy(ids), None if v is None else torch.from_numpy(v), torch.from_numpy(off), world)
+        assert torch.equal(g[0].cpu(), c[0]) and torch.equal(g[2].cpu(), c[2])
+        assert (g[1] is None and c[1] is None) or torch.equal(g[1].cpu(), c[1])
+        rows, tags = gops.unpack(g[0])
+        crows, ctags = cops.unpack(c[0])
+        assert torch.equal(rows.cpu(), crows) and torch.equal(tags.cpu(), ctags)
+        # against the unpacked routing
+        r = gops.route(torch.from_numpy(ids).cuda(), None, torch.from_numpy(off).cuda(), world)
+        assert torch.equal(tags, r[2])
+        big = r[0].cpu().numpy().astype(np.uint64) >= np.uint64(0x7fffffff)
+        assert np.array_equal(rows.cpu().numpy()[~big], r[0].cpu().numpy()[~big].astype(np.int32))
+        assert (rows.cpu().numpy()[big] == 0x7fffffff).all() and big.sum() >= 2

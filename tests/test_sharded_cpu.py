@@ -130,7 +130,7 @@ def test_two_tables_without_values_route_fewer_bytes():
     a = _run_tables(2, 6, False)
     b = _run_tables(2, 6, True)
     for r in range(2):
-        assert a[r][1] * 16 == b[r][1] * 12            # 12 bytes per routed id instead of 16
+        assert a[r][1] * 12 == b[r][1] * 8             # 8 bytes per routed id instead of 12
 
 
 def test_routing_rule_is_bit_exact():

@@ -84,6 +84,7 @@ SYMBOLS = {
     "xb_embedding_pool_static": (i32, [C.POINTER(PoolGroup), i32, vp]),
     "xb_route_scratch_bytes": (C.c_size_t, [i64, i32]),
     "xb_route_ids": (i32, [vp, vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, C.c_size_t, vp]),
+    "xb_unpack_routed": (i32, [vp, i64, vp, vp, vp]),
     "xb_tag_counts": (i32, [vp, i64, vp, i64, vp]),
     "xb_shard_combine": (i32, [vp, i32, i64, i32, vp, i32, vp, i64, i64, i32, vp]),
     "xb_gemm": (i32, [C.POINTER(GemmArgs), vp]),

@@ -1132,9 +1132,16 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int64_t* __res
       const int64_t pos = (int64_t)running[owner] + before + rank_in_warp;
       // segment of this id: last offset <= idx
       const int64_t lo = route_segment(seg_offsets, win_lo, win_hi, idx);
-      out_rows[pos] = (int64_t)route_row(id, shards);
+      const uint64_t row = route_row(id, shards);
+      if (out_tags) {
+        out_rows[pos] = (int64_t)row;
+        out_tags[pos] = (int32_t)lo;
+      } else {
+        // packed record: segment number in the high half, local row in the low half; a row that does not
+        // fit 31 bits cannot exist in a shard and is sent as 0x7fffffff, which no shard holds either
+        out_rows[pos] = (int64_t)(((uint64_t)lo << 32) | (row < 0x7fffffffull ? row : 0x7fffffffull));
+      }
       if (out_values) out_values[pos] = values ? values[idx] : 1.f;
-      out_tags[pos] = (int32_t)lo;
     }
     __syncthreads();
     if (threadIdx.x < shards) {
@@ -1143,6 +1150,16 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int64_t* __res
       running[threadIdx.x] += add;
     }
     __syncthreads();
+  }
+}
+
+// packed records (see route_scatter_kernel) -> int32 local rows and int32 segment numbers
+__global__ void unpack_routed_kernel(const int64_t* __restrict__ packed, int64_t n, int32_t* __restrict__ rows,
+                                     int32_t* __restrict__ tags) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint64_t v = (uint64_t)__ldcs(packed + i);
+    rows[i] = (int32_t)(v & 0xffffffffull);
+    tags[i] = (int32_t)(v >> 32);
   }
 }
 
@@ -1226,7 +1243,8 @@ extern "C" int xb_route_ids(const int64_t* ids, const float* values, const int32
                             int64_t* owner_counts, void* scratch, size_t scratch_bytes, xb_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   XB_REQUIRE(shards >= 1 && shards <= ROUTE_MAX_SHARDS, XB_ERR_LIMIT, "xb_route_ids: %d shards (1..%d)", shards, ROUTE_MAX_SHARDS);
-  XB_REQUIRE(n_ids >= 0 && segments >= 0 && owner_counts && out_rows && out_tags && seg_offsets, XB_ERR_ARG, "xb_route_ids: bad arguments");
+  XB_REQUIRE(n_ids >= 0 && segments >= 0 && owner_counts && out_rows && seg_offsets, XB_ERR_ARG, "xb_route_ids: bad arguments");
+  XB_REQUIRE(out_tags || segments < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_route_ids: packed records hold 31-bit segment numbers");
   XB_REQUIRE(n_ids == 0 || ids, XB_ERR_ARG, "xb_route_ids: ids missing");
   XB_REQUIRE(n_ids < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_route_ids: more than 2^31 ids per call");
   XB_REQUIRE(scratch_bytes >= xb_route_scratch_bytes(n_ids, shards) && scratch, XB_ERR_SCRATCH, "xb_route_ids: scratch too small");
@@ -1237,6 +1255,15 @@ extern "C" int xb_route_ids(const int64_t* ids, const float* values, const int32
   route_scatter_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, values, seg_offsets, segments, n_ids, shards, hist, out_rows,
                                                              out_values, out_tags);
   return check_launch("route kernels");
+}
+
+extern "C" int xb_unpack_routed(const int64_t* packed, int64_t n, int32_t* rows, int32_t* tags, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(n >= 0 && (n == 0 || (packed && rows && tags)), XB_ERR_ARG, "xb_unpack_routed: bad arguments");
+  if (n == 0) return 0;
+  const int64_t blocks = std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 16);
+  unpack_routed_kernel<<<(unsigned)blocks, 256, 0, stream>>>(packed, n, rows, tags);
+  return check_launch("unpack_routed_kernel");
 }
 
 extern "C" int xb_tag_counts(const int32_t* tags, int64_t n, int32_t* counts, int64_t n_counts, xb_stream_t stream_) {

@@ -59,6 +59,29 @@ class GpuShardOps:
                                  need, xops.stream()))
         return rows, vals, tags, owner_counts
 
+    def route_packed(self, ids, values, seg_offsets, shards):
+        """As route, with (segment << 32) | local row in one int64 per id instead of separate rows and tags."""
+        n = ids.numel()
+        packed = torch.empty(n, dtype=torch.int64, device=ids.device)
+        vals = torch.empty(n, dtype=torch.float32, device=ids.device) if values is not None else None
+        owner_counts = torch.zeros(shards, dtype=torch.int64, device=ids.device)
+        need = int(lib().xb_route_scratch_bytes(n, shards))
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=ids.device)
+        check(lib().xb_route_ids(xops.ptr(ids), xops.ptr(values), xops.ptr(seg_offsets), seg_offsets.numel() - 1, n, shards,
+                                 xops.ptr(packed), xops.ptr(vals), None, xops.ptr(owner_counts), xops.ptr(scratch),
+                                 need, xops.stream()))
+        return packed, vals, owner_counts
+
+    def unpack(self, packed):
+        rows = torch.empty(packed.numel(), dtype=torch.int32, device=packed.device)
+        tags = torch.empty(packed.numel(), dtype=torch.int32, device=packed.device)
+        check(lib().xb_unpack_routed(xops.ptr(packed), packed.numel(), xops.ptr(rows), xops.ptr(tags), xops.stream()))
+        return rows, tags
+
+    @staticmethod
+    def shard_rows(table):
+        return table.rows
+
     def tag_counts(self, tags, n_segments):
         counts = torch.empty(n_segments, dtype=torch.int32, device=tags.device)
         check(lib().xb_tag_counts(xops.ptr(tags), tags.numel(), xops.ptr(counts), n_segments, xops.stream()))
@@ -127,14 +150,22 @@ def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, 
         parts.append(torch.full((1,), base, dtype=seg_offsets[0].dtype, device=seg_offsets[0].device))
         all_off = torch.cat(parts)
     mark("concat")
-    rows, vals, tags, owner_counts = ops.route(all_ids, all_vals, all_off, W)
+    # one 8-byte record per id when local rows and segment numbers fit 31 bits, else rows and tags apart
+    packed = segments < (1 << 31) and all(ops.shard_rows(t) < (1 << 31) - 1 for t in table_shards)
+    if packed:
+        recs, vals, owner_counts = ops.route_packed(all_ids, all_vals, all_off, W)
+    else:
+        rows, vals, tags, owner_counts = ops.route(all_ids, all_vals, all_off, W)
     mark("route")
     both = torch.stack([owner_counts, comm.exchange_counts(owner_counts)]).cpu()   # bucket sizes drive the exchange
     send_counts, recv_counts = [int(c) for c in both[0]], [int(c) for c in both[1]]
     mark("counts")
-    r_rows = comm.all_to_all_v(rows, send_counts, recv_counts)
+    if packed:
+        r_rows, r_tags = ops.unpack(comm.all_to_all_v(recs, send_counts, recv_counts))
+    else:
+        r_rows = comm.all_to_all_v(rows, send_counts, recv_counts)
+        r_tags = comm.all_to_all_v(tags, send_counts, recv_counts)
     r_vals = comm.all_to_all_v(vals, send_counts, recv_counts) if all_vals is not None else None
-    r_tags = comm.all_to_all_v(tags, send_counts, recv_counts)
     mark("exchange_ids")
     # segment lengths of every source rank's slice (every rank has the same number of segments), then where
     # every (source, segment) starts in the received buffer
@@ -153,7 +184,7 @@ def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, 
     seg_len = (all_off[1:] - all_off[:-1]).to(torch.int32) if avg else None
     ops.combine(back, W, segments, dim, sum(groups), out, seg_len, avg)
     mark("combine")
-    per_id = 8 + 4 + (4 if all_vals is not None else 0)
+    per_id = (8 if packed else 12) + (4 if all_vals is not None else 0)
     return {"routed_bytes": sum(send_counts) * per_id, "returned_bytes": partial.numel() * 4}
 
 
