@@ -188,6 +188,17 @@ int xb_route_ids(const int64_t* ids, const float* values, const int32_t* seg_off
                  int64_t* owner_counts, void* scratch, size_t scratch_bytes, xb_stream_t stream);
 int xb_unpack_routed(const int64_t* packed, int64_t n, int32_t* rows, int32_t* tags, xb_stream_t stream);
 int xb_tag_counts(const int32_t* tags, int64_t n, int32_t* counts, int64_t n_counts, xb_stream_t stream);
+/* Step 3 for everything an owner received, in two calls instead of one per source rank and one pooling group per
+ * (source, table) built by the caller. source_counts (HOST, [sources]) are the lengths of the source ranks' slices
+ * of `tags`; counts[s * segments + t] receives the length of segment t of source s. xb_shard_pool then pools, for
+ * every source s and table t, the segments [sum(table_segments[:t]), +table_segments[t]) of that source against
+ * tables[t] (HOST arrays of n_tables entries); offsets [sources * S + 1] are the exclusive offsets of all
+ * (source, segment) pairs into `rows` (S = sum(table_segments)); out [sources * S, dim] fp32. */
+int xb_tag_counts_sources(const int32_t* tags, const int64_t* source_counts, int32_t sources, int32_t* counts,
+                          int64_t segments, xb_stream_t stream);
+int xb_shard_pool(const xb_table_desc* const* tables, const int64_t* table_segments, int32_t n_tables,
+                  const void* rows, int32_t row_dtype, int64_t n_rows, const float* values, const int32_t* offsets,
+                  int32_t sources, int32_t dim, float* out, xb_stream_t stream);
 int xb_shard_combine(const float* partial, int32_t shards, int64_t segments, int32_t dim, const int32_t* seg_len,
                      int32_t avg, void* out, int64_t out_stride, int64_t groups, int32_t out_dtype,
                      xb_stream_t stream);

@@ -35,6 +35,13 @@ class CpuShardOps:
     def tag_counts(self, tags, n_segments):
         return torch.from_numpy(np.bincount(tags.numpy(), minlength=n_segments).astype(np.int32))
 
+    def tag_counts_sources(self, tags, source_counts, n_segments):
+        out, pos = [], 0
+        for n in source_counts:
+            out.append(self.tag_counts(tags[pos:pos + n], n_segments))
+            pos += n
+        return torch.cat(out)
+
     def pool_partial(self, table, rows, vals, counts, dim):
         out = np.zeros((counts.numel(), dim), np.float32)
         orc.embedding_pool(table, rows.numpy(), vals.numpy(), counts.numpy(), [dict(udf=0, out=out, col=0)])

@@ -184,3 +184,14 @@ def test_packed_records_carry_the_same_routing(world):
         big = r[0].cpu().numpy().astype(np.uint64) >= np.uint64(0x7fffffff)
         assert np.array_equal(rows.cpu().numpy()[~big], r[0].cpu().numpy()[~big].astype(np.int32))
         assert (rows.cpu().numpy()[big] == 0x7fffffff).all() and big.sum() >= 2
+
+
+def test_segment_lengths_of_all_sources_in_one_launch():
+    pkg.load()
+    from x_deeplearning_b200 import sharded
+    rng = np.random.default_rng(77)
+    segments, source_counts = 500, [1200, 0, 37, 4000, 1]
+    tags = np.concatenate([np.sort(rng.integers(0, segments, n)) for n in source_counts]).astype(np.int32)
+    got = sharded.GpuShardOps().tag_counts_sources(torch.from_numpy(tags).cuda(), source_counts, segments)
+    want = CpuShardOps().tag_counts_sources(torch.from_numpy(tags), source_counts, segments)
+    assert torch.equal(got.cpu(), want)

@@ -1163,6 +1163,19 @@ __global__ void unpack_routed_kernel(const int64_t* __restrict__ packed, int64_t
   }
 }
 
+// segment lengths of everything an owner received, all source ranks in one launch: slice s of the tags
+// (bounds[s] .. bounds[s+1]) counts into counts[s * segments + tag]
+struct TagBounds { int64_t b[ROUTE_MAX_SHARDS + 1]; };
+__global__ void tag_count_sources_kernel(const int32_t* __restrict__ tags, const TagBounds bounds, int sources,
+                                         int64_t segments, int32_t* __restrict__ counts) {
+  const int64_t n = bounds.b[sources];
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int src = 0;
+    while (src + 1 < sources && i >= bounds.b[src + 1]) ++src;
+    atomicAdd(&counts[(int64_t)src * segments + tags[i]], 1);
+  }
+}
+
 // segment lengths at the owner: tags arrive sorted per source rank; counts are integer atomics (exact)
 __global__ void tag_count_kernel(const int32_t* __restrict__ tags, int64_t n, int32_t* __restrict__ counts) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
@@ -1274,6 +1287,68 @@ extern "C" int xb_tag_counts(const int32_t* tags, int64_t n, int32_t* counts, in
   const int64_t blocks = std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 8);
   tag_count_kernel<<<(unsigned)blocks, 256, 0, stream>>>(tags, n, counts);
   return check_launch("tag_count_kernel");
+}
+
+extern "C" int xb_tag_counts_sources(const int32_t* tags, const int64_t* source_counts, int32_t sources, int32_t* counts,
+                                     int64_t segments, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(source_counts && counts && segments >= 0, XB_ERR_ARG, "xb_tag_counts_sources: bad arguments");
+  XB_REQUIRE(sources >= 1 && sources <= ROUTE_MAX_SHARDS, XB_ERR_LIMIT, "xb_tag_counts_sources: %d sources (1..%d)", sources, ROUTE_MAX_SHARDS);
+  TagBounds bounds;
+  bounds.b[0] = 0;
+  for (int s = 0; s < sources; ++s) {
+    XB_REQUIRE(source_counts[s] >= 0, XB_ERR_ARG, "xb_tag_counts_sources: negative count");
+    bounds.b[s + 1] = bounds.b[s] + source_counts[s];
+  }
+  const int64_t n = bounds.b[sources];
+  XB_REQUIRE(n == 0 || tags, XB_ERR_ARG, "xb_tag_counts_sources: tags missing");
+  XB_CUDA(cudaMemsetAsync(counts, 0, (size_t)sources * (size_t)segments * sizeof(int32_t), stream));
+  if (n == 0) return 0;
+  const int64_t blocks = std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 8);
+  tag_count_sources_kernel<<<(unsigned)blocks, 256, 0, stream>>>(tags, bounds, sources, segments, counts);
+  return check_launch("tag_count_sources_kernel");
+}
+
+extern "C" int xb_shard_pool(const xb_table_desc* const* tables, const int64_t* table_segments, int32_t n_tables,
+                             const void* rows, int32_t row_dtype, int64_t n_rows, const float* values,
+                             const int32_t* offsets, int32_t sources, int32_t dim, float* out, xb_stream_t stream) {
+  XB_REQUIRE(tables && table_segments && n_tables >= 1 && sources >= 1 && offsets && out && dim >= 1, XB_ERR_ARG,
+             "xb_shard_pool: bad arguments");
+  int64_t S = 0;
+  for (int t = 0; t < n_tables; ++t) {
+    XB_REQUIRE(table_segments[t] >= 0, XB_ERR_ARG, "xb_shard_pool: negative segment count");
+    S += table_segments[t];
+  }
+  xb_pool_group groups[XB_MAX_POOL_GROUPS];
+  int n = 0;
+  for (int s = 0; s < sources; ++s) {
+    int64_t lo = (int64_t)s * S;
+    for (int t = 0; t < n_tables; ++t) {
+      xb_pool_group& g = groups[n];
+      memset(&g, 0, sizeof(g));
+      g.table = tables[t];
+      g.ids = rows;
+      g.values = values;
+      g.segments = offsets + lo;
+      g.segments_are_offsets = 1;
+      g.batch = table_segments[t];
+      // the exact share of this (source, table) is only known on the device; it sizes the work split only
+      g.n_ids = sources * S ? n_rows * table_segments[t] / ((int64_t)sources * S) : 0;
+      g.dim = dim;
+      g.id_dtype = row_dtype;
+      g.out_dtype = XB_F32;
+      g.n_items = 1;
+      g.items[0].udf = XB_UDF_SUM;
+      g.items[0].out = out + lo * dim;
+      g.items[0].stride = dim;
+      lo += table_segments[t];
+      if (++n == XB_MAX_POOL_GROUPS) {
+        if (int rc = xb_embedding_pool(groups, n, nullptr, 0, stream)) return rc;
+        n = 0;
+      }
+    }
+  }
+  return n ? xb_embedding_pool(groups, n, nullptr, 0, stream) : 0;
 }
 
 extern "C" int xb_shard_combine(const float* partial, int32_t shards, int64_t segments, int32_t dim, const int32_t* seg_len,

@@ -93,6 +93,15 @@ class GpuShardOps:
         xops.embedding_pool([g])
         return out
 
+    def tag_counts_sources(self, tags, source_counts, n_segments):
+        """Segment lengths of every source rank's slice of `tags` (slice lengths `source_counts`, host ints):
+        [len(source_counts) * n_segments] int32, one launch."""
+        W = len(source_counts)
+        counts = torch.empty(W * n_segments, dtype=torch.int32, device=tags.device)
+        sc = (C.c_int64 * W)(*source_counts)
+        check(lib().xb_tag_counts_sources(xops.ptr(tags), sc, W, xops.ptr(counts), n_segments, xops.stream()))
+        return counts
+
     def pool_partial_tables(self, tables, rows, vals, offsets, sources, table_segments, dim):
         """rows/vals: everything this owner received (source-major, and table-major inside a source);
         offsets [sources * S + 1] int32: where each (source, segment) starts in `rows`, S = sum(table_segments).
@@ -100,20 +109,11 @@ class GpuShardOps:
         group per (source, table), all over the same id buffer. Returns [sources * S, dim] fp32."""
         S = sum(table_segments)
         out = torch.empty((sources * S, dim), dtype=torch.float32, device=rows.device)
-        groups = []
-        for s in range(sources):
-            lo = s * S
-            for table, n in zip(tables, table_segments):
-                g = xops.make_group(table, rows, vals, offsets[lo:lo + n + 1],
-                                    [dict(udf=capi.XB_UDF_SUM, out=out[lo:lo + n], col=0)], torch.float32,
-                                    segments_are_offsets=True)
-                # the exact share of this (source, table) is only known on the device: the group's ids are
-                # taken as proportional to its segments (the number sizes the work split, nothing else)
-                g.n_ids = rows.numel() * n // max(sources * S, 1)
-                groups.append(g)
-                lo += n
-        for i in range(0, len(groups), capi.XB_MAX_POOL_GROUPS):
-            xops.embedding_pool(groups[i:i + capi.XB_MAX_POOL_GROUPS])
+        T = len(tables)
+        descs = (C.POINTER(capi.TableDesc) * T)(*[C.pointer(t.desc) for t in tables])
+        segs = (C.c_int64 * T)(*table_segments)
+        check(lib().xb_shard_pool(descs, segs, T, xops.ptr(rows), xops.dt(rows), rows.numel(), xops.ptr(vals),
+                                  xops.ptr(offsets), sources, dim, xops.ptr(out), xops.stream()))
         return out
 
     def combine(self, partial, shards, segments, dim, groups, out, seg_len=None, avg=False):
@@ -170,12 +170,7 @@ def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, 
     # segment lengths of every source rank's slice (every rank has the same number of segments), then where
     # every (source, segment) starts in the received buffer
     offsets = torch.zeros(W * segments + 1, dtype=torch.int32, device=r_tags.device)
-    counts = []
-    pos = 0
-    for s in range(W):
-        counts.append(ops.tag_counts(r_tags[pos:pos + recv_counts[s]], segments))
-        pos += recv_counts[s]
-    torch.cumsum(torch.cat(counts), 0, dtype=torch.int32, out=offsets[1:])
+    torch.cumsum(ops.tag_counts_sources(r_tags, recv_counts, segments), 0, dtype=torch.int32, out=offsets[1:])
     mark("offsets")
     partial = ops.pool_partial_tables(table_shards, r_rows, r_vals, offsets, W, table_segments, dim)   # [W*segments, dim] fp32
     mark("pool")
