@@ -55,6 +55,14 @@ const char* xb_version(void);
  * xb_device_status_clear() resets the word. */
 int xb_device_status(int* status);
 int xb_device_status_clear(void);
+/* Maps the status word of the current device into host memory and returns its address (one small pinned
+ * allocation per device, made by the first call; later calls return the same address). After a stream
+ * synchronisation *host_word != 0 says what xb_device_status would, without a device-to-host copy, so a
+ * serving loop can test it after every request. Once a wait has run out, later waits on that device give
+ * up after a few microseconds until xb_device_status_clear is called (it resets the mirror too): a
+ * long-lived process must clear the word when it has reported the failure. No counterpart in the
+ * reference, whose kernels have no bounded waits. */
+int xb_device_status_mirror(const volatile int** host_word);
 
 /* ------------------------------------------------------------------------- */
 /* Embedding tables in HBM.
@@ -82,6 +90,10 @@ int64_t xb_table_row_pitch(int32_t dim, int32_t dtype);
  * the device buffers until xb_table_destroy. A repeated key keeps its first row. */
 int xb_table_create(xb_table_desc** out, int64_t rows, int32_t dim, int32_t dtype,
                     const float* weights_host, const int64_t* keys_host);
+/* Replica of a table that lives on device `src_device`, on the CURRENT device (device-to-device copies; the
+ * host image is not needed again). One serving process holds one replica per device it serves
+ * (blaze/blaze/api/cpp_api/predictor_manager_impl.cc:142-177 creates predictors per device id). */
+int xb_table_clone(xb_table_desc** out, const xb_table_desc* src, int32_t src_device);
 void xb_table_destroy(xb_table_desc* t);
 /* Host-side builder of the open-addressing index: fills slot_keys/slot_rows
  * (host arrays of `slots` entries, slots a power of two >= 2*rows). */
@@ -147,10 +159,13 @@ int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, void* scrat
  * counts->offsets scratch in a 1 MiB array that is part of the library image
  * (every GPU that loads the library holds that 1 MiB until the process exits),
  * and it calls no allocator of any kind.
- *   - Limit: the groups that pass counts may need at most
- *     xb_embedding_pool_static_max_bytes() in total (each such group takes
- *     4*(batch+1) bytes rounded up to 256); a larger request is rejected with
- *     XB_ERR_LIMIT. Groups that pass exclusive offsets need none.
+ *   - Limit: xb_embedding_pool_scratch_bytes(groups, n_groups) must not exceed
+ *     xb_embedding_pool_static_max_bytes(); a larger request is rejected with
+ *     XB_ERR_LIMIT before anything is launched. Every group that passes counts
+ *     takes 4*(batch+1) bytes of offsets rounded up to 256 PLUS the partial sums
+ *     of the multi-block scan (4 bytes per 8192 samples, rounded up to 256), so
+ *     size by that function, not by the offsets alone. Groups that pass
+ *     exclusive offsets need none.
  *   - The first call on each device looks the array's address up; make that
  *     first call outside any stream capture.
  *   - All calls share the one array and it keeps whatever the previous call

@@ -130,7 +130,9 @@ GRU_KEEP = re.compile(r"gru_test_(\d+)_(\d+)_(\d+)_cpu\.conf$")
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("XDL_REFERENCE", "")
+    if not os.path.isdir(os.path.join(ref, "blaze")):
+        sys.exit("usage: make_golden.py <root of the reference checkout>   (or set XDL_REFERENCE)")
     root = os.path.join(ref, "blaze/blaze/test/utest_data/operator")
     out = {}
     for d in HOT_PATH_DIRS:

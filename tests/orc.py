@@ -19,10 +19,22 @@ def _p(a, t):
     return a.ctypes.data_as(t) if a is not None else None
 
 
+def reference_root():
+    """Root of a reference checkout when one is mounted (XDL_REFERENCE, or the sibling `reference` folder of
+    the repository), else ""."""
+    cands = [os.environ.get("XDL_REFERENCE", ""),
+             os.path.join(os.path.dirname(os.path.dirname(ORACLE_DIR)), "reference")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "blaze", "blaze", "store")):
+            return c
+    return ""
+
+
 def build(openmp=False):
     subprocess.check_call(["make", "-s", "-C", ORACLE_DIR, "oracle"])
-    if os.path.isdir("/root/reference/blaze"):
-        subprocess.call(["make", "-s", "-C", ORACLE_DIR, "ref"], stdout=subprocess.DEVNULL)
+    ref = reference_root()
+    if ref:
+        subprocess.call(["make", "-s", "-C", ORACLE_DIR, "ref", "REF=" + ref], stdout=subprocess.DEVNULL)
 
 
 _lib = None

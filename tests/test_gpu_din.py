@@ -38,3 +38,22 @@ def test_din_probabilities_match_oracle(emb_sigma, seq):
     # end to end from pinned host buffers gives the same answer
     got2 = net.forward(staged).numpy()
     np.testing.assert_array_equal(got, got2)
+
+
+def test_din_at_the_benchmark_size_matches_oracle():
+    """The configuration the benchmark times: 5 M x 18 item table, 10 k categories, 8 x 100 k user groups,
+    one request of 1 user x 1000 candidates, T = 100."""
+    pkg.load()
+    from x_deeplearning_b200 import din, ops, workloads
+    model = workloads.din_model(seed=0)
+    assert model["item"].shape[0] == 5_000_000
+    req = workloads.din_requests(model, 17, requests=1, n_cand=1000)
+    want, parts = din_oracle.forward(model, req, want_parts=True)
+    net = din.DinModel(model)
+    p = net.upload(net.stage(req))
+    got = net.forward_device(p).cpu().numpy()
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    np.testing.assert_array_equal(p["q"].float().cpu().numpy(), parts["q"])
+    assert got.shape == (1000, 2)
+    assert np.abs(got - want).max() <= 2e-3, np.abs(got - want).max()

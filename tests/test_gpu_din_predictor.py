@@ -2,6 +2,7 @@
 probabilities out) against the op-by-op CPU oracle: final probabilities within 2e-3."""
 import numpy as np
 import pytest
+import torch
 
 import din_oracle
 import pkg
@@ -77,3 +78,35 @@ def test_qed_file_written_by_the_reference_store_loads_into_hbm(tmp_path):
     np.testing.assert_allclose(p.output("out"), want, rtol=1e-6, atol=1e-6)
     p.close()
     mgr.close()
+
+
+def test_one_manager_serves_predictors_on_two_devices():
+    """One process, one PredictorManager, CreatePredictor(type, device_id) for two device ids (the reference's
+    deployment model, blaze/blaze/api/cpp_api/predictor_manager_impl.cc:142-177): tables are replicated per
+    device, launch attributes are set per device, and both predictors match the oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible devices")
+    pkg.load()
+    from x_deeplearning_b200 import blaze_api as api, din_netdef, workloads
+    model = workloads.din_model(0, item_rows=20000, cate_rows=500, user_rows=3000, emb_sigma=0.5)
+    text, _ = din_netdef.build(model)
+    mgr = api.PredictorManager()
+    din_netdef.register_tables(mgr, model)
+    mgr.load_model_text(text, optimize=True)
+    preds = [mgr.create_predictor(device_type=1, device_id=d) for d in (0, 1)]
+    for seed, p in zip((5, 6), preds):
+        req = workloads.din_requests(model, seed, requests=2, n_cand=300)
+        keep = [p.feed(n, a) for n, a in din_netdef.feeds_of(model, req).items()]
+        p.forward()
+        got = p.output("output").astype(np.float32)
+        assert np.abs(got - din_oracle.forward(model, req)).max() <= 2e-3
+    # and again in the other order: both devices keep working side by side
+    for seed, p in zip((8, 7), preds[::-1]):
+        req = workloads.din_requests(model, seed, requests=1, n_cand=130)
+        keep = [p.feed(n, a) for n, a in din_netdef.feeds_of(model, req).items()]
+        p.forward()
+        assert np.abs(p.output("output").astype(np.float32) - din_oracle.forward(model, req)).max() <= 2e-3
+    for p in preds:
+        p.close()
+    mgr.close()
+    torch.cuda.set_device(0)

@@ -35,6 +35,48 @@ def test_wait_runs_out_sets_status_and_context_survives():
     np.testing.assert_allclose(Y.float().cpu().numpy(), want, rtol=2e-3, atol=2e-3)
 
 
+def test_predictor_forward_fails_after_a_wait_ran_out_and_recovers():
+    """The host runtime reads the status word after every run: a Forward whose stream saw a bounded wait give
+    up returns false with the site in the error text, clears the word, and the next Forward succeeds."""
+    pkg.load()
+    from x_deeplearning_b200 import blaze_api as api, capi, ops
+    L = capi.lib()
+    text = api.netdef_text([api.op_text("Sigmoid", ["x"], ["y"], {})], [("x", 1)], [("y", 1)])
+    mgr = api.PredictorManager()
+    mgr.load_model_text(text)
+    p = mgr.create_predictor()
+    x = np.linspace(-2, 2, 64).astype(np.float32).reshape(8, 8)
+    keep = p.feed("x", x)
+    p.forward()
+    capi.check(L.xb_selftest_wait_timeout(200_000, None))      # legacy stream: ordered before the next run
+    torch.cuda.synchronize()
+    with pytest.raises(Exception, match="bounded wait ran out.*site 99"):
+        p.forward()
+    assert ops.device_status() == 0                              # cleared by the runtime
+    p.forward()
+    np.testing.assert_allclose(p.output("y"), 1 / (1 + np.exp(-x)), rtol=1e-6, atol=1e-6)
+    p.close()
+    mgr.close()
+
+
+def test_status_mirror_is_a_host_word():
+    pkg.load()
+    import ctypes as C
+    from x_deeplearning_b200 import capi, ops
+    L = capi.lib()
+    word = C.POINTER(C.c_int32)()
+    capi.check(L.xb_device_status_mirror(C.byref(word)))
+    again = C.POINTER(C.c_int32)()
+    capi.check(L.xb_device_status_mirror(C.byref(again)))
+    assert C.addressof(word.contents) == C.addressof(again.contents)
+    assert word[0] == 0
+    capi.check(L.xb_selftest_wait_timeout(200_000, ops.stream()))
+    torch.cuda.synchronize()
+    assert word[0] == (99 << 8 | 1) == ops.device_status()
+    capi.check(L.xb_device_status_clear())
+    assert word[0] == 0 and ops.device_status() == 0
+
+
 def test_wait_selftest_rejects_bad_limit():
     pkg.load()
     from x_deeplearning_b200 import capi, ops

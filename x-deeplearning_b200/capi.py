@@ -72,9 +72,11 @@ SYMBOLS = {
     "xb_version": (C.c_char_p, []),
     "xb_device_status": (i32, [C.POINTER(i32)]),
     "xb_device_status_clear": (i32, []),
+    "xb_device_status_mirror": (i32, [C.POINTER(C.POINTER(i32))]),
     "xb_selftest_wait_timeout": (i32, [i64, vp]),
     "xb_table_row_pitch": (i64, [i32, i32]),
     "xb_table_create": (i32, [C.POINTER(C.POINTER(TableDesc)), i64, i32, i32, vp, vp]),
+    "xb_table_clone": (i32, [C.POINTER(C.POINTER(TableDesc)), C.POINTER(TableDesc), i32]),
     "xb_table_destroy": (None, [C.POINTER(TableDesc)]),
     "xb_table_build_index_host": (i32, [vp, i64, i64, vp, vp]),
     "xb_copy_segments": (i32, [vp, i32, i64, vp]),

@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -47,6 +48,33 @@ inline size_t dtype_size(int dt) {
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+
+// A launch attribute such as cudaFuncAttributeMaxDynamicSharedMemorySize belongs to one device, and one process
+// may serve several (one workspace per device, blaze/blaze/api/cpp_api/predictor_manager_impl.cc:142-177): this
+// remembers, per launcher, on which devices the attribute was set. Safe for concurrent serving threads: two
+// threads that both find the bit clear both set the (idempotent) attribute.
+struct PerDeviceOnce {
+  std::atomic<uint64_t> bits{0};
+  // true when the caller still has to do the set-up on the current device (ordinal above 63: always)
+  bool needed(int* dev) {
+    *dev = 0;
+    if (cudaGetDevice(dev) != cudaSuccess || *dev < 0 || *dev >= 64) { *dev = -1; return true; }
+    return ((bits.load(std::memory_order_acquire) >> *dev) & 1u) == 0;
+  }
+  void done(int dev) {
+    if (dev >= 0) bits.fetch_or(uint64_t(1) << dev, std::memory_order_release);
+  }
+};
+#define XB_SET_MAX_SMEM_ONCE(once, bytes, ...)                                                        \
+  do {                                                                                                \
+    int dev__;                                                                                        \
+    if ((once).needed(&dev__)) {                                                                      \
+      const void* fns__[] = {__VA_ARGS__};                                                            \
+      for (const void* f__ : fns__)                                                                   \
+        XB_CUDA(cudaFuncSetAttribute(f__, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes))); \
+      (once).done(dev__);                                                                             \
+    }                                                                                                 \
+  } while (0)
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

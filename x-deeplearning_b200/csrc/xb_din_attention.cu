@@ -136,6 +136,7 @@ namespace xb {
 
 int att_status(int* out) { return umma::read_status_word(out); }
 int att_clear_status() { return umma::clear_status_word(); }
+int att_set_status_mirror(int* p) { return umma::set_status_mirror(p); }
 
 }  // namespace xb
 
@@ -185,11 +186,8 @@ extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
   const size_t smem = sizeof(float) * ((size_t)a->d + (size_t)a->h0 * SIMT_THREADS + a->T + SIMT_THREADS);
   XB_REQUIRE(smem <= 200 * 1024, XB_ERR_LIMIT, "xb_din_attention: shape too large for the CUDA-core engine");
   XB_REQUIRE(a->requests <= 65535, XB_ERR_LIMIT, "xb_din_attention: more than 65535 requests per call");
-  static bool simt_attr = false;
-  if (!simt_attr) {
-    XB_CUDA(cudaFuncSetAttribute(din_att_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    simt_attr = true;
-  }
+  static PerDeviceOnce simt_attr;
+  XB_SET_MAX_SMEM_ONCE(simt_attr, 200 * 1024, (const void*)din_att_simt_kernel);
   dim3 grid(a->n_cand, a->requests);
   din_att_simt_kernel<<<grid, SIMT_THREADS, smem, stream>>>(p);
   return check_launch("din_att_simt_kernel");
@@ -227,9 +225,3 @@ extern "C" int xb_din_attention_pack(const xb_din_att_args* a, void* packed, siz
     return launch_att_pair_pack(p, a->act, (char*)packed + first, (cudaStream_t)stream);
   return 0;
 }
-
-#ifdef XB_ATT_TRACE
-extern "C" int xb_debug_att_trace(long long* dst) {
-  return (int)cudaMemcpyFromSymbol(dst, xb::g_att_trace, sizeof(long long) * 6 * 128 * 12);
-}
-#endif

@@ -22,16 +22,6 @@
 namespace xb {
 namespace {
 
-#ifdef XB_ATT_TRACE
-__device__ long long g_att_trace[6 * 128 * 12];
-#define ATT_TRACE(slot, j, ev)                                                                       \
-  do {                                                                                               \
-    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (j) < 128) g_att_trace[((slot) * 128 + (j)) * 12 + (ev)] = clock64(); \
-  } while (0)
-#else
-#define ATT_TRACE(slot, j, ev)
-#endif
-
 constexpr int PAIR_THREADS = 640;        // 4 worker warpgroups, 2 MMA-issuing warps, 2 B-building warps
 constexpr int BUILD_WARP0 = 18;
 
@@ -306,7 +296,6 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
         const uint32_t ph = (uint32_t)(P >> 1) & 1u;
         if (!(mbar_wait(smem_u32(&b_full[pb]), ph, 10) && mbar_wait(smem_u32(&acc1_free[pb]), ph ^ 1u, 14))) break;
         tc_fence_after_sync();
-        ATT_TRACE(4, 2 * P, 1);
         uint64_t da = da0;
         uint64_t db = make_desc_interleaved(smem_u32(bop + pb * (n2 * kq * 2)), n2 * 16, 128);
         const uint32_t acc1 = tmem0 + pb * n2;
@@ -316,7 +305,6 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
           mma_f16_ss(acc1, da, db, p.idesc1, 1u);
         }
         mma_commit(smem_u32(&acc1_full[pb]));
-        ATT_TRACE(4, 2 * P, 2);
       }
     }
   } else if (warp == MMA2_WARP) {
@@ -332,7 +320,6 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
         ok = mbar_wait(smem_u32(&a2_full[b]), ph, 11) && mbar_wait(smem_u32(&acc2_free[b]), ph ^ 1u, 13);
         if (!ok) break;
         tc_fence_after_sync();
-        ATT_TRACE(5, j, 3);
         uint32_t ta = tmem0 + G.c_a2 + b * (k2 / 2);
         uint64_t db = db0;
         const uint32_t acc2 = tmem0 + G.c_acc2 + b * h1p;
@@ -342,7 +329,6 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
           mma_f16_ts(acc2, ta, db, p.idesc2, 1u);
         }
         mma_commit(smem_u32(&acc2_full[b]));
-        ATT_TRACE(5, j, 4);
       }
       // weighted sum over the steps: out = S * K; every earlier MMA has completed once all scores are written
       if (ok && mbar_wait(smem_u32(s_full), 0, 12)) {
@@ -369,7 +355,6 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
       // the pair buffer is free once the MMA of pair P-2 has read it
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[pb]), (uint32_t)((P - 2) >> 1) & 1u, 24))) break;
       const int t = 2 * P + hb;
-      ATT_TRACE(2 + hb, 2 * P, 8);
       if (t < tl) {
         uint8_t* dstb = bop + pb * (n2 * kq * 2) + (hb * h0p) * 16;
         const uint4* kt = reinterpret_cast<const uint4*>(khs + t * dp);
@@ -412,7 +397,6 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&b_full[pb]));
-      ATT_TRACE(2 + hb, 2 * P, 9);
     }
   } else if (warp < 8) {
     // ---- layer-1 warpgroups: half b of the pair accumulator -> activation -> A2[b] -------------------------
@@ -429,7 +413,6 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[pb]), php, 20));
       if (!ok) break;
       tc_fence_after_sync();
-      if ((warp & 3) == 0) ATT_TRACE(wb, j, 5);
       const uint32_t acc1 = lane_addr + pb * n2 + b * h0p;
       // blocks of 16 columns (8 fp16 pairs); the load of the next block is in flight while this one is
       // converted, activated and stored
@@ -460,12 +443,10 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
         if (blk + 1 < nblk && ok) block(blk + 1, vb, va);
       }
       if (!ok) break;
-      if ((warp & 3) == 0) ATT_TRACE(wb, j, 6);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&a2_full[b]));        // one arrival per warp
-      if ((warp & 3) == 0) ATT_TRACE(wb, j, 7);
     }
     // (with an odd number of steps the last pair is drained by warpgroup 0 alone; nobody waits for that)
   } else if (warp < 16) {
@@ -483,7 +464,6 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph, 21));
       if (!ok) break;
       tc_fence_after_sync();
-      if ((warp & 3) == 0) ATT_TRACE(2 + wb, j, 10);
       const uint32_t acc2 = lane_addr + G.c_acc2 + b * h1p;
       __half2 part[4];
 #pragma unroll
@@ -526,7 +506,6 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) din_att_pair_kernel(const __g
         block2(blk, va, vb);
         if (blk + 1 < nblk2) block2(blk + 1, vb, va);
       }
-      if ((warp & 3) == 0) ATT_TRACE(2 + wb, j, 11);
       const float2 f0 = __half22float2(part[0]), f1 = __half22float2(part[1]);
       const float2 f2 = __half22float2(part[2]), f3 = __half22float2(part[3]);
       const float s = p.b2 + ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
@@ -589,13 +568,9 @@ int launch_att_pair(AttParams& p, const xb_din_att_args& a, cudaStream_t stream)
   p.idesc1 = umma::make_idesc(128, g.n2, 0);
   p.idesc2 = umma::make_idesc(128, g.h1p, 0);
   p.idesc3 = umma::make_idesc(128, g.np, 0);
-  static bool attr_set = false;
-  if (!attr_set) {
-    XB_CUDA(cudaFuncSetAttribute(din_att_pair_kernel<XB_ACT_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    XB_CUDA(cudaFuncSetAttribute(din_att_pair_kernel<XB_ACT_SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    XB_CUDA(cudaFuncSetAttribute(din_att_pair_kernel<XB_ACT_DICE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_set;
+  XB_SET_MAX_SMEM_ONCE(attr_set, 220 * 1024, (const void*)din_att_pair_kernel<XB_ACT_NONE>,
+                       (const void*)din_att_pair_kernel<XB_ACT_SIGMOID>, (const void*)din_att_pair_kernel<XB_ACT_DICE>);
   const int64_t blocks = (int64_t)a.requests * p.tiles_per_req;
   XB_REQUIRE(blocks < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_din_attention: too many tiles");
   if (a.act == XB_ACT_DICE) din_att_pair_kernel<XB_ACT_DICE><<<(unsigned)blocks, PAIR_THREADS, g.total, stream>>>(p);

@@ -599,13 +599,9 @@ int launch_att_tc(AttParams& p, const xb_din_att_args& a, cudaStream_t stream) {
   p.idesc2 = umma::make_idesc(128, g.h1p, 0);
   p.idesc3 = umma::make_idesc(128, g.np, 0);
   const TcSmemLayout L = tc_layout(g, p.T);
-  static bool attr_set = false;
-  if (!attr_set) {
-    XB_CUDA(cudaFuncSetAttribute(din_att_tc_kernel<XB_ACT_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    XB_CUDA(cudaFuncSetAttribute(din_att_tc_kernel<XB_ACT_SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    XB_CUDA(cudaFuncSetAttribute(din_att_tc_kernel<XB_ACT_DICE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_set;
+  XB_SET_MAX_SMEM_ONCE(attr_set, 220 * 1024, (const void*)din_att_tc_kernel<XB_ACT_NONE>,
+                       (const void*)din_att_tc_kernel<XB_ACT_SIGMOID>, (const void*)din_att_tc_kernel<XB_ACT_DICE>);
   const int64_t blocks = (int64_t)a.requests * p.tiles_per_req;
   XB_REQUIRE(blocks < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_din_attention: too many tiles");
   if (a.act == XB_ACT_DICE) din_att_tc_kernel<XB_ACT_DICE><<<(unsigned)blocks, TC_THREADS, L.total, stream>>>(p);

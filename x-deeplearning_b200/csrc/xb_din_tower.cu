@@ -523,6 +523,7 @@ void fill_params(TowerParams& p, const xb_din_tower_args& a) {
 
 int tower_status(int* out) { return umma::read_status_word(out); }
 int tower_clear_status() { return umma::clear_status_word(); }
+int tower_set_status_mirror(int* p) { return umma::set_status_mirror(p); }
 
 }  // namespace xb
 
@@ -588,11 +589,8 @@ extern "C" int xb_din_tower(const xb_din_tower_args* a, void* workspace, size_t 
   din_tower_partial_kernel<<<dim3(a->requests, (a->n1 + PT_COLS - 1) / PT_COLS), PT_COLS * PT_SLICES,
                              sizeof(float) * (9 * a->d + a->du + PT_COLS * PT_SLICES + 2), stream>>>(p);
   if (int rc = check_launch("din_tower_partial_kernel")) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    XB_CUDA(cudaFuncSetAttribute(din_tower_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_set;
+  XB_SET_MAX_SMEM_ONCE(attr_set, 220 * 1024, (const void*)din_tower_tc_kernel);
   const int64_t tiles = (int64_t)a->requests * p.tiles_per_req;
   const int grid = (int)std::min<int64_t>(tiles, sm_count());
   din_tower_tc_kernel<<<grid, TW_THREADS, g.total, stream>>>(p);

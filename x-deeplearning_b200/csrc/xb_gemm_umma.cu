@@ -18,6 +18,7 @@
 // row stride, which is what lets parallel branches write side by side into one
 // wide output (axis-1 concat) or stacked (axis 0).
 #include <algorithm>
+#include <mutex>
 #include <cstring>
 
 #include "xb_common.cuh"
@@ -370,7 +371,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     float* s_c = s_b + 256;
     int it = 0, cur_n0 = -1, cur_b = -1;
     bool ok = true;
-    for (uint32_t tile = tile_first; tile < tile_end && ok; tile += tile_step, ++it) {
+    // A warp whose accumulator wait ran out keeps walking the tile sequence without touching tensor memory,
+    // global memory or the acc_empty barrier: the other epilogue warps may have passed the same wait (each
+    // lane keeps its own clock), and they still need this warp at the two named barriers below.
+    for (uint32_t tile = tile_first; tile < tile_end; tile += tile_step, ++it) {
       const int b = (int)(tile / tiles_mn);
       const uint32_t rem = tile - (uint32_t)b * tiles_mn, nt = rem / (uint32_t)p.tiles_m;
       const int m0 = (int)(rem - nt * (uint32_t)p.tiles_m) * BLOCK_M, n0 = (int)nt * p.block_n;
@@ -396,8 +400,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         asm volatile("bar.sync 2, 512;" ::: "memory");
       }
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_full[as]), (uint32_t)(it >> 1) & 1u, 3));
-      if (!ok) break;
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_full[as]), (uint32_t)(it >> 1) & 1u, 3));
+      if (!ok) continue;
       tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + as * acc_stride + ((uint32_t)(q * 32) << 16);
       TOut* yrow = reinterpret_cast<TOut*>(p.Y) + (int64_t)b * p.stride_y + (int64_t)gm * p.ldy;
@@ -534,11 +538,8 @@ bool umma_eligible(const xb_gemm_args& a) {
 template <typename TOut>
 int launch_umma(const CUtensorMap& ma, const CUtensorMap& mb, const UmmaGemmParams& p, dim3 grid, size_t smem,
                 cudaStream_t s) {
-  static bool attr_set = false;   // per instantiation
-  if (!attr_set) {
-    XB_CUDA(cudaFuncSetAttribute(gemm_umma_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 6 * 1024));
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_set;   // per instantiation
+  XB_SET_MAX_SMEM_ONCE(attr_set, SMEM_BUDGET + 6 * 1024, (const void*)gemm_umma_kernel<TOut>);
   gemm_umma_kernel<TOut><<<grid, GEMM_THREADS, smem, s>>>(ma, mb, p);
   return check_launch("gemm_umma_kernel");
 }
@@ -612,6 +613,13 @@ int att_status(int* out);
 int att_clear_status();
 int tower_status(int* out);
 int tower_clear_status();
+int att_set_status_mirror(int* p);
+int tower_set_status_mirror(int* p);
+
+// Host-mapped copy of the status word, one per device: {host address, device address}.
+struct StatusMirror { volatile int* host = nullptr; int* dev = nullptr; };
+static StatusMirror g_mirror[64];
+static std::mutex g_mirror_mu;
 }  // namespace xb
 
 // A wait that nothing will ever satisfy, with its own short limit: shows that a bounded wait gives up,
@@ -650,6 +658,42 @@ extern "C" int xb_device_status(int* status) {
 extern "C" int xb_device_status_clear(void) {
   XB_REQUIRE(gemm_umma_clear_status() == 0 && att_clear_status() == 0 && tower_clear_status() == 0, XB_ERR_CUDA,
              "xb_device_status_clear failed");
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+    std::lock_guard<std::mutex> lock(g_mirror_mu);
+    if (g_mirror[dev].host) *g_mirror[dev].host = 0;
+  }
+  return 0;
+}
+
+extern "C" int xb_device_status_mirror(const volatile int** host_word) {
+  XB_REQUIRE(host_word, XB_ERR_ARG, "xb_device_status_mirror: null pointer");
+  int dev = 0;
+  XB_CUDA(cudaGetDevice(&dev));
+  XB_REQUIRE(dev >= 0 && dev < 64, XB_ERR_LIMIT, "xb_device_status_mirror: device ordinal %d", dev);
+  std::lock_guard<std::mutex> lock(g_mirror_mu);
+  StatusMirror& m = g_mirror[dev];
+  if (m.host == nullptr) {
+    int* h = nullptr;
+    int* d = nullptr;
+    XB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&h), 64, cudaHostAllocMapped | cudaHostAllocPortable));
+    *h = 0;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&d), h, 0) != cudaSuccess) {
+      cudaFreeHost(h);
+      return fail(XB_ERR_CUDA, "xb_device_status_mirror: cudaHostGetDevicePointer failed");
+    }
+    if (umma::set_status_mirror(d) != 0 || att_set_status_mirror(d) != 0 || tower_set_status_mirror(d) != 0) {
+      umma::set_status_mirror(nullptr); att_set_status_mirror(nullptr); tower_set_status_mirror(nullptr);
+      cudaFreeHost(h);
+      return fail(XB_ERR_CUDA, "xb_device_status_mirror: could not publish the mirror address");
+    }
+    // a wait may have run out before the mirror existed
+    int now = 0;
+    if (xb_device_status(&now) == 0) *h = now;
+    m.host = h;
+    m.dev = d;
+  }
+  *host_word = m.host;
   return 0;
 }
 

@@ -810,6 +810,36 @@ extern "C" int xb_table_create(xb_table_desc** out, int64_t rows, int32_t dim, i
   return 0;
 }
 
+extern "C" int xb_table_clone(xb_table_desc** out, const xb_table_desc* src, int32_t src_device) {
+  XB_REQUIRE(out && src && src->weights && src->rows > 0, XB_ERR_ARG, "xb_table_clone: bad arguments");
+  int dev = 0;
+  XB_CUDA(cudaGetDevice(&dev));
+  xb_table_desc* t = (xb_table_desc*)calloc(1, sizeof(xb_table_desc));
+  *t = *src;
+  t->weights = nullptr; t->slot_keys = nullptr; t->slot_rows = nullptr;
+  void *dw = nullptr, *dk = nullptr, *dr = nullptr;
+  const size_t wbytes = (size_t)src->rows * src->row_pitch_bytes;
+  bool ok = cudaMalloc(&dw, wbytes) == cudaSuccess &&
+            cudaMemcpyPeer(dw, dev, src->weights, src_device, wbytes) == cudaSuccess;
+  if (ok && src->slot_keys) {
+    ok = cudaMalloc(&dk, (size_t)src->slots * 8) == cudaSuccess && cudaMalloc(&dr, (size_t)src->slots * 4) == cudaSuccess &&
+         cudaMemcpyPeer(dk, dev, src->slot_keys, src_device, (size_t)src->slots * 8) == cudaSuccess &&
+         cudaMemcpyPeer(dr, dev, src->slot_rows, src_device, (size_t)src->slots * 4) == cudaSuccess;
+  }
+  if (ok) ok = cudaDeviceSynchronize() == cudaSuccess;
+  if (!ok) {
+    const cudaError_t e = cudaGetLastError();
+    if (dw) cudaFree(dw);
+    if (dk) cudaFree(dk);
+    if (dr) cudaFree(dr);
+    free(t);
+    return fail(XB_ERR_CUDA, "xb_table_clone: %s", cudaGetErrorString(e));
+  }
+  t->weights = dw; t->slot_keys = (const int64_t*)dk; t->slot_rows = (const int32_t*)dr;
+  *out = t;
+  return 0;
+}
+
 extern "C" void xb_table_destroy(xb_table_desc* t) {
   if (!t) return;
   if (t->weights) cudaFree((void*)t->weights);
@@ -995,16 +1025,17 @@ extern "C" size_t xb_embedding_pool_static_max_bytes(void) { return XB_POOL_STAT
 extern "C" int xb_embedding_pool_static(const xb_pool_group* groups, int32_t n_groups, xb_stream_t stream) {
   // In host code the array's name is only a handle; its device address has to be asked for,
   // once per device, while that device is current.
-  static void* dev_ptr[64] = {nullptr};
+  // (threads that make the first call on a device at the same time all look up and store the same address)
+  static std::atomic<void*> dev_ptr[64];
   int dev = -1;
   XB_CUDA(cudaGetDevice(&dev));
   XB_REQUIRE(dev >= 0 && dev < 64, XB_ERR_LIMIT, "xb_embedding_pool_static: device ordinal %d out of range", dev);
-  if (dev_ptr[dev] == nullptr) {
+  if (dev_ptr[dev].load(std::memory_order_acquire) == nullptr) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_pool_static_scratch);
     if (e != cudaSuccess || p == nullptr)
       return fail(XB_ERR_CUDA, "xb_embedding_pool_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-    dev_ptr[dev] = p;
+    dev_ptr[dev].store(p, std::memory_order_release);
   }
   XB_REQUIRE(groups && n_groups > 0, XB_ERR_ARG, "xb_embedding_pool_static: no groups");
   const size_t need = xb_embedding_pool_scratch_bytes(groups, n_groups);
@@ -1012,7 +1043,8 @@ extern "C" int xb_embedding_pool_static(const xb_pool_group* groups, int32_t n_g
              "xb_embedding_pool_static: these groups need %zu bytes of offset scratch, the built-in buffer holds %u "
              "(pass exclusive offsets instead of counts, split the call, or use xb_embedding_pool)",
              need, XB_POOL_STATIC_SCRATCH_BYTES);
-  return xb_embedding_pool(groups, n_groups, dev_ptr[dev], XB_POOL_STATIC_SCRATCH_BYTES, stream);
+  return xb_embedding_pool(groups, n_groups, dev_ptr[dev].load(std::memory_order_acquire), XB_POOL_STATIC_SCRATCH_BYTES,
+                           stream);
 }
 
 // ---------------------------------------------------------------------------

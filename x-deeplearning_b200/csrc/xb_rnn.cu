@@ -123,8 +123,8 @@ extern "C" int xb_gru(const void* x, void* y, int64_t batch, int32_t T, int32_t 
   XB_REQUIRE(batch < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_gru: batch too large");
   if (batch == 0 || T == 0) return 0;
   const size_t smem = sizeof(float) * ((size_t)2 * H * 3 * H + 2 * H + 6 * H);
-  static bool attr = false;
-  if (!attr) { XB_CUDA(cudaFuncSetAttribute(gru_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024)); attr = true; }
+  static PerDeviceOnce attr;
+  XB_SET_MAX_SMEM_ONCE(attr, 110 * 1024, (const void*)gru_kernel);
   const int threads = (3 * H + 31) / 32 * 32;
   gru_kernel<<<(unsigned)batch, threads, smem, (cudaStream_t)s>>>(x, y, T, H, i2h, h2h, i2h_bias, h2h_bias, dtype);
   return check_launch("gru_kernel");
@@ -139,8 +139,8 @@ extern "C" int xb_augru(const void* x, const void* att, void* y, int64_t batch, 
   XB_REQUIRE(batch < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_augru: batch too large");
   if (batch == 0 || T == 0) return 0;
   const size_t smem = sizeof(float) * ((size_t)6 * H * H + 5 * H);
-  static bool attr = false;
-  if (!attr) { XB_CUDA(cudaFuncSetAttribute(augru_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024)); attr = true; }
+  static PerDeviceOnce attr;
+  XB_SET_MAX_SMEM_ONCE(attr, 110 * 1024, (const void*)augru_kernel);
   const int threads = (2 * H + 31) / 32 * 32;
   augru_kernel<<<(unsigned)batch, threads, smem, (cudaStream_t)s>>>(x, att, y, T, H, Wg, bg, Wc, bc, dtype);
   return check_launch("augru_kernel");

@@ -19,6 +19,10 @@ constexpr long long kWaitCycles = 1ll << 31;   // about one second at B200 clock
 // 0 = fine; otherwise (site << 8 | detail) of the first bounded wait that ran
 // out. Each unit exposes a reader that xb_device_status() combines.
 static __device__ int g_status = 0;
+// Optional mirror of the word in mapped host memory (set by xb_device_status_mirror): the first wait that runs
+// out also writes its code there, so a serving thread can test a plain host word after its stream
+// synchronisation instead of paying a device-to-host copy per request.
+static __device__ int* g_status_host = nullptr;
 
 inline int read_status_word(int* out) {
   return cudaMemcpyFromSymbol(out, g_status, sizeof(int)) == cudaSuccess ? 0 : -1;
@@ -26,6 +30,9 @@ inline int read_status_word(int* out) {
 inline int clear_status_word() {
   int z = 0;
   return cudaMemcpyToSymbol(g_status, &z, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
+inline int set_status_mirror(int* device_visible) {
+  return cudaMemcpyToSymbol(g_status_host, &device_visible, sizeof(int*)) == cudaSuccess ? 0 : -1;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -73,7 +80,13 @@ __device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity,
 __device__ __forceinline__ long long wait_limit() {
   return (*reinterpret_cast<volatile int*>(&g_status) != 0) ? (1ll << 16) : kWaitCycles;
 }
-__device__ __forceinline__ void wait_gave_up(int site) { atomicCAS(&g_status, 0, (site << 8) | 1); }
+static __device__ __noinline__ void wait_gave_up(int site) {
+  const int code = (site << 8) | 1;
+  if (atomicCAS(&g_status, 0, code) == 0 && g_status_host != nullptr) {
+    *reinterpret_cast<volatile int*>(g_status_host) = code;
+    __threadfence_system();
+  }
+}
 // Bounded wait. `site` identifies the caller in the status word.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int site) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -83,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int sit
   const long long limit = (*reinterpret_cast<volatile int*>(&g_status) != 0) ? (1ll << 16) : kWaitCycles;
   while (!mbar_try_wait(bar, parity)) {
     if (clock64() - t0 > limit) {
-      atomicCAS(&g_status, 0, (site << 8) | 1);
+      wait_gave_up(site);
       return false;
     }
   }

@@ -253,6 +253,7 @@ void BatchQueue::RunBatch(std::vector<Task>* batch) {
     BLAZE_CONDITION_THROW(net_->Run(), "the merged net did not run");
     SplitOutputs(*batch, stream);
     CUDA_CHECK(cudaStreamSynchronize(stream));
+    net_->CheckDeviceStatus();
     GlobalBatchingStats().batches += 1;
     GlobalBatchingStats().tasks += (int64_t)batch->size();
   } catch (const std::exception& e) {

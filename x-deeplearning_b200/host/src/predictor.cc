@@ -242,6 +242,7 @@ bool Predictor::Forward(const PredictorCallback&& cb) {
     impl_->net_->profile = impl_->profile_;
     if (!impl_->net_->Run()) return false;
     CUDA_CHECK(cudaStreamSynchronize(impl_->net_->stream()));
+    impl_->net_->CheckDeviceStatus();
     if (cb) cb();
     return true;
   } catch (const std::exception& e) {

@@ -25,7 +25,8 @@ struct FileTable {
 class B200SparsePuller : public SparsePuller {
  public:
   ~B200SparsePuller() override {
-    for (auto& kv : tables_) xb_table_destroy(kv.second.desc);
+    for (auto& kv : tables_)
+      for (auto& r : kv.second) xb_table_destroy(r.desc);
   }
 
   Status Load(const std::string& url) override {
@@ -87,7 +88,7 @@ class B200SparsePuller : public SparsePuller {
       LOG_ERROR("xb_table_create failed: ", xb_last_error());
       return kFail;
     }
-    tables_[name] = r;
+    tables_[name].push_back(r);
     return kOK;
   }
 
@@ -196,12 +197,21 @@ class B200SparsePuller : public SparsePuller {
       CUDA_CHECK(cudaSetDevice(device_id));
       BLAZE_CONDITION_THROW(xb_table_create(&res.desc, rows, dim, file_fp16_ ? XB_F16 : XB_F32, w.data(), keys.data()) == 0,
                             "xb_table_create failed: ", xb_last_error());
-      it = tables_.emplace(name, res).first;
+      it = tables_.emplace(name, std::vector<Resident>{res}).first;
       file_tables_.erase(f);
     }
-    BLAZE_CONDITION_THROW(it->second.device == device_id, "table ", name, " is resident on device ", it->second.device,
-                          ", the operator runs on device ", device_id);
-    return it->second.desc;
+    for (const Resident& r : it->second)
+      if (r.device == device_id) return r.desc;
+    // first use on another device of this process: one replica per device, copied device to device
+    // (one PredictorManager serves CreatePredictor(type, device_id) for any device id)
+    Resident rep;
+    rep.device = device_id;
+    CUDA_CHECK(cudaSetDevice(device_id));
+    const Resident& src = it->second.front();
+    BLAZE_CONDITION_THROW(xb_table_clone(&rep.desc, src.desc, src.device) == 0, "table ", name, ": replica on device ",
+                          device_id, " failed: ", xb_last_error());
+    it->second.push_back(rep);
+    return rep.desc;
   }
 
   void* Scratch(int device, size_t bytes) {
@@ -218,7 +228,7 @@ class B200SparsePuller : public SparsePuller {
   }
 
   std::mutex mu_;
-  std::unordered_map<std::string, Resident> tables_;
+  std::unordered_map<std::string, std::vector<Resident>> tables_;   // one replica per device that used the table
   std::unordered_map<std::string, FileTable> file_tables_;
   bool file_fp16_ = false;
 };
@@ -243,7 +253,7 @@ class MockSparsePuller : public B200SparsePuller {
           Resident r;
           r.device = device_id;
           BLAZE_CONDITION_THROW(xb_table_create(&r.desc, 1, g.dim, XB_F32, ones.data(), nullptr) == 0, xb_last_error());
-          tables_[g.name] = r;
+          tables_[g.name].push_back(r);
         }
       }
       g.key = zeros;

@@ -303,6 +303,16 @@ Net::Net(const NetDef& def, Workspace* ws) : def_(def), ws_(ws) {
   // typed external inputs exist before the operators that read them are built
   for (const auto& v : def.external_input) ws->CreateBlob(v.name, def.device_option)->set_data_type(v.dtype);
   for (const auto& od : def.op) ops_.push_back(CreateOperator(od, ws));
+  CUDA_CHECK(cudaSetDevice(def.device_option.device_id));
+  BLAZE_CONDITION_THROW(xb_device_status_mirror(&status_word_) == 0, "device status word: ", xb_last_error());
+}
+
+void Net::CheckDeviceStatus() {
+  const int st = status_word_ ? *status_word_ : 0;
+  if (st == 0) return;
+  xb_device_status_clear();
+  BLAZE_THROW("a bounded wait ran out inside a tensor-core kernel on device ", device_id(), " (site ", st >> 8,
+              "): the results of this run are invalid");
 }
 
 cudaStream_t Net::stream() const {

@@ -363,6 +363,10 @@ class Net {
   Workspace* workspace() { return ws_; }
   cudaStream_t stream() const;
   int device_id() const { return def_.device_option.device_id; }
+  // After the stream was synchronised: throws when a bounded wait inside a tensor-core kernel of this
+  // device ran out since the last check (the outputs of that run are not to be trusted), naming the
+  // site, and clears the device's status word so that later runs wait with their full limits again.
+  void CheckDeviceStatus();
   int last_launches = 0;
   // per-operator wall time of the last Run when profiling is on (observer "profile")
   bool profile = false;
@@ -373,6 +377,7 @@ class Net {
   Workspace* ws_;
   std::vector<std::unique_ptr<OperatorBase>> ops_;
   std::vector<std::string> ext_in_, ext_out_;
+  const volatile int* status_word_ = nullptr;   // host-mapped mirror of the device's status word
 };
 
 // Graph rewrite run by LoadModel(optimization_pass = true): folds Dice / PRelu / Sigmoid nodes
