@@ -300,6 +300,12 @@ def run_ours(args):
                      "pool_ms_per_step": pool_ms},
         "clocks": clocks,
     }
+    if world > 1 and not args.no_sharded:
+        # the path that has collectives: measured after the replica leg, on the same process group
+        del net, plans, staged, pred, mgr
+        torch.cuda.empty_cache()
+        leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype)
+        line["sharded"] = leg.run(min(K, 20), W)
     if rank == 0 and world == 1 and not args.no_cpu:
         line["embedding_pool"] = bench_pool(pk)
         line["cpu_baseline"] = cpu_baseline_din(model, workloads, cores=1, budget_s=args.cpu_seconds)
@@ -577,55 +583,77 @@ def run_batching(args):
                               "Forward() of every predictor in turn (alone) or Forward(cb) of all until the last callback (batched)"}))
 
 
-def run_sharded(args):
-    """Row-sharded pooling + MLP (the large-table configuration): 4 tables x `--table-rows` rows x dim 32
-    fp16 sharded by id % world, batch 65536 x 40 feature groups split by sample, ids routed and pooled
-    vectors returned with NCCL all-to-all, then the MLP 1280-1024-512-256-1 (PReLU, sigmoid) data-parallel.
-    Launch under torch.distributed.run; prints one JSON line on rank 0."""
-    import numpy as np
-    import torch
-    import torch.distributed as dist
-    load_package()
-    from x_deeplearning_b200 import capi, ops, sharded, workloads
-    rank, local_rank, world = dist_env()
-    torch.cuda.set_device(local_rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    comm, gops = sharded.DistComm(), sharded.GpuShardOps()
-    n_tables, gpt, dim = 4, 10, 32
-    rows_total = args.table_rows
-    B = 65536 // world
-    rng = np.random.default_rng(100 + rank)
-    tables = []
-    for t in range(n_tables):
-        local_rows = (rows_total - rank + world - 1) // world
-        tb = ops.Table.__new__(ops.Table)
-        tb.rows, tb.dim, tb.dtype, tb.pitch = local_rows, dim, torch.float16, dim * 2
-        tb.buf = torch.empty((local_rows, dim), dtype=torch.float16, device="cuda")
-        for r0 in range(0, local_rows, 1 << 24):
-            tb.buf[r0:r0 + (1 << 24)].normal_(0, 0.01)
-        tb.desc = capi.TableDesc()
-        tb.desc.weights, tb.desc.rows, tb.desc.dim, tb.desc.dtype, tb.desc.row_pitch_bytes = tb.buf.data_ptr(), local_rows, dim, capi.XB_F16, dim * 2
-        tb.slot_keys = tb.slot_rows = None
-        tables.append(tb)
-    feeds = []
-    for t in range(n_tables):
-        counts = rng.integers(1, 31, gpt * B).astype(np.int32)
-        n = int(counts.sum())
-        ids = workloads.zipf_ids(rng, rows_total, n, 1.05)
-        off = np.zeros(len(counts) + 1, np.int32)
-        np.cumsum(counts, out=off[1:])
-        feeds.append((torch.from_numpy(ids).cuda(), torch.from_numpy(off).cuda(), n))
-    dims = [n_tables * gpt * dim, 1024, 512, 256, 1]
-    Ws = [torch.randn((dims[i + 1], dims[i]), device="cuda", dtype=torch.float16) / dims[i] ** 0.5 for i in range(4)]
-    bs = [torch.randn(dims[i + 1], device="cuda") * 0.01 for i in range(4)]
-    slope = torch.full((1,), 0.25, device="cuda")
-    pooled = torch.empty((B, dims[0]), dtype=torch.float16, device="cuda")
-    acts = [torch.empty((B, dims[i + 1]), dtype=torch.float16, device="cuda") for i in range(4)]
+def shard_table_values(table, rows, dim, xp):
+    """Value of element (row, col) of sharded table `table`: a counter-based hash, so that any rank and the CPU
+    checker can materialise any row of a 200 M-row table without storing it. `rows` is an int64 array (numpy or
+    torch); returns [len(rows), dim] float32 in (-0.0301, 0.0301) on the same backend."""
+    if xp.__name__ == "numpy":
+        r = rows.astype(xp.int64)[:, None]
+        c = xp.arange(dim, dtype=xp.int64)[None, :]
+    else:
+        r = rows.to(xp.int64)[:, None]
+        c = xp.arange(dim, dtype=xp.int64, device=rows.device)[None, :]
+    h = (r * 1000003 + c * 7919 + (table + 1) * 104729) & 0x7fffffff
+    h = (h * 48271) % 2147483647                       # products stay below 2^62
+    h = (h >> 7) % 6021
+    if xp.__name__ == "numpy":
+        return (h - 3010).astype(xp.float32) * xp.float32(1e-5)
+    return (h - 3010).to(xp.float32) * 1e-5
 
-    phases = []
 
-    def step(timed=False):
-        # the four tables share the ownership rule: one routing pass and one pair of exchanges for all of them
+class ShardedLeg:
+    """Row-sharded pooling + MLP (the large-table configuration): 4 tables x `table_rows` rows x dim 32 fp16
+    sharded by id % world, 65536 x 40 feature groups split by sample over the ranks, ids routed and pooled
+    vectors returned with NCCL all-to-all, then the MLP 1280-1024-512-256-1 (PReLU, sigmoid) data-parallel."""
+    N_TABLES, GPT, DIM, BATCH = 4, 10, 32, 65536
+
+    def __init__(self, rank, world, table_rows, partial_dtype="f16"):
+        import numpy as np
+        import torch
+        from x_deeplearning_b200 import capi, ops, sharded, workloads
+        self.rank, self.world, self.rows_total = rank, world, table_rows
+        self.torch, self.ops, self.capi, self.sharded = torch, ops, capi, sharded
+        self.comm, self.gops = sharded.DistComm(), sharded.GpuShardOps(partial_dtype=partial_dtype)
+        self.partial_dtype = partial_dtype
+        n_tables, gpt, dim = self.N_TABLES, self.GPT, self.DIM
+        self.B = B = self.BATCH // world
+        rng = np.random.default_rng(100 + rank)
+        self.tables = []
+        for t in range(n_tables):
+            local_rows = (table_rows - rank + world - 1) // world
+            tb = ops.Table.__new__(ops.Table)
+            tb.rows, tb.dim, tb.dtype, tb.pitch = local_rows, dim, torch.float16, dim * 2
+            tb.buf = torch.empty((local_rows, dim), dtype=torch.float16, device="cuda")
+            for r0 in range(0, local_rows, 1 << 22):          # local row l of this shard is global row l*world + rank
+                l = torch.arange(r0, min(r0 + (1 << 22), local_rows), dtype=torch.int64, device="cuda")
+                tb.buf[r0:r0 + l.numel()] = shard_table_values(t, l * world + rank, dim, torch).to(torch.float16)
+            tb.desc = capi.TableDesc()
+            tb.desc.weights, tb.desc.rows, tb.desc.dim, tb.desc.dtype, tb.desc.row_pitch_bytes = \
+                tb.buf.data_ptr(), local_rows, dim, capi.XB_F16, dim * 2
+            tb.slot_keys = tb.slot_rows = None
+            self.tables.append(tb)
+        self.host_feeds, self.feeds = [], []
+        for t in range(n_tables):
+            counts = rng.integers(1, 31, gpt * B).astype(np.int32)
+            n = int(counts.sum())
+            ids = workloads.zipf_ids(rng, table_rows, n, 1.05)
+            off = np.zeros(len(counts) + 1, np.int32)
+            np.cumsum(counts, out=off[1:])
+            self.host_feeds.append((ids, off))
+            self.feeds.append((torch.from_numpy(ids).cuda(), torch.from_numpy(off).cuda(), n))
+        self.dims = dims = [n_tables * gpt * dim, 1024, 512, 256, 1]
+        wrng = np.random.default_rng(7)                       # the dense weights are replicated: same seed on every rank
+        self.W_host = [workloads.fp16_round(wrng.normal(0, 1.0 / dims[i] ** 0.5, (dims[i + 1], dims[i]))) for i in range(4)]
+        self.b_host = [workloads.fp16_round(wrng.normal(0, 0.01, dims[i + 1])) for i in range(4)]
+        self.Ws = [torch.from_numpy(w).cuda().to(torch.float16) for w in self.W_host]
+        self.bs = [torch.from_numpy(b).cuda() for b in self.b_host]
+        self.slope = torch.full((1,), 0.25, device="cuda")
+        self.pooled = torch.empty((B, dims[0]), dtype=torch.float16, device="cuda")
+        self.acts = [torch.empty((B, dims[i + 1]), dtype=torch.float16, device="cuda") for i in range(4)]
+        self.phases = []
+
+    def step(self, timed=False):
+        torch, ops, capi = self.torch, self.ops, self.capi
         events = []
 
         def mark(name):
@@ -634,50 +662,109 @@ def run_sharded(args):
             events.append((name, e))
         if timed:
             mark("start")
-        stats = [sharded.sharded_pool_tables(comm, gops, tables, dim, [f[0] for f in feeds], [None] * n_tables,
-                                             [f[1] for f in feeds], [gpt] * n_tables, pooled, mark=mark if timed else None)]
-        x = pooled
+        # the four tables share the ownership rule: one routing pass and one pair of exchanges for all of them
+        stats = self.sharded.sharded_pool_tables(self.comm, self.gops, self.tables, self.DIM, [f[0] for f in self.feeds],
+                                                 [None] * self.N_TABLES, [f[1] for f in self.feeds],
+                                                 [self.GPT] * self.N_TABLES, self.pooled, mark=mark if timed else None)
+        x = self.pooled
         for i in range(4):
             last = i == 3
-            ops.gemm(x, Ws[i], Y=acts[i], bias=bs[i], trans_b=True, M=B, N=dims[i + 1], K=dims[i],
-                     epilogue=capi.XB_EPI_SIGMOID if last else capi.XB_EPI_PRELU, ep=(None if last else slope, None, None),
-                     ep_count=0 if last else 1)
-            x = acts[i]
+            ops.gemm(x, self.Ws[i], Y=self.acts[i], bias=self.bs[i], trans_b=True, M=self.B, N=self.dims[i + 1], K=self.dims[i],
+                     epilogue=capi.XB_EPI_SIGMOID if last else capi.XB_EPI_PRELU,
+                     ep=(None if last else self.slope, None, None), ep_count=0 if last else 1)
+            x = self.acts[i]
         if timed:
             mark("mlp")
-            phases.append(events)
+            self.phases.append(events)
         return stats
 
-    for _ in range(args.warmup):
-        step()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    dist.barrier(); torch.cuda.synchronize()
-    e0.record()
-    for _ in range(args.steps):
-        stats = step()
-    e1.record()
-    dist.barrier(); torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    # where a step spends its time on this rank: a few more steps with an event after every phase (outside the
-    # timed region; the events themselves cost nothing but the host gaps between phases show up here too)
-    for _ in range(5):
-        step(timed=True)
-    torch.cuda.synchronize()
-    phase_ms = {}
-    for events in phases:
-        for (_, a), (name, b) in zip(events[:-1], events[1:]):
-            phase_ms[name] = phase_ms.get(name, 0.0) + a.elapsed_time(b) / len(phases)
-    assert ops.device_status() == 0
+    def check(self, n_check=48):
+        """One step, then this rank's first `n_check` samples against the CPU oracle: pooled vectors (un-sharded
+        QuickEmbeddingDict::Get semantics over the rows the hash generator names) and the final sigmoid."""
+        import numpy as np
+        checker_path()
+        import orc
+        torch = self.torch
+        self.step()
+        torch.cuda.synchronize()
+        B, dim, gpt = self.B, self.DIM, self.GPT
+        want = np.zeros((n_check, self.dims[0]), np.float32)
+        mag = np.zeros((n_check, self.dims[0]), np.float32)
+        for t, (ids, off) in enumerate(self.host_feeds):
+            for g in range(gpt):
+                lo, hi = int(off[g * B]), int(off[g * B + n_check])
+                seg_ids = ids[lo:hi]
+                counts = (off[g * B + 1:g * B + n_check + 1] - off[g * B:g * B + n_check]).astype(np.int32)
+                uniq, inv = np.unique(seg_ids, return_inverse=True)
+                rows = shard_table_values(t, uniq, dim, np).astype(np.float16).astype(np.float32)
+                col = (t * gpt + g) * dim
+                ones = np.ones(len(seg_ids), np.float32)
+                orc.embedding_pool(rows, inv.astype(np.int64), ones, counts, [dict(udf=0, out=want, col=col)])
+                orc.embedding_pool(np.abs(rows), inv.astype(np.int64), ones, counts, [dict(udf=0, out=mag, col=col)])
+        got = self.pooled[:n_check].float().cpu().numpy()
+        # fp16 partial sums and an fp16 result: a few half-precision roundings of the magnitude sum
+        tol = (4.0 if self.partial_dtype == "f16" else 1.0) * 2.0 ** -11
+        pooled_rel = float((np.abs(got - want) / np.maximum(mag, 1e-6)).max())
+        x = got                                                # the MLP of the oracle reads what the GPU pooled
+        for i in range(4):
+            x = orc.gemm_op(x, self.W_host[i], self.b_host[i], transb=True)
+            x = orc.sigmoid(x) if i == 3 else orc.prelu(x, np.full(1, 0.25, np.float32)).astype(np.float16).astype(np.float32)
+        prob_abs = float(np.abs(self.acts[3][:n_check].float().cpu().numpy() - x).max())
+        res = torch.tensor([pooled_rel / tol, prob_abs / 2e-3], dtype=torch.float64, device="cuda")
+        import torch.distributed as dist
+        dist.all_reduce(res, op=dist.ReduceOp.MAX)
+        ok = bool(res[0].item() <= 1.0 and res[1].item() <= 1.0)
+        return {"ok": ok, "samples_checked_per_rank": n_check, "pooled_max_err_over_tol": float(res[0].item()),
+                "pooled_tol_rel_to_magnitude_sum": tol, "prob_max_abs_err": float(res[1].item()) * 2e-3, "prob_tol": 2e-3,
+                "oracle": "orc.embedding_pool + orc.gemm_op on the rows the generator names (all ranks, max)"}
+
+    def run(self, steps, warmup):
+        import torch.distributed as dist
+        torch = self.torch
+        parity = self.check()
+        assert parity["ok"], "row-sharded path differs from the CPU oracle: %r" % (parity,)
+        for _ in range(max(warmup, 3)):
+            self.step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier(); torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            stats = self.step()
+        e1.record()
+        dist.barrier(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        # where a step spends its time on this rank: a few more steps with an event after every phase (outside the
+        # timed region; the host gaps between phases show up here too)
+        for _ in range(5):
+            self.step(timed=True)
+        torch.cuda.synchronize()
+        phase_ms = {}
+        for events in self.phases:
+            for (_, a), (name, b) in zip(events[:-1], events[1:]):
+                phase_ms[name] = phase_ms.get(name, 0.0) + a.elapsed_time(b) / len(self.phases)
+        assert self.ops.device_status() == 0
+        ms = float(t.item()) / steps
+        return {"ms_per_step": ms, "samples_per_s": self.BATCH / (ms * 1e-3), "steps": steps, "n_gpus": self.world,
+                "table_rows": self.rows_total, "tables": self.N_TABLES, "dim": self.DIM,
+                "ids_per_rank_step": sum(f[2] for f in self.feeds),
+                "routed_bytes_per_rank_step": stats["routed_bytes"], "returned_bytes_per_rank_step": stats["returned_bytes"],
+                "partial_dtype": self.partial_dtype, "phase_ms_rank0": {k: round(v, 4) for k, v in phase_ms.items()},
+                "parity": parity, "timing": "max over ranks, CUDA events; MLP 1280-1024-512-256-1 included"}
+
+
+def run_sharded(args):
+    """The row-sharded leg alone. Launch under torch.distributed.run; prints one JSON line on rank 0."""
+    import torch
+    import torch.distributed as dist
+    load_package()
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype)
+    out = leg.run(args.steps, args.warmup)
     if rank == 0:
-        ms = float(t.item()) / args.steps
-        n_ids = sum(f[2] for f in feeds)
-        print(json.dumps({"micro": "sharded", "n_gpus": world, "ms_per_step": ms, "samples_per_s": 65536 / (ms * 1e-3),
-                          "table_rows": rows_total, "ids_per_rank_step": n_ids,
-                          "routed_bytes_per_rank_step": sum(s["routed_bytes"] for s in stats),
-                          "returned_bytes_per_rank_step": sum(s["returned_bytes"] for s in stats),
-                          "phase_ms_rank0": {k: round(v, 4) for k, v in phase_ms.items()},
-                          "note": "max over ranks, CUDA events; MLP 1280-1024-512-256-1 included"}))
+        print(json.dumps(dict({"micro": "sharded"}, **out)))
     dist.destroy_process_group()
 
 
@@ -694,7 +781,10 @@ def main():
                     help="Predictors (one per host thread, each with its own stream) of the end-to-end leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and pooling side measurements")
-    ap.add_argument("--table-rows", type=int, default=200_000_000, help="rows per table of --micro sharded")
+    ap.add_argument("--table-rows", type=int, default=200_000_000, help="rows per table of the row-sharded leg")
+    ap.add_argument("--partial-dtype", default="f16", choices=["f16", "f32"],
+                    help="dtype of the partial sums the owners return in the row-sharded leg (f32 for the 1e-5 bar)")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the row-sharded leg of a multi-GPU run")
     ap.add_argument("--micro", choices=["att", "pool", "gemm", "gemm_mlp", "tower", "sharded", "batching"], help="run --steps launches of one kernel on a small case "
                     "(for profiler captures) instead of the benchmark")
     args = ap.parse_args()

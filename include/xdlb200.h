@@ -208,15 +208,19 @@ int xb_tag_counts(const int32_t* tags, int64_t n, int32_t* counts, int64_t n_cou
  * of `tags`; counts[s * segments + t] receives the length of segment t of source s. xb_shard_pool then pools, for
  * every source s and table t, the segments [sum(table_segments[:t]), +table_segments[t]) of that source against
  * tables[t] (HOST arrays of n_tables entries); offsets [sources * S + 1] are the exclusive offsets of all
- * (source, segment) pairs into `rows` (S = sum(table_segments)); out [sources * S, dim] fp32. */
+ * (source, segment) pairs into `rows` (S = sum(table_segments)); out [sources * S, dim] in out_dtype: XB_F32 (the
+ * 1e-5 bar of fp32 models) or XB_F16 (a model whose tables and activations are fp16: each partial sum is rounded
+ * once, which halves the bytes of the return exchange). xb_shard_combine takes the same dtype as partial_dtype and
+ * always accumulates in fp32. Tags outside [0, segments) - they come from a peer - are ignored by the counting
+ * kernels. */
 int xb_tag_counts_sources(const int32_t* tags, const int64_t* source_counts, int32_t sources, int32_t* counts,
                           int64_t segments, xb_stream_t stream);
 int xb_shard_pool(const xb_table_desc* const* tables, const int64_t* table_segments, int32_t n_tables,
                   const void* rows, int32_t row_dtype, int64_t n_rows, const float* values, const int32_t* offsets,
-                  int32_t sources, int32_t dim, float* out, xb_stream_t stream);
-int xb_shard_combine(const float* partial, int32_t shards, int64_t segments, int32_t dim, const int32_t* seg_len,
-                     int32_t avg, void* out, int64_t out_stride, int64_t groups, int32_t out_dtype,
-                     xb_stream_t stream);
+                  int32_t sources, int32_t dim, void* out, int32_t out_dtype, xb_stream_t stream);
+int xb_shard_combine(const void* partial, int32_t partial_dtype, int32_t shards, int64_t segments, int32_t dim,
+                     const int32_t* seg_len, int32_t avg, void* out, int64_t out_stride, int64_t groups,
+                     int32_t out_dtype, xb_stream_t stream);
 
 /* Self-test of the bounded waits (no counterpart in the reference): launches one warp that waits on a barrier
  * nothing will ever signal and gives up after `limit_cycles`. Afterwards xb_device_status reports a non-zero

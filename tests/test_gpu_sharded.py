@@ -195,3 +195,76 @@ def test_segment_lengths_of_all_sources_in_one_launch():
     got = sharded.GpuShardOps().tag_counts_sources(torch.from_numpy(tags).cuda(), source_counts, segments)
     want = CpuShardOps().tag_counts_sources(torch.from_numpy(tags), source_counts, segments)
     assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("world,dim,out_dtype,avg", [(8, 32, torch.float16, False), (3, 8, torch.float32, True),
+                                                     (5, 12, torch.float16, False)])
+def test_combine_of_fp16_partials_accumulates_in_fp32_in_owner_order(world, dim, out_dtype, avg):
+    """Partials that crossed the wire as fp16: the 16-byte path (dim % 8 == 0) and the element path."""
+    pkg.load()
+    from x_deeplearning_b200 import sharded
+    rng = np.random.default_rng(world * 10 + dim)
+    groups, rows = 5, 41
+    segments = groups * rows
+    partial = rng.normal(0, 1, (world * segments, dim)).astype(np.float16)
+    seg_len = rng.integers(0, 9, segments).astype(np.int32)
+    want = torch.zeros((rows, groups * dim), dtype=torch.float32)
+    CpuShardOps().combine(torch.from_numpy(partial.astype(np.float32)), world, segments, dim, groups, want,
+                          torch.from_numpy(seg_len), avg)
+    out = torch.zeros((rows, groups * dim), dtype=out_dtype, device="cuda")
+    sharded.GpuShardOps(partial_dtype="f16").combine(torch.from_numpy(partial).cuda(), world, segments, dim, groups, out,
+                                                     torch.from_numpy(seg_len).cuda() if avg else None, avg)
+    assert torch.equal(out.cpu(), want.to(out_dtype))
+
+
+def test_tags_from_a_peer_outside_the_segment_range_are_ignored():
+    pkg.load()
+    from x_deeplearning_b200 import sharded
+    segments, source_counts = 50, [6, 5]
+    tags = np.array([0, 3, 3, 50, -1, 49, 7, 1 << 30, 7, 7, 0], np.int32)
+    got = sharded.GpuShardOps().tag_counts_sources(torch.from_numpy(tags).cuda(), source_counts, segments).cpu().numpy()
+    want = np.zeros(2 * segments, np.int32)
+    for s, (lo, hi) in enumerate([(0, 6), (6, 11)]):
+        for t in tags[lo:hi]:
+            if 0 <= t < segments:
+                want[s * segments + t] += 1
+    np.testing.assert_array_equal(got, want)
+    one = sharded.GpuShardOps().tag_counts(torch.from_numpy(tags).cuda(), segments).cpu().numpy()
+    np.testing.assert_array_equal(one, want[:segments] + want[segments:])
+
+
+@pytest.mark.parametrize("partial_dtype", ["f16", "f32"])
+def test_large_table_configuration_shape_on_one_rank(partial_dtype):
+    """The large-table configuration's shape on a world of one rank: dim 32 fp16 tables, 4096 samples x 40 feature
+    groups over 4 tables, Zipf(1.05) ids, id lists of 1..30, through the whole path (route, unpack, counts, owner
+    pooling, combine) against the un-sharded oracle."""
+    pkg.load()
+    from x_deeplearning_b200 import ops, sharded, workloads
+    rng = np.random.default_rng(42)
+    n_tables, gpt, dim, B, rows_total = 4, 10, 32, 4096, 300_000
+    tables_np = [workloads.fp16_round(rng.normal(0, 0.01, (rows_total, dim))) for _ in range(n_tables)]
+    tables = [ops.Table(torch.from_numpy(t), torch.float16) for t in tables_np]
+    feeds = []
+    for t in range(n_tables):
+        counts = rng.integers(1, 31, gpt * B).astype(np.int32)
+        ids = workloads.zipf_ids(rng, rows_total, int(counts.sum()), 1.05)
+        off = np.zeros(len(counts) + 1, np.int32)
+        np.cumsum(counts, out=off[1:])
+        feeds.append((ids, counts, off))
+    out = torch.zeros((B, n_tables * gpt * dim), dtype=torch.float16, device="cuda")
+    sharded.sharded_pool_tables(_SelfComm(), sharded.GpuShardOps(partial_dtype=partial_dtype), tables, dim,
+                                [torch.from_numpy(f[0]).cuda() for f in feeds], [None] * n_tables,
+                                [torch.from_numpy(f[2]).cuda() for f in feeds], [gpt] * n_tables, out)
+    got = out.float().cpu().numpy()
+    for t, (ids, counts, off) in enumerate(feeds):
+        want = np.zeros((gpt * B, dim), np.float32)
+        mag = np.zeros((gpt * B, dim), np.float32)
+        ones = np.ones(len(ids), np.float32)
+        orc.embedding_pool(tables_np[t], ids, ones, counts, [dict(udf=0, out=want, col=0)])
+        orc.embedding_pool(np.abs(tables_np[t]), ids, ones, counts, [dict(udf=0, out=mag, col=0)])
+        want = want.reshape(gpt, B, dim).transpose(1, 0, 2).reshape(B, gpt * dim)
+        mag = mag.reshape(gpt, B, dim).transpose(1, 0, 2).reshape(B, gpt * dim)
+        err = np.abs(got[:, t * gpt * dim:(t + 1) * gpt * dim] - want)
+        # one fp16 rounding of the result (and one of the partial sum when it travels as fp16)
+        tol = (2.0 if partial_dtype == "f16" else 1.0) * 2.0 ** -11
+        assert (err <= tol * np.maximum(mag, 1e-6)).all(), float((err / np.maximum(mag, 1e-6)).max())

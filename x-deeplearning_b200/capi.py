@@ -89,8 +89,8 @@ SYMBOLS = {
     "xb_unpack_routed": (i32, [vp, i64, vp, vp, vp]),
     "xb_tag_counts": (i32, [vp, i64, vp, i64, vp]),
     "xb_tag_counts_sources": (i32, [vp, vp, i32, vp, i64, vp]),
-    "xb_shard_pool": (i32, [vp, vp, i32, vp, i32, i64, vp, vp, i32, i32, vp, vp]),
-    "xb_shard_combine": (i32, [vp, i32, i64, i32, vp, i32, vp, i64, i64, i32, vp]),
+    "xb_shard_pool": (i32, [vp, vp, i32, vp, i32, i64, vp, vp, i32, i32, vp, i32, vp]),
+    "xb_shard_combine": (i32, [vp, i32, i32, i64, i32, vp, i32, vp, i64, i64, i32, vp]),
     "xb_gemm": (i32, [C.POINTER(GemmArgs), vp]),
     "xb_gemm_uses_tcgen05": (i32, [C.POINTER(GemmArgs)]),
     "xb_pack_weight_kmajor": (i32, [vp, i32, i32, i32, i64, vp, i32, i64, i32, i64, i64, vp]),

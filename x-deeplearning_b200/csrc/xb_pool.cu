@@ -1204,14 +1204,19 @@ __global__ void tag_count_sources_kernel(const int32_t* __restrict__ tags, const
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     int src = 0;
     while (src + 1 < sources && i >= bounds.b[src + 1]) ++src;
-    atomicAdd(&counts[(int64_t)src * segments + tags[i]], 1);
+    // a tag comes from a peer: one outside [0, segments) is dropped, never used as an index
+    const uint32_t tag = (uint32_t)tags[i];
+    if (tag < (uint64_t)segments) atomicAdd(&counts[(int64_t)src * segments + tag], 1);
   }
 }
 
 // segment lengths at the owner: tags arrive sorted per source rank; counts are integer atomics (exact)
-__global__ void tag_count_kernel(const int32_t* __restrict__ tags, int64_t n, int32_t* __restrict__ counts) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-    atomicAdd(&counts[tags[i]], 1);
+__global__ void tag_count_kernel(const int32_t* __restrict__ tags, int64_t n, int32_t* __restrict__ counts,
+                                 int64_t n_counts) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t tag = (uint32_t)tags[i];
+    if (tag < (uint64_t)n_counts) atomicAdd(&counts[tag], 1);
+  }
 }
 
 // out[s, col0 + e] = scale(s) * sum_{w=0..shards-1} partial[w][s][e], w ascending (fixed order)
@@ -1276,6 +1281,78 @@ __global__ void __launch_bounds__(256) shard_combine4_kernel(const float4* __res
   }
 }
 
+// Partial sums that crossed the wire as fp16 (a model whose tables and activations are fp16): eight adjacent
+// elements per thread, one 16-byte load per owner, fp32 accumulation in owner order.
+template <int SHARDS>
+__global__ void __launch_bounds__(256) shard_combine_h8_kernel(const uint4* __restrict__ partial, int shards, int64_t segments,
+                                                               int dim8, const int32_t* __restrict__ seg_len, int avg,
+                                                               void* out, int64_t out_stride, int64_t rows, int out_dtype) {
+  const int64_t total = segments * dim8;
+  const int n_sh = SHARDS ? SHARDS : shards;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t s = i / dim8;
+    const int e8 = (int)(i - s * dim8);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    auto add = [&](const uint4& v) {
+      const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h[e]);
+        acc[2 * e] += f.x; acc[2 * e + 1] += f.y;
+      }
+    };
+    if (SHARDS) {
+      uint4 v[SHARDS ? SHARDS : 1];
+#pragma unroll
+      for (int w = 0; w < SHARDS; ++w) v[w] = __ldcs(partial + ((int64_t)w * segments + s) * dim8 + e8);
+#pragma unroll
+      for (int w = 0; w < SHARDS; ++w) add(v[w]);
+    } else {
+      for (int w = 0; w < n_sh; ++w) add(__ldcs(partial + ((int64_t)w * segments + s) * dim8 + e8));
+    }
+    if (avg && seg_len) {
+      const int32_t len = seg_len[s];
+      if (len != 0) {
+        const float sc = (float)(1.0 / (double)len);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] *= sc;
+      }
+    }
+    const int64_t grp = s / rows, sample = s - grp * rows;
+    const int64_t o = sample * out_stride + (grp * dim8 + e8) * 8;
+    if (out_dtype == XB_F32) {
+      float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + o);
+      d[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      d[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      uint4 r;
+      __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(out) + o) = r;
+    }
+  }
+}
+
+// fp16 partials of any shape, one element per thread
+__global__ void shard_combine_h_kernel(const __half* __restrict__ partial, int shards, int64_t segments, int dim,
+                                       const int32_t* __restrict__ seg_len, int avg, void* out, int64_t out_stride,
+                                       int64_t seg_per_row, int out_dtype) {
+  const int64_t total = segments * dim;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t s = i / dim;
+    const int e = (int)(i - s * dim);
+    float acc = 0.f;
+    for (int w = 0; w < shards; ++w) acc += __half2float(partial[((int64_t)w * segments + s) * dim + e]);
+    if (avg && seg_len && seg_len[s] != 0) acc = acc * (float)(1.0 / (double)seg_len[s]);
+    const int64_t rows = segments / seg_per_row;
+    const int64_t grp = s / rows, sample = s - grp * rows;
+    store_out(out, sample * out_stride + grp * dim + e, out_dtype, acc);
+  }
+}
+
 }  // namespace xb
 
 extern "C" size_t xb_route_scratch_bytes(int64_t n_ids, int32_t shards) {
@@ -1317,7 +1394,7 @@ extern "C" int xb_tag_counts(const int32_t* tags, int64_t n, int32_t* counts, in
   XB_CUDA(cudaMemsetAsync(counts, 0, (size_t)n_counts * sizeof(int32_t), stream));
   if (n == 0) return 0;
   const int64_t blocks = std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 8);
-  tag_count_kernel<<<(unsigned)blocks, 256, 0, stream>>>(tags, n, counts);
+  tag_count_kernel<<<(unsigned)blocks, 256, 0, stream>>>(tags, n, counts, n_counts);
   return check_launch("tag_count_kernel");
 }
 
@@ -1343,9 +1420,12 @@ extern "C" int xb_tag_counts_sources(const int32_t* tags, const int64_t* source_
 
 extern "C" int xb_shard_pool(const xb_table_desc* const* tables, const int64_t* table_segments, int32_t n_tables,
                              const void* rows, int32_t row_dtype, int64_t n_rows, const float* values,
-                             const int32_t* offsets, int32_t sources, int32_t dim, float* out, xb_stream_t stream) {
+                             const int32_t* offsets, int32_t sources, int32_t dim, void* out, int32_t out_dtype,
+                             xb_stream_t stream) {
   XB_REQUIRE(tables && table_segments && n_tables >= 1 && sources >= 1 && offsets && out && dim >= 1, XB_ERR_ARG,
              "xb_shard_pool: bad arguments");
+  XB_REQUIRE(out_dtype == XB_F32 || out_dtype == XB_F16, XB_ERR_UNSUPPORTED, "xb_shard_pool: partial dtype %d", out_dtype);
+  const size_t out_esz = out_dtype == XB_F32 ? 4 : 2;
   int64_t S = 0;
   for (int t = 0; t < n_tables; ++t) {
     XB_REQUIRE(table_segments[t] >= 0, XB_ERR_ARG, "xb_shard_pool: negative segment count");
@@ -1368,10 +1448,10 @@ extern "C" int xb_shard_pool(const xb_table_desc* const* tables, const int64_t* 
       g.n_ids = sources * S ? n_rows * table_segments[t] / ((int64_t)sources * S) : 0;
       g.dim = dim;
       g.id_dtype = row_dtype;
-      g.out_dtype = XB_F32;
+      g.out_dtype = out_dtype;
       g.n_items = 1;
       g.items[0].udf = XB_UDF_SUM;
-      g.items[0].out = out + lo * dim;
+      g.items[0].out = reinterpret_cast<char*>(out) + (size_t)lo * dim * out_esz;
       g.items[0].stride = dim;
       lo += table_segments[t];
       if (++n == XB_MAX_POOL_GROUPS) {
@@ -1383,10 +1463,38 @@ extern "C" int xb_shard_pool(const xb_table_desc* const* tables, const int64_t* 
   return n ? xb_embedding_pool(groups, n, nullptr, 0, stream) : 0;
 }
 
-extern "C" int xb_shard_combine(const float* partial, int32_t shards, int64_t segments, int32_t dim, const int32_t* seg_len,
-                                int32_t avg, void* out, int64_t out_stride, int64_t groups, int32_t out_dtype,
-                                xb_stream_t stream_) {
+extern "C" int xb_shard_combine(const void* partial_, int32_t partial_dtype, int32_t shards, int64_t segments, int32_t dim,
+                                const int32_t* seg_len, int32_t avg, void* out, int64_t out_stride, int64_t groups,
+                                int32_t out_dtype, xb_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(partial_dtype == XB_F32 || partial_dtype == XB_F16, XB_ERR_UNSUPPORTED, "xb_shard_combine: partial dtype %d",
+             partial_dtype);
+  if (partial_dtype == XB_F16) {
+    XB_REQUIRE(partial_ && out && shards >= 1 && segments >= 0 && dim >= 1 && groups >= 1, XB_ERR_ARG, "xb_shard_combine: bad arguments");
+    XB_REQUIRE(segments % groups == 0, XB_ERR_ARG, "xb_shard_combine: segments %lld not a multiple of groups %lld", (long long)segments, (long long)groups);
+    XB_REQUIRE(out_dtype == XB_F32 || out_dtype == XB_F16, XB_ERR_UNSUPPORTED, "xb_shard_combine: output dtype %d", out_dtype);
+    if (segments == 0) return 0;
+    const size_t esz = out_dtype == XB_F32 ? 4 : 2;
+    if (dim % 8 == 0 && out_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(partial_) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & (8 * esz - 1) & 15) == 0) {
+      const int dim8 = dim / 8;
+      const int64_t rows = segments / groups;
+      const int64_t blocks8 = std::min<int64_t>((segments * dim8 + 255) / 256, (int64_t)sm_count() * 16);
+      const uint4* p8 = reinterpret_cast<const uint4*>(partial_);
+      switch (shards) {
+        case 2: shard_combine_h8_kernel<2><<<(unsigned)blocks8, 256, 0, stream>>>(p8, shards, segments, dim8, seg_len, avg, out, out_stride, rows, out_dtype); break;
+        case 4: shard_combine_h8_kernel<4><<<(unsigned)blocks8, 256, 0, stream>>>(p8, shards, segments, dim8, seg_len, avg, out, out_stride, rows, out_dtype); break;
+        case 8: shard_combine_h8_kernel<8><<<(unsigned)blocks8, 256, 0, stream>>>(p8, shards, segments, dim8, seg_len, avg, out, out_stride, rows, out_dtype); break;
+        default: shard_combine_h8_kernel<0><<<(unsigned)blocks8, 256, 0, stream>>>(p8, shards, segments, dim8, seg_len, avg, out, out_stride, rows, out_dtype); break;
+      }
+      return check_launch("shard_combine_h8_kernel");
+    }
+    const int64_t blocks = std::min<int64_t>((segments * dim + 255) / 256, (int64_t)sm_count() * 8);
+    shard_combine_h_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const __half*>(partial_), shards, segments, dim,
+                                                                 seg_len, avg, out, out_stride, groups, out_dtype);
+    return check_launch("shard_combine_h_kernel");
+  }
+  const float* partial = reinterpret_cast<const float*>(partial_);
   XB_REQUIRE(partial && out && shards >= 1 && segments >= 0 && dim >= 1 && groups >= 1, XB_ERR_ARG, "xb_shard_combine: bad arguments");
   XB_REQUIRE(segments % groups == 0, XB_ERR_ARG, "xb_shard_combine: segments %lld not a multiple of groups %lld", (long long)segments, (long long)groups);
   XB_REQUIRE(out_dtype == XB_F32 || out_dtype == XB_F16, XB_ERR_UNSUPPORTED, "xb_shard_combine: output dtype %d", out_dtype);

@@ -43,8 +43,11 @@ class DistComm:
 class GpuShardOps:
     """Device work of the sharded path on the C-ABI kernels."""
 
-    def __init__(self, device="cuda"):
+    def __init__(self, device="cuda", partial_dtype="f32"):
+        """partial_dtype: what the owners return, "f32" (fp32 models, 1e-5 bar) or "f16" (fp16 models: half the
+        bytes of the return exchange)."""
         self.device = device
+        self.partial_torch = torch.float16 if partial_dtype == "f16" else torch.float32
 
     def route(self, ids, values, seg_offsets, shards):
         n = ids.numel()
@@ -108,16 +111,16 @@ class GpuShardOps:
         Table t pools the segments [sum(table_segments[:t]), +table_segments[t]) of every source: one pooling
         group per (source, table), all over the same id buffer. Returns [sources * S, dim] fp32."""
         S = sum(table_segments)
-        out = torch.empty((sources * S, dim), dtype=torch.float32, device=rows.device)
+        out = torch.empty((sources * S, dim), dtype=self.partial_torch, device=rows.device)
         T = len(tables)
         descs = (C.POINTER(capi.TableDesc) * T)(*[C.pointer(t.desc) for t in tables])
         segs = (C.c_int64 * T)(*table_segments)
         check(lib().xb_shard_pool(descs, segs, T, xops.ptr(rows), xops.dt(rows), rows.numel(), xops.ptr(vals),
-                                  xops.ptr(offsets), sources, dim, xops.ptr(out), xops.stream()))
+                                  xops.ptr(offsets), sources, dim, xops.ptr(out), xops.dt(out), xops.stream()))
         return out
 
     def combine(self, partial, shards, segments, dim, groups, out, seg_len=None, avg=False):
-        check(lib().xb_shard_combine(xops.ptr(partial), shards, segments, dim, xops.ptr(seg_len), int(avg), xops.ptr(out),
+        check(lib().xb_shard_combine(xops.ptr(partial), xops.dt(partial), shards, segments, dim, xops.ptr(seg_len), int(avg), xops.ptr(out),
                                      out.stride(0), groups, xops.dt(out), xops.stream()))
         return out
 
@@ -180,7 +183,7 @@ def sharded_pool_tables(comm, ops, table_shards, dim, ids, values, seg_offsets, 
     ops.combine(back, W, segments, dim, sum(groups), out, seg_len, avg)
     mark("combine")
     per_id = (8 if packed else 12) + (4 if all_vals is not None else 0)
-    return {"routed_bytes": sum(send_counts) * per_id, "returned_bytes": partial.numel() * 4}
+    return {"routed_bytes": sum(send_counts) * per_id, "returned_bytes": partial.numel() * partial.element_size()}
 
 
 def sharded_pool(comm, ops, table_shard, dim, ids, values, seg_offsets, groups, out, avg=False):
