@@ -296,7 +296,11 @@ int xb_pack_weight_kmajor(const void* W, int32_t w_dtype, int32_t K, int32_t N, 
 enum { XB_ACT_NONE = 0, XB_ACT_SIGMOID = 1, XB_ACT_DICE = 2 };
 /* `engine` of xb_din_att_args takes XB_GEMM_AUTO / XB_GEMM_SIMT / XB_GEMM_TCGEN05 or this value: the tcgen05
  * engine that regroups layer 1 as q x (Wq + Wd + diag(k_t) Wp) and runs two steps per MMA (needs `packed`). */
-enum { XB_ATT_ENGINE_PAIR = 3 };
+enum { XB_ATT_ENGINE_PAIR = 3,
+       /* the tcgen05 engine that splits layer 1 into (Wq + Wd) q + Wp (q * k_t) + [(Wk - Wd) k_t + b0], the last
+        * term once per request: half the MMAs per step, persistent CTAs. XB_GEMM_AUTO picks it when `packed` is
+        * given and the shape fits; XB_GEMM_TCGEN05 keeps the per-step engine. */
+       XB_ATT_ENGINE_SPLIT = 4 };
 
 typedef struct xb_din_att_weights {
   /* K-major packed fp16 weights: W0 [h0, 4d], W1 [h1, h0]; W2 fp32 [h1] */

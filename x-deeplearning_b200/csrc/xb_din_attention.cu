@@ -8,6 +8,7 @@
 // CUDA-core engine that does the same arithmetic in fp32 without intermediate
 // rounding, one CTA per candidate; it serves shapes the tcgen05 engine does not
 // take and cross-checks it in the tests.
+#include <algorithm>
 #include <cstring>
 
 #include "xb_common.cuh"
@@ -27,7 +28,7 @@ struct AttParams {
   const float *b0, *b1; float b2;
   const float *g0, *m0, *v0, *g1, *m1, *v1;
   // tcgen05 engine
-  int tiles_per_req;
+  int tiles_per_req, tiles_per_cta;
   uint32_t idesc1, idesc2, idesc3;
   const void* packed;      // weight operands laid out by xb_din_attention_pack, or null
 };
@@ -131,6 +132,7 @@ __global__ void __launch_bounds__(SIMT_THREADS) din_att_simt_kernel(const __grid
 
 #include "xb_din_attention_tc.cuh"
 #include "xb_din_attention_pair.cuh"
+#include "xb_din_attention_split.cuh"
 
 namespace xb {
 
@@ -141,6 +143,14 @@ int att_set_status_mirror(int* p) { return umma::set_status_mirror(p); }
 }  // namespace xb
 
 using namespace xb;
+
+// The packed image: per-step engine's operands, then the step-pair engine's, then the split engine's.
+static size_t split_image_offset(int d, int h0, int h1) {
+  size_t n = 0;
+  if (tc_eligible_shape(d, h0, h1)) n += (att_packed_bytes(d, h0, h1) + 15) / 16 * 16;
+  if (pair_image_wanted(d, h0, h1)) n += (att_pair_packed_bytes(d, h0, h1) + 15) / 16 * 16;
+  return n;
+}
 
 extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -179,6 +189,14 @@ extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
     p.packed = (const char*)a->w.packed + (first + 15) / 16 * 16;
     return launch_att_pair(p, *a, stream);
   }
+  // The split engine (half the MMAs, persistent CTAs) serves every shape it takes when the weights were packed;
+  // XB_GEMM_TCGEN05 asks for the per-step engine, which rounds where the un-fused graph does.
+  if ((a->engine == XB_ATT_ENGINE_SPLIT || a->engine == XB_GEMM_AUTO) && a->w.packed && split_eligible(*a, &why)) {
+    p.packed = (const char*)a->w.packed + split_image_offset(a->d, a->h0, a->h1);
+    return launch_att_split(p, *a, stream);
+  }
+  XB_REQUIRE(a->engine != XB_ATT_ENGINE_SPLIT, XB_ERR_UNSUPPORTED,
+             "xb_din_attention: shape outside the split engine (reason %d; it needs packed weights)", why);
   const bool tc = a->engine != XB_GEMM_SIMT && tc_eligible(*a, &why);
   XB_REQUIRE(tc || a->engine != XB_GEMM_TCGEN05, XB_ERR_UNSUPPORTED,
              "xb_din_attention: shape outside the tcgen05 engine (reason %d)", why);
@@ -197,7 +215,8 @@ extern "C" size_t xb_din_attention_packed_bytes(int32_t d, int32_t h0, int32_t h
   if (d <= 0 || h0 <= 0 || h1 <= 0) return 0;
   size_t n = 0;
   if (tc_eligible_shape(d, h0, h1)) n += (att_packed_bytes(d, h0, h1) + 15) / 16 * 16;
-  if (pair_image_wanted(d, h0, h1)) n += att_pair_packed_bytes(d, h0, h1);
+  if (pair_image_wanted(d, h0, h1)) n += (att_pair_packed_bytes(d, h0, h1) + 15) / 16 * 16;
+  if (split_eligible_shape(d, h0, h1)) n += att_split_packed_bytes(d, h0, h1);
   return n;
 }
 
@@ -222,6 +241,8 @@ extern "C" int xb_din_attention_pack(const xb_din_att_args* a, void* packed, siz
     first = (att_packed_bytes(a->d, a->h0, a->h1) + 15) / 16 * 16;
   }
   if (pair_image_wanted(a->d, a->h0, a->h1))
-    return launch_att_pair_pack(p, a->act, (char*)packed + first, (cudaStream_t)stream);
+    if (int rc = launch_att_pair_pack(p, a->act, (char*)packed + first, (cudaStream_t)stream)) return rc;
+  if (split_eligible_shape(a->d, a->h0, a->h1))
+    return launch_att_split_pack(p, a->act, (char*)packed + split_image_offset(a->d, a->h0, a->h1), (cudaStream_t)stream);
   return 0;
 }
