@@ -308,6 +308,7 @@ def run_ours(args):
         line["sharded"] = leg.run(min(K, 20), W)
     if rank == 0 and world == 1 and not args.no_cpu:
         line["embedding_pool"] = bench_pool(pk)
+        line["embedding_pool"]["hbm_resident"] = bench_pool_hbm(pk)
         line["cpu_baseline"] = cpu_baseline_din(model, workloads, cores=1, budget_s=args.cpu_seconds)
     if rank == 0:
         print(json.dumps(line))
@@ -335,29 +336,172 @@ def bench_pool(pk):
                                          torch.float32, segments_are_offsets=True))
         plan = ops.PoolPlan(groups)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        flush2 = torch.ones(64 << 20, dtype=torch.float32, device="cuda")
         for _ in range(5):
             plan.run()
-        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
-        torch.cuda.synchronize()
-        for a, b in ev:
-            if label == "config":
-                flush.zero_()                      # 256 MB write: evicts the 64 MB table from L2
-            a.record(); plan.run(); b.record()
-        torch.cuda.synchronize()
-        ms = statistics.median(a.elapsed_time(b) for a, b in ev)
         nbytes = n_ids * (8 + 4 + 64) + batch * 20 * 4 + batch * 320 * 4
-        gbs = nbytes / (ms * 1e-3) / 1e9
+
+        def timed(mode):
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+            torch.cuda.synchronize()
+            for a, b in ev:
+                if mode != "warm":
+                    flush.zero_()                  # 256 MB write: evicts the 64 MB table from L2
+                if mode == "clean":
+                    flush2.sum()                   # then a 256 MB read: the dirty lines are written back before
+                                                   # the timed launch, so it finds L2 cold AND clean
+                a.record(); plan.run(); b.record()
+            torch.cuda.synchronize()
+            ms = statistics.median(a.elapsed_time(b) for a, b in ev)
+            return ms, nbytes / (ms * 1e-3) / 1e9
+        ms, gbs = timed("dirty" if label == "config" else "warm")
         out[label] = {"ms_per_launch": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs,
                       "frac_of_measured_copy_peak": gbs / pk["hbm_gbs"], "frac_of_8tbs_nominal": gbs / 8000.0,
-                      "l2": "flushed before each launch" if label == "config" else "inputs exceed L2"}
+                      "l2": "flushed before each launch (256 MB written)" if label == "config" else "inputs exceed L2"}
+        if label == "config":
+            for mode, note in (("clean", "256 MB written then 256 MB read before each launch: cold L2 without "
+                                         "write-backs of the flush buffer inside the timed launch"),
+                               ("warm", "back to back, table (64 MB) L2-resident")):
+                ms2, gbs2 = timed(mode)
+                out[label]["l2_" + mode] = {"ms_per_launch": ms2, "achieved_gbs": gbs2,
+                                            "frac_of_measured_copy_peak": gbs2 / pk["hbm_gbs"], "l2": note}
         del table, y, groups, plan
     out["peak_gbs"] = pk["hbm_gbs"]
     out["peak_source"] = pk["source"]
     return out
 
 
+def bench_pool_hbm(pk, reps=40, only=None):
+    """Pooling against tables that do NOT fit L2, ids rotating over 8 pre-generated batches (only the Zipf head
+    of a table can stay L2-resident):
+      shard25m_dim32  one 25 M x 32 fp16 shard (1.6 GB) of the large-table configuration, 8192 samples x 40
+                      feature groups, id lists of 1..30, Zipf(1.05), sum pooling into [8192, 1280] fp16;
+      item5m_dim18    the DIN item table, 5 M x 18 fp16 (240 MB at its 48-byte pitch), 65536 x 4 segments,
+                      id lists of 1..50, Zipf(1.1), sum pooling into [65536, 72] fp16.
+    Algorithmic bytes per launch: 8 B id + one row (dim * 2 B) per id, 4 B offset + dim * 2 B output per segment."""
+    import numpy as np
+    import torch
+    from x_deeplearning_b200 import capi, ops, workloads
+    cases = {"shard25m_dim32": dict(rows=25_000_000, dim=32, batch=8192, groups=40, max_len=30, s=1.05),
+             "item5m_dim18": dict(rows=5_000_000, dim=18, batch=65536, groups=4, max_len=50, s=1.1)}
+    out = {}
+    for label, c in cases.items():
+        if only and label != only:
+            continue
+        rows, dim, batch, G = c["rows"], c["dim"], c["batch"], c["groups"]
+        tb = ops.Table.__new__(ops.Table)
+        pitch = int(capi.lib().xb_table_row_pitch(dim, capi.XB_F16))
+        tb.rows, tb.dim, tb.dtype, tb.pitch = rows, dim, torch.float16, pitch
+        tb.buf = torch.empty((rows, pitch // 2), dtype=torch.float16, device="cuda")
+        for r0 in range(0, rows, 1 << 22):
+            tb.buf[r0:r0 + (1 << 22)].normal_(0, 0.01)
+        tb.desc = capi.TableDesc()
+        tb.desc.weights, tb.desc.rows, tb.desc.dim, tb.desc.dtype, tb.desc.row_pitch_bytes = tb.buf.data_ptr(), rows, dim, capi.XB_F16, pitch
+        tb.slot_keys = tb.slot_rows = None
+        y = torch.zeros((batch, G * dim), dtype=torch.float16, device="cuda")
+        NB = 8
+        rng = np.random.default_rng(5)
+        plans, n_ids = [], 0
+        for b in range(NB):
+            groups = []
+            for g in range(G):
+                counts = rng.integers(1, c["max_len"] + 1, batch).astype(np.int32)
+                n = int(counts.sum())
+                ids = workloads.zipf_ids(rng, rows, n, c["s"])
+                off = np.zeros(batch + 1, np.int32)
+                np.cumsum(counts, out=off[1:])
+                if b == 0:
+                    n_ids += n
+                groups.append(ops.make_group(tb, torch.from_numpy(ids).cuda(), None, torch.from_numpy(off).cuda(),
+                                             [dict(udf=0, out=y, col=dim * g)], torch.float16, segments_are_offsets=True))
+            plans.append(ops.PoolPlan(groups))
+        for b in range(NB):
+            plans[b].run()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        torch.cuda.synchronize()
+        for i, (a, b_) in enumerate(ev):
+            a.record(); plans[i % NB].run(); b_.record()
+        torch.cuda.synchronize()
+        ms = statistics.median(a.elapsed_time(b_) for a, b_ in ev)
+        nbytes = n_ids * (8 + dim * 2) + batch * G * 4 + batch * G * dim * 2
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[label] = {"ms_per_launch": ms, "ids_per_launch": n_ids, "algorithmic_bytes": nbytes, "achieved_gbs": gbs,
+                      "frac_of_measured_copy_peak": gbs / pk["hbm_gbs"], "table_bytes": rows * pitch,
+                      "l2": "table exceeds L2; ids rotate over %d batches" % NB}
+        del tb, y, plans
+        torch.cuda.empty_cache()
+    return out
+
+
+class ReferenceDin:
+    """The DIN-style model on the reference's OWN CPU implementation (oracle/_ref/libblaze_cpu.so: its operators,
+    Workspace, Net and qed_sparse_puller compiled unmodified, driven through the un-fused NetDef of
+    din_netdef.build_unfused), one request of 1000 candidates per Net::Run. None when that library was not built."""
+
+    def __init__(self, model, workloads):
+        import tempfile
+        import numpy as np
+        checker_path()
+        import orc
+        import refnet
+        from x_deeplearning_b200 import din_netdef
+        self.np, self.refnet, self.din_netdef, self.workloads, self.model = np, refnet, din_netdef, workloads, model
+        self.dir = tempfile.mkdtemp(prefix="xdl_ref_")
+        self.qed = os.path.join(self.dir, "din.qed")
+        tables = {"item": (np.arange(len(model["item"]), dtype=np.int64), model["item"]),
+                  "cate": (np.arange(len(model["cate"]), dtype=np.int64), model["cate"])}
+        for g, w in enumerate(model["user"]):
+            tables["user%d" % g] = (np.arange(len(w), dtype=np.int64), w)
+        orc.RefStore(tables, self.qed).close()              # written by the reference's own store code
+        self.text, _ = din_netdef.build_unfused(model)
+        self.blas = refnet.blas_name()
+
+    @staticmethod
+    def available():
+        checker_path()
+        import orc
+        import refnet
+        return refnet.lib() is not None and orc.ref_lib() is not None
+
+    def net(self):
+        return self.refnet.RefNet(self.text, self.qed)
+
+    def feeds(self, seed, n_cand=N_CAND):
+        np = self.np
+        req = self.workloads.din_requests(self.model, seed, 1, n_cand)
+        return {n: (a.astype(np.float32) if n.endswith(".values") else a)
+                for n, a in self.din_netdef.feeds_of(self.model, req).items()}
+
+    @staticmethod
+    def run(net, feeds):
+        for n, a in feeds.items():
+            net.feed(n, a)
+        net.run()
+        return net.output("output")
+
+    def close(self):
+        import shutil
+        shutil.rmtree(self.dir, ignore_errors=True)
+
+
 def cpu_baseline_din(model, workloads, cores, budget_s):
-    """The CPU oracle (port of the reference path) on a bounded sample of the same workload."""
+    """The reference's CPU path on a bounded sample of the same workload: its own operators when
+    oracle/_ref/libblaze_cpu.so exists (kind "reference"), else the CPU oracle (kind "port")."""
+    if ReferenceDin.available():
+        ref = ReferenceDin(model, workloads)
+        net, feeds = ref.net(), ref.feeds(99)
+        ReferenceDin.run(net, feeds)
+        t0, n = time.time(), 0
+        while time.time() - t0 < budget_s:
+            ReferenceDin.run(net, feeds)
+            n += 1
+        dt = time.time() - t0
+        net.close()
+        ref.close()
+        return {"value": n * N_CAND / dt, "unit": "predictions/s", "cores": cores, "kind": "reference",
+                "sample": "%d requests of 1 user x %d candidates (T=100) in %.1f s; the reference's own CPU operators "
+                          "(Workspace::CreateNet + Net::Run on the un-fused NetDef, qed_sparse_puller), one thread; %s"
+                          % (n, N_CAND, dt, ref.blas)}
     checker_path()
     import din_oracle
     n_cand = 100                                        # 100 of the 1000 candidates of one request
@@ -390,40 +534,71 @@ def _ref_worker(a):
 
 
 def run_reference(args):
-    """The reference's CPU path (oracle port: the dense operators of the reference need generated
-    protobuf code and a BLAS that are not available, so they do not compile here) on all host cores."""
+    """The reference arm: the reference's own CPU implementation of the path on all host cores, same workload
+    (one request = 1 user x 1000 candidates, T = 100, the 5 M / 10 k / 8 x 100 k tables). One Net per host thread,
+    every step each thread serves one request (Blaze's deployment: one predictor per serving thread). Falls
+    back to the oracle port when oracle/_ref/libblaze_cpu.so was not built."""
     rank, _, world = dist_env()
     if rank != 0:
         return
-    import multiprocessing as mp
     load_package()
     from x_deeplearning_b200 import workloads
-    checker_path()
-    import orc
-    orc.lib()
     cores = os.cpu_count() or 1
-    global _REF_MODEL
-    n_cand = 200
-    _REF_MODEL = workloads.din_model(seed=0)
-    ctx = mp.get_context("fork")
-    with ctx.Pool(cores) as pool:
-        jobs = lambda: [(100 + i, n_cand, 1) for i in range(cores)]
-        for _ in range(max(1, min(args.warmup, 1))):
-            pool.map(_ref_worker, jobs())
+    config = {"workload": "DIN-style model, 1 user x 1000 candidates per request, T=100, tables 5M/10k/8x100k x 18 fp16",
+              "requests_per_step": cores, "parallelism": "%d host threads, one reference Net each" % cores}
+    model = workloads.din_model(seed=0)
+    if ReferenceDin.available():
+        import threading
+        ref = ReferenceDin(model, workloads)
+        nets = [ref.net() for _ in range(cores)]
+        feeds = [ref.feeds(100 + i) for i in range(cores)]
+
+        def step():
+            ths = [threading.Thread(target=ReferenceDin.run, args=(nets[i], feeds[i])) for i in range(cores)]
+            for t in ths:
+                t.start()
+            for t in ths:
+                t.join()
+        for _ in range(max(1, min(args.warmup, 2))):
+            step()
         t0 = time.time()
-        preds = 0
         for _ in range(args.steps):
-            preds += sum(pool.map(_ref_worker, jobs()))
+            step()
         dt = time.time() - t0
+        preds = args.steps * cores * N_CAND
+        kind = "reference"
+        sample = ("each step: %d threads x 1 request x %d candidates (T=100) through the reference's own CPU operators "
+                  "(un-fused NetDef, Workspace::CreateNet + Net::Run, qed_sparse_puller); %s" % (cores, N_CAND, ref.blas))
+        for n in nets:
+            n.close()
+        ref.close()
+    else:
+        import multiprocessing as mp
+        checker_path()
+        import orc
+        orc.lib()
+        global _REF_MODEL
+        n_cand = 200
+        _REF_MODEL = model
+        ctx = mp.get_context("fork")
+        with ctx.Pool(cores) as pool:
+            jobs = lambda: [(100 + i, n_cand, 1) for i in range(cores)]
+            for _ in range(max(1, min(args.warmup, 1))):
+                pool.map(_ref_worker, jobs())
+            t0 = time.time()
+            preds = 0
+            for _ in range(args.steps):
+                preds += sum(pool.map(_ref_worker, jobs()))
+            dt = time.time() - t0
+        kind = "port"
+        sample = "each step: %d processes x 1 request x %d candidates (T=100), plain-C restatement" % (cores, n_cand)
+        config["parallelism"] = "%d host processes" % cores
     v = preds / dt
-    sample = "each step: %d processes x 1 request x %d candidates (T=100)" % (cores, n_cand)
     print(json.dumps({
         "impl": "reference", "metric": "DIN predictions/sec", "value": v, "unit": "predictions/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "DIN-style model, 1 user x 1000 candidates per request, T=100, tables 5M/10k/8x100k x 18",
-                   "sample": sample},
-        "cpu_baseline": {"value": v, "unit": "predictions/s", "cores": cores, "kind": "port", "sample": sample},
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": v, "unit": "predictions/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": v, "unit": "predictions/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -468,6 +643,9 @@ def run_micro(args):
         t0.record()
         for _ in range(reps):
             plan.run()
+    elif args.micro == "pool_hbm":
+        print(json.dumps({"micro": "pool_hbm", **bench_pool_hbm(peaks(), reps=reps, only=args.case)}))
+        return
     elif args.micro == "gemm":
         P, M, K, N = 8, 65536, 256, 128            # the parallel-GEMM configuration with M scaled 16x (A = 268 MB)
         A = torch.randn((P, M, K), device="cuda", dtype=torch.float16)
@@ -785,7 +963,8 @@ def main():
     ap.add_argument("--partial-dtype", default="f16", choices=["f16", "f32"],
                     help="dtype of the partial sums the owners return in the row-sharded leg (f32 for the 1e-5 bar)")
     ap.add_argument("--no-sharded", action="store_true", help="skip the row-sharded leg of a multi-GPU run")
-    ap.add_argument("--micro", choices=["att", "pool", "gemm", "gemm_mlp", "tower", "sharded", "batching"], help="run --steps launches of one kernel on a small case "
+    ap.add_argument("--case", default=None, help="--micro pool_hbm: run one case only (shard25m_dim32 | item5m_dim18)")
+    ap.add_argument("--micro", choices=["att", "pool", "pool_hbm", "gemm", "gemm_mlp", "tower", "sharded", "batching"], help="run --steps launches of one kernel on a small case "
                     "(for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     if args.micro == "sharded":

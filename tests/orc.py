@@ -255,7 +255,11 @@ def ref_lib():
     """Returns the CDLL or None when oracle/_ref was never built."""
     global _ref
     if _ref is None:
-        path = os.path.join(ORACLE_DIR, "_ref", "libqed_ref.so")
+        # the reference's whole CPU library when it was built (it contains the sparse store too), else the
+        # sparse store alone; one process loads one of them, never both (each registers the reference's puller)
+        path = os.path.join(ORACLE_DIR, "_ref", "libblaze_cpu.so")
+        if not os.path.exists(path):
+            path = os.path.join(ORACLE_DIR, "_ref", "libqed_ref.so")
         if not os.path.exists(path):
             return None
         _ref = C.CDLL(path)

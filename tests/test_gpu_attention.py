@@ -24,7 +24,8 @@ def _weights(rng, d, h0, h1):
 def _case(engine_name, R, n_cand, T, d, h0, h1, act, softmax, seq_lens=None, seed=0, sigma=0.5):
     pkg.load()
     from x_deeplearning_b200 import ops, capi
-    engine = {"simt": capi.XB_GEMM_SIMT, "tc": capi.XB_GEMM_TCGEN05, "pair": capi.XB_ATT_ENGINE_PAIR}[engine_name]
+    engine = {"simt": capi.XB_GEMM_SIMT, "tc": capi.XB_GEMM_TCGEN05, "pair": capi.XB_ATT_ENGINE_PAIR,
+              "split": capi.XB_ATT_ENGINE_SPLIT}[engine_name]
     rng = np.random.default_rng(seed)
     w = _weights(rng, d, h0, h1)
     q = rng.normal(0, sigma, (R * n_cand, d)).astype(np.float16)
@@ -34,7 +35,7 @@ def _case(engine_name, R, n_cand, T, d, h0, h1, act, softmax, seq_lens=None, see
                            dice0=[t(w["g0"]), t(w["m0"]), t(w["v0"])], dice1=[t(w["g1"]), t(w["m1"]), t(w["v1"])],
                            act=act)
     sl = torch.tensor(seq_lens, dtype=torch.int32, device="cuda") if seq_lens is not None else None
-    want_scores = not (softmax and engine_name in ("tc", "pair"))
+    want_scores = not (softmax and engine_name in ("tc", "pair", "split"))
     scores = torch.zeros((R * n_cand, T), device="cuda") if want_scores else None
     out = att(t(q).cuda(), t(k).cuda(), R, n_cand, T, seq_len=sl, use_softmax=softmax, scores=scores, engine=engine)
     torch.cuda.synchronize()
@@ -46,29 +47,43 @@ def _case(engine_name, R, n_cand, T, d, h0, h1, act, softmax, seq_lens=None, see
                                  w, act=act, seq_len=L, use_softmax=softmax, want_scores=True)
         if want_scores:
             gs = scores[r * n_cand:(r + 1) * n_cand].cpu().numpy()
-            assert np.abs(gs - s).max() <= (5e-3 if engine_name in ("tc", "pair") else 1e-3), np.abs(gs - s).max()
+            assert np.abs(gs - s).max() <= (5e-3 if engine_name in ("tc", "pair", "split") else 1e-3), np.abs(gs - s).max()
         g = got[r * n_cand:(r + 1) * n_cand]
         bound = (np.abs(s) @ np.abs(k[r * T:(r + 1) * T].astype(np.float32)))
         assert (np.abs(g - o) <= 4e-3 * (1 + bound)).all(), float(np.abs(g - o).max())
 
 
-@pytest.mark.parametrize("engine", ["simt", "tc", "pair"])
+@pytest.mark.parametrize("engine", ["simt", "tc", "pair", "split"])
 def test_din_shape_dice_no_softmax(engine):
     _case(engine, R=2, n_cand=300, T=100, d=36, h0=80, h1=40, act=2, softmax=False)
 
 
-@pytest.mark.parametrize("engine", ["simt", "tc", "pair"])
+@pytest.mark.parametrize("engine", ["simt", "tc", "pair", "split"])
 def test_shipped_graph_variant_sigmoid_masked_softmax(engine):
     _case(engine, R=3, n_cand=130, T=100, d=36, h0=80, h1=40, act=1, softmax=True, seq_lens=[100, 37, 1], seed=1)
 
 
-@pytest.mark.parametrize("engine", ["simt", "tc", "pair"])
+@pytest.mark.parametrize("engine", ["simt", "tc", "pair", "split"])
 def test_ragged_and_empty_sequences(engine):
     _case(engine, R=4, n_cand=70, T=20, d=36, h0=80, h1=40, act=2, softmax=False, seq_lens=[20, 0, 1, 7], seed=2)
 
 
-@pytest.mark.parametrize("engine", ["simt", "tc", "pair"])
+@pytest.mark.parametrize("engine", ["simt", "tc", "pair", "split"])
 def test_other_dims(engine):
     _case(engine, R=1, n_cand=129, T=33, d=16, h0=32, h1=16, act=0, softmax=False, seed=3)
     _case(engine, R=1, n_cand=5, T=3, d=20, h0=48, h1=24, act=2, softmax=False, seed=4)
     _case(engine, R=2, n_cand=140, T=11, d=18, h0=32, h1=16, act=1, softmax=False, seed=5)    # d not a multiple of 4
+
+
+def test_split_engine_walks_several_requests_and_tiles_per_cta():
+    """More tiles than SMs: every CTA of the persistent engine walks a run of tiles that crosses request
+    boundaries (ragged sequence lengths, a partial last tile per request, an empty sequence in the middle)."""
+    _case("split", R=40, n_cand=1000, T=100, d=36, h0=80, h1=40, act=2, softmax=False,
+          seq_lens=[100, 99, 0, 1, 2, 3, 50, 100] * 5, seed=6)
+
+
+def test_split_engine_other_selector_layouts():
+    # d a multiple of 8: the selector slots get a chunk of their own; odd chunk counts straddle segments
+    _case("split", R=2, n_cand=200, T=37, d=24, h0=64, h1=32, act=2, softmax=False, seed=7)
+    _case("split", R=1, n_cand=64, T=9, d=32, h0=80, h1=40, act=1, softmax=True, seq_lens=[5], seed=8)
+    _case("split", R=3, n_cand=300, T=100, d=12, h0=48, h1=16, act=2, softmax=False, seq_lens=[100, 7, 64], seed=9)

@@ -11,7 +11,7 @@ XB_UDF_SUM, XB_UDF_AVG, XB_UDF_ASSIGN = 0, 1, 2
 XB_TRUNC_ORDER, XB_TRUNC_REVERSE = 0, 1
 XB_EPI_NONE, XB_EPI_PRELU, XB_EPI_DICE, XB_EPI_SIGMOID = 0, 1, 2, 3
 XB_BIAS_NONE, XB_BIAS_ROW, XB_BIAS_FULL = 0, 1, 2
-XB_ATT_ENGINE_PAIR = 3
+XB_ATT_ENGINE_PAIR, XB_ATT_ENGINE_SPLIT = 3, 4
 XB_GEMM_AUTO, XB_GEMM_SIMT, XB_GEMM_TCGEN05 = 0, 1, 2
 XB_ACT_NONE, XB_ACT_SIGMOID, XB_ACT_DICE = 0, 1, 2
 XB_MAX_POOL_ITEMS, XB_MAX_POOL_GROUPS = 4, 32

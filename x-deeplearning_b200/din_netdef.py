@@ -93,6 +93,80 @@ def build(model, fused_tower=True):
     return api.netdef_text(ops, feeds, [("output", F16)], name="din"), [n for n, _ in feeds]
 
 
+def build_unfused(model, dtype=F32, device_type=0):
+    """The same model for ONE request with reference operators only, composed the way the shipped DIN graph is
+    (blaze/tools/example_model/din/model/graph_ulf.txt: Sub, Mul, BroadcastTo x2, Concat, three Gemm layers with
+    their activations, the weighted sum as a batched MatMul, ReduceSum, Mul, Concat, Fuse, the tower Gemm / Dice
+    chain and Softmax). This is the graph the reference's own CPU operators run in the benchmark's reference arm,
+    and the graph the fusion pass of the host runtime turns back into DinAttention + DinTower.
+    Returns (netdef_text, input_names); output "output" [n_cand, 2] in `dtype`."""
+    D = model["dims"]
+    e, d, T, G = D["emb"], D["d"], D["T"], D["user_groups"]
+    users = ["u%d" % g for g in range(G)]
+    triple = lambda n: [n + ".ids", n + ".values", n + ".segments"]
+    O = api.op_text
+    ops = []
+
+    def reshape(x, y, shape):
+        # the reference's Reshape reads the new shape from an int32 tensor (blaze/blaze/operator/op/reshape_op.h:17-50)
+        ops.append(api.constant_text(y + "_shape", np.asarray(shape), I32))
+        ops.append(O("Reshape", [x, y + "_shape"], [y]))
+    conf = "".join(_fg(u, "user%d" % g, e) for g, u in enumerate(users))
+    conf += _fg("mid_list", "item", e) + _fg("cat_list", "cate", e)
+    conf += "block_config {\n" + "".join(_item(u, 0) for u in users) + "}\n"
+    conf += "block_config {\n" + _item("mid_list", 2, T) + "}\n"
+    conf += "block_config {\n" + _item("cat_list", 2, T) + "}\n"
+    user_in = sum([triple(u) for u in users], []) + triple("mid_list") + triple("cat_list")
+    ops.append(O("Embedding", user_in, ["uid_emb", "mid_list_emb", "cat_list_emb"], {"embedding_config": conf}, "user_embedding"))
+    conf = _fg("mid", "item", e) + _fg("cat", "cate", e) + "block_config {\n" + _item("mid", 0) + _item("cat", 0) + "}\n"
+    ops.append(O("Embedding", triple("mid") + triple("cat"), ["ad_emb"], {"embedding_config": conf}, "ad_embedding"))
+    reshape("mid_list_emb", "mid_list_3d", [1, -1, e])
+    reshape("cat_list_emb", "cat_list_3d", [1, -1, e])
+    ops.append(O("Concat", ["mid_list_3d", "cat_list_3d"], ["his_emb"], {"axis": 2}))          # [1, T, d]
+    reshape("ad_emb", "item_emb", [-1, 1, d])                  # [n, 1, d]
+    # attention unit, rows 7-16 of the shipped graph
+    ops.append(O("Sub", ["item_emb", "his_emb"], ["sub_emb"]))                                 # [n, T, d]
+    ops.append(O("Mul", ["item_emb", "his_emb"], ["mul_emb"]))
+    ops.append(O("BroadcastTo", ["his_emb", "sub_emb"], ["b_his_emb"]))
+    ops.append(O("BroadcastTo", ["item_emb", "sub_emb"], ["b_item_emb"]))
+    ops.append(O("Concat", ["b_item_emb", "b_his_emb", "sub_emb", "mul_emb"], ["att_in"], {"axis": 2}))   # [n, T, 4d]
+    a = model["att"]
+    for n in ("W0", "b0", "W1", "b1", "W2", "b2", "g0", "m0", "v0", "g1", "m1", "v1"):
+        ops.append(api.constant_text("att_" + n, a[n], dtype))
+    ops.append(O("Gemm", ["att_in", "att_W0", "att_b0"], ["att_h0"]))
+    ops.append(O("Dice", ["att_h0", "att_g0", "att_m0", "att_v0"], ["att_y0"]))
+    ops.append(O("Gemm", ["att_y0", "att_W1", "att_b1"], ["att_h1"]))
+    ops.append(O("Dice", ["att_h1", "att_g1", "att_m1", "att_v1"], ["att_y1"]))
+    ops.append(O("Gemm", ["att_y1", "att_W2", "att_b2"], ["att_s"]))                           # [n, T, 1]
+    reshape("att_s", "att_w", [-1, 1, T])                      # [n, 1, T]
+    ops.append(O("MatMul", ["att_w", "his_emb"], ["att_3d"]))                                  # [n, 1, d]
+    reshape("att_3d", "att", [-1, d])
+    # tower input, rows 17-22
+    ops.append(O("ReduceSum", ["his_emb"], ["his_sum"], {"axis": 1, "keepdims": 0}))           # [1, d]
+    ops.append(O("Mul", ["ad_emb", "his_sum"], ["mul_item"]))
+    ops.append(O("Sub", ["ad_emb", "his_sum"], ["sub_item"]))
+    ops.append(O("BroadcastTo", ["his_sum", "ad_emb"], ["b_his_sum"]))
+    ops.append(O("Concat", ["ad_emb", "b_his_sum", "mul_item", "att", "sub_item"], ["cand_side"], {"axis": 1}))
+    ops.append(O("Fuse", ["uid_emb", "cand_side"], ["tower_in"]))
+    tw = model["tower"]
+    for i, key in ((1, "dice1"), (2, "dice2"), (3, None)):
+        ops.append(api.constant_text("t_W%d" % i, tw["W%d" % i], dtype))
+        ops.append(api.constant_text("t_b%d" % i, tw["b%d" % i], dtype))
+        if key:
+            for n, arr in zip(("g", "m", "v"), tw[key]):
+                ops.append(api.constant_text("t_%s%d" % (n, i), arr, dtype))
+    ops.append(O("Gemm", ["tower_in", "t_W1", "t_b1"], ["h1"]))
+    ops.append(O("Dice", ["h1", "t_g1", "t_m1", "t_v1"], ["y1"]))
+    ops.append(O("Gemm", ["y1", "t_W2", "t_b2"], ["h2"]))
+    ops.append(O("Dice", ["h2", "t_g2", "t_m2", "t_v2"], ["y2"]))
+    ops.append(O("Gemm", ["y2", "t_W3", "t_b3"], ["logit"]))
+    ops.append(O("Softmax", ["logit"], ["output"], {"axis": 1}))
+    feeds = []
+    for n in users + ["mid_list", "cat_list", "mid", "cat"]:
+        feeds += [(n + ".ids", I64), (n + ".values", dtype), (n + ".segments", I32)]
+    return api.netdef_text(ops, feeds, [("output", dtype)], device_type=device_type, name="din_unfused"), [n for n, _ in feeds]
+
+
 def register_tables(mgr, model):
     mgr.load_sparse(None, "b200_sparse_puller")
     mgr.add_table("item", model["item"], F16)
