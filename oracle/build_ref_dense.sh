@@ -70,7 +70,8 @@ done
 
 echo "[3/4] reference CPU sources"
 FORCED="-include functional -include cstdint -include cstring -include numeric -include string -include cmath -include memory -include limits"
-FLAGS="-std=c++11 -O2 -fPIC -w -mavx -mavx2 -mf16c -mfma -fopenmp -DHAVE_PTHREAD $FORCED -I$B/gen -I$B/gen/blaze -I$HERE/ref_shim -I$BLZ -I$PB"
+# the reference's own flags (blaze/CMakeLists.txt:78), warnings off
+FLAGS="-O2 -DNDEBUG -std=c++11 -fPIC -ftree-vectorize -w -mavx -mavx2 -mf16c -fopenmp -DHAVE_PTHREAD $FORCED -I$B/gen -I$B/gen/blaze -I$HERE/ref_shim -I$BLZ -I$PB"
 cc_blz() {
   local o=$B/blaze/$(echo ${1#$BLZ/} | tr '/' '_').o
   [ -f $o ] || g++ $FLAGS -c $1 -o $o || echo "FAILED $1" >> $B/blaze/failed.txt
@@ -84,6 +85,6 @@ if [ -f $B/blaze/failed.txt ]; then cat $B/blaze/failed.txt; exit 1; fi
 
 echo "[4/4] link"
 RT_OBJS=$(for f in $RUNTIME; do echo $B/pb/$(echo google/protobuf/$f | tr '/' '_').o; done)
-g++ -std=c++11 -O2 -fPIC -w -shared -fopenmp $FORCED -I$B/gen -I$HERE/ref_shim -I$BLZ -I$PB \
+g++ -O2 -DNDEBUG -std=c++11 -fPIC -ftree-vectorize -w -mavx -mavx2 -mf16c -shared -fopenmp $FORCED -I$B/gen -I$HERE/ref_shim -I$BLZ -I$PB \
     $HERE/ref_dense_glue.cc $HERE/ref_glue.cc $B/blaze/*.o $RT_OBJS -o $OUT/libblaze_cpu.so -lpthread -ldl
 echo "built $OUT/libblaze_cpu.so"
