@@ -110,3 +110,31 @@ def test_one_manager_serves_predictors_on_two_devices():
         p.close()
     mgr.close()
     torch.cuda.set_device(0)
+
+
+@pytest.mark.parametrize("optimize", [True, False])
+def test_unfused_graph_through_the_predictor(optimize):
+    """The op-by-op graph of one request (what the reference's own CPU operators run in the benchmark's reference
+    arm), fp16, on the GPU: op by op as written, and rewritten by the fusion pass into DinAttention + DinTower."""
+    pkg.load()
+    from x_deeplearning_b200 import blaze_api as api, din_netdef, workloads
+    model = workloads.din_model(0, item_rows=20000, cate_rows=500, user_rows=3000, emb_sigma=0.5)
+    text, _ = din_netdef.build_unfused(model, dtype=12, device_type=1)
+    mgr = api.PredictorManager()
+    din_netdef.register_tables(mgr, model)
+    mgr.load_model_text(text, optimize=optimize)
+    assert ("DinTower" in mgr.op_types()) == optimize
+    p = mgr.create_predictor(device_type=1, device_id=0)
+    launches = []
+    for seed, n_cand, seq in ((4, 200, None), (5, 77, [31])):
+        req = workloads.din_requests(model, seed, requests=1, n_cand=n_cand, seq_len=seq)
+        keep = [p.feed(n, a) for n, a in din_netdef.feeds_of(model, req).items()]
+        p.forward()
+        got = p.output("output").astype(np.float32)
+        want = din_oracle.forward(model, req)
+        assert got.shape == want.shape
+        assert np.abs(got - want).max() <= 2e-3, np.abs(got - want).max()
+        launches.append(p.launches())
+    assert (launches[0] <= 12) if optimize else (launches[0] >= 25), launches
+    p.close()
+    mgr.close()

@@ -46,6 +46,7 @@ def lib():
         L.Blaze_B200_PredictorForwardAsync.argtypes = [vp, FORWARD_CB, vp]
         L.Blaze_B200_PlanBatch.argtypes = [vp, C.c_int, C.c_int, C.c_int, vp]
         L.Blaze_B200_BatchingStats.argtypes = [C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+        L.Blaze_B200_ModelOpTypes.argtypes = [vp, C.c_char_p, C.c_size_t]
         _lib = L
     return _lib
 
@@ -108,6 +109,13 @@ class PredictorManager:
 
     def load_model_file(self, path, optimize=True):
         _ck(lib().Blaze_PredcitorManagerLoadModel(self.h, path.encode(), int(optimize)))
+
+    def op_types(self):
+        """Operator types of the loaded model, in execution order (after the fusion passes if they ran)."""
+        n = lib().Blaze_B200_ModelOpTypes(self.h, None, 0)
+        buf = C.create_string_buffer(n)
+        _ck(lib().Blaze_B200_ModelOpTypes(self.h, buf, n))
+        return buf.value.decode().split(",") if buf.value else []
 
     def create_predictor(self, device_type=1, device_id=0):
         h = vp()

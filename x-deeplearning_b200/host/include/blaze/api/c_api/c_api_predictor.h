@@ -56,6 +56,9 @@ int Blaze_B200_LoadSparseModelWeight(PredictorManagerHandle handle, const char* 
 int Blaze_B200_AddTable(PredictorManagerHandle handle, const char* table_name, int64_t rows, int dim,
                         int storage_dtype, const float* weights, const int64_t* keys);
 /* Feed whose source is already in device memory (no host staging). */
+/* Operator types of the model the manager holds (after the optimization passes when LoadModel ran them), comma
+ * separated, into `buffer`. Returns 0, or the capacity needed when `buffer` is NULL or too small. */
+int Blaze_B200_ModelOpTypes(PredictorManagerHandle handle, char* buffer, size_t capacity);
 int Blaze_B200_PredictorFeedDevice(PredictorHandle handle, const char* name, const void* device_data, size_t len);
 /* Device pointer of an output (valid until the next Forward); no device-to-host copy. */
 int Blaze_B200_PredictorOutputDevice(PredictorHandle handle, const char* name, void** device_data, size_t* len);

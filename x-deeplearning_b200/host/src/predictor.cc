@@ -71,6 +71,7 @@ class PredictorManagerImpl {
     net_def_ = def;
     if (optimize) {
       FoldBatchNorm(&net_def_);
+      FuseDinSubgraphs(&net_def_);
       FuseGemmActivation(&net_def_);
     }
     loaded_ = true;
@@ -504,6 +505,15 @@ int Blaze_B200_AddTable(PredictorManagerHandle h, const char* table_name, int64_
   BLAZE_CONDITION_THROW(m->puller_->AddTable(table_name, rows, dim, storage_dtype, weights, keys) == store::kOK,
                         "AddTable ", table_name, " failed");
   API_END();
+}
+int Blaze_B200_ModelOpTypes(PredictorManagerHandle h, char* buffer, size_t capacity) {
+  // operator types of the loaded (and, with optimization_pass, rewritten) NetDef, comma separated
+  PredictorManagerImpl* m = ManagerAccess::impl(static_cast<PredictorManager*>(h));
+  std::string s;
+  for (const auto& op : m->net_def_.op) s += (s.empty() ? "" : ",") + op.type;
+  if (!buffer || capacity < s.size() + 1) return (int)s.size() + 1;
+  memcpy(buffer, s.c_str(), s.size() + 1);
+  return 0;
 }
 int Blaze_B200_PredictorFeedDevice(PredictorHandle h, const char* name, const void* device_data, size_t len) {
   API_BEGIN();

@@ -386,6 +386,11 @@ void FuseGemmActivation(NetDef* def);
 // Run before it: folds a BatchNormalization with constant parameters into the weight and bias of the Gemm it
 // feeds or follows (constants re-computed in fp32), so the node disappears from the graph.
 void FoldBatchNorm(NetDef* def);
+// Run between the two: recognises the op-by-op attention unit (Sub, Mul, BroadcastTo x2, Concat, three Gemm layers
+// with their activations, Reshape, MatMul, Reshape) and the op-by-op tower (ReduceSum, Mul, Sub, BroadcastTo,
+// Concat, Fuse, Gemm + Dice x2, Gemm, Softmax) of an fp16 DIN-style graph and replaces them by DinAttention and
+// DinTower. Returns the number of sub-graphs replaced.
+int FuseDinSubgraphs(NetDef* def);
 
 // fp32 <-> fp16 on the host (round to nearest even)
 uint16_t FloatToHalfBits(float f);
