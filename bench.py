@@ -168,6 +168,21 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    # ---- what is about to be timed gives the oracle's answer: one request of the first batch, outside the timed region
+    if rank == 0:
+        checker_path()
+        import din_oracle
+        req0 = workloads.din_requests(model, 1000 * rank + 17, R, N_CAND)
+        one = {k: v for k, v in req0.items()}
+        one.update(requests=1, user_ids=req0["user_ids"][:1], seq_len=req0["seq_len"][:1],
+                   hist_item=req0["hist_item"][:int(req0["seq_len"][0])], hist_cate=req0["hist_cate"][:int(req0["seq_len"][0])],
+                   cand_item=req0["cand_item"][:N_CAND], cand_cate=req0["cand_cate"][:N_CAND])
+        got0 = net.forward_device(plans[0]).cpu().numpy()[:N_CAND]
+        parity_err = float(np.abs(got0 - din_oracle.forward(model, one)).max())
+        assert parity_err <= 2e-3, "DIN probabilities of the benchmark's first request differ from the oracle by %g" % parity_err
+    else:
+        parity_err = None
+
     # ---- device-resident throughput (inputs already in HBM) --------------------------------
     for i in range(W):
         net.forward_device(plans[i % NB])
@@ -299,16 +314,19 @@ def run_ours(args):
                      "peak_source": pk["source"] + " (sustained bf16)", "ms_per_launch": att_ms,
                      "pool_ms_per_step": pool_ms},
         "clocks": clocks,
+        "parity": {"checked": "request 0 of batch 0 (1000 candidates) against the CPU oracle before timing",
+                   "max_abs_err": parity_err, "tol": 2e-3},
     }
     if world > 1 and not args.no_sharded:
         # the path that has collectives: measured after the replica leg, on the same process group
         del net, plans, staged, pred, mgr
         torch.cuda.empty_cache()
-        leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype)
+        leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype, args.sharded_impl)
         line["sharded"] = leg.run(min(K, 20), W)
     if rank == 0 and world == 1 and not args.no_cpu:
         line["embedding_pool"] = bench_pool(pk)
         line["embedding_pool"]["hbm_resident"] = bench_pool_hbm(pk)
+        line["fused_gemm"] = bench_gemm(pk)
         line["cpu_baseline"] = cpu_baseline_din(model, workloads, cores=1, budget_s=args.cpu_seconds)
     if rank == 0:
         print(json.dumps(line))
@@ -368,6 +386,60 @@ def bench_pool(pk):
         del table, y, groups, plan
     out["peak_gbs"] = pk["hbm_gbs"]
     out["peak_source"] = pk["source"]
+    return out
+
+
+def bench_gemm(pk, reps=30):
+    """The tcgen05 GEMM on three shapes: the parallel-GEMM configuration as written (8 branches of
+    [4096, 256] x [256, 128] + bias + PReLU into [4096, 1024]), the same with M = 65536 (launch overhead below
+    2 %), and the compute-bound first layer of the large-table MLP ([65536, 1280] x [1280, 1024])."""
+    import torch
+    from x_deeplearning_b200 import capi, ops
+    out = {}
+    slope = torch.full((1,), 0.25, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(run, flush_l2):
+        for _ in range(3):
+            run()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        torch.cuda.synchronize()
+        for a, b in ev:
+            if flush_l2:
+                flush.zero_()
+            a.record(); run(); b.record()
+        torch.cuda.synchronize()
+        return statistics.median(a.elapsed_time(b) for a, b in ev)
+
+    for label, M in (("parallel_gemm_config", 4096), ("parallel_gemm_m65536", 65536)):
+        P, K, N = 8, 256, 128
+        A = torch.randn((P, M, K), device="cuda", dtype=torch.float16)
+        Wk = torch.randn((P, N, K), device="cuda", dtype=torch.float16) / 16
+        bias = torch.randn((P, N), device="cuda") * 0.01
+        Y = torch.empty((M, P * N), device="cuda", dtype=torch.float16)
+        run = lambda: ops.gemm(A, Wk, Y=Y, bias=bias, trans_b=True, batch=P, M=M, N=N, K=K, lda=K, ldb=K, ldy=P * N,
+                               strides=(M * K, N * K, N, N), bias_kind=capi.XB_BIAS_ROW, epilogue=capi.XB_EPI_PRELU,
+                               ep=(slope, None, None), ep_count=1, engine=capi.XB_GEMM_TCGEN05)
+        ms = timed(run, flush_l2=(M == 4096))
+        nbytes = 2 * (P * M * K + P * N * K + M * P * N) + 4 * P * N
+        flops = 2.0 * P * M * N * K
+        out[label] = {"ms_per_launch": ms, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "tflops": flops / (ms * 1e-3) / 1e12,
+                      "frac_of_measured_copy_peak": nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "bound": "hbm (85 flop/B)",
+                      "l2": "flushed before each launch (256 MB written)" if M == 4096 else "inputs exceed L2"}
+        del A, Wk, Y
+    M, K, N = 65536, 1280, 1024
+    A = torch.randn((M, K), device="cuda", dtype=torch.float16)
+    Wk = torch.randn((N, K), device="cuda", dtype=torch.float16) / K ** 0.5
+    bias = torch.randn(N, device="cuda") * 0.01
+    Y = torch.empty((M, N), device="cuda", dtype=torch.float16)
+    run = lambda: ops.gemm(A, Wk, Y=Y, bias=bias, trans_b=True, M=M, N=N, K=K, epilogue=capi.XB_EPI_PRELU,
+                           ep=(slope, None, None), ep_count=1, engine=capi.XB_GEMM_TCGEN05)
+    ms = timed(run, flush_l2=False)
+    tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    out["mlp_layer1_m65536"] = {"ms_per_launch": ms, "tflops": tf, "frac_of_measured_burst_bf16": tf / pk["tf_burst"],
+                                "frac_of_measured_sustained_bf16": tf / pk["tf_sustained"], "bound": "tensor (512 flop/B)"}
+    out["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops_burst": pk["tf_burst"], "bf16_tflops_sustained": pk["tf_sustained"],
+                    "source": pk["source"]}
     return out
 
 
@@ -785,14 +857,14 @@ class ShardedLeg:
     vectors returned with NCCL all-to-all, then the MLP 1280-1024-512-256-1 (PReLU, sigmoid) data-parallel."""
     N_TABLES, GPT, DIM, BATCH = 4, 10, 32, 65536
 
-    def __init__(self, rank, world, table_rows, partial_dtype="f16"):
+    def __init__(self, rank, world, table_rows, partial_dtype="f16", impl="abi"):
         import numpy as np
         import torch
         from x_deeplearning_b200 import capi, ops, sharded, workloads
         self.rank, self.world, self.rows_total = rank, world, table_rows
         self.torch, self.ops, self.capi, self.sharded = torch, ops, capi, sharded
         self.comm, self.gops = sharded.DistComm(), sharded.GpuShardOps(partial_dtype=partial_dtype)
-        self.partial_dtype = partial_dtype
+        self.partial_dtype, self.impl = partial_dtype, impl
         n_tables, gpt, dim = self.N_TABLES, self.GPT, self.DIM
         self.B = B = self.BATCH // world
         rng = np.random.default_rng(100 + rank)
@@ -819,6 +891,24 @@ class ShardedLeg:
             np.cumsum(counts, out=off[1:])
             self.host_feeds.append((ids, off))
             self.feeds.append((torch.from_numpy(ids).cuda(), torch.from_numpy(off).cuda(), n))
+        self.ctx = None
+        if impl == "abi":
+            # the whole step behind the C ABI: one routing problem over all tables, NCCL called by the library
+            import torch.distributed as dist
+            uid = [sharded.ShardContext.unique_id() if rank == 0 else None]
+            if world > 1:
+                dist.broadcast_object_list(uid, src=0)
+            max_ids = int(1.05 * n_tables * gpt * B * 15.5) + 4096
+            self.ctx = sharded.ShardContext(rank, world, self.tables, [gpt * B] * n_tables, dim, max_ids, partial_dtype,
+                                            capacity_factor=2.0, unique_id=uid[0])
+            self.all_ids = torch.cat([f[0] for f in self.feeds])
+            base, parts = 0, []
+            for f in self.feeds:
+                parts.append(f[1][:-1] + base)
+                base += f[2]
+            parts.append(torch.full((1,), base, dtype=torch.int32, device="cuda"))
+            self.all_off = torch.cat(parts)
+            assert self.all_ids.numel() <= max_ids
         self.dims = dims = [n_tables * gpt * dim, 1024, 512, 256, 1]
         wrng = np.random.default_rng(7)                       # the dense weights are replicated: same seed on every rank
         self.W_host = [workloads.fp16_round(wrng.normal(0, 1.0 / dims[i] ** 0.5, (dims[i + 1], dims[i]))) for i in range(4)]
@@ -841,9 +931,17 @@ class ShardedLeg:
         if timed:
             mark("start")
         # the four tables share the ownership rule: one routing pass and one pair of exchanges for all of them
-        stats = self.sharded.sharded_pool_tables(self.comm, self.gops, self.tables, self.DIM, [f[0] for f in self.feeds],
-                                                 [None] * self.N_TABLES, [f[1] for f in self.feeds],
-                                                 [self.GPT] * self.N_TABLES, self.pooled, mark=mark if timed else None)
+        if self.ctx is not None:
+            self.ctx.pool(self.all_ids, self.all_off, self.N_TABLES * self.GPT, self.pooled)
+            esz = 2 if self.partial_dtype == "f16" else 4
+            stats = {"routed_bytes": self.world * self.ctx.bucket_capacity * 8,
+                     "returned_bytes": self.world * self.N_TABLES * self.GPT * self.B * self.DIM * esz}
+            if timed:
+                mark("sharded_pool")
+        else:
+            stats = self.sharded.sharded_pool_tables(self.comm, self.gops, self.tables, self.DIM, [f[0] for f in self.feeds],
+                                                     [None] * self.N_TABLES, [f[1] for f in self.feeds],
+                                                     [self.GPT] * self.N_TABLES, self.pooled, mark=mark if timed else None)
         x = self.pooled
         for i in range(4):
             last = i == 3
@@ -922,12 +1020,18 @@ class ShardedLeg:
             for (_, a), (name, b) in zip(events[:-1], events[1:]):
                 phase_ms[name] = phase_ms.get(name, 0.0) + a.elapsed_time(b) / len(self.phases)
         assert self.ops.device_status() == 0
+        if self.ctx is not None:
+            assert not self.ctx.overflow(), "an id bucket overflowed its fixed capacity: raise capacity_factor"
         ms = float(t.item()) / steps
         return {"ms_per_step": ms, "samples_per_s": self.BATCH / (ms * 1e-3), "steps": steps, "n_gpus": self.world,
                 "table_rows": self.rows_total, "tables": self.N_TABLES, "dim": self.DIM,
                 "ids_per_rank_step": sum(f[2] for f in self.feeds),
                 "routed_bytes_per_rank_step": stats["routed_bytes"], "returned_bytes_per_rank_step": stats["returned_bytes"],
-                "partial_dtype": self.partial_dtype, "phase_ms_rank0": {k: round(v, 4) for k, v in phase_ms.items()},
+                "partial_dtype": self.partial_dtype,
+                "impl": ("xb_sharded_pool: one C-ABI call per step, NCCL inside the library, fixed-capacity id buckets, "
+                         "no host synchronisation" if self.ctx is not None else
+                         "python orchestration over torch.distributed (bucket sizes read back every step)"),
+                "phase_ms_rank0": {k: round(v, 4) for k, v in phase_ms.items()},
                 "parity": parity, "timing": "max over ranks, CUDA events; MLP 1280-1024-512-256-1 included"}
 
 
@@ -939,7 +1043,7 @@ def run_sharded(args):
     rank, local_rank, world = dist_env()
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype)
+    leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype, args.sharded_impl)
     out = leg.run(args.steps, args.warmup)
     if rank == 0:
         print(json.dumps(dict({"micro": "sharded"}, **out)))
@@ -962,6 +1066,8 @@ def main():
     ap.add_argument("--table-rows", type=int, default=200_000_000, help="rows per table of the row-sharded leg")
     ap.add_argument("--partial-dtype", default="f16", choices=["f16", "f32"],
                     help="dtype of the partial sums the owners return in the row-sharded leg (f32 for the 1e-5 bar)")
+    ap.add_argument("--sharded-impl", default="abi", choices=["abi", "python"],
+                    help="row-sharded leg: the one-call C-ABI step (NCCL inside the library) or the Python orchestration")
     ap.add_argument("--no-sharded", action="store_true", help="skip the row-sharded leg of a multi-GPU run")
     ap.add_argument("--case", default=None, help="--micro pool_hbm: run one case only (shard25m_dim32 | item5m_dim18)")
     ap.add_argument("--micro", choices=["att", "pool", "pool_hbm", "gemm", "gemm_mlp", "tower", "sharded", "batching"], help="run --steps launches of one kernel on a small case "

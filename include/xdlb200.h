@@ -222,6 +222,65 @@ int xb_shard_combine(const void* partial, int32_t partial_dtype, int32_t shards,
                      const int32_t* seg_len, int32_t avg, void* out, int64_t out_stride, int64_t groups,
                      int32_t out_dtype, xb_stream_t stream);
 
+/* Fixed-capacity variant of step 1 for an exchange that never reads bucket sizes back to the host: bucket w starts
+ * at out_records + w * bucket_cap, its slot 0 holds the number of packed records that follow (at most
+ * bucket_cap - 1); a bucket that would not fit raises *overflow (device int, e.g. mapped host memory) and is cut.
+ * xb_unpack_routed_padded splits `sources` received buckets into rows and tags in place (slots past a bucket's
+ * count get tag -1, which the counting kernels ignore). xb_scan_counts turns n_arrays count arrays of `batch`
+ * entries (counts_stride apart) into exclusive offsets of batch + 1 entries (offsets_stride apart).
+ * xb_shard_pool_padded is xb_shard_pool over that layout: offsets [sources][S + 1] count from each source's
+ * first record. */
+int xb_route_ids_padded(const int64_t* ids, const int32_t* seg_offsets, int64_t segments, int64_t n_ids, int32_t shards,
+                        int64_t bucket_cap, int64_t* out_records, int32_t* overflow, void* scratch, size_t scratch_bytes,
+                        xb_stream_t stream);
+int xb_unpack_routed_padded(const int64_t* packed, int32_t sources, int64_t bucket_cap, int32_t* rows, int32_t* tags,
+                            xb_stream_t stream);
+size_t xb_scan_counts_scratch_bytes(int32_t n_arrays, int64_t batch);
+int xb_scan_counts(const int32_t* counts, int64_t counts_stride, int32_t* offsets, int64_t offsets_stride, int32_t n_arrays,
+                   int64_t batch, void* scratch, size_t scratch_bytes, xb_stream_t stream);
+int xb_shard_pool_padded(const xb_table_desc* const* tables, const int64_t* table_segments, int32_t n_tables,
+                         const int32_t* rows, int64_t bucket_cap, const int32_t* offsets, int32_t sources,
+                         int64_t n_rows_estimate, int32_t dim, void* out, int32_t out_dtype, xb_stream_t stream);
+
+/* The whole sharded step behind one call, with the two exchanges done by NCCL from inside the library (bound at
+ * run time: libnccl.so.2 is needed only by processes that create a context for more than one rank). A context
+ * belongs to one rank = one process and device; it owns every buffer of a step (allocated at creation) and its
+ * NCCL communicator. xb_shard_unique_id makes the 128-byte communicator id on one rank; the caller hands it to
+ * the others (any transport) and every rank calls xb_shard_ctx_create with it.
+ *   tables[t]          this rank's shard of table t (identity keys: row = local row), all of `dim`
+ *   table_segments[t]  segments of table t per step on THIS rank (feature groups of t x samples of this rank)
+ *   max_ids            most ids one step of this rank may carry
+ *   capacity_factor    bucket capacity = factor x max_ids / world (+ header): head room for owners that hold hot
+ *                      rows; a step that exceeds it reports overflow = 1 through xb_shard_ctx_status
+ * xb_sharded_pool enqueues the step on `stream` and returns; nothing in it waits for the device. ids / seg_offsets
+ * as for xb_route_ids (segments numbered table after table, group-major inside a table); out [rows, >= groups * dim]
+ * receives sum-pooled vectors, out[sample, g * dim + e] for segment g * rows + sample. xb_a2a_route and
+ * xb_a2a_return are the two exchanges alone (ids out, partial sums back) for callers that run the owner-side
+ * kernels themselves. xb_shard_ctx_status is read after the caller synchronised the stream: *overflow != 0 says
+ * the last steps dropped ids (raise capacity_factor); an NCCL asynchronous error is returned as XB_ERR_CUDA. */
+typedef struct xb_shard_ctx xb_shard_ctx;
+typedef struct xb_shard_config {
+  int32_t rank, world;
+  int32_t dim;
+  int32_t n_tables;
+  const xb_table_desc* const* tables;   /* HOST array of HOST pointers */
+  const int64_t* table_segments;        /* HOST */
+  int64_t max_ids;
+  int32_t partial_dtype;                /* XB_F32 or XB_F16 */
+  float capacity_factor;                /* <= 1 means 1 */
+} xb_shard_config;
+int xb_shard_unique_id(void* id128);
+int64_t xb_shard_bucket_capacity(int64_t max_ids, int32_t world, float capacity_factor);
+int xb_shard_ctx_create(xb_shard_ctx** out, const void* unique_id128, const xb_shard_config* cfg);
+void xb_shard_ctx_destroy(xb_shard_ctx* ctx);
+int xb_sharded_pool(xb_shard_ctx* ctx, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids, int64_t groups,
+                    int32_t avg, void* out, int64_t out_stride, int32_t out_dtype, xb_stream_t stream);
+int xb_a2a_route(xb_shard_ctx* ctx, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids, xb_stream_t stream);
+int xb_a2a_return(xb_shard_ctx* ctx, xb_stream_t stream);
+int xb_shard_ctx_status(xb_shard_ctx* ctx, int32_t* overflow);
+int64_t xb_shard_ctx_bucket_capacity(const xb_shard_ctx* ctx);
+size_t xb_shard_ctx_device_bytes(const xb_shard_ctx* ctx);
+
 /* Self-test of the bounded waits (no counterpart in the reference): launches one warp that waits on a barrier
  * nothing will ever signal and gives up after `limit_cycles`. Afterwards xb_device_status reports a non-zero
  * word (site 99) until xb_device_status_clear, and every other entry point keeps working. */

@@ -268,3 +268,89 @@ def test_large_table_configuration_shape_on_one_rank(partial_dtype):
         # one fp16 rounding of the result (and one of the partial sum when it travels as fp16)
         tol = (2.0 if partial_dtype == "f16" else 1.0) * 2.0 ** -11
         assert (err <= tol * np.maximum(mag, 1e-6)).all(), float((err / np.maximum(mag, 1e-6)).max())
+
+
+@pytest.mark.parametrize("partial_dtype", ["f16", "f32"])
+def test_one_call_sharded_step_on_one_rank_matches_the_unsharded_oracle(partial_dtype):
+    """xb_sharded_pool (context owned by the library, fixed-capacity buckets, no host synchronisation) on a world of
+    one rank at the large-table configuration's shape, twice in a row with different ids (the context's buffers
+    keep the previous step's contents)."""
+    pkg.load()
+    from x_deeplearning_b200 import ops, sharded, workloads
+    rng = np.random.default_rng(43)
+    n_tables, gpt, dim, B, rows_total = 4, 10, 32, 2048, 200_000
+    tables_np = [workloads.fp16_round(rng.normal(0, 0.01, (rows_total, dim))) for _ in range(n_tables)]
+    tables = [ops.Table(torch.from_numpy(t), torch.float16) for t in tables_np]
+    ctx = sharded.ShardContext(0, 1, tables, [gpt * B] * n_tables, dim, max_ids=n_tables * gpt * B * 30,
+                               partial_dtype=partial_dtype)
+    assert ctx.bucket_capacity >= n_tables * gpt * B * 30 + 1
+    out = torch.zeros((B, n_tables * gpt * dim), dtype=torch.float16, device="cuda")
+    for step in range(2):
+        feeds = []
+        for t in range(n_tables):
+            counts = rng.integers(0 if step else 1, 31, gpt * B).astype(np.int32)       # second step: some empty segments
+            ids = workloads.zipf_ids(rng, rows_total, int(counts.sum()), 1.05)
+            feeds.append((ids, counts))
+        all_ids = np.concatenate([f[0] for f in feeds])
+        all_counts = np.concatenate([f[1] for f in feeds])
+        off = np.zeros(len(all_counts) + 1, np.int32)
+        np.cumsum(all_counts, out=off[1:])
+        ctx.pool(torch.from_numpy(all_ids).cuda(), torch.from_numpy(off).cuda(), n_tables * gpt, out)
+        torch.cuda.synchronize()
+        assert not ctx.overflow()
+        got = out.float().cpu().numpy()
+        for t, (ids, counts) in enumerate(feeds):
+            want = np.zeros((gpt * B, dim), np.float32)
+            mag = np.zeros((gpt * B, dim), np.float32)
+            ones = np.ones(len(ids), np.float32)
+            orc.embedding_pool(tables_np[t], ids, ones, counts, [dict(udf=0, out=want, col=0)])
+            orc.embedding_pool(np.abs(tables_np[t]), ids, ones, counts, [dict(udf=0, out=mag, col=0)])
+            want = want.reshape(gpt, B, dim).transpose(1, 0, 2).reshape(B, gpt * dim)
+            mag = mag.reshape(gpt, B, dim).transpose(1, 0, 2).reshape(B, gpt * dim)
+            err = np.abs(got[:, t * gpt * dim:(t + 1) * gpt * dim] - want)
+            tol = (2.0 if partial_dtype == "f16" else 1.0) * 2.0 ** -11
+            assert (err <= tol * np.maximum(mag, 1e-6)).all(), float((err / np.maximum(mag, 1e-6)).max())
+    ctx.close()
+
+
+def test_fixed_capacity_buckets_carry_the_same_records_and_flag_overflow():
+    """xb_route_ids_padded against the compact packed routing: same records in the same order behind each bucket's
+    count; a capacity that is too small cuts the bucket and raises the flag."""
+    pkg.load()
+    from x_deeplearning_b200 import capi, ops, sharded
+    L = capi.lib()
+    rng = np.random.default_rng(9)
+    world = 4
+    counts = rng.integers(0, 30, 3000).astype(np.int32)
+    n = int(counts.sum())
+    ids = rng.integers(0, 1 << 33, n).astype(np.int64)
+    ids[: n // 3] = (ids[: n // 3] // world) * world + 1            # owner 1 is hot
+    off = np.zeros(len(counts) + 1, np.int32)
+    np.cumsum(counts, out=off[1:])
+    d_ids, d_off = torch.from_numpy(ids).cuda(), torch.from_numpy(off).cuda()
+    compact, _, owner_counts = sharded.GpuShardOps().route_packed(d_ids, None, d_off, world)
+    oc = owner_counts.cpu().numpy()
+    need = int(L.xb_route_scratch_bytes(n, world))
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    for cap, expect_overflow in ((int(oc.max()) + 1, False), (int(oc.max()) - 5, True)):
+        rec = torch.full((world * cap,), -7, dtype=torch.int64, device="cuda")
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        capi.check(L.xb_route_ids_padded(ops.ptr(d_ids), ops.ptr(d_off), len(counts), n, world, cap, ops.ptr(rec),
+                                         ops.ptr(flag), ops.ptr(scratch), need, ops.stream()))
+        torch.cuda.synchronize()
+        assert bool(flag.item()) == expect_overflow
+        r, c = rec.cpu().numpy().reshape(world, cap), compact.cpu().numpy()
+        pos = 0
+        for w in range(world):
+            kept = min(int(oc[w]), cap - 1)
+            assert r[w, 0] == kept
+            np.testing.assert_array_equal(r[w, 1:1 + kept], c[pos:pos + kept])
+            pos += int(oc[w])
+        # at the owner: rows and tags, slots past the count tagged -1
+        rows = torch.empty(world * cap, dtype=torch.int32, device="cuda")
+        tags = torch.empty(world * cap, dtype=torch.int32, device="cuda")
+        capi.check(L.xb_unpack_routed_padded(ops.ptr(rec), world, cap, ops.ptr(rows), ops.ptr(tags), ops.stream()))
+        tg = tags.cpu().numpy().reshape(world, cap)
+        for w in range(world):
+            kept = min(int(oc[w]), cap - 1)
+            assert (tg[w, 0] == -1) and (tg[w, 1 + kept:] == -1).all() and (tg[w, 1:1 + kept] >= 0).all()

@@ -37,6 +37,11 @@ class PoolGroup(C.Structure):
                 ("n_items", i32), ("values_dtype", i32), ("items", PoolItem * XB_MAX_POOL_ITEMS)]
 
 
+class ShardConfig(C.Structure):
+    _fields_ = [("rank", i32), ("world", i32), ("dim", i32), ("n_tables", i32), ("tables", vp), ("table_segments", vp),
+                ("max_ids", i64), ("partial_dtype", i32), ("capacity_factor", f32)]
+
+
 class GemmArgs(C.Structure):
     _fields_ = [("M", i32), ("N", i32), ("K", i32), ("trans_a", i32), ("trans_b", i32), ("alpha", f32),
                 ("beta", f32), ("A", vp), ("lda", i64), ("stride_a", i64), ("B", vp), ("ldb", i64),
@@ -91,6 +96,21 @@ SYMBOLS = {
     "xb_tag_counts_sources": (i32, [vp, vp, i32, vp, i64, vp]),
     "xb_shard_pool": (i32, [vp, vp, i32, vp, i32, i64, vp, vp, i32, i32, vp, i32, vp]),
     "xb_shard_combine": (i32, [vp, i32, i32, i64, i32, vp, i32, vp, i64, i64, i32, vp]),
+    "xb_route_ids_padded": (i32, [vp, vp, i64, i64, i32, i64, vp, vp, vp, C.c_size_t, vp]),
+    "xb_unpack_routed_padded": (i32, [vp, i32, i64, vp, vp, vp]),
+    "xb_scan_counts_scratch_bytes": (C.c_size_t, [i32, i64]),
+    "xb_scan_counts": (i32, [vp, i64, vp, i64, i32, i64, vp, C.c_size_t, vp]),
+    "xb_shard_pool_padded": (i32, [vp, vp, i32, vp, i64, vp, i32, i64, i32, vp, i32, vp]),
+    "xb_shard_unique_id": (i32, [vp]),
+    "xb_shard_bucket_capacity": (i64, [i64, i32, f32]),
+    "xb_shard_ctx_create": (i32, [C.POINTER(vp), vp, C.POINTER(ShardConfig)]),
+    "xb_shard_ctx_destroy": (None, [vp]),
+    "xb_sharded_pool": (i32, [vp, vp, vp, i64, i64, i32, vp, i64, i32, vp]),
+    "xb_a2a_route": (i32, [vp, vp, vp, i64, vp]),
+    "xb_a2a_return": (i32, [vp, vp]),
+    "xb_shard_ctx_status": (i32, [vp, C.POINTER(i32)]),
+    "xb_shard_ctx_bucket_capacity": (i64, [vp]),
+    "xb_shard_ctx_device_bytes": (C.c_size_t, [vp]),
     "xb_gemm": (i32, [C.POINTER(GemmArgs), vp]),
     "xb_gemm_uses_tcgen05": (i32, [C.POINTER(GemmArgs)]),
     "xb_pack_weight_kmajor": (i32, [vp, i32, i32, i32, i64, vp, i32, i64, i32, i64, i64, vp]),

@@ -1094,8 +1094,12 @@ __global__ void __launch_bounds__(256) route_count_kernel(const int64_t* __restr
 
 // pass 2 (one CTA): exclusive scan in (owner, CTA) order -> first output slot of every (CTA, owner);
 // owner_counts[w] = ids routed to w, owner_offsets[w] = start of bucket w
+// With bucket_cap > 0 the buckets have a fixed capacity: bucket w starts at w * bucket_cap, its first slot holds
+// the number of records that follow (the receiver reads it from there), and a bucket that would not fit sets
+// *overflow and is cut at the capacity.
 __global__ void __launch_bounds__(256) route_scan_kernel(int32_t* __restrict__ block_hist, int64_t blocks, int shards,
-                                                         int64_t* __restrict__ owner_counts) {
+                                                         int64_t* __restrict__ owner_counts, int64_t bucket_cap,
+                                                         int64_t* __restrict__ headers, int32_t* __restrict__ overflow) {
   __shared__ int64_t total_s;
   __shared__ int32_t part[256];
   if (threadIdx.x == 0) total_s = 0;
@@ -1114,12 +1118,21 @@ __global__ void __launch_bounds__(256) route_scan_kernel(int32_t* __restrict__ b
         part[threadIdx.x] += add;
         __syncthreads();
       }
-      if (b < blocks) block_hist[b * shards + w] = (int32_t)(total_s + part[threadIdx.x] - v);
+      if (b < blocks)
+        block_hist[b * shards + w] = bucket_cap > 0 ? (int32_t)(w * bucket_cap + 1 + (total_s - start) + part[threadIdx.x] - v)
+                                                    : (int32_t)(total_s + part[threadIdx.x] - v);
       __syncthreads();
       if (threadIdx.x == 255) total_s += part[255];
       __syncthreads();
     }
-    if (threadIdx.x == 0) owner_counts[w] = total_s - start;
+    if (threadIdx.x == 0) {
+      const int64_t cnt = total_s - start;
+      if (owner_counts) owner_counts[w] = cnt;
+      if (bucket_cap > 0) {
+        headers[w * bucket_cap] = cnt < bucket_cap ? cnt : bucket_cap - 1;
+        if (cnt >= bucket_cap) atomicExch(overflow, 1);
+      }
+    }
     __syncthreads();
   }
 }
@@ -1130,7 +1143,7 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int64_t* __res
                                                             const int32_t* __restrict__ seg_offsets, int64_t segments,
                                                             int64_t n, int shards, const int32_t* __restrict__ block_base,
                                                             int64_t* __restrict__ out_rows, float* __restrict__ out_values,
-                                                            int32_t* __restrict__ out_tags) {
+                                                            int32_t* __restrict__ out_tags, int64_t bucket_cap) {
   __shared__ int32_t running[ROUTE_MAX_SHARDS];
   __shared__ int32_t warp_cnt[8][ROUTE_MAX_SHARDS];
   __shared__ int64_t window[2];
@@ -1165,7 +1178,9 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int64_t* __res
       // segment of this id: last offset <= idx
       const int64_t lo = route_segment(seg_offsets, win_lo, win_hi, idx);
       const uint64_t row = route_row(id, shards);
-      if (out_tags) {
+      if (bucket_cap > 0 && pos >= (int64_t)(owner + 1) * bucket_cap) {
+        // beyond the bucket's capacity: dropped (route_scan_kernel has raised the overflow flag)
+      } else if (out_tags) {
         out_rows[pos] = (int64_t)row;
         out_tags[pos] = (int32_t)lo;
       } else {
@@ -1173,7 +1188,7 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int64_t* __res
         // fit 31 bits cannot exist in a shard and is sent as 0x7fffffff, which no shard holds either
         out_rows[pos] = (int64_t)(((uint64_t)lo << 32) | (row < 0x7fffffffull ? row : 0x7fffffffull));
       }
-      if (out_values) out_values[pos] = values ? values[idx] : 1.f;
+      if (out_values && bucket_cap == 0) out_values[pos] = values ? values[idx] : 1.f;
     }
     __syncthreads();
     if (threadIdx.x < shards) {
@@ -1373,10 +1388,88 @@ extern "C" int xb_route_ids(const int64_t* ids, const float* values, const int32
   const int64_t blocks = std::max<int64_t>((n_ids + ROUTE_CHUNK - 1) / ROUTE_CHUNK, 1);
   int32_t* hist = reinterpret_cast<int32_t*>(scratch);
   route_count_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, n_ids, shards, hist);
-  route_scan_kernel<<<1, 256, 0, stream>>>(hist, blocks, shards, owner_counts);
+  route_scan_kernel<<<1, 256, 0, stream>>>(hist, blocks, shards, owner_counts, 0, nullptr, nullptr);
   route_scatter_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, values, seg_offsets, segments, n_ids, shards, hist, out_rows,
-                                                             out_values, out_tags);
+                                                             out_values, out_tags, 0);
   return check_launch("route kernels");
+}
+
+extern "C" int xb_route_ids_padded(const int64_t* ids, const int32_t* seg_offsets, int64_t segments, int64_t n_ids,
+                                   int32_t shards, int64_t bucket_cap, int64_t* out_records, int32_t* overflow,
+                                   void* scratch, size_t scratch_bytes, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(shards >= 1 && shards <= ROUTE_MAX_SHARDS, XB_ERR_LIMIT, "xb_route_ids_padded: %d shards (1..%d)", shards, ROUTE_MAX_SHARDS);
+  XB_REQUIRE(n_ids >= 0 && segments >= 0 && out_records && seg_offsets && overflow, XB_ERR_ARG, "xb_route_ids_padded: bad arguments");
+  XB_REQUIRE(segments < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_route_ids_padded: packed records hold 31-bit segment numbers");
+  XB_REQUIRE(n_ids == 0 || ids, XB_ERR_ARG, "xb_route_ids_padded: ids missing");
+  XB_REQUIRE(bucket_cap >= 2 && bucket_cap * shards < ((int64_t)1 << 31), XB_ERR_LIMIT,
+             "xb_route_ids_padded: bucket capacity %lld (2 .. 2^31 / shards)", (long long)bucket_cap);
+  XB_REQUIRE(n_ids < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_route_ids_padded: more than 2^31 ids per call");
+  XB_REQUIRE(scratch_bytes >= xb_route_scratch_bytes(n_ids, shards) && scratch, XB_ERR_SCRATCH, "xb_route_ids_padded: scratch too small");
+  const int64_t blocks = std::max<int64_t>((n_ids + ROUTE_CHUNK - 1) / ROUTE_CHUNK, 1);
+  int32_t* hist = reinterpret_cast<int32_t*>(scratch);
+  route_count_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, n_ids, shards, hist);
+  route_scan_kernel<<<1, 256, 0, stream>>>(hist, blocks, shards, nullptr, bucket_cap, out_records, overflow);
+  route_scatter_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, nullptr, seg_offsets, segments, n_ids, shards, hist, out_records,
+                                                             nullptr, nullptr, bucket_cap);
+  return check_launch("route kernels (fixed-capacity buckets)");
+}
+
+// fixed-capacity buckets as received: slot 0 of every bucket is its record count; slots past the count get tag -1
+__global__ void unpack_padded_kernel(const int64_t* __restrict__ packed, int sources, int64_t cap, int32_t* __restrict__ rows,
+                                     int32_t* __restrict__ tags) {
+  const int64_t n = (int64_t)sources * cap;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t s = i / cap, j = i - s * cap;
+    int64_t cnt = __ldg(packed + s * cap);
+    cnt = cnt < 0 ? 0 : (cnt > cap - 1 ? cap - 1 : cnt);          // the header comes from a peer: bounded here
+    const bool live = j >= 1 && j <= cnt;
+    const uint64_t v = live ? (uint64_t)__ldcs(packed + i) : 0ull;
+    rows[i] = (int32_t)(v & 0xffffffffull);
+    tags[i] = live ? (int32_t)(v >> 32) : -1;
+  }
+}
+
+extern "C" int xb_unpack_routed_padded(const int64_t* packed, int32_t sources, int64_t bucket_cap, int32_t* rows, int32_t* tags,
+                                       xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(packed && rows && tags && sources >= 1 && bucket_cap >= 2, XB_ERR_ARG, "xb_unpack_routed_padded: bad arguments");
+  const int64_t n = (int64_t)sources * bucket_cap;
+  const int64_t blocks = std::min<int64_t>((n + 255) / 256, (int64_t)sm_count() * 16);
+  unpack_padded_kernel<<<(unsigned)blocks, 256, 0, stream>>>(packed, sources, bucket_cap, rows, tags);
+  return check_launch("unpack_padded_kernel");
+}
+
+extern "C" size_t xb_scan_counts_scratch_bytes(int32_t n_arrays, int64_t batch) {
+  return (size_t)n_arrays * align256(scan_chunks(batch) * 4);
+}
+
+extern "C" int xb_scan_counts(const int32_t* counts, int64_t counts_stride, int32_t* offsets, int64_t offsets_stride,
+                              int32_t n_arrays, int64_t batch, void* scratch, size_t scratch_bytes, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(counts && offsets && n_arrays >= 1 && n_arrays <= XB_MAX_POOL_GROUPS && batch >= 0, XB_ERR_ARG,
+             "xb_scan_counts: bad arguments (1..%d arrays)", XB_MAX_POOL_GROUPS);
+  XB_REQUIRE(scratch && scratch_bytes >= xb_scan_counts_scratch_bytes(n_arrays, batch), XB_ERR_SCRATCH, "xb_scan_counts: scratch too small");
+  static thread_local ScanParams sp;
+  sp.n = n_arrays;
+  sp.chunk_begin[0] = 0;
+  const size_t per = align256(scan_chunks(batch) * 4);
+  for (int i = 0; i < n_arrays; ++i) {
+    sp.counts[i] = counts + (int64_t)i * counts_stride;
+    sp.offsets[i] = offsets + (int64_t)i * offsets_stride;
+    sp.batch[i] = batch;
+    sp.chunk_sums[i] = reinterpret_cast<int32_t*>((char*)scratch + i * per);
+    sp.chunk_begin[i + 1] = sp.chunk_begin[i] + (int32_t)scan_chunks(batch);
+  }
+  if (batch == 0) return 0;
+  if (sp.chunk_begin[sp.n] > sp.n) {
+    scan_sums_kernel<<<sp.chunk_begin[sp.n], SCAN_THREADS, 0, stream>>>(sp);
+    if (int rc = check_launch("scan_sums_kernel")) return rc;
+    scan_apply_kernel<<<sp.chunk_begin[sp.n], SCAN_THREADS, 0, stream>>>(sp);
+    return check_launch("scan_apply_kernel");
+  }
+  scan_counts_kernel<<<sp.n, SCAN_THREADS, 0, stream>>>(sp);
+  return check_launch("scan_counts_kernel");
 }
 
 extern "C" int xb_unpack_routed(const int64_t* packed, int64_t n, int32_t* rows, int32_t* tags, xb_stream_t stream_) {
@@ -1452,6 +1545,48 @@ extern "C" int xb_shard_pool(const xb_table_desc* const* tables, const int64_t* 
       g.n_items = 1;
       g.items[0].udf = XB_UDF_SUM;
       g.items[0].out = reinterpret_cast<char*>(out) + (size_t)lo * dim * out_esz;
+      g.items[0].stride = dim;
+      lo += table_segments[t];
+      if (++n == XB_MAX_POOL_GROUPS) {
+        if (int rc = xb_embedding_pool(groups, n, nullptr, 0, stream)) return rc;
+        n = 0;
+      }
+    }
+  }
+  return n ? xb_embedding_pool(groups, n, nullptr, 0, stream) : 0;
+}
+
+extern "C" int xb_shard_pool_padded(const xb_table_desc* const* tables, const int64_t* table_segments, int32_t n_tables,
+                                    const int32_t* rows, int64_t bucket_cap, const int32_t* offsets, int32_t sources,
+                                    int64_t n_rows_estimate, int32_t dim, void* out, int32_t out_dtype, xb_stream_t stream) {
+  XB_REQUIRE(tables && table_segments && n_tables >= 1 && sources >= 1 && offsets && rows && out && dim >= 1 && bucket_cap >= 2,
+             XB_ERR_ARG, "xb_shard_pool_padded: bad arguments");
+  XB_REQUIRE(out_dtype == XB_F32 || out_dtype == XB_F16, XB_ERR_UNSUPPORTED, "xb_shard_pool_padded: partial dtype %d", out_dtype);
+  const size_t out_esz = out_dtype == XB_F32 ? 4 : 2;
+  int64_t S = 0;
+  for (int t = 0; t < n_tables; ++t) {
+    XB_REQUIRE(table_segments[t] >= 0, XB_ERR_ARG, "xb_shard_pool_padded: negative segment count");
+    S += table_segments[t];
+  }
+  xb_pool_group groups[XB_MAX_POOL_GROUPS];
+  int n = 0;
+  for (int s = 0; s < sources; ++s) {
+    int64_t lo = 0;
+    for (int t = 0; t < n_tables; ++t) {
+      xb_pool_group& g = groups[n];
+      memset(&g, 0, sizeof(g));
+      g.table = tables[t];
+      g.ids = rows + (int64_t)s * bucket_cap + 1;            // the records of source s follow its header slot
+      g.segments = offsets + (int64_t)s * (S + 1) + lo;      // offsets of source s count from its first record
+      g.segments_are_offsets = 1;
+      g.batch = table_segments[t];
+      g.n_ids = sources * S ? n_rows_estimate * table_segments[t] / ((int64_t)sources * S) : 0;   // sizes the work split only
+      g.dim = dim;
+      g.id_dtype = XB_I32;
+      g.out_dtype = out_dtype;
+      g.n_items = 1;
+      g.items[0].udf = XB_UDF_SUM;
+      g.items[0].out = reinterpret_cast<char*>(out) + ((size_t)s * S + lo) * dim * out_esz;
       g.items[0].stride = dim;
       lo += table_segments[t];
       if (++n == XB_MAX_POOL_GROUPS) {

@@ -190,3 +190,59 @@ def sharded_pool(comm, ops, table_shard, dim, ids, values, seg_offsets, groups, 
     """One table: ids/values/seg_offsets are this rank's ids of `groups` feature groups (group-major segments),
     out [rows, >= groups*dim] receives the pooled vectors of this rank's samples."""
     return sharded_pool_tables(comm, ops, [table_shard], dim, [ids], [values], [seg_offsets], [groups], out, avg)
+
+
+class ShardContext:
+    """One rank's context of the sharded step that runs entirely behind the C ABI (xb_shard_ctx_create /
+    xb_sharded_pool): buffers allocated once, NCCL called from inside the library, no host synchronisation in a
+    step. `tables` are this rank's shards (ops.Table with identity keys), `table_segments[t]` the segments of
+    table t per step on this rank. With world > 1 every rank calls this with the same `unique_id`
+    (ShardContext.unique_id() on one rank, handed to the others by any transport)."""
+
+    def __init__(self, rank, world, tables, table_segments, dim, max_ids, partial_dtype="f16", capacity_factor=2.0,
+                 unique_id=None):
+        T = len(tables)
+        self._tables = tables
+        self._descs = (C.POINTER(capi.TableDesc) * T)(*[C.pointer(t.desc) for t in tables])
+        self._segs = (C.c_int64 * T)(*table_segments)
+        cfg = capi.ShardConfig()
+        cfg.rank, cfg.world, cfg.dim, cfg.n_tables = rank, world, dim, T
+        cfg.tables, cfg.table_segments = C.cast(self._descs, C.c_void_p), C.cast(self._segs, C.c_void_p)
+        cfg.max_ids = max_ids
+        cfg.partial_dtype = capi.XB_F16 if partial_dtype == "f16" else capi.XB_F32
+        cfg.capacity_factor = capacity_factor
+        self.h = C.c_void_p()
+        self.segments, self.dim, self.world = sum(table_segments), dim, world
+        self._id = unique_id
+        check(lib().xb_shard_ctx_create(C.byref(self.h), unique_id, C.byref(cfg)))
+
+    @staticmethod
+    def unique_id():
+        buf = C.create_string_buffer(128)
+        check(lib().xb_shard_unique_id(buf))
+        return buf.raw
+
+    def pool(self, ids, seg_offsets, groups, out):
+        """ids int64 [n], seg_offsets int32 [segments + 1] (all tables, group-major), out [rows, >= groups * dim]."""
+        check(lib().xb_sharded_pool(self.h, xops.ptr(ids), xops.ptr(seg_offsets), ids.numel(), groups, 0, xops.ptr(out),
+                                    out.stride(0), xops.dt(out), xops.stream()))
+        return out
+
+    def overflow(self):
+        """After a stream synchronisation: True when a step since the last call dropped ids (bucket capacity)."""
+        f = C.c_int32(0)
+        check(lib().xb_shard_ctx_status(self.h, C.byref(f)))
+        return bool(f.value)
+
+    @property
+    def bucket_capacity(self):
+        return int(lib().xb_shard_ctx_bucket_capacity(self.h))
+
+    @property
+    def device_bytes(self):
+        return int(lib().xb_shard_ctx_device_bytes(self.h))
+
+    def close(self):
+        if self.h:
+            lib().xb_shard_ctx_destroy(self.h)
+            self.h = C.c_void_p()
