@@ -354,3 +354,51 @@ def test_fixed_capacity_buckets_carry_the_same_records_and_flag_overflow():
         for w in range(world):
             kept = min(int(oc[w]), cap - 1)
             assert (tg[w, 0] == -1) and (tg[w, 1 + kept:] == -1).all() and (tg[w, 1:1 + kept] >= 0).all()
+
+
+def test_sharded_puller_behind_the_embedding_operator_on_one_rank():
+    """An Embedding operator whose tables are served by b200_sharded_sparse_puller (world of one rank), through the
+    Predictor API, against the same operator on the plain HBM puller and against the oracle."""
+    pkg.load()
+    from x_deeplearning_b200 import blaze_api as api
+    rng = np.random.default_rng(21)
+    dim, B = 32, 700
+    tables = {"ta": rng.normal(0, 0.1, (5000, dim)).astype(np.float16).astype(np.float32),
+              "tb": rng.normal(0, 0.1, (800, dim)).astype(np.float16).astype(np.float32)}
+    groups = [("g0", "ta"), ("g1", "ta"), ("g2", "ta"), ("g3", "tb"), ("g4", "tb")]
+    conf = "".join('feature_group_config { feature_group: "%s" table_name: "%s" dim: %d }\n' % (g, t, dim) for g, t in groups)
+    conf += "block_config {\n" + "".join('  embedding_block_config_item { feature_group: "%s" udf_type: 0 }\n' % g for g, _ in groups) + "}\n"
+    ins, feeds = [], {}
+    for g, t in groups:
+        counts = rng.integers(0, 12, B).astype(np.int32)
+        ids = rng.integers(0, len(tables[t]), int(counts.sum())).astype(np.int64)
+        feeds[g] = (ids, counts)
+        ins += [g + ".ids", g + ".values", g + ".segments"]
+    text = api.netdef_text([api.op_text("Embedding", ins, ["out"], {"embedding_config": conf})],
+                           [(n, 10 if n.endswith(".ids") else 2 if n.endswith(".segments") else 12) for n in ins], [("out", 12)])
+    results = []
+    for sharded_puller in (False, True):
+        mgr = api.PredictorManager()
+        if sharded_puller:
+            mgr.init_sharded(0, 1, None, max_ids_per_step=B * 12 * len(groups), partial_dtype=1)
+        else:
+            mgr.load_sparse(None, "b200_sparse_puller")
+        for t, w in tables.items():
+            mgr.add_table(t, w, 12)
+        mgr.load_model_text(text)
+        p = mgr.create_predictor()
+        keep = []
+        for g, (ids, counts) in feeds.items():
+            keep += [p.feed(g + ".ids", ids), p.feed(g + ".values", np.ones(len(ids), np.float16)), p.feed(g + ".segments", counts)]
+        p.forward()
+        results.append(p.output("out").astype(np.float32))
+        p.forward()                                            # the context and its buffers are reused
+        np.testing.assert_array_equal(results[-1], p.output("out").astype(np.float32))
+        p.close()
+        mgr.close()
+    np.testing.assert_array_equal(results[0], results[1])      # fp32 partial sums, one owner: the same bits
+    want = np.zeros((B, len(groups) * dim), np.float32)
+    for k, (g, t) in enumerate(groups):
+        ids, counts = feeds[g]
+        orc.embedding_pool(tables[t], ids, np.ones(len(ids), np.float32), counts, [dict(udf=0, out=want, col=k * dim)])
+    np.testing.assert_allclose(results[1], want, rtol=2e-3, atol=2e-3)

@@ -47,6 +47,9 @@ def lib():
         L.Blaze_B200_PlanBatch.argtypes = [vp, C.c_int, C.c_int, C.c_int, vp]
         L.Blaze_B200_BatchingStats.argtypes = [C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         L.Blaze_B200_ModelOpTypes.argtypes = [vp, C.c_char_p, C.c_size_t]
+        L.Blaze_B200_ShardUniqueId.argtypes = [vp]
+        L.Blaze_B200_ShardedInit.argtypes = [vp, C.c_int, C.c_int, vp, C.c_int64, C.c_int, C.c_float]
+        L.Blaze_B200_AddDeviceShard.argtypes = [vp, cp, C.c_int64, C.c_int, C.c_int, vp, C.c_int64]
         _lib = L
     return _lib
 
@@ -89,6 +92,12 @@ def batching_stats():
     return b.value, t.value
 
 
+def shard_unique_id():
+    buf = C.create_string_buffer(128)
+    _ck(lib().Blaze_B200_ShardUniqueId(buf))
+    return buf.raw
+
+
 class PredictorManager:
     def __init__(self):
         self.h = vp()
@@ -109,6 +118,17 @@ class PredictorManager:
 
     def load_model_file(self, path, optimize=True):
         _ck(lib().Blaze_PredcitorManagerLoadModel(self.h, path.encode(), int(optimize)))
+
+    def init_sharded(self, rank, world, unique_id, max_ids_per_step, partial_dtype=12, capacity_factor=2.0):
+        """This process is shard `rank` of `world`; loads b200_sharded_sparse_puller."""
+        self.load_sparse(None, "b200_sharded_sparse_puller")
+        _ck(lib().Blaze_B200_ShardedInit(self.h, rank, world, unique_id, max_ids_per_step, partial_dtype, capacity_factor))
+
+    def add_device_shard(self, name, tensor, dim, storage_dtype=12):
+        """A shard already in device memory (a 2-D CUDA tensor, kept alive by the caller)."""
+        self._keep.append(tensor)
+        _ck(lib().Blaze_B200_AddDeviceShard(self.h, name.encode(), tensor.shape[0], dim, storage_dtype, tensor.data_ptr(),
+                                            tensor.stride(0) * tensor.element_size()))
 
     def op_types(self):
         """Operator types of the loaded model, in execution order (after the fusion passes if they ran)."""

@@ -56,6 +56,18 @@ int Blaze_B200_LoadSparseModelWeight(PredictorManagerHandle handle, const char* 
 int Blaze_B200_AddTable(PredictorManagerHandle handle, const char* table_name, int64_t rows, int dim,
                         int storage_dtype, const float* weights, const int64_t* keys);
 /* Feed whose source is already in device memory (no host staging). */
+/* Row-sharded tables (tables too large for one GPU; one process per GPU of a box). Load the puller
+ * "b200_sharded_sparse_puller" (Blaze_B200_LoadSparseModelWeight(handle, NULL, type)), make the 128-byte communicator
+ * id on one rank with Blaze_B200_ShardUniqueId and hand it to the others, call Blaze_B200_ShardedInit on every rank,
+ * then register this rank's shards: row r of a table lives on rank r % world at local row r / world. An Embedding
+ * operator over such tables is pooled by one xb_sharded_pool call (see include/xdlb200.h). */
+int Blaze_B200_ShardUniqueId(void* unique_id128);
+int Blaze_B200_ShardedInit(PredictorManagerHandle handle, int rank, int world, const void* unique_id128,
+                           int64_t max_ids_per_step, int partial_dtype, float capacity_factor);
+/* A shard that already lives in device memory (rows x dim elements of storage_dtype, pitch_bytes apart). The caller
+ * keeps the memory alive while predictors exist. */
+int Blaze_B200_AddDeviceShard(PredictorManagerHandle handle, const char* table_name, int64_t rows, int dim,
+                              int storage_dtype, const void* device_weights, int64_t pitch_bytes);
 /* Operator types of the model the manager holds (after the optimization passes when LoadModel ran them), comma
  * separated, into `buffer`. Returns 0, or the capacity needed when `buffer` is NULL or too small. */
 int Blaze_B200_ModelOpTypes(PredictorManagerHandle handle, char* buffer, size_t capacity);

@@ -506,6 +506,28 @@ int Blaze_B200_AddTable(PredictorManagerHandle h, const char* table_name, int64_
                         "AddTable ", table_name, " failed");
   API_END();
 }
+int Blaze_B200_ShardedInit(PredictorManagerHandle h, int rank, int world, const void* unique_id128, int64_t max_ids_per_step,
+                           int partial_dtype, float capacity_factor) {
+  API_BEGIN();
+  PredictorManagerImpl* m = ManagerAccess::impl(static_cast<PredictorManager*>(h));
+  if (!m->puller_) BLAZE_CONDITION_THROW(m->LoadSparse(nullptr, "b200_sharded_sparse_puller"), "cannot create the sharded puller");
+  BLAZE_CONDITION_THROW(m->puller_->InitSharded(rank, world, unique_id128, max_ids_per_step, partial_dtype, capacity_factor) == store::kOK,
+                        "the loaded sparse puller does not shard tables (load b200_sharded_sparse_puller) or the arguments are invalid");
+  API_END();
+}
+int Blaze_B200_ShardUniqueId(void* unique_id128) {
+  if (xb_shard_unique_id(unique_id128) != 0) { SetError(xb_last_error()); return -1; }
+  return 0;
+}
+int Blaze_B200_AddDeviceShard(PredictorManagerHandle h, const char* table_name, int64_t rows, int dim, int storage_dtype,
+                              const void* device_weights, int64_t pitch_bytes) {
+  API_BEGIN();
+  PredictorManagerImpl* m = ManagerAccess::impl(static_cast<PredictorManager*>(h));
+  BLAZE_CONDITION_THROW(m->puller_ != nullptr, "no sparse puller loaded");
+  BLAZE_CONDITION_THROW(m->puller_->AddDeviceShard(table_name, rows, dim, storage_dtype, device_weights, pitch_bytes) == store::kOK,
+                        "AddDeviceShard ", table_name, " failed (only the sharded puller takes device shards)");
+  API_END();
+}
 int Blaze_B200_ModelOpTypes(PredictorManagerHandle h, char* buffer, size_t capacity) {
   // operator types of the loaded (and, with optimization_pass, rewritten) NetDef, comma separated
   PredictorManagerImpl* m = ManagerAccess::impl(static_cast<PredictorManager*>(h));

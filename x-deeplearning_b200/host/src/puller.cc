@@ -233,6 +233,171 @@ class B200SparsePuller : public SparsePuller {
   bool file_fp16_ = false;
 };
 
+// "b200_sharded_sparse_puller": tables too large for one GPU, row-sharded over the ranks of one box (one process
+// per GPU). The Embedding operator's groups are pooled by ONE xb_sharded_pool call: ids routed to the owners,
+// pooled there, partial sums returned and combined, the two exchanges done by NCCL inside the kernel library.
+// It takes what the large-table configuration needs: every feature group of the operator feeds one kSum item,
+// all tables have one dim, the items of a table's groups are adjacent and the whole operator writes one block
+// (group g at column g * dim). Per-id weights are NOT routed: every id counts with weight 1.0, whatever the
+// `.values` input holds (the configuration feeds ones).
+class ShardedSparsePuller : public B200SparsePuller {
+ public:
+  ~ShardedSparsePuller() override {
+    if (ctx_) xb_shard_ctx_destroy(ctx_);
+    for (void* p : {(void*)ids_, (void*)counts_, (void*)offsets_, (void*)items_dev_, scan_scratch_}) if (p) cudaFree(p);
+    if (items_host_) cudaFreeHost(items_host_);
+  }
+
+  Status InitSharded(int rank, int world, const void* unique_id, int64_t max_ids_per_step, int partial_dtype,
+                     float capacity_factor) override {
+    if (world < 1 || rank < 0 || rank >= world || max_ids_per_step <= 0) return kFail;
+    rank_ = rank; world_ = world; max_ids_ = max_ids_per_step; partial_dtype_ = partial_dtype; factor_ = capacity_factor;
+    if (unique_id) { uid_.assign((const char*)unique_id, (const char*)unique_id + 128); }
+    return kOK;
+  }
+
+  Status AddDeviceShard(const std::string& name, int64_t rows, int dim, int storage_dtype, const void* device_weights,
+                        int64_t pitch_bytes) override {
+    std::lock_guard<std::mutex> lock(mu_);
+    if (tables_.count(name) || borrowed_.count(name)) { LOG_ERROR("table ", name, " already registered"); return kFail; }
+    std::unique_ptr<xb_table_desc> d(new xb_table_desc());
+    memset(d.get(), 0, sizeof(xb_table_desc));
+    d->weights = device_weights; d->rows = rows; d->dim = dim; d->dtype = storage_dtype; d->row_pitch_bytes = pitch_bytes;
+    borrowed_[name] = std::move(d);
+    return kOK;
+  }
+
+  Status GetAsync(const std::vector<SparsePullerInput>& input, std::vector<SparsePullerOutput>& output, int device_id,
+                  cudaStream_t stream, int* launches) override {
+    if (world_ == 0) { LOG_ERROR("sharded puller used before InitSharded"); return kFail; }
+    if (input.size() != output.size() || input.empty()) return kFail;
+    const size_t G = input.size();
+    const int dim = input[0].dim;
+    const size_t B = input[0].key_num_size;
+    const int vtype = input[0].value_type;
+    const size_t esz = vtype == kFloat16 ? 2 : 4;
+    char* base = reinterpret_cast<char*>(output[0].out_item.empty() ? nullptr : output[0].out_item[0].out);
+    int64_t n_ids = 0;
+    std::vector<std::string> table_order;
+    std::vector<int64_t> table_groups;
+    for (size_t g = 0; g < G; ++g) {
+      const SparsePullerInput& in = input[g];
+      const bool shape_ok = in.in_item.size() == 1 && output[g].out_item.size() == 1 && in.in_item[0].udf_type == kSum &&
+                            in.dim == dim && in.key_num_size == B && in.key_type == kInt64 && in.num_type == kInt32 &&
+                            output[g].out_item[0].stride == output[0].out_item[0].stride &&
+                            reinterpret_cast<char*>(output[g].out_item[0].out) == base + g * dim * esz;
+      if (!shape_ok) {
+        LOG_ERROR("sharded puller: feature group ", g, " is outside what it takes (one kSum item per group, one dim, "
+                  "int64 ids, int32 counts, one output block with group g at column g * dim)");
+        return kFail;
+      }
+      if (table_order.empty() || table_order.back() != in.name) {
+        for (const auto& t : table_order)
+          if (t == in.name) { LOG_ERROR("sharded puller: the groups of table ", in.name, " are not adjacent"); return kFail; }
+        table_order.push_back(in.name);
+        table_groups.push_back(0);
+      }
+      ++table_groups.back();
+      n_ids += (int64_t)in.key_size;
+    }
+    if (n_ids > max_ids_) { LOG_ERROR("sharded puller: ", n_ids, " ids in one step, InitSharded allowed ", max_ids_); return kFail; }
+    CUDA_CHECK(cudaSetDevice(device_id));
+    if (!ctx_ || batch_ != B || tables_sig_ != table_order || groups_sig_ != table_groups) {
+      if (ctx_) { CUDA_CHECK(cudaDeviceSynchronize()); xb_shard_ctx_destroy(ctx_); ctx_ = nullptr; }
+      std::vector<const xb_table_desc*> descs;
+      std::vector<int64_t> segs;
+      for (size_t t = 0; t < table_order.size(); ++t) {
+        const xb_table_desc* d = Shard(table_order[t], dim, device_id);
+        if (!d) { LOG_ERROR("sharded puller: no shard of table ", table_order[t], " on this rank"); return kFail; }
+        descs.push_back(d);
+        segs.push_back(table_groups[t] * (int64_t)B);
+      }
+      xb_shard_config cfg;
+      memset(&cfg, 0, sizeof(cfg));
+      cfg.rank = rank_; cfg.world = world_; cfg.dim = dim; cfg.n_tables = (int)descs.size();
+      cfg.tables = descs.data(); cfg.table_segments = segs.data(); cfg.max_ids = max_ids_;
+      cfg.partial_dtype = partial_dtype_; cfg.capacity_factor = factor_;
+      if (xb_shard_ctx_create(&ctx_, uid_.empty() ? nullptr : uid_.data(), &cfg) != 0) {
+        LOG_ERROR("xb_shard_ctx_create failed: ", xb_last_error());
+        return kFail;
+      }
+      batch_ = B; tables_sig_ = table_order; groups_sig_ = table_groups;
+      // staging for the operator's inputs as one routing problem: ids and counts of all groups back to back
+      for (void** p : {(void**)&ids_, (void**)&counts_, (void**)&offsets_, (void**)&items_dev_, &scan_scratch_}) {
+        if (*p) cudaFree(*p);
+        *p = nullptr;
+      }
+      CUDA_CHECK(cudaMalloc((void**)&ids_, (size_t)max_ids_ * 8));
+      CUDA_CHECK(cudaMalloc((void**)&counts_, G * B * 4));
+      CUDA_CHECK(cudaMalloc((void**)&offsets_, (G * B + 1) * 4));
+      CUDA_CHECK(cudaMalloc((void**)&items_dev_, 2 * G * sizeof(xb_copy_item)));
+      scan_bytes_ = xb_scan_counts_scratch_bytes(1, (int64_t)(G * B));
+      CUDA_CHECK(cudaMalloc(&scan_scratch_, std::max<size_t>(scan_bytes_, 256)));
+      if (items_host_) cudaFreeHost(items_host_);
+      CUDA_CHECK(cudaHostAlloc((void**)&items_host_, 2 * G * sizeof(xb_copy_item), cudaHostAllocDefault));
+    }
+    // one descriptor-table copy gathers the ids and the counts of every group (the pinned table is reused: the
+    // previous call's copy of it must have been consumed, which by now it long has)
+    if (consumed_recorded_) CUDA_CHECK(cudaEventSynchronize(Consumed()));
+    int64_t at = 0, max_bytes = 0;
+    for (size_t g = 0; g < G; ++g) {
+      items_host_[2 * g] = {input[g].key, ids_ + at, (int64_t)input[g].key_size * 8};
+      items_host_[2 * g + 1] = {input[g].key_num, counts_ + g * B, (int64_t)B * 4};
+      max_bytes = std::max<int64_t>(max_bytes, std::max<int64_t>((int64_t)input[g].key_size * 8, (int64_t)B * 4));
+      at += (int64_t)input[g].key_size;
+    }
+    CUDA_CHECK(cudaMemcpyAsync(items_dev_, items_host_, 2 * G * sizeof(xb_copy_item), cudaMemcpyHostToDevice, stream));
+    XB_CHECK(xb_copy_segments(items_dev_, (int)(2 * G), max_bytes, stream));
+    CUDA_CHECK(cudaEventRecord(Consumed(), stream));
+    consumed_recorded_ = true;
+    XB_CHECK(xb_scan_counts(counts_, 0, offsets_, 0, 1, (int64_t)(G * B), scan_scratch_, scan_bytes_, stream));
+    if (xb_sharded_pool(ctx_, ids_, offsets_, n_ids, (int64_t)G, 0, base, (int64_t)output[0].out_item[0].stride,
+                        vtype, stream) != 0) {
+      LOG_ERROR("xb_sharded_pool failed: ", xb_last_error());
+      return kFail;
+    }
+    *launches += 12;
+    return kOK;
+  }
+
+  // after the caller synchronised its stream: did a step drop ids because a bucket overflowed?
+  bool Overflowed() {
+    int32_t f = 0;
+    return ctx_ && xb_shard_ctx_status(ctx_, &f) == 0 && f != 0;
+  }
+
+ private:
+  const xb_table_desc* Shard(const std::string& name, int dim, int device_id) {
+    {
+      std::lock_guard<std::mutex> lock(mu_);
+      auto b = borrowed_.find(name);
+      if (b != borrowed_.end()) return b->second.get();
+    }
+    return Find(name, dim, device_id);
+  }
+  cudaEvent_t Consumed() {
+    if (!consumed_) cudaEventCreateWithFlags(&consumed_, cudaEventDisableTiming);
+    return consumed_;
+  }
+
+  int rank_ = 0, world_ = 0, partial_dtype_ = XB_F16;
+  int64_t max_ids_ = 0;
+  float factor_ = 2.f;
+  std::vector<char> uid_;
+  xb_shard_ctx* ctx_ = nullptr;
+  size_t batch_ = 0;
+  std::vector<std::string> tables_sig_;
+  std::vector<int64_t> groups_sig_;
+  std::unordered_map<std::string, std::unique_ptr<xb_table_desc>> borrowed_;
+  int64_t* ids_ = nullptr;
+  int32_t *counts_ = nullptr, *offsets_ = nullptr;
+  xb_copy_item *items_dev_ = nullptr, *items_host_ = nullptr;
+  void* scan_scratch_ = nullptr;
+  size_t scan_bytes_ = 0;
+  cudaEvent_t consumed_ = nullptr;
+  bool consumed_recorded_ = false;
+};
+
 class MockSparsePuller : public B200SparsePuller {
  public:
   Status Load(const std::string&) override { return kOK; }
@@ -279,12 +444,14 @@ class MockSparsePuller : public B200SparsePuller {
 
 SparsePuller* CreateB200() { return new B200SparsePuller(); }
 SparsePuller* CreateMock() { return new MockSparsePuller(); }
+SparsePuller* CreateSharded() { return new ShardedSparsePuller(); }
 
 struct RegisterAll {
   RegisterAll() {
     SparsePullerCreationRegisterer::Get()->Register("b200_sparse_puller", CreateB200);
     SparsePullerCreationRegisterer::Get()->Register("qed_sparse_puller", CreateB200);
     SparsePullerCreationRegisterer::Get()->Register("mock_sparse_puller", CreateMock);
+    SparsePullerCreationRegisterer::Get()->Register("b200_sharded_sparse_puller", CreateSharded);
   }
 } g_register_all;
 

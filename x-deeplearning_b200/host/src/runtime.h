@@ -216,6 +216,19 @@ class SparsePuller {
                           const int64_t* keys) {
     return kFail;
   }
+  // A device-resident shard registered without a host copy (row-sharded tables are generated or loaded shard by
+  // shard): `rows` local rows of `dim` elements at `device_weights`, `pitch_bytes` apart, identity keys.
+  virtual Status AddDeviceShard(const std::string& name, int64_t rows, int dim, int storage_dtype, const void* device_weights,
+                                int64_t pitch_bytes) {
+    return kFail;
+  }
+  // Row-sharded pullers: this process is shard `rank` of `world`; `unique_id` (128 bytes, xb_shard_unique_id) is the
+  // same on every rank. Tables registered afterwards are this rank's shards (row r of the table lives on rank
+  // r % world at local row r / world).
+  virtual Status InitSharded(int rank, int world, const void* unique_id, int64_t max_ids_per_step, int partial_dtype,
+                             float capacity_factor) {
+    return kFail;
+  }
 };
 
 using FCreateSparsePuller = std::function<SparsePuller*(void)>;
