@@ -135,6 +135,7 @@ def test_unfused_graph_through_the_predictor(optimize):
         assert got.shape == want.shape
         assert np.abs(got - want).max() <= 2e-3, np.abs(got - want).max()
         launches.append(p.launches())
-    assert (launches[0] <= 12) if optimize else (launches[0] >= 25), launches
+    # (the first run also packs the weights; the second one is the steady state)
+    assert (launches[1] <= 12) if optimize else (launches[1] >= 25), launches
     p.close()
     mgr.close()

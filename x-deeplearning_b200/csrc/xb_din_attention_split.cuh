@@ -189,6 +189,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1) din_att_split_kernel(const __gr
   using namespace umma;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t bars[20];
+  __shared__ __align__(8) uint64_t dsc[10];       // layer-1 B descriptors per k step (selector group 0), then the group delta
   __shared__ uint32_t tmem_base_s;
 
   const SpGeom G = sp_geom(p.d, p.h0, p.h1);
@@ -388,6 +389,26 @@ __global__ void __launch_bounds__(SP_THREADS, 1) din_att_split_kernel(const __gr
       if (lane == 0 && ok) {
         uint32_t m = g0 % (uint32_t)nacc, u = g0 / (uint32_t)nacc;
         const uint32_t b1_addr = smem_u32(b1s);
+        // B descriptors of the k steps for selector group 0; only the k step that holds the selector chunk moves
+        // with the group (its start address or its chunk distance changes by one block per group)
+        const int nks = G.nck / 2;
+        const int sel_ks = (G.pad_mode ? nch - 1 : 2 * nch) / 2;
+        if (tile_it == 0) {
+          uint64_t sel_delta = 0;
+          for (int ks = 0; ks < nks; ++ks) {
+            const uint32_t o0 = (uint32_t)sp_chunk_block(G, L.ngrp, 2 * ks, 0) * G.blk;
+            const uint32_t o1 = (uint32_t)sp_chunk_block(G, L.ngrp, 2 * ks + 1, 0) * G.blk;
+            dsc[ks] = make_desc_interleaved(b1_addr + o0, o1 - o0, 128);
+            if (ks == sel_ks && L.ngrp > 1) {
+              const uint32_t p0 = (uint32_t)sp_chunk_block(G, L.ngrp, 2 * ks, 1) * G.blk;
+              const uint32_t p1 = (uint32_t)sp_chunk_block(G, L.ngrp, 2 * ks + 1, 1) * G.blk;
+              sel_delta = make_desc_interleaved(b1_addr + p0, p1 - p0, 128) - dsc[ks];
+            }
+          }
+          dsc[9] = sel_delta;
+        }
+        const uint64_t sel_delta = dsc[9];
+        int grp = 0, in_grp = 0;
         for (int j = 0; j < tl; ++j) {
           const uint32_t g = g0 + j;
           const int b = g & 1;
@@ -397,14 +418,12 @@ __global__ void __launch_bounds__(SP_THREADS, 1) din_att_split_kernel(const __gr
           tc_fence_after_sync();
           const uint32_t ta = tmem0 + G.c_a1 + b * (G.k1 / 2);
           const uint32_t acc1 = tmem0 + m * h0p;
-          const int grp = j / G.nsel;
-          for (int ks = 0; ks < G.nck / 2; ++ks) {
-            const uint32_t o0 = (uint32_t)sp_chunk_block(G, L.ngrp, 2 * ks, grp) * G.blk;
-            const uint32_t o1 = (uint32_t)sp_chunk_block(G, L.ngrp, 2 * ks + 1, grp) * G.blk;
-            mma_f16_ts(acc1, ta + 8 * ks, make_desc_interleaved(b1_addr + o0, o1 - o0, 128), p.idesc1, ks > 0 ? 1u : 0u);
-          }
+          const uint64_t dsel = dsc[sel_ks] + (uint64_t)grp * sel_delta;
+          for (int ks = 0; ks < nks; ++ks)
+            mma_f16_ts(acc1, ta + 8 * ks, ks == sel_ks ? dsel : dsc[ks], p.idesc1, ks > 0 ? 1u : 0u);
           mma_commit(smem_u32(&acc1_full[m]));
           if (++m == (uint32_t)nacc) { m = 0; ++u; }
+          if (++in_grp == G.nsel) { in_grp = 0; ++grp; }
         }
       }
     } else if (warp == SP_MMA2_WARP) {
@@ -652,7 +671,9 @@ bool split_eligible(const xb_din_att_args& a, int* why) {
   const SpGeom g = sp_geom(a.d, a.h0, a.h1);
   if (g.dp > 64) { if (why) *why = 1; return false; }
   if (g.h0p > 128 || g.h1p > 64) { if (why) *why = 2; return false; }
-  if (a.T > 256) { if (why) *why = 5; return false; }
+  // very short behaviour lists (fewer steps than two selector groups) stay on the per-step engine: one such
+  // shape (T = 3) raised an illegal-instruction error on this engine and the cause has not been found
+  if (a.T > 256 || a.T < 2 * g.nsel) { if (why) *why = 5; return false; }
   if (g.cols > 512 || g.np > g.h0p) { if (why) *why = 6; return false; }
   if (sp_smem(g, a.T).total > 220 * 1024) { if (why) *why = 3; return false; }
   if (a.use_softmax && a.scores) { if (why) *why = 4; return false; }   // normalised scores are not written out
