@@ -457,6 +457,14 @@ int xb_gru(const void* x, void* y, int64_t batch, int32_t T, int32_t H, const vo
            const void* i2h_bias, const void* h2h_bias, int32_t dtype, xb_stream_t stream);
 int xb_augru(const void* x, const void* att, void* y, int64_t batch, int32_t T, int32_t H, const void* Wg,
              const void* bg, const void* Wc, const void* bc, int32_t dtype, xb_stream_t stream);
+/* The AUGRU as the DIEN-style model uses it: every candidate of a request walks the request's own sequence
+ * x [requests, T, H] with its own scores att [requests * n_cand, T], and only the final state
+ * y_final [requests * n_cand, H] is kept. All tensors fp16. `engine`: XB_GEMM_AUTO / _SIMT / _TCGEN05; the tcgen05
+ * engine (one CTA per 128 candidates, both per-candidate products as MMAs with the state in tensor memory, the
+ * request-side terms x_t Wg_x + bg and x_t Wc_x + bc computed once per request) takes an even H <= 64 whose padding
+ * to a multiple of 8 leaves at least 4 slots (H = 36 does). Same cell as xb_augru. */
+int xb_augru_shared(const void* x, const void* att, void* y_final, int32_t requests, int32_t n_cand, int32_t T, int32_t H,
+                    const void* Wg, const void* bg, const void* Wc, const void* bc, int32_t engine, xb_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
 /* Stand-alone operators for graphs that were not fused. x/y share `dtype`;

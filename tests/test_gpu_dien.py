@@ -11,14 +11,15 @@ import pkg
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("augru_engine", [1, 0])        # CUDA-core AUGRU, then the tcgen05 one (XB_GEMM_AUTO picks it)
 @pytest.mark.parametrize("R,n_cand,emb_sigma", [(2, 64, 0.5), (1, 1000, 0.3)])
-def test_dien_probabilities_match_oracle(R, n_cand, emb_sigma):
+def test_dien_probabilities_match_oracle(R, n_cand, emb_sigma, augru_engine):
     pkg.load()
     from x_deeplearning_b200 import dien, ops, workloads
     model = workloads.dien_model(0, item_rows=20000, cate_rows=500, user_rows=3000, emb_sigma=emb_sigma)
     req = workloads.din_requests(model, 5, requests=R, n_cand=n_cand)
     want, wparts = dien_oracle.forward(model, req)
-    net = dien.DienModel(model)
+    net = dien.DienModel(model, augru_engine=augru_engine)
     p = net.upload(net.stage(req))
     prob, parts = net.forward_dien(p)
     torch.cuda.synchronize()

@@ -125,6 +125,7 @@ SYMBOLS = {
     "xb_din_tower_input_split": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, vp]),
     "xb_gru": (i32, [vp, vp, i64, i32, i32, vp, vp, vp, vp, i32, vp]),
     "xb_augru": (i32, [vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, i32, vp]),
+    "xb_augru_shared": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp]),
     "xb_dice": (i32, [vp, vp, i64, i32, vp, vp, vp, i32, i32, vp]),
     "xb_prelu": (i32, [vp, vp, i64, vp, i64, i32, i32, vp]),
     "xb_sigmoid": (i32, [vp, vp, i64, i32, vp]),

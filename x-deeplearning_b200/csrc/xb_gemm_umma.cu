@@ -615,6 +615,9 @@ int tower_status(int* out);
 int tower_clear_status();
 int att_set_status_mirror(int* p);
 int tower_set_status_mirror(int* p);
+int rnn_status(int* out);
+int rnn_clear_status();
+int rnn_set_status_mirror(int* p);
 
 // Host-mapped copy of the status word, one per device: {host address, device address}.
 struct StatusMirror { volatile int* host = nullptr; int* dev = nullptr; };
@@ -648,15 +651,15 @@ extern "C" int xb_selftest_wait_timeout(int64_t limit_cycles, xb_stream_t stream
 
 extern "C" int xb_device_status(int* status) {
   XB_REQUIRE(status, XB_ERR_ARG, "xb_device_status: null pointer");
-  int a = 0, b = 0, c = 0;
-  XB_REQUIRE(gemm_umma_status(&a) == 0 && att_status(&b) == 0 && tower_status(&c) == 0, XB_ERR_CUDA,
+  int a = 0, b = 0, c = 0, d = 0;
+  XB_REQUIRE(gemm_umma_status(&a) == 0 && att_status(&b) == 0 && tower_status(&c) == 0 && rnn_status(&d) == 0, XB_ERR_CUDA,
              "xb_device_status: read failed");
-  *status = a ? a : (b ? b : c);
+  *status = a ? a : (b ? b : (c ? c : d));
   return 0;
 }
 
 extern "C" int xb_device_status_clear(void) {
-  XB_REQUIRE(gemm_umma_clear_status() == 0 && att_clear_status() == 0 && tower_clear_status() == 0, XB_ERR_CUDA,
+  XB_REQUIRE(gemm_umma_clear_status() == 0 && att_clear_status() == 0 && tower_clear_status() == 0 && rnn_clear_status() == 0, XB_ERR_CUDA,
              "xb_device_status_clear failed");
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
@@ -682,8 +685,10 @@ extern "C" int xb_device_status_mirror(const volatile int** host_word) {
       cudaFreeHost(h);
       return fail(XB_ERR_CUDA, "xb_device_status_mirror: cudaHostGetDevicePointer failed");
     }
-    if (umma::set_status_mirror(d) != 0 || att_set_status_mirror(d) != 0 || tower_set_status_mirror(d) != 0) {
+    if (umma::set_status_mirror(d) != 0 || att_set_status_mirror(d) != 0 || tower_set_status_mirror(d) != 0 ||
+        rnn_set_status_mirror(d) != 0) {
       umma::set_status_mirror(nullptr); att_set_status_mirror(nullptr); tower_set_status_mirror(nullptr);
+      rnn_set_status_mirror(nullptr);
       cudaFreeHost(h);
       return fail(XB_ERR_CUDA, "xb_device_status_mirror: could not publish the mirror address");
     }

@@ -238,6 +238,22 @@ __device__ __forceinline__ void unpack_chunk(const uint4& raw, int tdtype, float
   }
 }
 
+// Per-load cache behaviour. Table rows are the data worth keeping: they are read with an L2 evict_last
+// policy, so the hot rows of a Zipf-distributed id stream stay resident while the streams that are touched
+// once (ids, per-id weights, outputs) pass through with streaming loads and stores (evict first).
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint4 ld_row16(const void* ptr, uint64_t policy) {
+  uint4 v;
+  asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(ptr), "l"(policy));
+  return v;
+}
+
 __device__ __forceinline__ uint4 load_row_chunk(const PoolGroupDev& g, int64_t row, int chunk) {
   const uint4* p = reinterpret_cast<const uint4*>(g.weights + row * g.pitch) + chunk;
   return __ldg(p);
@@ -402,7 +418,7 @@ __device__ __forceinline__ void store_vec(void* out, int64_t o, bool out16, cons
     if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
       for (int e = 0; e < N; e += 4) {
-        if (e + 4 <= nvalid) *reinterpret_cast<float4*>(dst + e) = make_float4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+        if (e + 4 <= nvalid) __stcs(reinterpret_cast<float4*>(dst + e), make_float4(r[e], r[e + 1], r[e + 2], r[e + 3]));
         else {
 #pragma unroll
           for (int u = 0; u < 4; ++u)
@@ -422,7 +438,7 @@ __device__ __forceinline__ void store_vec(void* out, int64_t o, bool out16, cons
       __half2* h = reinterpret_cast<__half2*>(&v);
 #pragma unroll
       for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(r[2 * e], r[2 * e + 1]);
-      *reinterpret_cast<uint4*>(dst) = v;
+      __stcs(reinterpret_cast<uint4*>(dst), v);
     } else if ((a & 3) == 0) {
 #pragma unroll
       for (int e = 0; e < N; e += 2) {
@@ -470,6 +486,7 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
   const bool reverse = it.trunc_dir != XB_TRUNC_ORDER;
   const char* wrow = g.weights + chunk * 16;
   const int pitch = (int)g.pitch;                    // a row is at most 256 bytes here: 32 x 32 -> 64-bit multiply
+  const uint64_t keep = l2_policy_keep();
   const int64_t batch = g.batch;
   // this warp walks `segs` consecutive rounds of `spw` segments; the offsets of round i+2 and the ids of
   // round i+1 are fetched while the rows of round i are in flight
@@ -489,10 +506,10 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
     row = -1; v = 1.f;
     if (idx < nm) {
       const int64_t at = (int64_t)st + idx;
-      const int64_t key = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + at)
-                               : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + at);
+      const int64_t key = id64 ? (int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at)
+                               : (int64_t)__ldcs(reinterpret_cast<const int32_t*>(g.ids) + at);
       if (has_table) row = (int)lookup_row(g, key);
-      if (vmode == 1) v = __ldg(reinterpret_cast<const float*>(g.values) + at);
+      if (vmode == 1) v = __ldcs(reinterpret_cast<const float*>(g.values) + at);
       else if (vmode == 2) v = __half2float(reinterpret_cast<const __half*>(g.values)[at]);
     }
   };
@@ -531,7 +548,7 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
 #pragma unroll
         for (int u = 0; u < RB; ++u) {
           raw[u] = make_uint4(0, 0, 0, 0);
-          if (rr[u] >= 0 && cvalid) raw[u] = __ldg(reinterpret_cast<const uint4*>(wrow + (int64_t)rr[u] * pitch));
+          if (rr[u] >= 0 && cvalid) raw[u] = ld_row16(wrow + (int64_t)rr[u] * pitch, keep);
         }
 #pragma unroll
         for (int u = 0; u < RB; ++u) {
@@ -616,6 +633,7 @@ __global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constan
   const bool avg = it.udf == XB_UDF_AVG;
   const char* wrow = g.weights + tlane * 16;
   const int pitch = (int)g.pitch;
+  const uint64_t keep = l2_policy_keep();
   const int64_t s0 = (warp_id - g.warp_begin) * 32;
   const int nseg = (int)min((int64_t)32, g.batch - s0);
 
@@ -630,10 +648,10 @@ __global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constan
     row = -1; v = 1.f;
     if (idx < nm) {
       const int64_t at = (int64_t)st + idx;
-      const int64_t key = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + at)
-                               : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + at);
+      const int64_t key = id64 ? (int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at)
+                               : (int64_t)__ldcs(reinterpret_cast<const int32_t*>(g.ids) + at);
       if (has_table) row = (int)lookup_row(g, key);
-      if (vmode == 1) v = __ldg(reinterpret_cast<const float*>(g.values) + at);
+      if (vmode == 1) v = __ldcs(reinterpret_cast<const float*>(g.values) + at);
       else if (vmode == 2) v = __half2float(reinterpret_cast<const __half*>(g.values)[at]);
     }
   };
@@ -682,7 +700,7 @@ __global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constan
       for (int u = 0; u < 4; ++u) {
         raw[u] = make_uint4(0, 0, 0, 0);
         if (r0 + u < LPR && rr[r0 + u] >= 0 && cvalid)
-          raw[u] = __ldg(reinterpret_cast<const uint4*>(wrow + (int64_t)rr[r0 + u] * pitch));
+          raw[u] = ld_row16(wrow + (int64_t)rr[r0 + u] * pitch, keep);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -883,6 +901,12 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
   sp.n = 0;
   sp.chunk_begin[0] = 0;
   size_t soff = 0;
+  // how much parallelism the whole call offers: the groups of one call share its launches, so the choice between
+  // wider teams (more warps, for small calls) and one sub-team per segment (fewest instructions per id, for
+  // large ones) looks at all single-output groups together
+  int64_t call_segments = 0;
+  for (int i = 0; i < n_groups; ++i)
+    if (groups[i].n_items == 1 && groups[i].batch > 0) call_segments += groups[i].batch;
   for (int i = 0; i < n_groups; ++i) {
     const xb_pool_group& h = groups[i];
     XB_REQUIRE(h.batch >= 0 && h.n_ids >= 0, XB_ERR_ARG, "xb_embedding_pool: group %d negative size", i);
@@ -929,8 +953,8 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     if (fast) {
       // one sub-team per segment gives the fewest instructions per id (no cross-lane combine, whole rows
       // per lane group); teams only grow while the launch would otherwise leave SMs without warps
-      const int64_t want_warps = (int64_t)sm_count() * 16;
-      while (ns < 32 / d.lpr && ns < avg && h.batch * (int64_t)(d.lpr * ns) / 32 < want_warps) ns <<= 1;
+      const int64_t want_warps = (int64_t)sm_count() * 32;
+      while (ns < 32 / d.lpr && ns < avg && call_segments * (int64_t)(d.lpr * ns) / 32 < want_warps) ns <<= 1;
     } else {
       while (ns < 32 / d.lpr && ns < avg) ns <<= 1;
     }
@@ -966,7 +990,7 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     const int bucket = (d.tdtype == XB_F32 ? 0 : 4) + lg;
     // sum / average groups with plenty of segments go to the segment-queue kernel: 32 segments per warp
     const bool queue = fast && d.tl == d.lpr && h.items[0].udf != XB_UDF_ASSIGN && avg >= 3.0 &&
-                       (h.batch + 31) / 32 >= (int64_t)sm_count() * 8;
+                       (call_segments + 31) / 32 >= (int64_t)sm_count() * 8;
     PoolParams& dst = queue ? qp[bucket] : fast ? fp[bucket] : p;
     d.warp_begin = dst.total_warps;
     const int spw = 32 / d.tl;

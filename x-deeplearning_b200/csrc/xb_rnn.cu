@@ -7,10 +7,16 @@
 // reference CUDA GRU spins on global atomics between blocks,
 // blaze/blaze/operator/op/gru_op.cu:73-85; nothing here waits on another CTA).
 // Latency-bound by design: throughput comes from batch-many independent CTAs.
+#include <cstring>
+
 #include "xb_common.cuh"
+#include "xb_umma.cuh"
 
 namespace xb {
 namespace {
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
 
 __device__ __forceinline__ float sigm(float v) { return 1.f / (1.f + expf(-v)); }
 
@@ -65,8 +71,10 @@ __global__ void gru_kernel(const void* x, void* y, int T, int H, const void* i2h
 // AUGRU after VecAttGRUCell.call (xdl-algorithm-solution/DIEN/script/utils.py:139-207):
 // [r|u] = sigmoid([x,h] Wg + bg); c = tanh([x, r*h] Wc + bc); u' = (1 - a_t) u; h' = u' h + (1 - u') c.
 // Wg [2H, 2H] (rows x then h; columns r then u), Wc [2H, H]; att [B, T].
+// `share` > 0: the input sequence is shared by groups of `share` consecutive batch entries (x is [B / share, T, H],
+// the candidates of one request), and only the final state is written (y is [B, H]).
 __global__ void augru_kernel(const void* x, const void* att, void* y, int T, int H, const void* Wg_, const void* bg_,
-                             const void* Wc_, const void* bc_, int dt) {
+                             const void* Wc_, const void* bc_, int dt, int share) {
   extern __shared__ float sm[];
   float* Wg = sm;                     // [2H][2H]
   float* Wc = Wg + 4 * H * H;         // [2H][H]
@@ -83,7 +91,8 @@ __global__ void augru_kernel(const void* x, const void* att, void* y, int T, int
   __syncthreads();
   for (int t = 0; t < T; ++t) {
     const int64_t base = (b * T + t) * H;
-    if (j < H) xs[j] = load_as_f32(x, base + j, dt);
+    const int64_t xbase = share > 0 ? ((b / share) * T + t) * H : base;
+    if (j < H) xs[j] = load_as_f32(x, xbase + j, dt);
     __syncthreads();
     if (j < G) {
       float s = bgj;
@@ -102,7 +111,8 @@ __global__ void augru_kernel(const void* x, const void* att, void* y, int T, int
       const float a = load_as_f32(att, b * T + t, dt);
       const float u = (1.f - a) * g[H + j];
       out = u * h[j] + (1.f - u) * tanhf(s);
-      store_from_f32(y, base + j, dt, out);
+      if (share <= 0) store_from_f32(y, base + j, dt, out);
+      else if (t == T - 1) store_from_f32(y, b * H + j, dt, out);
     }
     __syncthreads();
     if (j < H) h[j] = out;
@@ -110,6 +120,14 @@ __global__ void augru_kernel(const void* x, const void* att, void* y, int T, int
 }
 
 }  // namespace
+}  // namespace xb
+
+#include "xb_augru_tc.cuh"
+
+namespace xb {
+int rnn_status(int* out) { return umma::read_status_word(out); }
+int rnn_clear_status() { return umma::clear_status_word(); }
+int rnn_set_status_mirror(int* p) { return umma::set_status_mirror(p); }
 }  // namespace xb
 
 using namespace xb;
@@ -142,6 +160,35 @@ extern "C" int xb_augru(const void* x, const void* att, void* y, int64_t batch, 
   static PerDeviceOnce attr;
   XB_SET_MAX_SMEM_ONCE(attr, 110 * 1024, (const void*)augru_kernel);
   const int threads = (2 * H + 31) / 32 * 32;
-  augru_kernel<<<(unsigned)batch, threads, smem, (cudaStream_t)s>>>(x, att, y, T, H, Wg, bg, Wc, bc, dtype);
+  augru_kernel<<<(unsigned)batch, threads, smem, (cudaStream_t)s>>>(x, att, y, T, H, Wg, bg, Wc, bc, dtype, 0);
+  return check_launch("augru_kernel");
+}
+
+extern "C" int xb_augru_shared(const void* x, const void* att, void* y_final, int32_t requests, int32_t n_cand, int32_t T,
+                               int32_t H, const void* Wg, const void* bg, const void* Wc, const void* bc, int32_t engine,
+                               xb_stream_t s) {
+  XB_REQUIRE(x && att && y_final && Wg && bg && Wc && bc, XB_ERR_ARG, "xb_augru_shared: null tensor");
+  XB_REQUIRE(requests >= 0 && n_cand >= 0 && T >= 1 && H >= 1, XB_ERR_ARG, "xb_augru_shared: bad sizes");
+  XB_REQUIRE(H <= 64, XB_ERR_LIMIT, "xb_augru_shared: hidden size %d, at most 64", H);
+  XB_REQUIRE(engine == XB_GEMM_AUTO || engine == XB_GEMM_SIMT || engine == XB_GEMM_TCGEN05, XB_ERR_ARG, "xb_augru_shared: engine %d", engine);
+  if (requests == 0 || n_cand == 0) return 0;
+  const bool tc = engine != XB_GEMM_SIMT && augru_tc_eligible(H, T);
+  XB_REQUIRE(tc || engine != XB_GEMM_TCGEN05, XB_ERR_UNSUPPORTED,
+             "xb_augru_shared: the tcgen05 engine takes an even H <= 64 whose padding to a multiple of 8 leaves 4 slots");
+  if (tc) {
+    AuParams p;
+    memset(&p, 0, sizeof(p));
+    p.x = (const __half*)x; p.att = (const __half*)att; p.y = (__half*)y_final;
+    p.Wg = (const __half*)Wg; p.bg = (const __half*)bg; p.Wc = (const __half*)Wc; p.bc = (const __half*)bc;
+    p.requests = requests; p.n_cand = n_cand; p.T = T; p.H = H;
+    return launch_augru_tc(p, (cudaStream_t)s);
+  }
+  const int64_t batch = (int64_t)requests * n_cand;
+  XB_REQUIRE(batch < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_augru_shared: batch too large");
+  const size_t smem = sizeof(float) * ((size_t)6 * H * H + 5 * H);
+  static PerDeviceOnce attr;
+  XB_SET_MAX_SMEM_ONCE(attr, 110 * 1024, (const void*)augru_kernel);
+  const int threads = (2 * H + 31) / 32 * 32;
+  augru_kernel<<<(unsigned)batch, threads, smem, (cudaStream_t)s>>>(x, att, y_final, T, H, Wg, bg, Wc, bc, XB_F16, n_cand);
   return check_launch("augru_kernel");
 }

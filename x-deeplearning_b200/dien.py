@@ -20,8 +20,9 @@ from .din import DinModel
 
 
 class DienModel(DinModel):
-    def __init__(self, model, device="cuda", engine=0):
+    def __init__(self, model, device="cuda", engine=0, augru_engine=0):
         super().__init__(model, device, engine)
+        self.augru_engine = augru_engine
         t = torch.from_numpy
         h = lambda x: t(np.ascontiguousarray(x)).to(device=device, dtype=torch.float16)
         f32 = lambda x: t(np.ascontiguousarray(x)).to(device=device, dtype=torch.float32)
@@ -34,7 +35,9 @@ class DienModel(DinModel):
         tw = model["dien_tower"]
         D = self.D
         self.dtin = D["user_groups"] * D["emb"] + 4 * D["d"]
-        self.dldx = (self.dtin + 7) // 8 * 8
+        # the tower input is assembled by xb_din_tower_input, which writes a fifth candidate-side segment
+        # (q - his_sum) after the four this model uses: the first layer's packed weight is zero there
+        self.dldx = (D["user_groups"] * D["emb"] + 5 * D["d"] + 7) // 8 * 8
         self.dW1 = ops.pack_weight_kmajor(t(tw["W1"]).to(device), torch.float16, ldk=self.dldx)
         self.dW2 = ops.pack_weight_kmajor(t(tw["W2"]).to(device), torch.float16)
         self.dW3 = ops.pack_weight_kmajor(t(tw["W3"]).to(device), torch.float16)
@@ -62,32 +65,16 @@ class DienModel(DinModel):
         check(L.xb_softmax(ops.ptr(raw), ops.ptr(sm), N, T, 1, F32, s))
         score16 = e16(N, T)
         check(L.xb_copy2d(ops.ptr(sm), T, F32, ops.ptr(score16), T, F16, N, T, s))
-        # interest evolution: every candidate runs the AUGRU over its request's GRU states
-        hx, X = e16(N, T * H), torch.zeros((N, self.dldx), dtype=torch.float16, device=dev)
-        hs = e16(R, H)
-        check(L.xb_reduce_sum(ops.ptr(k), ops.ptr(hs), R, T, H, F16, s))
-        esz = 2
-        for r in range(R):
-            rows = slice(r * n_cand, (r + 1) * n_cand)
-            at = lambda tensor, off=0: C.c_void_p(tensor.data_ptr() + off * esz)
-            # a source row stride of 0 repeats one row for every candidate of the request
-            check(L.xb_copy2d(at(hseq[r]), 0, F16, at(hx[rows]), T * H, F16, n_cand, T * H, s))
-            check(L.xb_copy2d(at(p["user_emb"][r]), 0, F16, at(X[rows]), self.dldx, F16, n_cand, du, s))
-            check(L.xb_copy2d(at(hs[r]), 0, F16, at(X[rows], du + H), self.dldx, F16, n_cand, H, s))
-        yseq = e16(N, T * H)
+        # interest evolution: every candidate runs the AUGRU over its request's GRU states, which are read once
+        # per 128-candidate tile; only the final state is kept
+        final = e16(N, H)
         a = self.augru
-        check(L.xb_augru(ops.ptr(hx), ops.ptr(score16), ops.ptr(yseq), N, T, H, ops.ptr(a["Wg"]), ops.ptr(a["bg"]),
-                         ops.ptr(a["Wc"]), ops.ptr(a["bc"]), F16, s))
-        # tower input [user | q | his_sum | q*his_sum | final state]
-        xq = C.c_void_p(X.data_ptr() + du * esz)
-        check(L.xb_copy2d(ops.ptr(q), H, F16, xq, self.dldx, F16, N, H, s))
-        prod = e16(N, H)
-        i64x4 = lambda *v: (C.c_int64 * 4)(*v)
-        check(L.xb_elementwise(capi.XB_EW_MUL, ops.ptr(q), i64x4(0, 0, H, 1), C.c_void_p(X.data_ptr() + (du + H) * esz),
-                               i64x4(0, 0, self.dldx, 1), None, None, ops.ptr(prod), i64x4(1, 1, N, H), F16, s))
-        check(L.xb_copy2d(ops.ptr(prod), H, F16, C.c_void_p(X.data_ptr() + (du + 2 * H) * esz), self.dldx, F16, N, H, s))
-        check(L.xb_copy2d(C.c_void_p(yseq.data_ptr() + (T - 1) * H * esz), T * H, F16,
-                          C.c_void_p(X.data_ptr() + (du + 3 * H) * esz), self.dldx, F16, N, H, s))
+        check(L.xb_augru_shared(ops.ptr(hseq), ops.ptr(score16), ops.ptr(final), R, n_cand, T, H, ops.ptr(a["Wg"]),
+                                ops.ptr(a["bg"]), ops.ptr(a["Wc"]), ops.ptr(a["bc"]), self.augru_engine, s))
+        # tower input [user | q | his_sum | q*his_sum | final state | (q - his_sum: zero weights)]
+        X = e16(N, self.dldx)
+        check(L.xb_din_tower_input(ops.ptr(p["user_emb"]), du, ops.ptr(q), H, ops.ptr(k), H, ops.ptr(final), H, ops.ptr(X),
+                                   self.dldx, R, n_cand, T, H, du, s))
         E = capi
         t1, t2, t3 = D["tower"]
         y1, y2 = e16(N, t1), e16(N, t2)
@@ -99,6 +86,6 @@ class DienModel(DinModel):
         ops.gemm(y2, self.dW3, Y=logit, bias=self.db[2], trans_b=True, engine=self.engine, K=t2, M=N, N=t3)
         prob = torch.empty_like(logit)
         check(L.xb_softmax(ops.ptr(logit), ops.ptr(prob), N, t3, 1, F32, s))
-        keep = (hseq, raw, sm, score16, hx, X, hs, yseq, prod, y1, y2, logit)          # alive until the stream drains
+        keep = (hseq, raw, sm, score16, X, final, y1, y2, logit)                       # alive until the stream drains
         p["dien_keep"] = keep
-        return prob, dict(hseq=hseq, scores=sm, final=yseq.view(N, T, H)[:, T - 1, :])
+        return prob, dict(hseq=hseq, scores=sm, final=final)
