@@ -693,7 +693,7 @@ def run_micro(args):
         torch.cuda.synchronize()
         t0.record()
         for _ in range(reps):
-            net.att(p["q"], p["k"].view(-1, 36), p["R"], N_CAND, T_STEPS, out=p["att"])
+            net.att(p["q"], p["k"].view(-1, 36), p["R"], N_CAND, T_STEPS, out=p["att"], engine=args.att_engine)
     elif args.micro == "tower":
         model = workloads.din_model(seed=0, item_rows=200_000, cate_rows=10_000, user_rows=10_000, emb_sigma=0.5)
         net = din.DinModel(model)
@@ -1069,6 +1069,8 @@ def main():
     ap.add_argument("--sharded-impl", default="abi", choices=["abi", "python"],
                     help="row-sharded leg: the one-call C-ABI step (NCCL inside the library) or the Python orchestration")
     ap.add_argument("--no-sharded", action="store_true", help="skip the row-sharded leg of a multi-GPU run")
+    ap.add_argument("--att-engine", type=int, default=0, help="--micro att: 0 library's choice, 2 per-step tcgen05, "
+                    "3 paired, 4 split")
     ap.add_argument("--case", default=None, help="--micro pool_hbm: run one case only (shard25m_dim32 | item5m_dim18)")
     ap.add_argument("--micro", choices=["att", "pool", "pool_hbm", "gemm", "gemm_mlp", "tower", "sharded", "batching"], help="run --steps launches of one kernel on a small case "
                     "(for profiler captures) instead of the benchmark")

@@ -76,6 +76,13 @@ def test_other_dims(engine):
     _case(engine, R=2, n_cand=140, T=11, d=18, h0=32, h1=16, act=1, softmax=False, seed=5)    # d not a multiple of 4
 
 
+def test_per_step_engine_with_two_layer2_operand_buffers():
+    """A first hidden layer of 96 leaves tensor memory for two (not three) layer-2 operand buffers: the
+    layer-1 warps then wait for the layer-2 MMA two steps back before they overwrite its operand."""
+    _case("tc", R=2, n_cand=200, T=37, d=36, h0=96, h1=32, act=2, softmax=False, seq_lens=[37, 12], seed=6)
+    _case("tc", R=1, n_cand=128, T=2, d=32, h0=96, h1=48, act=1, softmax=True, seed=7)
+
+
 def test_split_engine_walks_several_requests_and_tiles_per_cta():
     """More tiles than SMs: every CTA of the persistent engine walks a run of tiles that crosses request
     boundaries (ragged sequence lengths, a partial last tile per request, an empty sequence in the middle)."""

@@ -189,9 +189,9 @@ extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
     p.packed = (const char*)a->w.packed + (first + 15) / 16 * 16;
     return launch_att_pair(p, *a, stream);
   }
-  // The split engine (half the MMAs, persistent CTAs) serves every shape it takes when the weights were packed;
-  // XB_GEMM_TCGEN05 asks for the per-step engine, which rounds where the un-fused graph does.
-  if ((a->engine == XB_ATT_ENGINE_SPLIT || a->engine == XB_GEMM_AUTO) && a->w.packed && split_eligible(*a, &why)) {
+  // The split engine (the request-side term of layer 1 looked up through a selector column, persistent CTAs)
+  // runs on request only: it issues fewer MMAs but measures slower than the per-step engine.
+  if (a->engine == XB_ATT_ENGINE_SPLIT && a->w.packed && split_eligible(*a, &why)) {
     p.packed = (const char*)a->w.packed + split_image_offset(a->d, a->h0, a->h1);
     return launch_att_split(p, *a, stream);
   }

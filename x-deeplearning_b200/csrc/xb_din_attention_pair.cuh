@@ -23,6 +23,7 @@ namespace xb {
 namespace {
 
 constexpr int PAIR_THREADS = 640;        // 4 worker warpgroups, 2 MMA-issuing warps, 2 B-building warps
+constexpr int MMA1_WARP = 16, MMA2_WARP = 17;
 constexpr int BUILD_WARP0 = 18;
 
 struct PairGeom {

@@ -4,11 +4,15 @@
 // Four worker warpgroups (one candidate row per thread each) split the work by
 // phase and step parity: warpgroup b (b = 0, 1) runs the layer-1 activations of
 // the steps of parity b, warpgroup 2+b builds A1 two steps ahead and runs the
-// layer-2 activations for parity b; two more warps issue the MMAs (one per layer).
-// Operands and accumulators are double-buffered by step parity, so in steady
-// state nobody waits: the tensor pipe, the SFU and the FP16 pipe overlap.
-//   worker: A1 = [q|k_t|q-k_t|q*k_t] (fp16, 128 x k1) into tensor memory (tcgen05.st)
-//   MMA   : acc1[128 x h0p] = A1 * W0^T                  (A from tensor memory, W0 from shared memory)
+// layer-2 activations for parity b; one more warp issues every MMA, in the order
+// the workers need them (the tensor pipe runs MMAs in issue order).
+// Operands and accumulators are double-buffered by step parity (A2 three deep
+// when tensor memory has room), so in steady state the tensor pipe, the SFU and
+// the FP16 pipe overlap.
+//   worker: A1 = [q|k_t|q*k_t] (fp16, 128 x k1) into tensor memory (tcgen05.st); the q - k_t
+//           segment of the reference's input is folded into the weights:
+//           q Wq + k Wk + (q-k) Wd + (q*k) Wp = q (Wq+Wd) + k (Wk-Wd) + (q*k) Wp
+//   MMA   : acc1[128 x h0p] = A1 * W0'^T                 (A from tensor memory, W0' from shared memory)
 //   worker: acc1 -> activation -> fp16 A2 in tensor memory
 //   MMA   : acc2[128 x h1p] = A2 * W1^T
 //   worker: acc2 -> activation, dot with W2 -> score s[n,t] -> fp16 column t of S
@@ -16,8 +20,9 @@
 //   MMA   : out[128 x d] = S[128 x T] * K[T x d]          (the weighted sum is a GEMM too)
 //
 // Biases ride in the MMAs: A1 carries a constant-1 column (a padding column of
-// the q segment when d is not a multiple of 8) whose W0 row is b0, and A2 has
-// 16 extra columns, the first constant 1 with W1 row b1.
+// the q segment when d is not a multiple of 8) whose W0 row is b0, and the last
+// k step of layer 2 reads 16 columns shared by all A2 buffers, the first
+// constant 1 with W1 row b1.
 //
 // Activations run on packed fp16 pairs with one SFU instruction per pair:
 //   sigmoid(z) = 1/2 + 1/2 tanh(z/2), so Dice(x) = x * (C + D*tanh(A*x + B)) with
@@ -34,32 +39,35 @@
 namespace xb {
 namespace {
 
-constexpr int TC_THREADS = 576;          // 4 worker warpgroups + 2 MMA-issuing warps
-constexpr int MMA1_WARP = 16, MMA2_WARP = 17;
+constexpr int TC_THREADS = 544;          // 4 worker warpgroups + the MMA-issuing warp
+constexpr int MMA_WARP = 16;
 constexpr int TMEM_COLS = 512;
 
-// Tensor-memory columns of one step parity: [acc1 | acc2 | A2 | A1]; the closing product's
-// accumulator reuses parity 0's A1 columns, which are idle by then.
+// Tensor-memory columns: [acc1 x2 | acc2 x2 | A1 x2 | A2 x na2 | ones]; the closing product's accumulator
+// reuses the first A1 buffer, which is idle by then.
 struct TcGeom {
   int dp, nch, k1, ones1, h0p, k2, h1p, tp, np;
-  int c_acc2, c_a2, c_a1, wg;
+  int c_acc2, c_a1, c_a2, c_ones, na2, cols;
 };
 
 __host__ __device__ inline TcGeom tc_geom(int d, int h0, int h1, int T) {
   TcGeom g;
   g.dp = (d + 7) / 8 * 8;
   g.nch = g.dp / 8;
-  g.ones1 = (d < g.dp) ? d : 4 * g.dp;               // column of A1 that is constant 1
-  g.k1 = 4 * g.dp + ((d < g.dp) ? 0 : 16);
+  g.ones1 = (d < g.dp) ? d : 3 * g.dp;               // column of A1 that is constant 1
+  g.k1 = (3 * g.dp + ((d < g.dp) ? 0 : 8) + 15) / 16 * 16;
   g.h0p = (h0 + 15) / 16 * 16;
   g.k2 = g.h0p + 16;                                 // column h0p of A2 is constant 1
   g.h1p = (h1 + 15) / 16 * 16;
   g.tp = (T + 15) / 16 * 16;
   g.np = (g.dp + 15) / 16 * 16;
-  g.c_acc2 = g.h0p;
-  g.c_a2 = g.h0p + g.h1p;
-  g.c_a1 = g.c_a2 + g.k2 / 2;
-  g.wg = g.c_a1 + g.k1 / 2;
+  g.c_acc2 = 2 * g.h0p;
+  g.c_a1 = g.c_acc2 + 2 * g.h1p;
+  g.c_a2 = g.c_a1 + g.k1;                            // two A1 buffers of k1 / 2 columns
+  const int fixed = g.c_a2 + 8;
+  g.na2 = (fixed + 3 * (g.h0p / 2) <= TMEM_COLS) ? 3 : 2;
+  g.c_ones = g.c_a2 + g.na2 * (g.h0p / 2);
+  g.cols = g.c_ones + 8;
   return g;
 }
 
@@ -116,9 +124,15 @@ __device__ __forceinline__ void pack_weights(const AttParams& p, const TcGeom& G
     __half v = zero;
     if (n < p.h0) {
       if (kk == G.ones1) v = __float2half_rn(p.b0 ? p.b0[n] : 0.f);
-      else if (kk < 4 * dp) {
+      else if (kk < 3 * dp) {
+        // segments [q | k | q*k] with the weights of the q - k segment folded into the first two
         const int seg = kk / dp, i = kk - seg * dp;
-        if (i < d) v = p.W0[(int64_t)n * 4 * d + seg * d + i];
+        if (i < d) {
+          const __half* w = p.W0 + (int64_t)n * 4 * d + i;
+          const float wd = __half2float(w[2 * d]);
+          v = seg == 0 ? __float2half_rn(__half2float(w[0]) + wd)
+                       : (seg == 1 ? __float2half_rn(__half2float(w[d]) - wd) : w[3 * d]);
+        }
       }
     }
     w0s[(kk >> 3) * (h0p * 8) + n * 8 + (kk & 7)] = v;
@@ -190,7 +204,10 @@ __global__ void att_pack_kernel(const __grid_constant__ AttParams p, uint8_t* ds
                     reinterpret_cast<uint4*>(dst + w0_bytes + w1_bytes) + G.h0p / 2, threadIdx.x, blockDim.x);
 }
 
-template <int ACT>
+// D0 / H0 / H1: the shape as compile-time constants (0 = read it from the arguments). With the shape known the
+// block loops of both activation phases unroll completely and every tensor-memory column, shared-memory offset and
+// padding test folds into the instruction stream: the kernel is bound by issue slots, so this is time.
+template <int ACT, int D0, int H0, int H1>
 __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_constant__ AttParams p) {
   using namespace umma;
   using umma::tanh_f16x2;
@@ -198,11 +215,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   __shared__ __align__(8) uint64_t bars[12];
   __shared__ uint32_t tmem_base_s;
 
-  const TcGeom G = tc_geom(p.d, p.h0, p.h1, p.T);
+  const int d_ = D0 ? D0 : p.d, h0_ = H0 ? H0 : p.h0, h1_ = H1 ? H1 : p.h1;
+  const TcGeom G = tc_geom(d_, h0_, h1_, p.T);
   const TcSmemLayout L = tc_layout(G, p.T);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x / p.tiles_per_req, tile = blockIdx.x % p.tiles_per_req;
-  const int d = p.d, dp = G.dp, nch = G.nch, k1 = G.k1, h0p = G.h0p, k2 = G.k2, h1p = G.h1p, tp = G.tp, np = G.np;
+  const int d = d_, dp = G.dp, nch = G.nch, k1 = G.k1, h0p = G.h0p, k2 = G.k2, h1p = G.h1p, tp = G.tp, np = G.np;
   int tl = p.seq_len ? p.seq_len[r] : p.T;
   tl = tl < 0 ? 0 : (tl > p.T ? p.T : tl);
 
@@ -269,7 +287,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     kts[(t >> 3) * (np * 8) + e * 8 + (t & 7)] = v;
   }
   // barriers, per accumulator/operand buffer b = step & 1:
-  //   a1_full[b]   4 builder warps       -> MMA warp: A1 of a step is in shared memory
+  //   a1_full[b]   4 builder warps       -> MMA warp: A1 of a step is in tensor memory
   //   acc1_full[b] tcgen05.commit        -> both warpgroups: layer-1 accumulator complete
   //   a2_full[b]   4 layer-1 warps       -> MMA warp: A2 written and acc1[b] drained
   //   acc2_full[b] tcgen05.commit        -> both warpgroups: layer-2 accumulator complete
@@ -294,58 +312,68 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     mbar_init(smem_u32(acc3_full), 1);
     fence_barrier_init();
   }
-  if (warp == MMA1_WARP) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
   fence_proxy_async_smem();          // operands were written through the generic proxy
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem0 = tmem_base_s;
 
-  if (warp == MMA1_WARP) {
-    // ---- layer-1 MMA issue: one thread, descriptors advanced by constant steps -----------------------
+  if (warp == MMA_WARP) {
+    // ---- MMA issue: one thread for both layers and the closing product --------------------------------
+    // The tensor pipe runs MMAs in issue order, so the order is chosen here: when the layer-1 warps finish
+    // step j, layer 1 of step j+2 goes first (the warps that just finished are idle until it completes),
+    // then layer 2 of step j.
     if (lane == 0) {
-      const uint64_t db0 = make_desc_interleaved(smem_u32(w0s), h0p * 16, 128);
-      const uint64_t db_step = (uint64_t)((2 * h0p * 16) >> 4);
-      const int nks = k1 / 16;
-      for (int j = 0; j < tl; ++j) {
+      const uint64_t db1_0 = make_desc_interleaved(smem_u32(w0s), h0p * 16, 128);
+      const uint64_t db1_step = (uint64_t)((2 * h0p * 16) >> 4);
+      const uint64_t db2_0 = make_desc_interleaved(smem_u32(w1s), h1p * 16, 128);
+      const uint64_t db2_step = (uint64_t)((2 * h1p * 16) >> 4), da_step = (uint64_t)((2 * 128 * 16) >> 4);
+      const int nks1 = k1 / 16, nks2 = h0p / 16;
+      auto issue_l1 = [&](int j) {
         const int b = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        // A1 of step j is written; acc1[b] was drained before the layer-1 warps signalled a2_full(j-2)
-        if (!(mbar_wait(smem_u32(&a1_full[b]), ph, 10) && mbar_wait(smem_u32(&a2_full[b]), ph ^ 1u, 14))) break;
-        tc_fence_after_sync();
-        uint32_t ta = tmem0 + b * G.wg + G.c_a1;                // A1 lives in tensor memory
-        uint64_t db = db0;
-        const uint32_t acc1 = tmem0 + b * G.wg;
+        uint32_t ta = tmem0 + G.c_a1 + b * (k1 / 2);
+        uint64_t db = db1_0;
+        const uint32_t acc1 = tmem0 + b * h0p;
         mma_f16_ts(acc1, ta, db, p.idesc1, 0u);
-        for (int ks = 1; ks < nks; ++ks) {
-          ta += 8; db += db_step;
+        for (int ks = 1; ks < nks1; ++ks) {
+          ta += 8; db += db1_step;
           mma_f16_ts(acc1, ta, db, p.idesc1, 1u);
         }
         mma_commit(smem_u32(&acc1_full[b]));
-      }
-    }
-  } else if (warp == MMA2_WARP) {
-    // ---- layer-2 MMA issue, then the closing S*K product -----------------------------------------------
-    if (lane == 0) {
-      const uint64_t db0 = make_desc_interleaved(smem_u32(w1s), h1p * 16, 128);
-      const uint64_t db_step = (uint64_t)((2 * h1p * 16) >> 4), da_step = (uint64_t)((2 * 128 * 16) >> 4);
-      const int nks = k2 / 16;
+      };
       bool ok = true;
-      for (int j = 0; j < tl; ++j) {
+      for (int j = 0; j < 2 && j < tl && ok; ++j) {
+        ok = mbar_wait(smem_u32(&a1_full[j]), 0u, 10);
+        if (ok) { tc_fence_after_sync(); issue_l1(j); }
+      }
+      int a2i = 0;                                            // A2 buffer of step j: j % na2
+      for (int j = 0; j < tl && ok; ++j) {
         const int b = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        ok = mbar_wait(smem_u32(&a2_full[b]), ph, 11) && mbar_wait(smem_u32(&acc2_free[b]), ph ^ 1u, 13);
+        // the layer-1 warps have written A2 of step j and drained acc1[b]
+        ok = mbar_wait(smem_u32(&a2_full[b]), ph, 11);
+        if (!ok) break;
+        if (j + 2 < tl) {
+          ok = mbar_wait(smem_u32(&a1_full[b]), ph ^ 1u, 14);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_l1(j + 2);
+        }
+        ok = mbar_wait(smem_u32(&acc2_free[b]), ph ^ 1u, 13);  // the layer-2 warps have drained acc2[b] (step j-2)
         if (!ok) break;
         tc_fence_after_sync();
-        uint32_t ta = tmem0 + b * G.wg + G.c_a2;                // A2 lives in tensor memory
-        uint64_t db = db0;
-        const uint32_t acc2 = tmem0 + b * G.wg + G.c_acc2;
+        uint32_t ta = tmem0 + G.c_a2 + a2i * (h0p / 2);
+        uint64_t db = db2_0;
+        const uint32_t acc2 = tmem0 + G.c_acc2 + b * h1p;
         mma_f16_ts(acc2, ta, db, p.idesc2, 0u);
-        for (int ks = 1; ks < nks; ++ks) {
-          ta += 8; db += db_step;
+        for (int ks = 1; ks < nks2; ++ks) {
+          ta += 8; db += db2_step;
           mma_f16_ts(acc2, ta, db, p.idesc2, 1u);
         }
+        mma_f16_ts(acc2, tmem0 + G.c_ones, db + db2_step, p.idesc2, 1u);   // bias b1: the shared constant-1 columns
         mma_commit(smem_u32(&acc2_full[b]));
+        a2i = a2i + 1 == G.na2 ? 0 : a2i + 1;
       }
       // weighted sum over the steps: out = S * K
       if (ok && mbar_wait(smem_u32(s_full), 0, 12)) {
@@ -364,22 +392,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     // ---- layer-1 warpgroups: acc1 -> activation -> A2, for the steps of parity wb ---------------------
     const int wb = warp >> 2;
     const uint32_t lane_addr = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);   // TMEM lane == candidate row of the tile
-    {
-      // columns h0p.. of A2: the constant 1 that carries bias b1, then zeros (fp16 pairs per 32-bit column)
-      const uint32_t a2t = lane_addr + wb * G.wg + G.c_a2 + h0p / 2;
-      tmem_st4(a2t, 0x00003C00u, 0u, 0u, 0u);
-      tmem_st4(a2t + 4, 0u, 0u, 0u, 0u);
+    if (wb == 0) {
+      // the 16 columns every A2 buffer ends with: the constant 1 that carries bias b1, then zeros (fp16 pairs
+      // per 32-bit column); complete before this warpgroup's first arrival on a2_full, which precedes every
+      // layer-2 MMA
+      tmem_st4(lane_addr + G.c_ones, 0x00003C00u, 0u, 0u, 0u);
+      tmem_st4(lane_addr + G.c_ones + 4, 0u, 0u, 0u, 0u);
       tmem_wait_st();
     }
     bool ok = true;
+    int a2i = wb % G.na2;
     for (int j = wb; j < tl; j += 2) {
       const int b = wb;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      const uint32_t a2t = lane_addr + b * G.wg + G.c_a2;
+      const uint32_t a2t = lane_addr + G.c_a2 + a2i * (h0p / 2);
+      a2i += 2; if (a2i >= G.na2) a2i -= G.na2;
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[b]), ph, 20));
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t acc1 = lane_addr + b * G.wg;
+      const uint32_t acc1 = lane_addr + b * h0p;
       // blocks of 16 columns (8 fp16 pairs): the load of the next block is in flight while this one is
       // converted, activated and stored
       const int nblk = h0p / 16;
@@ -389,9 +420,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         if (blk + 1 < nblk) tmem_ld16_nowait(acc1 + 16 * (blk + 1), nxt);
         uint32_t y[8];
         pair_l1_block<ACT>(cur, c1 + 8 * blk, y);
-        if (blk == 0) {
-          // A2[b] is free once the layer-2 MMA of step j-2 has read it: waited for after the first block's
-          // arithmetic, so that that MMA overlaps the start of this step
+        if (blk == 0 && G.na2 == 2) {
+          // with two A2 buffers, this one is free once the layer-2 MMA of step j-2 has read it: waited for
+          // after the first block's arithmetic (with three buffers the MMA of step j-3 completed before this
+          // step's layer-1 MMA did)
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph ^ 1u, 23));
           if (ok) tc_fence_after_sync();
         }
@@ -424,19 +456,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     // constant part of this parity's A1 buffer: the q segment (and the ones column)
     // (chunk c of 8 fp16 is 4 tensor-memory columns of this thread's lane)
     {
-      const uint32_t a1t = lane_addr + wb * G.wg + G.c_a1;
+      const uint32_t a1t = lane_addr + G.c_a1 + wb * (k1 / 2);
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         if (c < nch) tmem_st4(a1t + 4 * c, qv[c].x, qv[c].y, qv[c].z, qv[c].w);
-      if (G.ones1 == 4 * dp) {
-        tmem_st4(a1t + 16 * nch, 0x00003C00u, 0u, 0u, 0u);
-        tmem_st4(a1t + 16 * nch + 4, 0u, 0u, 0u, 0u);
-      }
+      // chunks past the three segments: the constant 1 when q has no padding column for it, zeros otherwise
+      for (int c = 3 * nch; c < k1 / 8; ++c)
+        tmem_st4(a1t + 4 * c, (c == 3 * nch && G.ones1 == 3 * dp) ? 0x00003C00u : 0u, 0u, 0u, 0u);
       tmem_wait_st();
     }
 
     auto build_a1 = [&](int t) {
-      const uint32_t a1t = lane_addr + (t & 1) * G.wg + G.c_a1;
+      const uint32_t a1t = lane_addr + G.c_a1 + (t & 1) * (k1 / 2);
       const uint4* kt = reinterpret_cast<const uint4*>(khs + t * dp);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -444,15 +475,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
           const uint4 kc = kt[c];
           const __half2* kh = reinterpret_cast<const __half2*>(&kc);
           const __half2* qh = reinterpret_cast<const __half2*>(&qv[c]);
-          uint4 df, pr;
-          __half2* dh = reinterpret_cast<__half2*>(&df);
+          uint4 pr;
           __half2* ph2 = reinterpret_cast<__half2*>(&pr);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) { dh[e] = __hsub2(qh[e], kh[e]); ph2[e] = __hmul2(qh[e], kh[e]); }
-          // q's padding column holding the constant 1 gives 1-0 in `df`; harmless, its W0 rows are zero
+          for (int e = 0; e < 4; ++e) ph2[e] = __hmul2(qh[e], kh[e]);
+          // q's padding column holding the constant 1 gives 1*0 in `pr`; its W0 rows are zero anyway
           tmem_st4(a1t + 4 * (nch + c), kc.x, kc.y, kc.z, kc.w);
-          tmem_st4(a1t + 4 * (2 * nch + c), df.x, df.y, df.z, df.w);
-          tmem_st4(a1t + 4 * (3 * nch + c), pr.x, pr.y, pr.z, pr.w);
+          tmem_st4(a1t + 4 * (2 * nch + c), pr.x, pr.y, pr.z, pr.w);
         }
       }
       tmem_wait_st();
@@ -462,7 +491,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     };
 
     bool ok = true;
-    const int npairs2 = (p.h1 + 1) / 2;
+    const int npairs2 = (h1_ + 1) / 2;
     if (tl > wb) build_a1(wb);
     for (int j = wb; j < tl; j += 2) {
       const int b = wb;
@@ -476,7 +505,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph, 21));
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t acc2 = lane_addr + b * G.wg + G.c_acc2;
+      const uint32_t acc2 = lane_addr + G.c_acc2 + b * h1p;
       __half2 part[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) part[e] = __floats2half2_rn(0.f, 0.f);
@@ -555,7 +584,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == MMA1_WARP) {
+  if (warp == MMA_WARP) {
     tc_fence_after_sync();
     tmem_dealloc(tmem0, TMEM_COLS);
   }
@@ -563,10 +592,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
 
 bool tc_eligible(const xb_din_att_args& a, int* why) {
   const TcGeom g = tc_geom(a.d, a.h0, a.h1, a.T);
-  if (g.dp > 64 || g.k1 > 272) { if (why) *why = 1; return false; }
+  if (g.dp > 64) { if (why) *why = 1; return false; }
   if (g.h0p > 128 || g.h1p > 64) { if (why) *why = 2; return false; }
   if (g.tp > 256) { if (why) *why = 5; return false; }
-  if (2 * g.wg > TMEM_COLS || g.np > g.k1 / 2) { if (why) *why = 6; return false; }
+  if (g.cols > TMEM_COLS || g.np > g.k1 / 2) { if (why) *why = 6; return false; }
   if (tc_layout(g, a.T).total > 220 * 1024) { if (why) *why = 3; return false; }
   if (a.use_softmax && a.scores) { if (why) *why = 4; return false; }   // normalised scores are not written out
   return true;
@@ -600,13 +629,18 @@ int launch_att_tc(AttParams& p, const xb_din_att_args& a, cudaStream_t stream) {
   p.idesc3 = umma::make_idesc(128, g.np, 0);
   const TcSmemLayout L = tc_layout(g, p.T);
   static PerDeviceOnce attr_set;
-  XB_SET_MAX_SMEM_ONCE(attr_set, 220 * 1024, (const void*)din_att_tc_kernel<XB_ACT_NONE>,
-                       (const void*)din_att_tc_kernel<XB_ACT_SIGMOID>, (const void*)din_att_tc_kernel<XB_ACT_DICE>);
+  XB_SET_MAX_SMEM_ONCE(attr_set, 220 * 1024, (const void*)din_att_tc_kernel<XB_ACT_NONE, 0, 0, 0>,
+                       (const void*)din_att_tc_kernel<XB_ACT_SIGMOID, 0, 0, 0>, (const void*)din_att_tc_kernel<XB_ACT_DICE, 0, 0, 0>,
+                       (const void*)din_att_tc_kernel<XB_ACT_SIGMOID, 36, 80, 40>, (const void*)din_att_tc_kernel<XB_ACT_DICE, 36, 80, 40>);
   const int64_t blocks = (int64_t)a.requests * p.tiles_per_req;
   XB_REQUIRE(blocks < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_din_attention: too many tiles");
-  if (a.act == XB_ACT_DICE) din_att_tc_kernel<XB_ACT_DICE><<<(unsigned)blocks, TC_THREADS, L.total, stream>>>(p);
-  else if (a.act == XB_ACT_SIGMOID) din_att_tc_kernel<XB_ACT_SIGMOID><<<(unsigned)blocks, TC_THREADS, L.total, stream>>>(p);
-  else din_att_tc_kernel<XB_ACT_NONE><<<(unsigned)blocks, TC_THREADS, L.total, stream>>>(p);
+  // the shape of the DIN / DIEN attention unit (d = 36, MLP 144-80-40-1) has instantiations of its own
+  const bool din_shape = a.d == 36 && a.h0 == 80 && a.h1 == 40;
+  if (din_shape && a.act == XB_ACT_DICE) din_att_tc_kernel<XB_ACT_DICE, 36, 80, 40><<<(unsigned)blocks, TC_THREADS, L.total, stream>>>(p);
+  else if (din_shape && a.act == XB_ACT_SIGMOID) din_att_tc_kernel<XB_ACT_SIGMOID, 36, 80, 40><<<(unsigned)blocks, TC_THREADS, L.total, stream>>>(p);
+  else if (a.act == XB_ACT_DICE) din_att_tc_kernel<XB_ACT_DICE, 0, 0, 0><<<(unsigned)blocks, TC_THREADS, L.total, stream>>>(p);
+  else if (a.act == XB_ACT_SIGMOID) din_att_tc_kernel<XB_ACT_SIGMOID, 0, 0, 0><<<(unsigned)blocks, TC_THREADS, L.total, stream>>>(p);
+  else din_att_tc_kernel<XB_ACT_NONE, 0, 0, 0><<<(unsigned)blocks, TC_THREADS, L.total, stream>>>(p);
   return check_launch("din_att_tc_kernel");
 }
 

@@ -94,7 +94,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int sit
   // once any wait on this device has run out, later waits give up at once, so a
   // broken launch drains in about one timeout instead of one per CTA
   const long long limit = (*reinterpret_cast<volatile int*>(&g_status) != 0) ? (1ll << 16) : kWaitCycles;
-  while (!mbar_try_wait(bar, parity)) {
+  // Each further try suspends the thread in hardware until the phase completes or about a microsecond has passed,
+  // so a waiting warp issues a handful of instructions per microsecond instead of competing for issue slots
+  // with the warps that do the work.
+  while (!mbar_try_wait_for(bar, parity, 1000u)) {
     if (clock64() - t0 > limit) {
       wait_gave_up(site);
       return false;
