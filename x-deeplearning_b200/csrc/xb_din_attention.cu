@@ -211,6 +211,12 @@ extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
   return check_launch("din_att_simt_kernel");
 }
 
+#ifdef XB_ATT_TRACE
+extern "C" int xb_debug_att_trace(long long* host) {
+  return cudaMemcpyFromSymbol(host, xb::g_att_trace, sizeof(long long) * 6 * 128 * 4) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 extern "C" size_t xb_din_attention_packed_bytes(int32_t d, int32_t h0, int32_t h1) {
   if (d <= 0 || h0 <= 0 || h1 <= 0) return 0;
   size_t n = 0;

@@ -1,18 +1,19 @@
 // tcgen05 engine of the fused DIN attention unit (included by xb_din_attention.cu).
 //
 // One CTA owns 128 candidates of one request and walks the behaviour steps.
-// Four worker warpgroups (one candidate row per thread each) split the work by
+// Five worker warpgroups (one candidate row per thread each) split the work by
 // phase and step parity: warpgroup b (b = 0, 1) runs the layer-1 activations of
-// the steps of parity b, warpgroup 2+b builds A1 two steps ahead and runs the
-// layer-2 activations for parity b; one more warp issues every MMA, in the order
-// the workers need them (the tensor pipe runs MMAs in issue order).
-// Operands and accumulators are double-buffered by step parity (A2 three deep
-// when tensor memory has room), so in steady state the tensor pipe, the SFU and
-// the FP16 pipe overlap.
-//   worker: A1 = [q|k_t|q*k_t] (fp16, 128 x k1) into tensor memory (tcgen05.st); the q - k_t
+// the steps of parity b, warpgroup 2+b the layer-2 activations for parity b, the
+// fifth builds A1 of every step two steps ahead; one more warp issues every MMA,
+// in the order the workers need them (the tensor pipe runs MMAs in issue order).
+// The layer-1 accumulator and the layer-2 operand are three deep when tensor
+// memory has room (two otherwise), the rest is double-buffered by step parity,
+// so in steady state the tensor pipe, the SFU and the FP16 pipe overlap: the
+// layer-1 MMA of a later step runs while the layer-1 warps still work on this one.
+//   worker: A1 = [q|k_t|q*k_t] (fp16, 128 x k1) into shared memory; the q - k_t
 //           segment of the reference's input is folded into the weights:
 //           q Wq + k Wk + (q-k) Wd + (q*k) Wp = q (Wq+Wd) + k (Wk-Wd) + (q*k) Wp
-//   MMA   : acc1[128 x h0p] = A1 * W0'^T                 (A from tensor memory, W0' from shared memory)
+//   MMA   : acc1[128 x h0p] = A1 * W0'^T                 (both operands from shared memory)
 //   worker: acc1 -> activation -> fp16 A2 in tensor memory
 //   MMA   : acc2[128 x h1p] = A2 * W1^T
 //   worker: acc2 -> activation, dot with W2 -> score s[n,t] -> fp16 column t of S
@@ -28,9 +29,9 @@
 //   sigmoid(z) = 1/2 + 1/2 tanh(z/2), so Dice(x) = x * (C + D*tanh(A*x + B)) with
 //   A = rstd/2, B = -mean*rstd/2, C = (1+gamma)/2, D = (1-gamma)/2 per column.
 //
-// The A operands never touch shared memory: a thread owns one candidate row = one
+// The layer-2 operand never touches shared memory: a thread owns one candidate row = one
 // tensor-memory lane and stores its fp16 pairs into that lane's columns (two
-// consecutive k per 32-bit column). Shared-memory operands (weights, S, K^T) use
+// consecutive k per 32-bit column). Shared-memory operands (A1, weights, S, K^T) use
 // the un-swizzled K-major core-matrix layout: the 16-byte chunk c (8 consecutive k)
 // of row r sits at c*(rows*16) + r*16, the descriptor's leading-dimension offset
 // is rows*16 and its stride offset 128.
@@ -39,19 +40,27 @@
 namespace xb {
 namespace {
 
-constexpr int TC_THREADS = 544;          // 4 worker warpgroups + the MMA-issuing warp
-constexpr int MMA_WARP = 16;
+#ifdef XB_ATT_TRACE
+// debug builds only: cycle stamps of CTA 0, [slot][step][event]
+__device__ long long g_att_trace[6 * 128 * 4];
+#define ATT_TR(slot, j, ev) do { if (blockIdx.x == 0 && (j) < 128) g_att_trace[((slot) * 128 + (j)) * 4 + (ev)] = clock64(); } while (0)
+#else
+#define ATT_TR(slot, j, ev) do { } while (0)
+#endif
+
+constexpr int TC_THREADS = 672;          // 5 worker warpgroups + the MMA-issuing warp
+constexpr int MMA_WARP = 20;
 constexpr int TMEM_COLS = 512;
 
-// Tensor-memory columns: [acc1 x2 | acc2 x2 | A1 x2 | A2 x na2 | ones]; the closing product's accumulator
-// reuses the first A1 buffer, which is idle by then.
+// Tensor-memory columns: [acc1 x na1 | acc2 x2 | A2 x na2 | ones | acc3]; when there is no room for the closing
+// product's accumulator it reuses the acc1 buffers, which are idle by then.
 struct TcGeom {
   int dp, nch, k1, ones1, h0p, k2, h1p, tp, np;
-  int c_acc2, c_a1, c_a2, c_ones, na2, cols;
+  int c_acc2, c_a2, c_ones, c_acc3, na1, na2, cols;
 };
 
-__host__ __device__ inline TcGeom tc_geom(int d, int h0, int h1, int T) {
-  TcGeom g;
+__host__ __device__ constexpr TcGeom tc_geom(int d, int h0, int h1, int T) {
+  TcGeom g{};
   g.dp = (d + 7) / 8 * 8;
   g.nch = g.dp / 8;
   g.ones1 = (d < g.dp) ? d : 3 * g.dp;               // column of A1 that is constant 1
@@ -61,24 +70,32 @@ __host__ __device__ inline TcGeom tc_geom(int d, int h0, int h1, int T) {
   g.h1p = (h1 + 15) / 16 * 16;
   g.tp = (T + 15) / 16 * 16;
   g.np = (g.dp + 15) / 16 * 16;
-  g.c_acc2 = 2 * g.h0p;
-  g.c_a1 = g.c_acc2 + 2 * g.h1p;
-  g.c_a2 = g.c_a1 + g.k1;                            // two A1 buffers of k1 / 2 columns
-  const int fixed = g.c_a2 + 8;
-  g.na2 = (fixed + 3 * (g.h0p / 2) <= TMEM_COLS) ? 3 : 2;
+  // deepest buffering that fits: (acc1, A2) = (3, 3), (3, 2), (2, 3), (2, 2)
+  g.na1 = 2; g.na2 = 2;
+  for (int c = 0; c < 3; ++c) {
+    const int n1 = c < 2 ? 3 : 2, n2 = c == 1 ? 2 : 3;
+    if (n1 * g.h0p + 2 * g.h1p + n2 * (g.h0p / 2) + 8 <= TMEM_COLS) { g.na1 = n1; g.na2 = n2; break; }
+  }
+#ifdef XB_ATT_FORCE_NA1_2
+  g.na1 = 2;
+#endif
+  g.c_acc2 = g.na1 * g.h0p;
+  g.c_a2 = g.c_acc2 + 2 * g.h1p;
   g.c_ones = g.c_a2 + g.na2 * (g.h0p / 2);
   g.cols = g.c_ones + 8;
+  g.c_acc3 = (g.cols + g.np <= TMEM_COLS) ? g.cols : 0;
   return g;
 }
 
 struct TcSmemLayout {
-  int w0, w1, s, kt, kh, q, c1, c2, total;
+  int w0, w1, a1, s, kt, kh, q, c1, c2, total;
 };
 __host__ __device__ inline TcSmemLayout tc_layout(const TcGeom& g, int T) {
   TcSmemLayout L;
   int off = 0;
   L.w0 = off; off += g.h0p * g.k1 * 2;          // W0 operand [h0p rows, k1]
   L.w1 = off; off += g.h1p * g.k2 * 2;          // W1 operand [h1p rows, k2]
+  L.a1 = off; off += 2 * 128 * g.k1 * 2;        // A1 operand [128 rows, k1], one per step parity
   L.s = off; off += 128 * g.tp * 2;             // scores [128, tp]
   L.kt = off; off += g.np * g.tp * 2;           // K^T operand [np rows (feature), tp (step)]
   L.kh = off; off += T * g.dp * 2;              // k rows for building A1
@@ -212,7 +229,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   using namespace umma;
   using umma::tanh_f16x2;
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t bars[12];
+  __shared__ __align__(8) uint64_t bars[13];
   __shared__ uint32_t tmem_base_s;
 
   const int d_ = D0 ? D0 : p.d, h0_ = H0 ? H0 : p.h0, h1_ = H1 ? H1 : p.h1;
@@ -226,6 +243,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
 
   __half* w0s = reinterpret_cast<__half*>(smem + L.w0);
   __half* w1s = reinterpret_cast<__half*>(smem + L.w1);
+  uint8_t* a1s = smem + L.a1;
   __half* ss = reinterpret_cast<__half*>(smem + L.s);
   __half* kts = reinterpret_cast<__half*>(smem + L.kt);
   __half* khs = reinterpret_cast<__half*>(smem + L.kh);
@@ -286,28 +304,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     const __half v = (e < d && t < tl) ? khs[t * dp + e] : zero;
     kts[(t >> 3) * (np * 8) + e * 8 + (t & 7)] = v;
   }
-  // barriers, per accumulator/operand buffer b = step & 1:
-  //   a1_full[b]   4 builder warps       -> MMA warp: A1 of a step is in tensor memory
-  //   acc1_full[b] tcgen05.commit        -> both warpgroups: layer-1 accumulator complete
-  //   a2_full[b]   4 layer-1 warps       -> MMA warp: A2 written and acc1[b] drained
+  // barriers (b = step & 1, i = step % na1):
+  //   a1_full[b]   4 builder warps       -> MMA warp: A1 of a step is in shared memory
+  //   acc1_full[i] tcgen05.commit        -> layer-1 warpgroups: layer-1 accumulator complete; builder: A1 read
+  //   a2_full[b]   4 layer-1 warps       -> MMA warp: A2 written and the step's acc1 buffer drained
   //   acc2_full[b] tcgen05.commit        -> both warpgroups: layer-2 accumulator complete
   //   acc2_free[b] 4 layer-2 warps       -> MMA warp: acc2[b] drained
   //   s_full, acc3_full: the closing S*K product
+  // A barrier never runs two phases ahead of a waiter: the MMA of a later step on the same barrier needs
+  // something that waiter produces after its wait (the drained accumulator, the next A1).
   uint64_t* a1_full = &bars[0];
   uint64_t* acc1_full = &bars[2];
-  uint64_t* a2_full = &bars[4];
-  uint64_t* acc2_full = &bars[6];
-  uint64_t* acc2_free = &bars[8];
-  uint64_t* s_full = &bars[10];
-  uint64_t* acc3_full = &bars[11];
+  uint64_t* a2_full = &bars[5];
+  uint64_t* acc2_full = &bars[7];
+  uint64_t* acc2_free = &bars[9];
+  uint64_t* s_full = &bars[11];
+  uint64_t* acc3_full = &bars[12];
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&a1_full[b]), 4);
-      mbar_init(smem_u32(&acc1_full[b]), 1);
       mbar_init(smem_u32(&a2_full[b]), 4);
       mbar_init(smem_u32(&acc2_full[b]), 1);
       mbar_init(smem_u32(&acc2_free[b]), 4);
     }
+    for (int i = 0; i < 3; ++i) mbar_init(smem_u32(&acc1_full[i]), 1);
     mbar_init(smem_u32(s_full), 8);
     mbar_init(smem_u32(acc3_full), 1);
     fence_barrier_init();
@@ -321,73 +341,85 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
 
   if (warp == MMA_WARP) {
     // ---- MMA issue: one thread for both layers and the closing product --------------------------------
-    // The tensor pipe runs MMAs in issue order, so the order is chosen here: when the layer-1 warps finish
-    // step j, layer 1 of step j+2 goes first (the warps that just finished are idle until it completes),
-    // then layer 2 of step j.
-    if (lane == 0) {
+    // The whole warp runs this code in uniform control flow and one elected lane issues: that keeps the
+    // descriptors in uniform registers, and with the chains unrolled over descriptors computed once an MMA
+    // issues in about 36 cycles instead of 100. The tensor pipe runs MMAs in issue order, so the order is
+    // chosen here. When the layer-1 warps finish step j they have written A2 of step j and drained that step's
+    // acc1 buffer: layer 2 of step j goes first (its warps wait for it), layer 1 of step j + na1 (the next
+    // user of the buffer) follows.
+    constexpr int NK1 = D0 ? tc_geom(D0, H0, H1, 16).k1 / 16 : 13;       // k steps of layer 1 (d <= 64)
+    constexpr int NK2 = H0 ? tc_geom(D0, H0, H1, 16).h0p / 16 + 1 : 9;   // and layer 2; its last is the bias chunk
+    const int nks1 = D0 ? NK1 : k1 / 16, nks2 = H0 ? NK2 : h0p / 16 + 1;
+    const int na1 = G.na1;
+    uint64_t db1[NK1], db2[NK2];
+    {
       const uint64_t db1_0 = make_desc_interleaved(smem_u32(w0s), h0p * 16, 128);
-      const uint64_t db1_step = (uint64_t)((2 * h0p * 16) >> 4);
       const uint64_t db2_0 = make_desc_interleaved(smem_u32(w1s), h1p * 16, 128);
-      const uint64_t db2_step = (uint64_t)((2 * h1p * 16) >> 4), da_step = (uint64_t)((2 * 128 * 16) >> 4);
-      const int nks1 = k1 / 16, nks2 = h0p / 16;
-      auto issue_l1 = [&](int j) {
-        const int b = j & 1;
-        uint32_t ta = tmem0 + G.c_a1 + b * (k1 / 2);
-        uint64_t db = db1_0;
-        const uint32_t acc1 = tmem0 + b * h0p;
-        mma_f16_ts(acc1, ta, db, p.idesc1, 0u);
-        for (int ks = 1; ks < nks1; ++ks) {
-          ta += 8; db += db1_step;
-          mma_f16_ts(acc1, ta, db, p.idesc1, 1u);
-        }
-        mma_commit(smem_u32(&acc1_full[b]));
-      };
-      bool ok = true;
-      for (int j = 0; j < 2 && j < tl && ok; ++j) {
-        ok = mbar_wait(smem_u32(&a1_full[j]), 0u, 10);
-        if (ok) { tc_fence_after_sync(); issue_l1(j); }
-      }
-      int a2i = 0;                                            // A2 buffer of step j: j % na2
-      for (int j = 0; j < tl && ok; ++j) {
-        const int b = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        // the layer-1 warps have written A2 of step j and drained acc1[b]
-        ok = mbar_wait(smem_u32(&a2_full[b]), ph, 11);
-        if (!ok) break;
-        if (j + 2 < tl) {
-          ok = mbar_wait(smem_u32(&a1_full[b]), ph ^ 1u, 14);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_l1(j + 2);
-        }
-        ok = mbar_wait(smem_u32(&acc2_free[b]), ph ^ 1u, 13);  // the layer-2 warps have drained acc2[b] (step j-2)
-        if (!ok) break;
-        tc_fence_after_sync();
-        uint32_t ta = tmem0 + G.c_a2 + a2i * (h0p / 2);
-        uint64_t db = db2_0;
-        const uint32_t acc2 = tmem0 + G.c_acc2 + b * h1p;
-        mma_f16_ts(acc2, ta, db, p.idesc2, 0u);
-        for (int ks = 1; ks < nks2; ++ks) {
-          ta += 8; db += db2_step;
-          mma_f16_ts(acc2, ta, db, p.idesc2, 1u);
-        }
-        mma_f16_ts(acc2, tmem0 + G.c_ones, db + db2_step, p.idesc2, 1u);   // bias b1: the shared constant-1 columns
-        mma_commit(smem_u32(&acc2_full[b]));
-        a2i = a2i + 1 == G.na2 ? 0 : a2i + 1;
-      }
-      // weighted sum over the steps: out = S * K
-      if (ok && mbar_wait(smem_u32(s_full), 0, 12)) {
-        tc_fence_after_sync();
-        uint64_t da = make_desc_interleaved(smem_u32(ss), 128 * 16, 128);
-        uint64_t db = make_desc_interleaved(smem_u32(kts), np * 16, 128);
-        const uint64_t db3 = (uint64_t)((2 * np * 16) >> 4);
-        for (int ks = 0; ks < tp / 16; ++ks) {
-          mma_f16_ss(tmem0 + G.c_a1, da, db, p.idesc3, ks > 0 ? 1u : 0u);
-          da += da_step; db += db3;
-        }
-      }
-      mma_commit(smem_u32(acc3_full));
+#pragma unroll
+      for (int ks = 0; ks < NK1; ++ks) db1[ks] = db1_0 + (uint64_t)(ks * ((2 * h0p * 16) >> 4));
+#pragma unroll
+      for (int ks = 0; ks < NK2; ++ks) db2[ks] = db2_0 + (uint64_t)(ks * ((2 * h1p * 16) >> 4));
     }
+    const uint64_t da_step = (uint64_t)((2 * 128 * 16) >> 4);
+    const uint64_t da1_0 = make_desc_interleaved(smem_u32(a1s), 128 * 16, 128);
+    const uint64_t da1_buf = (uint64_t)((128 * k1 * 2) >> 4);
+    bool ok = true;
+    auto issue_l1 = [&](int j, int i1) {                       // layer 1 of step j into acc1 buffer i1
+      const uint64_t da = da1_0 + ((j & 1) ? da1_buf : 0);
+      const uint32_t acc1 = tmem0 + i1 * h0p;
+#pragma unroll
+      for (int ks = 0; ks < NK1; ++ks)
+        if (ks < nks1) mma_f16_ss_elect(acc1, da + (uint64_t)ks * da_step, db1[ks], p.idesc1, ks > 0 ? 1u : 0u);
+      mma_commit_elect(smem_u32(&acc1_full[i1]));
+      if (lane == 0) ATT_TR(4, j, 2);
+    };
+    auto issue_l2 = [&](int j, int a2i) {                      // layer 2 of step j from A2 buffer a2i
+      const uint32_t acc2 = tmem0 + G.c_acc2 + (j & 1) * h1p;
+      const uint32_t ta = tmem0 + G.c_a2 + a2i * (h0p / 2);
+#pragma unroll
+      for (int ks = 0; ks < NK2; ++ks)
+        if (ks < nks2)
+          mma_f16_ts_elect(acc2, ks == nks2 - 1 ? tmem0 + G.c_ones : ta + 8 * ks, db2[ks], p.idesc2, ks > 0 ? 1u : 0u);
+      mma_commit_elect(smem_u32(&acc2_full[j & 1]));
+      if (lane == 0) ATT_TR(4, j, 1);
+    };
+    for (int j = 0; j < na1 && j < tl && ok; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a1_full[j & 1]), (uint32_t)(j >> 1) & 1u, 10));
+      if (ok) { tc_fence_after_sync(); issue_l1(j, j); }
+    }
+    int a2i = 0, i1 = 0;                                      // j % na2, j % na1
+    for (int j = 0; j < tl && ok; ++j) {
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      // the layer-1 warps have written A2 of step j and drained its acc1 buffer; acc2 of this parity was
+      // drained by the layer-2 warps (step j-2)
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a2_full[j & 1]), ph, 11) &&
+                                       mbar_wait(smem_u32(&acc2_free[j & 1]), ph ^ 1u, 13));
+      if (!ok) break;
+      if (lane == 0) ATT_TR(4, j, 0);
+      tc_fence_after_sync();
+      issue_l2(j, a2i);
+      const int jn = j + na1;
+      if (jn < tl) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a1_full[jn & 1]), (uint32_t)(jn >> 1) & 1u, 14));
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_l1(jn, i1);
+      }
+      a2i = a2i + 1 == G.na2 ? 0 : a2i + 1;
+      i1 = i1 + 1 == na1 ? 0 : i1 + 1;
+    }
+    // weighted sum over the steps: out = S * K
+    if (ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full), 0, 12))) {
+      tc_fence_after_sync();
+      uint64_t da = make_desc_interleaved(smem_u32(ss), 128 * 16, 128);
+      uint64_t db = make_desc_interleaved(smem_u32(kts), np * 16, 128);
+      const uint64_t db3 = (uint64_t)((2 * np * 16) >> 4);
+      for (int ks = 0; ks < tp / 16; ++ks) {
+        mma_f16_ss_elect(tmem0 + G.c_acc3, da, db, p.idesc3, ks > 0 ? 1u : 0u);
+        da += da_step; db += db3;
+      }
+    }
+    mma_commit_elect(smem_u32(acc3_full));
   } else if (warp < 8) {
     // ---- layer-1 warpgroups: acc1 -> activation -> A2, for the steps of parity wb ---------------------
     const int wb = warp >> 2;
@@ -407,10 +439,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
       const uint32_t a2t = lane_addr + G.c_a2 + a2i * (h0p / 2);
       a2i += 2; if (a2i >= G.na2) a2i -= G.na2;
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[b]), ph, 20));
+      const int i1 = j % G.na1;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[i1]), (uint32_t)(j / G.na1) & 1u, 20));
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t acc1 = lane_addr + b * h0p;
+      if (lane == 0 && (warp & 3) == 0) ATT_TR(wb, j, 0);
+      const uint32_t acc1 = lane_addr + i1 * h0p;
       // blocks of 16 columns (8 fp16 pairs): the load of the next block is in flight while this one is
       // converted, activated and stored
       const int nblk = h0p / 16;
@@ -422,8 +456,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         pair_l1_block<ACT>(cur, c1 + 8 * blk, y);
         if (blk == 0 && G.na2 == 2) {
           // with two A2 buffers, this one is free once the layer-2 MMA of step j-2 has read it: waited for
-          // after the first block's arithmetic (with three buffers the MMA of step j-3 completed before this
-          // step's layer-1 MMA did)
+          // after the first block's arithmetic (with three buffers the MMA of step j-3 was issued before this
+          // step's layer-1 MMA, so it completed first)
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph ^ 1u, 23));
           if (ok) tc_fence_after_sync();
         }
@@ -439,35 +473,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&a2_full[b]));        // one arrival per warp
+      if (lane == 0 && (warp & 3) == 0) ATT_TR(wb, j, 1);
     }
-  } else {
-    // ---- builder / layer-2 warpgroups: A1 two steps ahead, acc2 -> score -> S, steps of parity wb --
-    const int wb = (warp >> 2) & 1;
+  } else if (warp >= 16) {
+    // ---- builder warpgroup: A1 of step t (buffer t & 1) as soon as the layer-1 MMA of step t-2 has read it --
     const int row = (warp & 3) * 32 + lane;
-    const int n = tile * 128 + row;
-    const bool valid = n < p.n_cand;
-    const uint32_t lane_addr = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);
-
     // q row as 16-byte chunks (dp <= 64 -> at most 8), with the constant-1 column when it lives here
     uint4 qv[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c)
       qv[c] = c < nch ? *reinterpret_cast<const uint4*>(qs + (c * 128 + row) * 8) : make_uint4(0, 0, 0, 0);
-    // constant part of this parity's A1 buffer: the q segment (and the ones column)
-    // (chunk c of 8 fp16 is 4 tensor-memory columns of this thread's lane)
-    {
-      const uint32_t a1t = lane_addr + G.c_a1 + wb * (k1 / 2);
+    // constant part of both A1 buffers: the q segment and the chunks past the three segments (the constant 1
+    // when q has no padding column for it, zeros otherwise); chunk c of row `row` is 16 bytes at
+    // c * (128 * 16) + row * 16
+    for (int b = 0; b < 2; ++b) {
+      uint8_t* a1b = a1s + b * (128 * k1 * 2) + row * 16;
 #pragma unroll
       for (int c = 0; c < 8; ++c)
-        if (c < nch) tmem_st4(a1t + 4 * c, qv[c].x, qv[c].y, qv[c].z, qv[c].w);
-      // chunks past the three segments: the constant 1 when q has no padding column for it, zeros otherwise
+        if (c < nch) *reinterpret_cast<uint4*>(a1b + c * (128 * 16)) = qv[c];
       for (int c = 3 * nch; c < k1 / 8; ++c)
-        tmem_st4(a1t + 4 * c, (c == 3 * nch && G.ones1 == 3 * dp) ? 0x00003C00u : 0u, 0u, 0u, 0u);
-      tmem_wait_st();
+        *reinterpret_cast<uint4*>(a1b + c * (128 * 16)) =
+            make_uint4((c == 3 * nch && G.ones1 == 3 * dp) ? 0x00003C00u : 0u, 0u, 0u, 0u);
     }
-
-    auto build_a1 = [&](int t) {
-      const uint32_t a1t = lane_addr + G.c_a1 + (t & 1) * (k1 / 2);
+    for (int t = 0; t < tl; ++t) {
+      if (t >= 2) {
+        const int jf = t - 2;                                   // the step whose layer-1 MMA read this buffer last
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[jf % G.na1]), (uint32_t)(jf / G.na1) & 1u, 24))) break;
+      }
+      if (lane == 0 && (warp & 3) == 0) ATT_TR(5, t, 0);
+      uint8_t* a1b = a1s + (t & 1) * (128 * k1 * 2) + row * 16;
       const uint4* kt = reinterpret_cast<const uint4*>(khs + t * dp);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -480,31 +514,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
 #pragma unroll
           for (int e = 0; e < 4; ++e) ph2[e] = __hmul2(qh[e], kh[e]);
           // q's padding column holding the constant 1 gives 1*0 in `pr`; its W0 rows are zero anyway
-          tmem_st4(a1t + 4 * (nch + c), kc.x, kc.y, kc.z, kc.w);
-          tmem_st4(a1t + 4 * (2 * nch + c), pr.x, pr.y, pr.z, pr.w);
+          *reinterpret_cast<uint4*>(a1b + (nch + c) * (128 * 16)) = kc;
+          *reinterpret_cast<uint4*>(a1b + (2 * nch + c) * (128 * 16)) = pr;
         }
       }
-      tmem_wait_st();
-      tc_fence_before_sync();
+      fence_proxy_async_smem();                               // the MMA reads A1 through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&a1_full[t & 1]));
-    };
+      if (lane == 0 && (warp & 3) == 0) ATT_TR(5, t, 1);
+    }
+  } else {
+    // ---- layer-2 warpgroups: acc2 -> score -> S, steps of parity wb ------------------------------------
+    const int wb = (warp >> 2) & 1;
+    const int row = (warp & 3) * 32 + lane;
+    const int n = tile * 128 + row;
+    const bool valid = n < p.n_cand;
+    const uint32_t lane_addr = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);
 
     bool ok = true;
     const int npairs2 = (h1_ + 1) / 2;
-    if (tl > wb) build_a1(wb);
     for (int j = wb; j < tl; j += 2) {
       const int b = wb;
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      if (j + 2 < tl) {
-        // A1[b] is free once M1(j) has read it
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[b]), ph, 24));
-        if (!ok) break;
-        build_a1(j + 2);
-      }
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph, 21));
       if (!ok) break;
       tc_fence_after_sync();
+      if (lane == 0 && (warp & 3) == 0) ATT_TR(2 + wb, j, 2);
       const uint32_t acc2 = lane_addr + G.c_acc2 + b * h1p;
       __half2 part[4];
 #pragma unroll
@@ -541,6 +576,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc2_free[b]));
+      if (lane == 0 && (warp & 3) == 0) ATT_TR(2 + wb, j, 3);
       // short fp16 chains (h1p/8 terms each), combined in fp32
       const float2 f0 = __half22float2(part[0]), f1 = __half22float2(part[1]);
       const float2 f2 = __half22float2(part[2]), f3 = __half22float2(part[3]);
@@ -572,7 +608,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       __half* o = p.out + ((int64_t)r * p.n_cand + n) * p.ldo;
       for (int c = 0; c < np; c += 16) {
         float v[16];
-        tmem_ld16(lane_addr + G.c_a1 + c, v);
+        tmem_ld16(lane_addr + G.c_acc3 + c, v);
         if (valid) {
 #pragma unroll
           for (int e = 0; e < 16; ++e)
@@ -595,7 +631,7 @@ bool tc_eligible(const xb_din_att_args& a, int* why) {
   if (g.dp > 64) { if (why) *why = 1; return false; }
   if (g.h0p > 128 || g.h1p > 64) { if (why) *why = 2; return false; }
   if (g.tp > 256) { if (why) *why = 5; return false; }
-  if (g.cols > TMEM_COLS || g.np > g.k1 / 2) { if (why) *why = 6; return false; }
+  if (g.cols > TMEM_COLS || (g.c_acc3 == 0 && g.np > g.na1 * g.h0p)) { if (why) *why = 6; return false; }
   if (tc_layout(g, a.T).total > 220 * 1024) { if (why) *why = 3; return false; }
   if (a.use_softmax && a.scores) { if (why) *why = 4; return false; }   // normalised scores are not written out
   return true;
