@@ -164,7 +164,8 @@ __global__ void __launch_bounds__(AU_THREADS, 2) augru_tc_kernel(const __grid_co
   const uint32_t tmem0 = tmem_base_s;
 
   if (warp == AU_MMA_WARP) {
-    if (lane == 0) {
+    // whole warp in uniform control flow, one elected lane issues: the descriptors stay in uniform registers
+    {
       const int nks = G.k / 16, sel_ks = (nch - 1) / 2;            // nks <= 4 (H <= 64)
       const uint32_t b1a = smem_u32(b1s), b2a = smem_u32(b2s);
       // descriptors for selector group 0; only the k step with the selector chunk moves with the group
@@ -188,21 +189,21 @@ __global__ void __launch_bounds__(AU_THREADS, 2) augru_tc_kernel(const __grid_co
       for (int t = 0; t < T; ++t) {
         const uint32_t ph = (uint32_t)t & 1u;
         const uint64_t grp = (uint64_t)(t >> 2);
-        if (!mbar_wait(smem_u32(a1_full), ph, 30)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(a1_full), ph, 30))) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           if (ks < nks)
-            mma_f16_ts(tmem0, tmem0 + G.c_a1 + 8 * ks, d1[ks] + (ks == sel_ks ? grp * delta1 : 0ull), p.idesc1, ks > 0 ? 1u : 0u);
-        mma_commit(smem_u32(acc1_full));
-        if (!mbar_wait(smem_u32(a2_full), ph, 31)) break;
+            mma_f16_ts_elect(tmem0, tmem0 + G.c_a1 + 8 * ks, d1[ks] + (ks == sel_ks ? grp * delta1 : 0ull), p.idesc1, ks > 0 ? 1u : 0u);
+        mma_commit_elect(smem_u32(acc1_full));
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(a2_full), ph, 31))) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           if (ks < nks)
-            mma_f16_ts(tmem0 + G.c_acc2, tmem0 + G.c_a2 + 8 * ks, d2[ks] + (ks == sel_ks ? grp * delta2 : 0ull), p.idesc2,
-                       ks > 0 ? 1u : 0u);
-        mma_commit(smem_u32(acc2_full));
+            mma_f16_ts_elect(tmem0 + G.c_acc2, tmem0 + G.c_a2 + 8 * ks, d2[ks] + (ks == sel_ks ? grp * delta2 : 0ull), p.idesc2,
+                             ks > 0 ? 1u : 0u);
+        mma_commit_elect(smem_u32(acc2_full));
       }
     }
   } else {

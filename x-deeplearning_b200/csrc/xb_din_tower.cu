@@ -252,7 +252,10 @@ __global__ void __launch_bounds__(TW_THREADS, 1) din_tower_tc_kernel(const __gri
   const uint32_t tmem0 = tmem_base_s;
 
   if (warp == TW_MMA_WARP) {
-    if (lane == 0) {
+    // the whole warp runs the issue loop in uniform control flow and one elected lane issues: the descriptors
+    // stay in uniform registers, which the MMA instruction reads, and an MMA issues several times faster than
+    // from one thread under `if (lane == 0)`
+    {
       const uint64_t db1_0 = make_desc_interleaved(smem_u32(smem + G.o_w1), n1p * 16, 128);
       const uint64_t db2_0 = make_desc_interleaved(smem_u32(smem + G.o_w2), n2p * 16, 128);
       const uint64_t db1_step = (uint64_t)((2 * n1p * 16) >> 4), db2_step = (uint64_t)((2 * n2p * 16) >> 4);
@@ -260,26 +263,19 @@ __global__ void __launch_bounds__(TW_THREADS, 1) din_tower_tc_kernel(const __gri
       uint32_t it = 0;
       for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
         const uint32_t ph = it & 1u;
-        if (!mbar_wait(smem_u32(a1_full), ph, 30)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(a1_full), ph, 30))) break;
         tc_fence_after_sync();
-        uint32_t ta = tmem0 + G.c_a1;
-        uint64_t db = db1_0;
-        mma_f16_ts(tmem0, ta, db, p.idesc1, 0u);
-        for (int ks = 1; ks < nks1; ++ks) {
-          ta += 8; db += db1_step;
-          mma_f16_ts(tmem0, ta, db, p.idesc1, 1u);
-        }
-        mma_commit(smem_u32(acc1_full));
-        if (!mbar_wait(smem_u32(a2_full), ph, 31)) break;
+#pragma unroll 4
+        for (int ks = 0; ks < nks1; ++ks)
+          mma_f16_ts_elect(tmem0, tmem0 + G.c_a1 + 8 * ks, db1_0 + (uint64_t)ks * db1_step, p.idesc1, ks > 0 ? 1u : 0u);
+        mma_commit_elect(smem_u32(acc1_full));
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(a2_full), ph, 31))) break;
         tc_fence_after_sync();
-        ta = tmem0 + G.c_a2;
-        db = db2_0;
-        mma_f16_ts(tmem0 + G.c_acc2, ta, db, p.idesc2, 0u);
-        for (int ks = 1; ks < nks2; ++ks) {
-          ta += 8; db += db2_step;
-          mma_f16_ts(tmem0 + G.c_acc2, ta, db, p.idesc2, 1u);
-        }
-        mma_commit(smem_u32(acc2_full));
+#pragma unroll 4
+        for (int ks = 0; ks < nks2; ++ks)
+          mma_f16_ts_elect(tmem0 + G.c_acc2, tmem0 + G.c_a2 + 8 * ks, db2_0 + (uint64_t)ks * db2_step, p.idesc2,
+                           ks > 0 ? 1u : 0u);
+        mma_commit_elect(smem_u32(acc2_full));
       }
     }
   } else {

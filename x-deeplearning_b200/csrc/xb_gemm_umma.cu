@@ -312,7 +312,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // The whole warp runs the issue loop in uniform control flow and one elected lane issues: the descriptors then
+    // live in uniform registers, which is what the MMA instruction reads, and the issue cost per MMA drops to about
+    // a third of what one thread under `if (lane == 0)` pays.
+    {
       int s = 0, it = 0;
       uint32_t ph = 0;
       uint32_t b_loads = 0;
@@ -320,18 +323,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       for (uint32_t tile = tile_first; tile < tile_end && ok; tile += tile_step, ++it) {
         const int as = it & 1;
-        ok = mbar_wait(smem_u32(&acc_empty[as]), ((uint32_t)(it >> 1) & 1u) ^ 1u, 4);   // epilogue drained it
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc_empty[as]), ((uint32_t)(it >> 1) & 1u) ^ 1u, 4));   // epilogue drained it
         if (!ok) break;
         if (bres && tile / (uint32_t)p.tiles_m != cur_bn) {
           cur_bn = tile / (uint32_t)p.tiles_m;
-          ok = mbar_wait(smem_u32(&b_full), b_loads & 1u, 6);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&b_full), b_loads & 1u, 6));
           if (!ok) break;
           ++b_loads;
         }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + as * acc_stride;
         for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
-          ok = mbar_wait(smem_u32(&full_bar[s]), ph, 2);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[s]), ph, 2));
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem_a + s * A_STAGE_BYTES);
@@ -340,14 +343,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           for (int k = 0; k < BLOCK_K / 16; ++k) {
             const uint64_t da = make_desc_sw128(a_addr + k * 32, 1024);
             const uint64_t db = make_desc_sw128(b_addr + k * 32, 1024);
-            mma_f16_ss(tmem_acc, da, db, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            mma_f16_ss_elect(tmem_acc, da, db, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          mma_commit(smem_u32(&empty_bar[s]));     // slot free once these MMAs have read it
+          mma_commit_elect(smem_u32(&empty_bar[s]));     // slot free once these MMAs have read it
         }
-        mma_commit(smem_u32(&acc_full[as]));       // accumulator complete
+        mma_commit_elect(smem_u32(&acc_full[as]));       // accumulator complete
         // the next tile of this CTA needs another B tile: tell the producer when these MMAs are done with this one
         if (bres && ok && tile + tile_step < tile_end && (tile + tile_step) / (uint32_t)p.tiles_m != cur_bn)
-          mma_commit(smem_u32(&b_free));
+          mma_commit_elect(smem_u32(&b_free));
       }
     }
   } else {

@@ -952,9 +952,13 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     int ns = 1;
     if (fast) {
       // one sub-team per segment gives the fewest instructions per id (no cross-lane combine, whole rows
-      // per lane group); teams only grow while the launch would otherwise leave SMs without warps
+      // per lane group); teams grow while the launch would otherwise leave SMs without warps, or while a
+      // segment is so long that one sub-team would walk it in more than a dozen dependent batches of ids
+      // (a 100-step behaviour list on 4 lanes is 25 id-load -> row-load round trips in a row; on a whole warp, 4)
       const int64_t want_warps = (int64_t)sm_count() * 32;
-      while (ns < 32 / d.lpr && ns < avg && call_segments * (int64_t)(d.lpr * ns) / 32 < want_warps) ns <<= 1;
+      while (ns < 32 / d.lpr && ns < avg &&
+             (call_segments * (int64_t)(d.lpr * ns) / 32 < want_warps || (avg >= 48.0 && avg > 12.0 * ns)))
+        ns <<= 1;
     } else {
       while (ns < 32 / d.lpr && ns < avg) ns <<= 1;
     }
