@@ -4,8 +4,8 @@
 // Five worker warpgroups (one candidate row per thread each) split the work by
 // phase and step parity: warpgroup b (b = 0, 1) runs the layer-1 activations of
 // the steps of parity b, warpgroup 2+b the layer-2 activations for parity b, the
-// fifth builds A1 of every step two steps ahead; one more warp issues every MMA,
-// in the order the workers need them (the tensor pipe runs MMAs in issue order).
+// fifth builds A1 of every step two steps ahead; two more warps issue the MMAs,
+// one per layer (the closing product goes with layer 2).
 // The layer-1 accumulator and the layer-2 operand are three deep when tensor
 // memory has room (two otherwise), the rest is double-buffered by step parity,
 // so in steady state the tensor pipe, the SFU and the FP16 pipe overlap: the
@@ -44,12 +44,16 @@ namespace {
 // debug builds only: cycle stamps of CTA 0, [slot][step][event]
 __device__ long long g_att_trace[6 * 128 * 4];
 #define ATT_TR(slot, j, ev) do { if (blockIdx.x == 0 && (j) < 128) g_att_trace[((slot) * 128 + (j)) * 4 + (ev)] = clock64(); } while (0)
+#define ATT_TR_VAL(slot, j, ev, val) do { if (blockIdx.x == 0 && (j) < 128) g_att_trace[((slot) * 128 + (j)) * 4 + (ev)] = (val); } while (0)
+#define ATT_CLK() clock64()
 #else
 #define ATT_TR(slot, j, ev) do { } while (0)
+#define ATT_TR_VAL(slot, j, ev, val) do { } while (0)
+#define ATT_CLK() 0ll
 #endif
 
-constexpr int TC_THREADS = 672;          // 5 worker warpgroups + the MMA-issuing warp
-constexpr int MMA_WARP = 20;
+constexpr int TC_THREADS = 704;          // 5 worker warpgroups + one MMA-issuing warp per layer
+constexpr int MMA1_TC_WARP = 20, MMA2_TC_WARP = 21;
 constexpr int TMEM_COLS = 512;
 
 // Tensor-memory columns: [acc1 x na1 | acc2 x2 | A2 x na2 | ones | acc3]; when there is no room for the closing
@@ -173,8 +177,12 @@ __device__ __forceinline__ void pack_weights(const AttParams& p, const TcGeom& G
         A[u] = 0.5f * rs; B[u] = -0.5f * p.m0[col] * rs; C[u] = 0.5f * (1.f + g); D[u] = 0.5f * (1.f - g);
       } else if (ACT == XB_ACT_SIGMOID) { A[u] = 0.5f; C[u] = 0.5f; D[u] = 0.5f; }
     }
-    c1[j] = make_uint4(h2_bits(__floats2half2_rn(A[0], A[1])), h2_bits(__floats2half2_rn(B[0], B[1])),
-                       h2_bits(__floats2half2_rn(C[0], C[1])), h2_bits(__floats2half2_rn(D[0], D[1])));
+    // layer 1 keeps {A, B} and {C, D} apart (two column pairs per 16 bytes each): the activation runs in two
+    // stages, the first needs A and B, the second C and D
+    uint32_t* ab = reinterpret_cast<uint32_t*>(c1) + 2 * j;
+    uint32_t* cd = reinterpret_cast<uint32_t*>(c1 + h0p / 4) + 2 * j;
+    ab[0] = h2_bits(__floats2half2_rn(A[0], A[1])); ab[1] = h2_bits(__floats2half2_rn(B[0], B[1]));
+    cd[0] = h2_bits(__floats2half2_rn(C[0], C[1])); cd[1] = h2_bits(__floats2half2_rn(D[0], D[1]));
   }
   for (int j = tid; j < h1p / 2; j += nthreads) {
     float A[2] = {0, 0}, B[2] = {0, 0}, C[2] = {0, 0}, D[2] = {0, 0};
@@ -229,7 +237,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   using namespace umma;
   using umma::tanh_f16x2;
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t bars[13];
+  __shared__ __align__(8) uint64_t bars[16];
   __shared__ uint32_t tmem_base_s;
 
   const int d_ = D0 ? D0 : p.d, h0_ = H0 ? H0 : p.h0, h1_ = H1 ? H1 : p.h1;
@@ -305,21 +313,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     kts[(t >> 3) * (np * 8) + e * 8 + (t & 7)] = v;
   }
   // barriers (b = step & 1, i = step % na1):
-  //   a1_full[b]   4 builder warps       -> MMA warp: A1 of a step is in shared memory
+  //   a1_full[b]   4 builder warps       -> layer-1 MMA warp: A1 of a step is in shared memory
   //   acc1_full[i] tcgen05.commit        -> layer-1 warpgroups: layer-1 accumulator complete; builder: A1 read
-  //   a2_full[b]   4 layer-1 warps       -> MMA warp: A2 written and the step's acc1 buffer drained
-  //   acc2_full[b] tcgen05.commit        -> both warpgroups: layer-2 accumulator complete
-  //   acc2_free[b] 4 layer-2 warps       -> MMA warp: acc2[b] drained
+  //   acc1_free[i] 4 layer-1 warps       -> layer-1 MMA warp: the accumulator's last block is in registers
+  //   a2_full[b]   4 layer-1 warps       -> layer-2 MMA warp: A2 written
+  //   acc2_full[b] tcgen05.commit        -> layer-2 warpgroups: layer-2 accumulator complete; layer-1
+  //                                         warpgroups: the MMA has read A2 (and the MMA warp saw a2_full)
+  //   acc2_free[b] 4 layer-2 warps       -> layer-2 MMA warp: acc2[b] drained
   //   s_full, acc3_full: the closing S*K product
-  // A barrier never runs two phases ahead of a waiter: the MMA of a later step on the same barrier needs
-  // something that waiter produces after its wait (the drained accumulator, the next A1).
+  // A barrier never runs two phases ahead of a waiter: whatever completes its next phase needs something that
+  // waiter produces after its wait (the drained accumulator, the next A1, the next A2).
   uint64_t* a1_full = &bars[0];
   uint64_t* acc1_full = &bars[2];
-  uint64_t* a2_full = &bars[5];
-  uint64_t* acc2_full = &bars[7];
-  uint64_t* acc2_free = &bars[9];
-  uint64_t* s_full = &bars[11];
-  uint64_t* acc3_full = &bars[12];
+  uint64_t* acc1_free = &bars[5];
+  uint64_t* a2_full = &bars[8];
+  uint64_t* acc2_full = &bars[10];
+  uint64_t* acc2_free = &bars[12];
+  uint64_t* s_full = &bars[14];
+  uint64_t* acc3_full = &bars[15];
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&a1_full[b]), 4);
@@ -327,44 +338,49 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       mbar_init(smem_u32(&acc2_full[b]), 1);
       mbar_init(smem_u32(&acc2_free[b]), 4);
     }
-    for (int i = 0; i < 3; ++i) mbar_init(smem_u32(&acc1_full[i]), 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(smem_u32(&acc1_full[i]), 1);
+      mbar_init(smem_u32(&acc1_free[i]), 4);
+    }
     mbar_init(smem_u32(s_full), 8);
     mbar_init(smem_u32(acc3_full), 1);
     fence_barrier_init();
   }
-  if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
+  if (warp == MMA1_TC_WARP) tmem_alloc(smem_u32(&tmem_base_s), TMEM_COLS);
   fence_proxy_async_smem();          // operands were written through the generic proxy
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem0 = tmem_base_s;
 
-  if (warp == MMA_WARP) {
-    // ---- MMA issue: one thread for both layers and the closing product --------------------------------
-    // The whole warp runs this code in uniform control flow and one elected lane issues: that keeps the
+  if (warp == MMA1_TC_WARP) {
+    // ---- layer-1 MMA issue -----------------------------------------------------------------------------
+    // Both MMA warps run their loops in uniform control flow and one elected lane issues: that keeps the
     // descriptors in uniform registers, and with the chains unrolled over descriptors computed once an MMA
-    // issues in about 36 cycles instead of 100. The tensor pipe runs MMAs in issue order, so the order is
-    // chosen here. When the layer-1 warps finish step j they have written A2 of step j and drained that step's
-    // acc1 buffer: layer 2 of step j goes first (its warps wait for it), layer 1 of step j + na1 (the next
-    // user of the buffer) follows.
+    // issues in about 36 cycles instead of 100. Step j + na1 reuses the accumulator of step j: it is issued as
+    // soon as the layer-1 warps have that accumulator's last block in registers.
     constexpr int NK1 = D0 ? tc_geom(D0, H0, H1, 16).k1 / 16 : 13;       // k steps of layer 1 (d <= 64)
-    constexpr int NK2 = H0 ? tc_geom(D0, H0, H1, 16).h0p / 16 + 1 : 9;   // and layer 2; its last is the bias chunk
-    const int nks1 = D0 ? NK1 : k1 / 16, nks2 = H0 ? NK2 : h0p / 16 + 1;
+    const int nks1 = D0 ? NK1 : k1 / 16;
     const int na1 = G.na1;
-    uint64_t db1[NK1], db2[NK2];
+    uint64_t db1[NK1];
     {
       const uint64_t db1_0 = make_desc_interleaved(smem_u32(w0s), h0p * 16, 128);
-      const uint64_t db2_0 = make_desc_interleaved(smem_u32(w1s), h1p * 16, 128);
 #pragma unroll
       for (int ks = 0; ks < NK1; ++ks) db1[ks] = db1_0 + (uint64_t)(ks * ((2 * h0p * 16) >> 4));
-#pragma unroll
-      for (int ks = 0; ks < NK2; ++ks) db2[ks] = db2_0 + (uint64_t)(ks * ((2 * h1p * 16) >> 4));
     }
     const uint64_t da_step = (uint64_t)((2 * 128 * 16) >> 4);
     const uint64_t da1_0 = make_desc_interleaved(smem_u32(a1s), 128 * 16, 128);
     const uint64_t da1_buf = (uint64_t)((128 * k1 * 2) >> 4);
-    bool ok = true;
-    auto issue_l1 = [&](int j, int i1) {                       // layer 1 of step j into acc1 buffer i1
+    int i1 = 0;                                               // acc1 buffer of the step being issued
+    for (int j = 0; j < tl; ++j) {
+      bool ok = true;
+      if (j >= na1) {
+        const int jf = j - na1;                               // the step that used this accumulator before
+        ok = mbar_wait(smem_u32(&acc1_free[i1]), (uint32_t)(jf / na1) & 1u, 11);
+      }
+      ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(&a1_full[j & 1]), (uint32_t)(j >> 1) & 1u, 10));
+      if (!ok) break;
+      tc_fence_after_sync();
       const uint64_t da = da1_0 + ((j & 1) ? da1_buf : 0);
       const uint32_t acc1 = tmem0 + i1 * h0p;
 #pragma unroll
@@ -372,8 +388,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         if (ks < nks1) mma_f16_ss_elect(acc1, da + (uint64_t)ks * da_step, db1[ks], p.idesc1, ks > 0 ? 1u : 0u);
       mma_commit_elect(smem_u32(&acc1_full[i1]));
       if (lane == 0) ATT_TR(4, j, 2);
-    };
-    auto issue_l2 = [&](int j, int a2i) {                      // layer 2 of step j from A2 buffer a2i
+      i1 = i1 + 1 == na1 ? 0 : i1 + 1;
+    }
+  } else if (warp == MMA2_TC_WARP) {
+    // ---- layer-2 MMA issue, then the closing S*K product -----------------------------------------------
+    constexpr int NK2 = H0 ? tc_geom(D0, H0, H1, 16).h0p / 16 + 1 : 9;   // the last k step is the bias chunk
+    const int nks2 = H0 ? NK2 : h0p / 16 + 1;
+    uint64_t db2[NK2];
+    {
+      const uint64_t db2_0 = make_desc_interleaved(smem_u32(w1s), h1p * 16, 128);
+#pragma unroll
+      for (int ks = 0; ks < NK2; ++ks) db2[ks] = db2_0 + (uint64_t)(ks * ((2 * h1p * 16) >> 4));
+    }
+    bool ok = true;
+    int a2i = 0;                                              // j % na2
+    for (int j = 0; j < tl; ++j) {
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      // the layer-1 warps have written A2 of step j; acc2 of this parity was drained (step j-2)
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a2_full[j & 1]), ph, 12) &&
+                                       mbar_wait(smem_u32(&acc2_free[j & 1]), ph ^ 1u, 13));
+      if (!ok) break;
+      if (lane == 0) ATT_TR(4, j, 0);
+      tc_fence_after_sync();
       const uint32_t acc2 = tmem0 + G.c_acc2 + (j & 1) * h1p;
       const uint32_t ta = tmem0 + G.c_a2 + a2i * (h0p / 2);
 #pragma unroll
@@ -382,35 +418,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
           mma_f16_ts_elect(acc2, ks == nks2 - 1 ? tmem0 + G.c_ones : ta + 8 * ks, db2[ks], p.idesc2, ks > 0 ? 1u : 0u);
       mma_commit_elect(smem_u32(&acc2_full[j & 1]));
       if (lane == 0) ATT_TR(4, j, 1);
-    };
-    for (int j = 0; j < na1 && j < tl && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a1_full[j & 1]), (uint32_t)(j >> 1) & 1u, 10));
-      if (ok) { tc_fence_after_sync(); issue_l1(j, j); }
-    }
-    int a2i = 0, i1 = 0;                                      // j % na2, j % na1
-    for (int j = 0; j < tl && ok; ++j) {
-      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-      // the layer-1 warps have written A2 of step j and drained its acc1 buffer; acc2 of this parity was
-      // drained by the layer-2 warps (step j-2)
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a2_full[j & 1]), ph, 11) &&
-                                       mbar_wait(smem_u32(&acc2_free[j & 1]), ph ^ 1u, 13));
-      if (!ok) break;
-      if (lane == 0) ATT_TR(4, j, 0);
-      tc_fence_after_sync();
-      issue_l2(j, a2i);
-      const int jn = j + na1;
-      if (jn < tl) {
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a1_full[jn & 1]), (uint32_t)(jn >> 1) & 1u, 14));
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_l1(jn, i1);
-      }
       a2i = a2i + 1 == G.na2 ? 0 : a2i + 1;
-      i1 = i1 + 1 == na1 ? 0 : i1 + 1;
     }
     // weighted sum over the steps: out = S * K
-    if (ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full), 0, 12))) {
+    if (ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full), 0, 14))) {
       tc_fence_after_sync();
+      const uint64_t da_step = (uint64_t)((2 * 128 * 16) >> 4);
       uint64_t da = make_desc_interleaved(smem_u32(ss), 128 * 16, 128);
       uint64_t db = make_desc_interleaved(smem_u32(kts), np * 16, 128);
       const uint64_t db3 = (uint64_t)((2 * np * 16) >> 4);
@@ -445,35 +458,83 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       tc_fence_after_sync();
       if (lane == 0 && (warp & 3) == 0) ATT_TR(wb, j, 0);
       const uint32_t acc1 = lane_addr + i1 * h0p;
-      // blocks of 16 columns (8 fp16 pairs): the load of the next block is in flight while this one is
-      // converted, activated and stored
-      const int nblk = h0p / 16;
-      uint32_t va[16], vb[16];
-      auto block = [&](int blk, uint32_t (&cur)[16], uint32_t (&nxt)[16]) {
-        tmem_wait_ld(cur);
-        if (blk + 1 < nblk) tmem_ld16_nowait(acc1 + 16 * (blk + 1), nxt);
+      // Blocks of 16 columns (8 fp16 pairs), as a two-stage software pipeline: stage one of block b+1 (convert,
+      // tanh argument, SFU) is issued before stage two of block b (scale, multiply, store), so the SFU latency of
+      // one block hides behind the arithmetic of the other instead of being exposed at every block boundary (the
+      // tensor-memory instructions are ordered among themselves, which would otherwise serialise the blocks).
+      constexpr int NBLK = H0 ? tc_geom(D0, H0, H1, 16).h0p / 16 : 8;
+      const int nblk = H0 ? NBLK : h0p / 16;
+      const uint4* __restrict__ cab = c1;                   // {A, B} of two column pairs per entry
+      const uint4* __restrict__ ccd = c1 + h0p / 4;         // {C, D}
+      uint32_t v[2][16], x[2][8], th[2][8];
+      auto stage1 = [&](int blk, int s) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          x[s][e] = h2_bits(__floats2half2_rn(__uint_as_float(v[s][2 * e]), __uint_as_float(v[s][2 * e + 1])));
+        if (ACT != XB_ACT_NONE) {
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const uint4 k = cab[4 * blk + e / 2];
+            th[s][e] = umma::tanh_f16x2(h2_bits(__hfma2(bits_h2(x[s][e]), bits_h2(k.x), bits_h2(k.y))));
+            th[s][e + 1] = umma::tanh_f16x2(h2_bits(__hfma2(bits_h2(x[s][e + 1]), bits_h2(k.z), bits_h2(k.w))));
+          }
+        }
+      };
+      auto stage2 = [&](int blk, int s) {
         uint32_t y[8];
-        pair_l1_block<ACT>(cur, c1 + 8 * blk, y);
-        if (blk == 0 && G.na2 == 2) {
-          // with two A2 buffers, this one is free once the layer-2 MMA of step j-2 has read it: waited for
-          // after the first block's arithmetic (with three buffers the MMA of step j-3 was issued before this
-          // step's layer-1 MMA, so it completed first)
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          if (ACT == XB_ACT_NONE) { y[e] = x[s][e]; y[e + 1] = x[s][e + 1]; continue; }
+          const uint4 k = ccd[4 * blk + e / 2];
+          const __half2 g0 = __hfma2(bits_h2(th[s][e]), bits_h2(k.y), bits_h2(k.x));
+          const __half2 g1 = __hfma2(bits_h2(th[s][e + 1]), bits_h2(k.w), bits_h2(k.z));
+          y[e] = h2_bits(ACT == XB_ACT_DICE ? __hmul2(bits_h2(x[s][e]), g0) : g0);
+          y[e + 1] = h2_bits(ACT == XB_ACT_DICE ? __hmul2(bits_h2(x[s][e + 1]), g1) : g1);
+        }
+        if (blk == 0) {
+          // Before the first store: the layer-2 MMA of step j-2 has completed, and with it every layer-2 MMA
+          // issued before it (one warp issues them in order), so the A2 buffer this step overwrites has been
+          // read whether there are two or three of them. That MMA's commit also tells that its warp has seen
+          // a2_full of step j-2, so this warpgroup's next arrival cannot run that barrier two phases ahead.
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph ^ 1u, 23));
           if (ok) tc_fence_after_sync();
         }
         if (ok) tmem_st8(a2t + 8 * blk, y);
       };
-      tmem_ld16_nowait(acc1, va);
-      for (int blk = 0; blk < nblk && ok; blk += 2) {
-        block(blk, va, vb);
-        if (blk + 1 < nblk && ok) block(blk + 1, vb, va);
+      auto release_acc1 = [&]() {                            // the accumulator's last block is in registers
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&acc1_free[i1]));
+      };
+      tmem_ld16_nowait(acc1, v[0]);
+      tmem_wait_ld(v[0]);
+      if (nblk > 1) tmem_ld16_nowait(acc1 + 16, v[1]);
+      else release_acc1();
+      stage1(0, 0);
+#pragma unroll
+      for (int blk = 0; blk < NBLK; ++blk) {
+        if (blk < nblk && ok) {
+          const int s = blk & 1;
+          if (blk + 1 < nblk) {
+            tmem_wait_ld(v[s ^ 1]);
+            // v[s] was consumed by stage one of this block: its registers take the block after the next
+            if (blk + 2 < nblk) tmem_ld16_nowait(acc1 + 16 * (blk + 2), v[s]);
+            else release_acc1();
+            stage1(blk + 1, s ^ 1);
+          }
+          stage2(blk, s);
+        }
       }
       if (!ok) break;
+      const long long tr1 = ATT_CLK();
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&a2_full[b]));        // one arrival per warp
-      if (lane == 0 && (warp & 3) == 0) ATT_TR(wb, j, 1);
+      if (lane == 0 && (warp & 3) == 0) {
+        ATT_TR(wb, j, 1);
+        ATT_TR_VAL(wb, j, 3, ATT_CLK() - tr1);
+      }
     }
   } else if (warp >= 16) {
     // ---- builder warpgroup: A1 of step t (buffer t & 1) as soon as the layer-1 MMA of step t-2 has read it --
@@ -620,7 +681,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == MMA_WARP) {
+  if (warp == MMA1_TC_WARP) {
     tc_fence_after_sync();
     tmem_dealloc(tmem0, TMEM_COLS);
   }
