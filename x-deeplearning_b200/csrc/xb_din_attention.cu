@@ -213,7 +213,7 @@ extern "C" int xb_din_attention(const xb_din_att_args* a, xb_stream_t stream_) {
 
 #ifdef XB_ATT_TRACE
 extern "C" int xb_debug_att_trace(long long* host) {
-  return cudaMemcpyFromSymbol(host, xb::g_att_trace, sizeof(long long) * 6 * 128 * 4) == cudaSuccess ? 0 : 1;
+  return cudaMemcpyFromSymbol(host, xb::g_att_trace, sizeof(long long) * 7 * 128 * 4) == cudaSuccess ? 0 : 1;
 }
 #endif
 

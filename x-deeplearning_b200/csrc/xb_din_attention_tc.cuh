@@ -1,13 +1,15 @@
 // tcgen05 engine of the fused DIN attention unit (included by xb_din_attention.cu).
 //
 // One CTA owns 128 candidates of one request and walks the behaviour steps.
-// Five worker warpgroups (one candidate row per thread each) split the work by
-// phase and step parity: warpgroup b (b = 0, 1) runs the layer-1 activations of
-// the steps of parity b, warpgroup 2+b the layer-2 activations for parity b, the
-// fifth builds A1 of every step two steps ahead; two more warps issue the MMAs,
-// one per layer (the closing product goes with layer 2).
+// Worker warpgroups (one candidate row per thread) split the work by phase and
+// step: layer-1 warpgroup w (one per acc1 buffer: three, or two when tensor
+// memory is short) runs the layer-1 activations of the steps j with j % na1 == w,
+// layer-2 warpgroup b (b = 0, 1) the layer-2 activations of the steps of parity b,
+// two builder warps write A1 of every step two steps ahead; two more warps issue
+// the MMAs, one per layer (the closing product goes with layer 2).
 // The layer-1 accumulator and the layer-2 operand are three deep when tensor
 // memory has room (two otherwise), the rest is double-buffered by step parity,
+// and the activation math of up to five steps is in flight on each scheduler,
 // so in steady state the tensor pipe, the SFU and the FP16 pipe overlap: the
 // layer-1 MMA of a later step runs while the layer-1 warps still work on this one.
 //   worker: A1 = [q|k_t|q*k_t] (fp16, 128 x k1) into shared memory; the q - k_t
@@ -42,7 +44,7 @@ namespace {
 
 #ifdef XB_ATT_TRACE
 // debug builds only: cycle stamps of CTA 0, [slot][step][event]
-__device__ long long g_att_trace[6 * 128 * 4];
+__device__ long long g_att_trace[7 * 128 * 4];
 #define ATT_TR(slot, j, ev) do { if (blockIdx.x == 0 && (j) < 128) g_att_trace[((slot) * 128 + (j)) * 4 + (ev)] = clock64(); } while (0)
 #define ATT_TR_VAL(slot, j, ev, val) do { if (blockIdx.x == 0 && (j) < 128) g_att_trace[((slot) * 128 + (j)) * 4 + (ev)] = (val); } while (0)
 #define ATT_CLK() clock64()
@@ -52,8 +54,8 @@ __device__ long long g_att_trace[6 * 128 * 4];
 #define ATT_CLK() 0ll
 #endif
 
-constexpr int TC_THREADS = 704;          // 5 worker warpgroups + one MMA-issuing warp per layer
-constexpr int MMA1_TC_WARP = 20, MMA2_TC_WARP = 21;
+constexpr int TC_THREADS = 768;          // warps 0-11 layer 1, 12-19 layer 2, 20-21 A1 builder, 22 and 23 MMA issue
+constexpr int TC_L2_WARP0 = 12, TC_BUILD_WARP0 = 20, MMA1_TC_WARP = 22, MMA2_TC_WARP = 23;
 constexpr int TMEM_COLS = 512;
 
 // Tensor-memory columns: [acc1 x na1 | acc2 x2 | A2 x na2 | ones | acc3]; when there is no room for the closing
@@ -74,11 +76,11 @@ __host__ __device__ constexpr TcGeom tc_geom(int d, int h0, int h1, int T) {
   g.h1p = (h1 + 15) / 16 * 16;
   g.tp = (T + 15) / 16 * 16;
   g.np = (g.dp + 15) / 16 * 16;
-  // deepest buffering that fits: (acc1, A2) = (3, 3), (3, 2), (2, 3), (2, 2)
+  // deepest buffering that fits: (acc1, A2) = (3, 3), (3, 2), (2, 2); never more A2 buffers than accumulators
   g.na1 = 2; g.na2 = 2;
-  for (int c = 0; c < 3; ++c) {
-    const int n1 = c < 2 ? 3 : 2, n2 = c == 1 ? 2 : 3;
-    if (n1 * g.h0p + 2 * g.h1p + n2 * (g.h0p / 2) + 8 <= TMEM_COLS) { g.na1 = n1; g.na2 = n2; break; }
+  for (int c = 0; c < 2; ++c) {
+    const int n2 = c == 0 ? 3 : 2;
+    if (3 * g.h0p + 2 * g.h1p + n2 * (g.h0p / 2) + 8 <= TMEM_COLS) { g.na1 = 3; g.na2 = n2; break; }
   }
 #ifdef XB_ATT_FORCE_NA1_2
   g.na1 = 2;
@@ -237,7 +239,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   using namespace umma;
   using umma::tanh_f16x2;
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t bars[16];
+  __shared__ __align__(8) uint64_t bars[20];
   __shared__ uint32_t tmem_base_s;
 
   const int d_ = D0 ? D0 : p.d, h0_ = H0 ? H0 : p.h0, h1_ = H1 ? H1 : p.h1;
@@ -312,13 +314,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     const __half v = (e < d && t < tl) ? khs[t * dp + e] : zero;
     kts[(t >> 3) * (np * 8) + e * 8 + (t & 7)] = v;
   }
-  // barriers (b = step & 1, i = step % na1):
-  //   a1_full[b]   4 builder warps       -> layer-1 MMA warp: A1 of a step is in shared memory
-  //   acc1_full[i] tcgen05.commit        -> layer-1 warpgroups: layer-1 accumulator complete; builder: A1 read
+  // barriers (b = step & 1, i = step % na1, a = step % na2):
+  //   a1_full[b]   2 builder warps       -> layer-1 MMA warp: A1 of a step is in shared memory
+  //   acc1_full[i] tcgen05.commit        -> layer-1 warpgroup i: layer-1 accumulator complete; builder: A1 read
   //   acc1_free[i] 4 layer-1 warps       -> layer-1 MMA warp: the accumulator's last block is in registers
-  //   a2_full[b]   4 layer-1 warps       -> layer-2 MMA warp: A2 written
-  //   acc2_full[b] tcgen05.commit        -> layer-2 warpgroups: layer-2 accumulator complete; layer-1
-  //                                         warpgroups: the MMA has read A2 (and the MMA warp saw a2_full)
+  //   a2_full[i]   4 layer-1 warps       -> layer-2 MMA warp: A2 written
+  //   a2_free[a]   tcgen05.commit        -> layer-1 warpgroups: the layer-2 MMA has read A2 buffer a
+  //   acc2_full[b] tcgen05.commit        -> layer-2 warpgroup b: layer-2 accumulator complete
   //   acc2_free[b] 4 layer-2 warps       -> layer-2 MMA warp: acc2[b] drained
   //   s_full, acc3_full: the closing S*K product
   // A barrier never runs two phases ahead of a waiter: whatever completes its next phase needs something that
@@ -327,20 +329,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   uint64_t* acc1_full = &bars[2];
   uint64_t* acc1_free = &bars[5];
   uint64_t* a2_full = &bars[8];
-  uint64_t* acc2_full = &bars[10];
-  uint64_t* acc2_free = &bars[12];
-  uint64_t* s_full = &bars[14];
-  uint64_t* acc3_full = &bars[15];
+  uint64_t* a2_free = &bars[11];
+  uint64_t* acc2_full = &bars[14];
+  uint64_t* acc2_free = &bars[16];
+  uint64_t* s_full = &bars[18];
+  uint64_t* acc3_full = &bars[19];
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&a1_full[b]), 4);
-      mbar_init(smem_u32(&a2_full[b]), 4);
+      mbar_init(smem_u32(&a1_full[b]), 2);
       mbar_init(smem_u32(&acc2_full[b]), 1);
       mbar_init(smem_u32(&acc2_free[b]), 4);
     }
     for (int i = 0; i < 3; ++i) {
       mbar_init(smem_u32(&acc1_full[i]), 1);
       mbar_init(smem_u32(&acc1_free[i]), 4);
+      mbar_init(smem_u32(&a2_full[i]), 4);
+      mbar_init(smem_u32(&a2_free[i]), 1);
     }
     mbar_init(smem_u32(s_full), 8);
     mbar_init(smem_u32(acc3_full), 1);
@@ -387,7 +391,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       for (int ks = 0; ks < NK1; ++ks)
         if (ks < nks1) mma_f16_ss_elect(acc1, da + (uint64_t)ks * da_step, db1[ks], p.idesc1, ks > 0 ? 1u : 0u);
       mma_commit_elect(smem_u32(&acc1_full[i1]));
-      if (lane == 0) ATT_TR(4, j, 2);
+      if (lane == 0) ATT_TR(5, j, 2);
       i1 = i1 + 1 == na1 ? 0 : i1 + 1;
     }
   } else if (warp == MMA2_TC_WARP) {
@@ -401,14 +405,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       for (int ks = 0; ks < NK2; ++ks) db2[ks] = db2_0 + (uint64_t)(ks * ((2 * h1p * 16) >> 4));
     }
     bool ok = true;
-    int a2i = 0;                                              // j % na2
+    int a2i = 0, w1 = 0;                                      // j % na2, j % na1
+    uint32_t ph1 = 0;                                         // (j / na1) & 1
     for (int j = 0; j < tl; ++j) {
       const uint32_t ph = (uint32_t)(j >> 1) & 1u;
       // the layer-1 warps have written A2 of step j; acc2 of this parity was drained (step j-2)
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a2_full[j & 1]), ph, 12) &&
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a2_full[w1]), ph1, 12) &&
                                        mbar_wait(smem_u32(&acc2_free[j & 1]), ph ^ 1u, 13));
       if (!ok) break;
-      if (lane == 0) ATT_TR(4, j, 0);
+      if (lane == 0) ATT_TR(5, j, 0);
       tc_fence_after_sync();
       const uint32_t acc2 = tmem0 + G.c_acc2 + (j & 1) * h1p;
       const uint32_t ta = tmem0 + G.c_a2 + a2i * (h0p / 2);
@@ -417,8 +422,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         if (ks < nks2)
           mma_f16_ts_elect(acc2, ks == nks2 - 1 ? tmem0 + G.c_ones : ta + 8 * ks, db2[ks], p.idesc2, ks > 0 ? 1u : 0u);
       mma_commit_elect(smem_u32(&acc2_full[j & 1]));
-      if (lane == 0) ATT_TR(4, j, 1);
+      mma_commit_elect(smem_u32(&a2_free[a2i]));
+      if (lane == 0) ATT_TR(5, j, 1);
       a2i = a2i + 1 == G.na2 ? 0 : a2i + 1;
+      if (++w1 == G.na1) { w1 = 0; ph1 ^= 1u; }
     }
     // weighted sum over the steps: out = S * K
     if (ok && __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full), 0, 14))) {
@@ -433,8 +440,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       }
     }
     mma_commit_elect(smem_u32(acc3_full));
-  } else if (warp < 8) {
-    // ---- layer-1 warpgroups: acc1 -> activation -> A2, for the steps of parity wb ---------------------
+  } else if (warp < TC_L2_WARP0) {
+    // ---- layer-1 warpgroups: acc1 -> activation -> A2; warpgroup wb owns acc1 buffer wb and takes the steps
+    //      j with j % na1 == wb (with two buffers the third warpgroup has nothing to do) -----------------------
     const int wb = warp >> 2;
     const uint32_t lane_addr = tmem0 + ((uint32_t)((warp & 3) * 32) << 16);   // TMEM lane == candidate row of the tile
     if (wb == 0) {
@@ -446,18 +454,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       tmem_wait_st();
     }
     bool ok = true;
-    int a2i = wb % G.na2;
-    for (int j = wb; j < tl; j += 2) {
-      const int b = wb;
-      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+    const int i1 = wb;
+    const uint32_t acc1 = lane_addr + i1 * h0p;
+    uint32_t ph1 = 0;                                         // (j / na1) & 1
+    for (int j = wb < G.na1 ? wb : tl; j < tl; j += G.na1, ph1 ^= 1u) {
+      const int a2i = j % G.na2;
       const uint32_t a2t = lane_addr + G.c_a2 + a2i * (h0p / 2);
-      a2i += 2; if (a2i >= G.na2) a2i -= G.na2;
-      const int i1 = j % G.na1;
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[i1]), (uint32_t)(j / G.na1) & 1u, 20));
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[i1]), ph1, 20));
       if (!ok) break;
       tc_fence_after_sync();
       if (lane == 0 && (warp & 3) == 0) ATT_TR(wb, j, 0);
-      const uint32_t acc1 = lane_addr + i1 * h0p;
       // Blocks of 16 columns (8 fp16 pairs), as a two-stage software pipeline: stage one of block b+1 (convert,
       // tanh argument, SFU) is issued before stage two of block b (scale, multiply, store), so the SFU latency of
       // one block hides behind the arithmetic of the other instead of being exposed at every block boundary (the
@@ -492,11 +498,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
           y[e + 1] = h2_bits(ACT == XB_ACT_DICE ? __hmul2(bits_h2(x[s][e + 1]), g1) : g1);
         }
         if (blk == 0) {
-          // Before the first store: the layer-2 MMA of step j-2 has completed, and with it every layer-2 MMA
-          // issued before it (one warp issues them in order), so the A2 buffer this step overwrites has been
-          // read whether there are two or three of them. That MMA's commit also tells that its warp has seen
-          // a2_full of step j-2, so this warpgroup's next arrival cannot run that barrier two phases ahead.
-          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph ^ 1u, 23));
+          // Before the first store: the layer-2 MMA that read this A2 buffer last (step j - na2) has completed.
+          // Its commit also tells that its warp has seen a2_full of every step up to j - na2, which includes
+          // this warpgroup's previous step (na2 <= na1), so the arrival that follows cannot run a2_full two
+          // phases ahead of that warp.
+          if (j >= G.na2) {
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a2_free[a2i]), (uint32_t)((j - G.na2) / G.na2) & 1u, 23));
+          }
           if (ok) tc_fence_after_sync();
         }
         if (ok) tmem_st8(a2t + 8 * blk, y);
@@ -530,38 +538,43 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&a2_full[b]));        // one arrival per warp
+      if (lane == 0) mbar_arrive(smem_u32(&a2_full[i1]));       // one arrival per warp
       if (lane == 0 && (warp & 3) == 0) {
         ATT_TR(wb, j, 1);
         ATT_TR_VAL(wb, j, 3, ATT_CLK() - tr1);
       }
     }
-  } else if (warp >= 16) {
-    // ---- builder warpgroup: A1 of step t (buffer t & 1) as soon as the layer-1 MMA of step t-2 has read it --
-    const int row = (warp & 3) * 32 + lane;
-    // q row as 16-byte chunks (dp <= 64 -> at most 8), with the constant-1 column when it lives here
-    uint4 qv[8];
+  } else if (warp >= TC_BUILD_WARP0) {
+    // ---- builder warps: A1 of step t (buffer t & 1) as soon as the layer-1 MMA of step t-2 has read it; a
+    //      thread owns rows `row` and `row + 64` and loads each chunk of k_t once for both -----------------------
+    const int row = (warp - TC_BUILD_WARP0) * 32 + lane;
+    // q rows as 16-byte chunks (dp <= 64 -> at most 8), with the constant-1 column when it lives here
+    uint4 qv[2][8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c)
-      qv[c] = c < nch ? *reinterpret_cast<const uint4*>(qs + (c * 128 + row) * 8) : make_uint4(0, 0, 0, 0);
-    // constant part of both A1 buffers: the q segment and the chunks past the three segments (the constant 1
-    // when q has no padding column for it, zeros otherwise); chunk c of row `row` is 16 bytes at
-    // c * (128 * 16) + row * 16
-    for (int b = 0; b < 2; ++b) {
-      uint8_t* a1b = a1s + b * (128 * k1 * 2) + row * 16;
+    for (int h = 0; h < 2; ++h)
 #pragma unroll
       for (int c = 0; c < 8; ++c)
-        if (c < nch) *reinterpret_cast<uint4*>(a1b + c * (128 * 16)) = qv[c];
-      for (int c = 3 * nch; c < k1 / 8; ++c)
-        *reinterpret_cast<uint4*>(a1b + c * (128 * 16)) =
-            make_uint4((c == 3 * nch && G.ones1 == 3 * dp) ? 0x00003C00u : 0u, 0u, 0u, 0u);
+        qv[h][c] = c < nch ? *reinterpret_cast<const uint4*>(qs + (c * 128 + row + 64 * h) * 8) : make_uint4(0, 0, 0, 0);
+    // constant part of both A1 buffers: the q segment and the chunks past the three segments (the constant 1
+    // when q has no padding column for it, zeros otherwise); chunk c of row r is 16 bytes at c * (128 * 16) + r * 16
+    for (int b = 0; b < 2; ++b) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint8_t* a1b = a1s + b * (128 * k1 * 2) + (row + 64 * h) * 16;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (c < nch) *reinterpret_cast<uint4*>(a1b + c * (128 * 16)) = qv[h][c];
+        for (int c = 3 * nch; c < k1 / 8; ++c)
+          *reinterpret_cast<uint4*>(a1b + c * (128 * 16)) =
+              make_uint4((c == 3 * nch && G.ones1 == 3 * dp) ? 0x00003C00u : 0u, 0u, 0u, 0u);
+      }
     }
     for (int t = 0; t < tl; ++t) {
       if (t >= 2) {
         const int jf = t - 2;                                   // the step whose layer-1 MMA read this buffer last
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[jf % G.na1]), (uint32_t)(jf / G.na1) & 1u, 24))) break;
       }
-      if (lane == 0 && (warp & 3) == 0) ATT_TR(5, t, 0);
+      if (lane == 0 && warp == TC_BUILD_WARP0) ATT_TR(6, t, 0);
       uint8_t* a1b = a1s + (t & 1) * (128 * k1 * 2) + row * 16;
       const uint4* kt = reinterpret_cast<const uint4*>(khs + t * dp);
 #pragma unroll
@@ -569,20 +582,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         if (c < nch) {
           const uint4 kc = kt[c];
           const __half2* kh = reinterpret_cast<const __half2*>(&kc);
-          const __half2* qh = reinterpret_cast<const __half2*>(&qv[c]);
-          uint4 pr;
-          __half2* ph2 = reinterpret_cast<__half2*>(&pr);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) ph2[e] = __hmul2(qh[e], kh[e]);
-          // q's padding column holding the constant 1 gives 1*0 in `pr`; its W0 rows are zero anyway
-          *reinterpret_cast<uint4*>(a1b + (nch + c) * (128 * 16)) = kc;
-          *reinterpret_cast<uint4*>(a1b + (2 * nch + c) * (128 * 16)) = pr;
+          for (int h = 0; h < 2; ++h) {
+            const __half2* qh = reinterpret_cast<const __half2*>(&qv[h][c]);
+            uint4 pr;
+            __half2* ph2 = reinterpret_cast<__half2*>(&pr);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ph2[e] = __hmul2(qh[e], kh[e]);
+            // q's padding column holding the constant 1 gives 1*0 in `pr`; its W0 rows are zero anyway
+            *reinterpret_cast<uint4*>(a1b + h * (64 * 16) + (nch + c) * (128 * 16)) = kc;
+            *reinterpret_cast<uint4*>(a1b + h * (64 * 16) + (2 * nch + c) * (128 * 16)) = pr;
+          }
         }
       }
       fence_proxy_async_smem();                               // the MMA reads A1 through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&a1_full[t & 1]));
-      if (lane == 0 && (warp & 3) == 0) ATT_TR(5, t, 1);
+      if (lane == 0 && warp == TC_BUILD_WARP0) ATT_TR(6, t, 1);
     }
   } else {
     // ---- layer-2 warpgroups: acc2 -> score -> S, steps of parity wb ------------------------------------
@@ -600,7 +616,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&acc2_full[b]), ph, 21));
       if (!ok) break;
       tc_fence_after_sync();
-      if (lane == 0 && (warp & 3) == 0) ATT_TR(2 + wb, j, 2);
+      if (lane == 0 && (warp & 3) == 0) ATT_TR(3 + wb, j, 2);
       const uint32_t acc2 = lane_addr + G.c_acc2 + b * h1p;
       __half2 part[4];
 #pragma unroll
@@ -637,7 +653,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc2_free[b]));
-      if (lane == 0 && (warp & 3) == 0) ATT_TR(2 + wb, j, 3);
+      if (lane == 0 && (warp & 3) == 0) ATT_TR(3 + wb, j, 3);
       // short fp16 chains (h1p/8 terms each), combined in fp32
       const float2 f0 = __half22float2(part[0]), f1 = __half22float2(part[1]);
       const float2 f2 = __half22float2(part[2]), f3 = __half22float2(part[3]);
