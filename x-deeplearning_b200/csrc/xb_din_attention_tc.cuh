@@ -54,8 +54,14 @@ __device__ long long g_att_trace[7 * 128 * 4];
 #define ATT_CLK() 0ll
 #endif
 
-constexpr int TC_THREADS = 768;          // warps 0-11 layer 1, 12-19 layer 2, 20-21 A1 builder, 22 and 23 MMA issue
-constexpr int TC_L2_WARP0 = 12, TC_BUILD_WARP0 = 20, MMA1_TC_WARP = 22, MMA2_TC_WARP = 23;
+#ifndef XB_TC_BUILD_WARPS
+#define XB_TC_BUILD_WARPS 2
+#endif
+constexpr int TC_BUILD_WARPS = XB_TC_BUILD_WARPS;          // 2 (two rows per thread) or 4 (one)
+constexpr int TC_BROWS = 4 / TC_BUILD_WARPS;
+// warps 0-11 layer 1, 12-19 layer 2, then the A1 builder warps, then one MMA-issuing warp per layer
+constexpr int TC_L2_WARP0 = 12, TC_BUILD_WARP0 = 20, MMA1_TC_WARP = 20 + TC_BUILD_WARPS, MMA2_TC_WARP = 21 + TC_BUILD_WARPS;
+constexpr int TC_THREADS = 32 * (22 + TC_BUILD_WARPS);
 constexpr int TMEM_COLS = 512;
 
 // Tensor-memory columns: [acc1 x na1 | acc2 x2 | A2 x na2 | ones | acc3]; when there is no room for the closing
@@ -101,7 +107,7 @@ __host__ __device__ inline TcSmemLayout tc_layout(const TcGeom& g, int T) {
   int off = 0;
   L.w0 = off; off += g.h0p * g.k1 * 2;          // W0 operand [h0p rows, k1]
   L.w1 = off; off += g.h1p * g.k2 * 2;          // W1 operand [h1p rows, k2]
-  L.a1 = off; off += 2 * 128 * g.k1 * 2;        // A1 operand [128 rows, k1], one per step parity
+  L.a1 = off; off += g.na1 * 128 * g.k1 * 2;    // A1 operand [128 rows, k1], one per acc1 buffer
   L.s = off; off += 128 * g.tp * 2;             // scores [128, tp]
   L.kt = off; off += g.np * g.tp * 2;           // K^T operand [np rows (feature), tp (step)]
   L.kh = off; off += T * g.dp * 2;              // k rows for building A1
@@ -239,7 +245,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   using namespace umma;
   using umma::tanh_f16x2;
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t bars[20];
+  __shared__ __align__(8) uint64_t bars[21];
   __shared__ uint32_t tmem_base_s;
 
   const int d_ = D0 ? D0 : p.d, h0_ = H0 ? H0 : p.h0, h1_ = H1 ? H1 : p.h1;
@@ -251,6 +257,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   int tl = p.seq_len ? p.seq_len[r] : p.T;
   tl = tl < 0 ? 0 : (tl > p.T ? p.T : tl);
 
+  if (threadIdx.x == 0) ATT_TR(6, 120, 0);
   __half* w0s = reinterpret_cast<__half*>(smem + L.w0);
   __half* w1s = reinterpret_cast<__half*>(smem + L.w1);
   uint8_t* a1s = smem + L.a1;
@@ -292,22 +299,38 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   }
   cp_async_commit();
   // what no copy writes: padding columns, rows past the last candidate, the constant-1 column, S
-  for (int idx = threadIdx.x; idx < 128 * dp; idx += TC_THREADS) {
-    const int row = idx / dp, i = idx - row * dp;
-    const bool have = i < d && tile * 128 + row < p.n_cand;
-    __half* dst = &qs[(i >> 3) * (128 * 8) + row * 8 + (i & 7)];
-    if (!async8) *dst = have ? p.q[((int64_t)r * p.n_cand + tile * 128 + row) * p.ldq + i] : (i == G.ones1 ? one : zero);
-    else if (!have) *dst = (i == G.ones1) ? one : zero;
-  }
-  for (int idx = threadIdx.x; idx < p.T * dp; idx += TC_THREADS) {
-    const int t = idx / dp, i = idx - t * dp;
-    if (!async8) khs[idx] = (i < d) ? p.k[((int64_t)r * p.T + t) * p.ldk + i] : zero;
-    else if (i >= d) khs[idx] = zero;
+  if (async8) {
+    const int rows = min(128, p.n_cand - tile * 128), npad = dp - d;
+    for (int idx = threadIdx.x; idx < 128 * npad; idx += TC_THREADS) {         // padding columns of every q row
+      const int row = idx / npad, i = d + idx - row * npad;
+      qs[(i >> 3) * (128 * 8) + row * 8 + (i & 7)] = (i == G.ones1) ? one : zero;
+    }
+    for (int idx = threadIdx.x; idx < (128 - rows) * d; idx += TC_THREADS) {   // rows past the last candidate
+      const int row = rows + idx / d, i = idx % d;
+      qs[(i >> 3) * (128 * 8) + row * 8 + (i & 7)] = zero;
+    }
+    for (int idx = threadIdx.x; idx < p.T * npad; idx += TC_THREADS) {         // padding columns of the k rows
+      const int t = idx / npad;
+      khs[t * dp + d + idx - t * npad] = zero;
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < 128 * dp; idx += TC_THREADS) {
+      const int row = idx / dp, i = idx - row * dp;
+      const bool have = i < d && tile * 128 + row < p.n_cand;
+      qs[(i >> 3) * (128 * 8) + row * 8 + (i & 7)] =
+          have ? p.q[((int64_t)r * p.n_cand + tile * 128 + row) * p.ldq + i] : (i == G.ones1 ? one : zero);
+    }
+    for (int idx = threadIdx.x; idx < p.T * dp; idx += TC_THREADS) {
+      const int t = idx / dp, i = idx - t * dp;
+      khs[idx] = (i < d) ? p.k[((int64_t)r * p.T + t) * p.ldk + i] : zero;
+    }
   }
   for (int idx = threadIdx.x; idx < 128 * tp / 8; idx += TC_THREADS)
     reinterpret_cast<uint4*>(ss)[idx] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) ATT_TR(6, 120, 3);
   cp_async_wait_all();
   __syncthreads();
+  if (threadIdx.x == 0) ATT_TR(6, 120, 1);
   // K^T operand of the closing product, from the k rows now in shared memory
   for (int idx = threadIdx.x; idx < np * tp; idx += TC_THREADS) {
     const int t = idx / np, e = idx - t * np;
@@ -315,9 +338,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     kts[(t >> 3) * (np * 8) + e * 8 + (t & 7)] = v;
   }
   // barriers (b = step & 1, i = step % na1, a = step % na2):
-  //   a1_full[b]   2 builder warps       -> layer-1 MMA warp: A1 of a step is in shared memory
+  //   a1_full[i]   2 builder warps       -> layer-1 MMA warp: A1 of a step is in shared memory
   //   acc1_full[i] tcgen05.commit        -> layer-1 warpgroup i: layer-1 accumulator complete; builder: A1 read
-  //   acc1_free[i] 4 layer-1 warps       -> layer-1 MMA warp: the accumulator's last block is in registers
+  //   acc1_free[i] 128 layer-1 threads   -> layer-1 MMA warp: the accumulator's last block is in registers
   //   a2_full[i]   4 layer-1 warps       -> layer-2 MMA warp: A2 written
   //   a2_free[a]   tcgen05.commit        -> layer-1 warpgroups: the layer-2 MMA has read A2 buffer a
   //   acc2_full[b] tcgen05.commit        -> layer-2 warpgroup b: layer-2 accumulator complete
@@ -326,23 +349,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   // A barrier never runs two phases ahead of a waiter: whatever completes its next phase needs something that
   // waiter produces after its wait (the drained accumulator, the next A1, the next A2).
   uint64_t* a1_full = &bars[0];
-  uint64_t* acc1_full = &bars[2];
-  uint64_t* acc1_free = &bars[5];
-  uint64_t* a2_full = &bars[8];
-  uint64_t* a2_free = &bars[11];
-  uint64_t* acc2_full = &bars[14];
-  uint64_t* acc2_free = &bars[16];
-  uint64_t* s_full = &bars[18];
-  uint64_t* acc3_full = &bars[19];
+  uint64_t* acc1_full = &bars[3];
+  uint64_t* acc1_free = &bars[6];
+  uint64_t* a2_full = &bars[9];
+  uint64_t* a2_free = &bars[12];
+  uint64_t* acc2_full = &bars[15];
+  uint64_t* acc2_free = &bars[17];
+  uint64_t* s_full = &bars[19];
+  uint64_t* acc3_full = &bars[20];
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&a1_full[b]), 2);
       mbar_init(smem_u32(&acc2_full[b]), 1);
       mbar_init(smem_u32(&acc2_free[b]), 4);
     }
     for (int i = 0; i < 3; ++i) {
+      mbar_init(smem_u32(&a1_full[i]), TC_BUILD_WARPS);
       mbar_init(smem_u32(&acc1_full[i]), 1);
-      mbar_init(smem_u32(&acc1_free[i]), 4);
+      mbar_init(smem_u32(&acc1_free[i]), 128);
       mbar_init(smem_u32(&a2_full[i]), 4);
       mbar_init(smem_u32(&a2_free[i]), 1);
     }
@@ -356,6 +379,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem0 = tmem_base_s;
+  if (threadIdx.x == 0) ATT_TR(6, 120, 2);
 
   if (warp == MMA1_TC_WARP) {
     // ---- layer-1 MMA issue -----------------------------------------------------------------------------
@@ -375,24 +399,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     const uint64_t da_step = (uint64_t)((2 * 128 * 16) >> 4);
     const uint64_t da1_0 = make_desc_interleaved(smem_u32(a1s), 128 * 16, 128);
     const uint64_t da1_buf = (uint64_t)((128 * k1 * 2) >> 4);
-    int i1 = 0;                                               // acc1 buffer of the step being issued
+    int i1 = 0;                                               // acc1 and A1 buffer of the step being issued
+    uint32_t ph1 = 0;                                         // (j / na1) & 1
     for (int j = 0; j < tl; ++j) {
       bool ok = true;
-      if (j >= na1) {
-        const int jf = j - na1;                               // the step that used this accumulator before
-        ok = mbar_wait(smem_u32(&acc1_free[i1]), (uint32_t)(jf / na1) & 1u, 11);
-      }
-      ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(&a1_full[j & 1]), (uint32_t)(j >> 1) & 1u, 10));
+      if (j >= na1) ok = mbar_wait(smem_u32(&acc1_free[i1]), ph1 ^ 1u, 11);   // drained by the step that used it before
+      ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(&a1_full[i1]), ph1, 10));
       if (!ok) break;
       tc_fence_after_sync();
-      const uint64_t da = da1_0 + ((j & 1) ? da1_buf : 0);
+      const uint64_t da = da1_0 + (uint64_t)i1 * da1_buf;
       const uint32_t acc1 = tmem0 + i1 * h0p;
 #pragma unroll
       for (int ks = 0; ks < NK1; ++ks)
         if (ks < nks1) mma_f16_ss_elect(acc1, da + (uint64_t)ks * da_step, db1[ks], p.idesc1, ks > 0 ? 1u : 0u);
       mma_commit_elect(smem_u32(&acc1_full[i1]));
       if (lane == 0) ATT_TR(5, j, 2);
-      i1 = i1 + 1 == na1 ? 0 : i1 + 1;
+      if (++i1 == na1) { i1 = 0; ph1 ^= 1u; }
     }
   } else if (warp == MMA2_TC_WARP) {
     // ---- layer-2 MMA issue, then the closing S*K product -----------------------------------------------
@@ -509,15 +531,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         }
         if (ok) tmem_st8(a2t + 8 * blk, y);
       };
-      auto release_acc1 = [&]() {                            // the accumulator's last block is in registers
+      // the accumulator's last block is in registers: every thread arrives, tied to a register of that block so
+      // that the arrive is issued before the block's arithmetic, not after it
+      auto release_acc1 = [&](uint32_t& dep) {
         tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&acc1_free[i1]));
+        mbar_arrive_before(smem_u32(&acc1_free[i1]), dep);
       };
       tmem_ld16_nowait(acc1, v[0]);
       tmem_wait_ld(v[0]);
       if (nblk > 1) tmem_ld16_nowait(acc1 + 16, v[1]);
-      else release_acc1();
+      else release_acc1(v[0][0]);
       stage1(0, 0);
 #pragma unroll
       for (int blk = 0; blk < NBLK; ++blk) {
@@ -527,7 +550,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
             tmem_wait_ld(v[s ^ 1]);
             // v[s] was consumed by stage one of this block: its registers take the block after the next
             if (blk + 2 < nblk) tmem_ld16_nowait(acc1 + 16 * (blk + 2), v[s]);
-            else release_acc1();
+            else release_acc1(v[s ^ 1][0]);
             stage1(blk + 1, s ^ 1);
           }
           stage2(blk, s);
@@ -545,21 +568,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       }
     }
   } else if (warp >= TC_BUILD_WARP0) {
-    // ---- builder warps: A1 of step t (buffer t & 1) as soon as the layer-1 MMA of step t-2 has read it; a
+    // ---- builder warps: A1 of step t (buffer t % na1) as soon as the layer-1 MMA of step t - na1 has read it; a
     //      thread owns rows `row` and `row + 64` and loads each chunk of k_t once for both -----------------------
     const int row = (warp - TC_BUILD_WARP0) * 32 + lane;
     // q rows as 16-byte chunks (dp <= 64 -> at most 8), with the constant-1 column when it lives here
-    uint4 qv[2][8];
+    uint4 qv[TC_BROWS][8];
 #pragma unroll
-    for (int h = 0; h < 2; ++h)
+    for (int h = 0; h < TC_BROWS; ++h)
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         qv[h][c] = c < nch ? *reinterpret_cast<const uint4*>(qs + (c * 128 + row + 64 * h) * 8) : make_uint4(0, 0, 0, 0);
     // constant part of both A1 buffers: the q segment and the chunks past the three segments (the constant 1
     // when q has no padding column for it, zeros otherwise); chunk c of row r is 16 bytes at c * (128 * 16) + r * 16
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < G.na1; ++b) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < TC_BROWS; ++h) {
         uint8_t* a1b = a1s + b * (128 * k1 * 2) + (row + 64 * h) * 16;
 #pragma unroll
         for (int c = 0; c < 8; ++c)
@@ -569,13 +592,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
               make_uint4((c == 3 * nch && G.ones1 == 3 * dp) ? 0x00003C00u : 0u, 0u, 0u, 0u);
       }
     }
+    int bi = 0;                                               // t % na1: A1 buffer, and acc1 buffer of the MMA that reads it
+    uint32_t bph = 0;                                         // (t / na1) & 1
     for (int t = 0; t < tl; ++t) {
-      if (t >= 2) {
-        const int jf = t - 2;                                   // the step whose layer-1 MMA read this buffer last
-        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[jf % G.na1]), (uint32_t)(jf / G.na1) & 1u, 24))) break;
-      }
+      // the layer-1 MMA of step t - na1 read this buffer last
+      if (t >= G.na1 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&acc1_full[bi]), bph ^ 1u, 24))) break;
       if (lane == 0 && warp == TC_BUILD_WARP0) ATT_TR(6, t, 0);
-      uint8_t* a1b = a1s + (t & 1) * (128 * k1 * 2) + row * 16;
+      uint8_t* a1b = a1s + bi * (128 * k1 * 2) + row * 16;
       const uint4* kt = reinterpret_cast<const uint4*>(khs + t * dp);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -583,7 +606,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
           const uint4 kc = kt[c];
           const __half2* kh = reinterpret_cast<const __half2*>(&kc);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < TC_BROWS; ++h) {
             const __half2* qh = reinterpret_cast<const __half2*>(&qv[h][c]);
             uint4 pr;
             __half2* ph2 = reinterpret_cast<__half2*>(&pr);
@@ -597,8 +620,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
       }
       fence_proxy_async_smem();                               // the MMA reads A1 through the async proxy
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&a1_full[t & 1]));
+      if (lane == 0) mbar_arrive(smem_u32(&a1_full[bi]));
       if (lane == 0 && warp == TC_BUILD_WARP0) ATT_TR(6, t, 1);
+      if (++bi == G.na1) { bi = 0; bph ^= 1u; }
     }
   } else {
     // ---- layer-2 warpgroups: acc2 -> score -> S, steps of parity wb ------------------------------------
@@ -679,24 +703,39 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(s_full));
 
+    if (lane == 0 && warp == 16) ATT_TR(6, 121, 0);
     if (wb == 0) ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(acc3_full), 0, 22));
     tc_fence_after_sync();
+    if (lane == 0 && warp == 16) ATT_TR(6, 121, 1);
     if (ok && wb == 0) {
       __half* o = p.out + ((int64_t)r * p.n_cand + n) * p.ldo;
+      // 8-byte stores when every row starts on an 8-byte boundary and d is a multiple of 4
+      const bool vec = (d % 4 == 0) && (p.ldo % 4 == 0) && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0;
       for (int c = 0; c < np; c += 16) {
         float v[16];
         tmem_ld16(lane_addr + G.c_acc3 + c, v);
         if (valid) {
+          if (vec) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e)
-            if (c + e < d) o[c + e] = __float2half_rn(v[e]);
+            for (int e = 0; e < 16; e += 4)
+              if (c + e < d) {
+                const __half2 lo = __floats2half2_rn(v[e], v[e + 1]), hi = __floats2half2_rn(v[e + 2], v[e + 3]);
+                *reinterpret_cast<uint2*>(o + c + e) = make_uint2(h2_bits(lo), h2_bits(hi));
+              }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              if (c + e < d) o[c + e] = __float2half_rn(v[e]);
+          }
         }
       }
     }
   }
 
+  if (lane == 0 && warp == 16) ATT_TR(6, 121, 2);
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) ATT_TR(6, 121, 3);
   if (warp == MMA1_TC_WARP) {
     tc_fence_after_sync();
     tmem_dealloc(tmem0, TMEM_COLS);

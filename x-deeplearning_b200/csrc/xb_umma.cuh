@@ -51,6 +51,11 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive that the compiler must place before the first later use of `dep` (a register whose value it leaves
+// unchanged): without the tie an arrive has no dependents and the scheduler sinks it below independent arithmetic.
+__device__ __forceinline__ void mbar_arrive_before(uint32_t bar, uint32_t& dep) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%1];" : "+r"(dep) : "r"(bar) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
