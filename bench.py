@@ -321,12 +321,13 @@ def run_ours(args):
         # the path that has collectives: measured after the replica leg, on the same process group
         del net, plans, staged, pred, mgr
         torch.cuda.empty_cache()
-        leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype, args.sharded_impl)
+        leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype, args.sharded_impl, args.capacity_factor)
         line["sharded"] = leg.run(min(K, 20), W)
     if rank == 0 and world == 1 and not args.no_cpu:
         line["embedding_pool"] = bench_pool(pk)
         line["embedding_pool"]["hbm_resident"] = bench_pool_hbm(pk)
         line["fused_gemm"] = bench_gemm(pk)
+        line["dien"] = bench_dien()
         line["cpu_baseline"] = cpu_baseline_din(model, workloads, cores=1, budget_s=args.cpu_seconds)
     if rank == 0:
         print(json.dumps(line))
@@ -675,6 +676,32 @@ def run_reference(args):
     }))
 
 
+def bench_dien(reps=20, R=16):
+    """C4: the DIEN-style model (GRU over the behaviour list, attention scores, AUGRU per candidate, tower) on
+    R requests x 1000 candidates, device-resident inputs, CUDA events. Parity of this path is a test
+    (tests/test_gpu_dien.py); here it is timed."""
+    import torch
+    from x_deeplearning_b200 import dien, ops, workloads
+    model = workloads.dien_model(0, item_rows=200_000, cate_rows=10_000, user_rows=10_000, emb_sigma=0.5)
+    net = dien.DienModel(model)
+    plans = [net.upload(net.stage(workloads.din_requests(model, 40 + i, R, N_CAND)), slot=i) for i in range(4)]
+    for i in range(3):
+        net.forward_dien(plans[i % 4])
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(reps):
+        net.forward_dien(plans[i % 4])
+    t1.record()
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    ms = t0.elapsed_time(t1) / reps
+    return {"ms_per_step": ms, "requests_per_step": R, "candidates_per_request": N_CAND, "T": T_STEPS,
+            "predictions_per_s": R * N_CAND / (ms * 1e-3),
+            "path": "pooling, xb_gru, attention scores (sigmoid, softmax over steps), xb_augru_shared (tcgen05), "
+                    "tower GEMMs with PReLU epilogues"}
+
+
 def run_micro(args):
     """Small stand-alone cases of single kernels, sized for a profiler capture that ends by itself
     (a few launches, inputs larger than L2 where DRAM figures matter, well under a few GB)."""
@@ -857,7 +884,7 @@ class ShardedLeg:
     vectors returned with NCCL all-to-all, then the MLP 1280-1024-512-256-1 (PReLU, sigmoid) data-parallel."""
     N_TABLES, GPT, DIM, BATCH = 4, 10, 32, 65536
 
-    def __init__(self, rank, world, table_rows, partial_dtype="f16", impl="abi"):
+    def __init__(self, rank, world, table_rows, partial_dtype="f16", impl="abi", capacity_factor=2.0):
         import numpy as np
         import torch
         from x_deeplearning_b200 import capi, ops, sharded, workloads
@@ -900,7 +927,7 @@ class ShardedLeg:
                 dist.broadcast_object_list(uid, src=0)
             max_ids = int(1.05 * n_tables * gpt * B * 15.5) + 4096
             self.ctx = sharded.ShardContext(rank, world, self.tables, [gpt * B] * n_tables, dim, max_ids, partial_dtype,
-                                            capacity_factor=2.0, unique_id=uid[0])
+                                            capacity_factor=capacity_factor, unique_id=uid[0])
             self.all_ids = torch.cat([f[0] for f in self.feeds])
             base, parts = 0, []
             for f in self.feeds:
@@ -1012,8 +1039,17 @@ class ShardedLeg:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         # where a step spends its time on this rank: a few more steps with an event after every phase (outside the
         # timed region; the host gaps between phases show up here too)
+        if self.ctx is not None:
+            self.ctx.profile(True)
+        lib_phases = {}
         for _ in range(5):
             self.step(timed=True)
+            if self.ctx is not None:
+                torch.cuda.synchronize()
+                for k, v in self.ctx.phase_ms().items():
+                    lib_phases[k] = lib_phases.get(k, 0.0) + v / 5
+        if self.ctx is not None:
+            self.ctx.profile(False)
         torch.cuda.synchronize()
         phase_ms = {}
         for events in self.phases:
@@ -1031,7 +1067,9 @@ class ShardedLeg:
                 "impl": ("xb_sharded_pool: one C-ABI call per step, NCCL inside the library, fixed-capacity id buckets, "
                          "no host synchronisation" if self.ctx is not None else
                          "python orchestration over torch.distributed (bucket sizes read back every step)"),
-                "phase_ms_rank0": {k: round(v, 4) for k, v in phase_ms.items()},
+                "phase_ms_rank0": dict({k: round(v, 4) for k, v in phase_ms.items()},
+                                       **({"inside_sharded_pool": {k: round(v, 4) for k, v in lib_phases.items()}}
+                                          if lib_phases else {})),
                 "parity": parity, "timing": "max over ranks, CUDA events; MLP 1280-1024-512-256-1 included"}
 
 
@@ -1043,7 +1081,7 @@ def run_sharded(args):
     rank, local_rank, world = dist_env()
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype, args.sharded_impl)
+    leg = ShardedLeg(rank, world, args.table_rows, args.partial_dtype, args.sharded_impl, args.capacity_factor)
     out = leg.run(args.steps, args.warmup)
     if rank == 0:
         print(json.dumps(dict({"micro": "sharded"}, **out)))
@@ -1068,15 +1106,23 @@ def main():
                     help="dtype of the partial sums the owners return in the row-sharded leg (f32 for the 1e-5 bar)")
     ap.add_argument("--sharded-impl", default="abi", choices=["abi", "python"],
                     help="row-sharded leg: the one-call C-ABI step (NCCL inside the library) or the Python orchestration")
+    ap.add_argument("--capacity-factor", type=float, default=2.0,
+                    help="row-sharded leg: id bucket capacity as a multiple of the mean bucket (an overflow is reported, never silent)")
     ap.add_argument("--no-sharded", action="store_true", help="skip the row-sharded leg of a multi-GPU run")
     ap.add_argument("--att-engine", type=int, default=0, help="--micro att: 0 library's choice, 2 per-step tcgen05, "
                     "3 paired, 4 split")
     ap.add_argument("--case", default=None, help="--micro pool_hbm: run one case only (shard25m_dim32 | item5m_dim18)")
-    ap.add_argument("--micro", choices=["att", "pool", "pool_hbm", "gemm", "gemm_mlp", "tower", "sharded", "batching"], help="run --steps launches of one kernel on a small case "
+    ap.add_argument("--micro", choices=["att", "pool", "pool_hbm", "gemm", "gemm_mlp", "tower", "sharded", "batching", "dien"], help="run --steps launches of one kernel on a small case "
                     "(for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     if args.micro == "sharded":
         return run_sharded(args)
+    if args.micro == "dien":
+        load_package()
+        import torch
+        torch.cuda.set_device(0)
+        print(json.dumps(dict({"micro": "dien"}, **bench_dien(reps=args.steps))))
+        return
     if args.micro == "batching":
         return run_batching(args)
     if args.micro:

@@ -280,6 +280,12 @@ int xb_a2a_return(xb_shard_ctx* ctx, xb_stream_t stream);
 int xb_shard_ctx_status(xb_shard_ctx* ctx, int32_t* overflow);
 int64_t xb_shard_ctx_bucket_capacity(const xb_shard_ctx* ctx);
 size_t xb_shard_ctx_device_bytes(const xb_shard_ctx* ctx);
+/* Optional phase timing of xb_sharded_pool (no reference counterpart): when enabled, the call records seven events on
+ * its stream; after a stream synchronisation xb_shard_ctx_phase_ms gives the milliseconds of the last call's six
+ * phases: bucket ids by owner, exchange ids, unpack + segment lengths + offsets, pool, exchange partial sums, combine. */
+int xb_shard_ctx_profile(xb_shard_ctx* ctx, int32_t enable);
+int xb_shard_ctx_phase_ms(xb_shard_ctx* ctx, float* ms6);
+
 
 /* Self-test of the bounded waits (no counterpart in the reference): launches one warp that waits on a barrier
  * nothing will ever signal and gives up after `limit_cycles`. Afterwards xb_device_status reports a non-zero

@@ -111,6 +111,8 @@ SYMBOLS = {
     "xb_shard_ctx_status": (i32, [vp, C.POINTER(i32)]),
     "xb_shard_ctx_bucket_capacity": (i64, [vp]),
     "xb_shard_ctx_device_bytes": (C.c_size_t, [vp]),
+    "xb_shard_ctx_profile": (C.c_int, [vp, i32]),
+    "xb_shard_ctx_phase_ms": (C.c_int, [vp, vp]),
     "xb_gemm": (i32, [C.POINTER(GemmArgs), vp]),
     "xb_gemm_uses_tcgen05": (i32, [C.POINTER(GemmArgs)]),
     "xb_pack_weight_kmajor": (i32, [vp, i32, i32, i32, i64, vp, i32, i64, i32, i64, i64, vp]),

@@ -97,7 +97,14 @@ struct xb_shard_ctx {
   int32_t* overflow_dev = nullptr;                  // device view of the mapped flag
   volatile int32_t* overflow_host = nullptr;
   std::vector<int64_t> source_counts;               // world x cap: slice lengths of the received buffer
+  // optional phase timing: events recorded at the phase boundaries of the last xb_sharded_pool call
+  bool profile = false;
+  cudaEvent_t ev[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
+
+static inline void mark(xb_shard_ctx* c, int i, cudaStream_t stream) {
+  if (c->profile) cudaEventRecord(c->ev[i], stream);
+}
 
 extern "C" int xb_shard_unique_id(void* id128) {
   XB_REQUIRE(id128, XB_ERR_ARG, "xb_shard_unique_id: null pointer");
@@ -113,6 +120,8 @@ extern "C" void xb_shard_ctx_destroy(xb_shard_ctx* c) {
   if (c->comm) nccl().CommDestroy(c->comm);
   if (c->arena) cudaFree(c->arena);
   if (c->overflow_host) cudaFreeHost((void*)c->overflow_host);
+  for (cudaEvent_t e : c->ev)
+    if (e) cudaEventDestroy(e);
   delete c;
 }
 
@@ -204,8 +213,10 @@ extern "C" int xb_a2a_route(xb_shard_ctx* c, const int64_t* ids, const int32_t* 
   XB_REQUIRE(c && seg_offsets && n_ids >= 0 && (n_ids == 0 || ids), XB_ERR_ARG, "xb_a2a_route: bad arguments");
   XB_REQUIRE(n_ids <= c->max_ids, XB_ERR_LIMIT, "xb_a2a_route: %lld ids, the context was sized for %lld", (long long)n_ids,
              (long long)c->max_ids);
+  mark(c, 0, stream);
   if (int rc = xb_route_ids_padded(ids, seg_offsets, c->S, n_ids, c->world, c->cap, c->send, c->overflow_dev, c->route_scratch,
                                    c->route_scratch_bytes, stream)) return rc;
+  mark(c, 1, stream);
   return all_to_all_equal(c, c->send, c->recv, (size_t)c->cap * 8, stream);
 }
 
@@ -224,6 +235,7 @@ extern "C" int xb_sharded_pool(xb_shard_ctx* c, const int64_t* ids, const int32_
   const int W = c->world;
   // 1. bucket the ids by owner (fixed-capacity buckets) and exchange them
   if (int rc = xb_a2a_route(c, ids, seg_offsets, n_ids, stream)) return rc;
+  mark(c, 2, (cudaStream_t)stream);
   // 2. at the owner: records -> rows and segment numbers, segment lengths per source, offsets per source
   if (int rc = xb_unpack_routed_padded(c->recv, W, c->cap, c->rows, c->tags, stream)) return rc;
   if (int rc = xb_tag_counts_sources(c->tags, c->source_counts.data(), W, c->counts, c->S, stream)) return rc;
@@ -232,14 +244,37 @@ extern "C" int xb_sharded_pool(xb_shard_ctx* c, const int64_t* ids, const int32_
     if (int rc = xb_scan_counts(c->counts + (int64_t)s0 * c->S, c->S, c->offsets + (int64_t)s0 * (c->S + 1), c->S + 1, n, c->S,
                                 c->scan_scratch, c->scan_scratch_bytes, stream)) return rc;
   }
+  mark(c, 3, (cudaStream_t)stream);
   // 3. pool every (source, table) segment range against that table's shard
   if (int rc = xb_shard_pool_padded(c->tables.data(), c->table_segments.data(), c->n_tables, c->rows, c->cap, c->offsets, W,
                                     n_ids, c->dim, c->partial, c->partial_dtype, stream)) return rc;
+  mark(c, 4, (cudaStream_t)stream);
   // 4. partial sums back to the sources, 5. owner-ordered combine
   if (int rc = xb_a2a_return(c, stream)) return rc;
+  mark(c, 5, (cudaStream_t)stream);
   const int32_t* seg_len = nullptr;
   XB_REQUIRE(!avg, XB_ERR_UNSUPPORTED, "xb_sharded_pool: average pooling needs the segment lengths; use kSum and scale");
-  return xb_shard_combine(c->back, c->partial_dtype, W, c->S, c->dim, seg_len, 0, out, out_stride, groups, out_dtype, stream);
+  const int rc = xb_shard_combine(c->back, c->partial_dtype, W, c->S, c->dim, seg_len, 0, out, out_stride, groups, out_dtype, stream);
+  mark(c, 6, (cudaStream_t)stream);
+  return rc;
+}
+
+// Phase timing of xb_sharded_pool: off by default (seven event records per call when on).
+extern "C" int xb_shard_ctx_profile(xb_shard_ctx* c, int32_t enable) {
+  XB_REQUIRE(c, XB_ERR_ARG, "xb_shard_ctx_profile: null context");
+  if (enable)
+    for (cudaEvent_t& e : c->ev)
+      if (!e) XB_CUDA(cudaEventCreate(&e));
+  c->profile = enable != 0;
+  return 0;
+}
+
+// Milliseconds of the six phases of the last profiled call, after the caller has synchronised its stream:
+// bucket ids by owner, exchange ids, unpack + segment lengths + offsets, pool, exchange partial sums, combine.
+extern "C" int xb_shard_ctx_phase_ms(xb_shard_ctx* c, float* ms6) {
+  XB_REQUIRE(c && ms6 && c->profile, XB_ERR_ARG, "xb_shard_ctx_phase_ms: profiling is off");
+  for (int i = 0; i < 6; ++i) XB_CUDA(cudaEventElapsedTime(&ms6[i], c->ev[i], c->ev[i + 1]));
+  return 0;
 }
 
 extern "C" int xb_shard_ctx_status(xb_shard_ctx* c, int32_t* overflow) {

@@ -242,6 +242,19 @@ class ShardContext:
     def device_bytes(self):
         return int(lib().xb_shard_ctx_device_bytes(self.h))
 
+    PHASES = ("bucket_ids", "exchange_ids", "unpack_scan", "pool", "exchange_partials", "combine")
+
+    def profile(self, enable=True):
+        """Record events at the phase boundaries of every pool() call from now on (off by default)."""
+        check(lib().xb_shard_ctx_profile(self.h, int(enable)))
+
+    def phase_ms(self):
+        """Milliseconds of the six phases of the last profiled pool() call; synchronise the stream first."""
+        import ctypes as C
+        buf = (C.c_float * 6)()
+        check(lib().xb_shard_ctx_phase_ms(self.h, C.cast(buf, C.c_void_p)))
+        return dict(zip(self.PHASES, (float(x) for x in buf)))
+
     def close(self):
         if self.h:
             lib().xb_shard_ctx_destroy(self.h)
