@@ -308,9 +308,9 @@ def run_ours(args):
         "gpu_launches": din.DinModel.LAUNCHES_PER_FORWARD * K,
         "roofline": {"kernel": "din_att_tc_kernel", "bound": "tensor", "achieved": achieved_tf,
                      "peak": pk["tf_sustained"], "unit": "TFLOP/s", "frac": achieved_tf / pk["tf_sustained"],
-                     # DRAM bytes per launch: 440 KB measured by ncu on a 4-request launch (q, k and the result
+                     # DRAM bytes per launch: 415 KB measured by ncu on a 4-request launch (q, k and the result
                      # only), scaled by the requests of one launch
-                     "traffic": 110016 * R, "traffic_source": "ncu capture of 4 requests scaled by requests per launch",
+                     "traffic": 103872 * R, "traffic_source": "ncu capture of 4 requests scaled by requests per launch",
                      "peak_source": pk["source"] + " (sustained bf16)", "ms_per_launch": att_ms,
                      "pool_ms_per_step": pool_ms},
         "clocks": clocks,
@@ -498,9 +498,29 @@ def bench_pool_hbm(pk, reps=40, only=None):
         ms = statistics.median(a.elapsed_time(b_) for a, b_ in ev)
         nbytes = n_ids * (8 + dim * 2) + batch * G * 4 + batch * G * dim * 2
         gbs = nbytes / (ms * 1e-3) / 1e9
+        # what a bare gather of uniformly random rows of this table reaches (no pooling, no output)
+        n_probe = 8_000_000
+        probe_rows = torch.randint(0, rows, (n_probe,), dtype=torch.int32, device="cuda")
+        sink = torch.zeros(1, device="cuda")
+        probe = lambda: ops.check(capi.lib().xb_gather_probe(tb.desc, probe_rows.data_ptr(), n_probe, sink.data_ptr(), ops.stream()))
+        probe()
+        pa, pb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        pa.record()
+        for _ in range(5):
+            probe()
+        pb.record()
+        torch.cuda.synchronize()
+        probe_ms = pa.elapsed_time(pb) / 5
+        ceiling = n_probe * (dim * 2 + 4) / (probe_ms * 1e-3) / 1e9
         out[label] = {"ms_per_launch": ms, "ids_per_launch": n_ids, "algorithmic_bytes": nbytes, "achieved_gbs": gbs,
                       "frac_of_measured_copy_peak": gbs / pk["hbm_gbs"], "table_bytes": rows * pitch,
+                      "random_gather_ceiling_gbs": ceiling,
+                      "random_gather_ceiling_note": "xb_gather_probe: %d uniformly random rows of this table, row bytes + 4 B "
+                                                    "row number each, nothing else; Zipf ids let the pooling launch exceed "
+                                                    "it through L2 hits" % n_probe,
+                      "frac_of_random_gather_ceiling": gbs / ceiling,
                       "l2": "table exceeds L2; ids rotate over %d batches" % NB}
+        del probe_rows
         del tb, y, plans
         torch.cuda.empty_cache()
     return out

@@ -287,6 +287,11 @@ int xb_shard_ctx_profile(xb_shard_ctx* ctx, int32_t enable);
 int xb_shard_ctx_phase_ms(xb_shard_ctx* ctx, float* ms6);
 
 
+/* Measurement aid (no reference counterpart): gathers the `n` rows `row_ids` of `table` (rows of at most 64 bytes) and
+ * discards them. Timed by the caller, it gives the rate at which this GPU can fetch rows at random addresses - the
+ * ceiling of a pooling kernel on a table that does not fit L2. `sink` is one float of device memory. */
+int xb_gather_probe(const xb_table_desc* table, const int32_t* row_ids, int64_t n, float* sink, xb_stream_t stream);
+
 /* Self-test of the bounded waits (no counterpart in the reference): launches one warp that waits on a barrier
  * nothing will ever signal and gives up after `limit_cycles`. Afterwards xb_device_status reports a non-zero
  * word (site 99) until xb_device_status_clear, and every other entry point keeps working. */

@@ -111,6 +111,7 @@ SYMBOLS = {
     "xb_shard_ctx_status": (i32, [vp, C.POINTER(i32)]),
     "xb_shard_ctx_bucket_capacity": (i64, [vp]),
     "xb_shard_ctx_device_bytes": (C.c_size_t, [vp]),
+    "xb_gather_probe": (C.c_int, [C.POINTER(TableDesc), vp, i64, vp, vp]),
     "xb_shard_ctx_profile": (C.c_int, [vp, i32]),
     "xb_shard_ctx_phase_ms": (C.c_int, [vp, vp]),
     "xb_gemm": (i32, [C.POINTER(GemmArgs), vp]),

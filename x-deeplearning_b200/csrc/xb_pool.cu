@@ -1043,6 +1043,40 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
 }
 
 // ---------------------------------------------------------------------------
+// Measurement aid: the rate at which this GPU gathers rows at given (uniformly random) row numbers, with nothing
+// else to do - four lanes per row, 16-byte loads, four rows in flight per lane. It is the ceiling a pooling kernel
+// can reach on a table that does not fit L2, far below the streaming-copy bandwidth for 64-byte rows.
+__global__ void __launch_bounds__(256) gather_probe_kernel(const uint4* __restrict__ table, int pitch16, int chunks,
+                                                           const int32_t* __restrict__ rows, int64_t n, float* sink) {
+  const int lane = threadIdx.x & 31, sub = lane >> 2, chunk = lane & 3;
+  const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (int64_t)gridDim.x * 8;
+  float acc = 0.f;
+  for (int64_t base = warp * 32; base < n; base += nwarps * 32) {
+    int r[4];
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { const int64_t i = base + u * 8 + sub; r[u] = i < n ? __ldcs(rows + i) : -1; }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      v[u] = (r[u] >= 0 && chunk < chunks) ? __ldg(table + (int64_t)r[u] * pitch16 + chunk) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc += __uint_as_float(v[u].x) + __uint_as_float(v[u].w);
+  }
+  if (acc == 12345.678f) sink[0] = acc;                // keeps the loads alive
+}
+
+extern "C" int xb_gather_probe(const xb_table_desc* table, const int32_t* row_ids, int64_t n, float* sink, xb_stream_t stream) {
+  XB_REQUIRE(table && table->weights && row_ids && sink && n >= 0, XB_ERR_ARG, "xb_gather_probe: bad arguments");
+  XB_REQUIRE(table->row_pitch_bytes % 16 == 0 && table->row_pitch_bytes <= 64, XB_ERR_LIMIT,
+             "xb_gather_probe: rows of at most 64 bytes at a 16-byte pitch");
+  const int esz = table->dtype == XB_F32 ? 4 : 2;
+  const int chunks = (table->dim * esz + 15) / 16;
+  gather_probe_kernel<<<sm_count() * 32, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint4*>(table->weights),
+                                                                       (int)(table->row_pitch_bytes / 16), chunks, row_ids, n, sink);
+  return check_launch("gather_probe_kernel");
+}
+
+// ---------------------------------------------------------------------------
 // Allocation-free variant: the counts->offsets scratch lives in a file-scope
 // device array instead of caller-provided memory.
 #define XB_POOL_STATIC_SCRATCH_BYTES (1u << 20)
