@@ -41,7 +41,8 @@ enum xb_dtype {
   XB_I32 = 2,
   XB_I64 = 10,
   XB_F16 = 12,
-  XB_BF16 = 14           /* extension: not a Blaze type */
+  XB_BF16 = 14,          /* extension: not a Blaze type */
+  XB_REC64 = 110         /* extension, id lists only: 8-byte routing records (segment << 32) | row, the row is used */
 };
 
 /* Reason of the last non-zero return on this thread ("" if none). */
@@ -133,7 +134,7 @@ typedef struct xb_pool_group {
   int64_t batch;
   int32_t dim;                 /* the group's configured dim (EmbeddingFeatureGroupConfig.dim); must
                                   equal table->dim when the table exists */
-  int32_t id_dtype;            /* XB_I64 or XB_I32 */
+  int32_t id_dtype;            /* XB_I64 or XB_I32 (XB_REC64: routing records as received by an owner rank) */
   int32_t segments_are_offsets;
   int32_t out_dtype;           /* XB_F32 or XB_F16 */
   int32_t n_items;
@@ -241,6 +242,14 @@ int xb_scan_counts(const int32_t* counts, int64_t counts_stride, int32_t* offset
 int xb_shard_pool_padded(const xb_table_desc* const* tables, const int64_t* table_segments, int32_t n_tables,
                          const int32_t* rows, int64_t bucket_cap, const int32_t* offsets, int32_t sources,
                          int64_t n_rows_estimate, int32_t dim, void* out, int32_t out_dtype, xb_stream_t stream);
+/* The same two steps without an unpacked copy of the received buckets: segment lengths counted from the records
+ * themselves (counts [sources * segments], zeroed here), and pooling that reads the records as its id list. */
+int xb_record_counts_padded(const int64_t* packed, int32_t sources, int64_t bucket_cap, int32_t* counts, int64_t segments,
+                            xb_stream_t stream);
+int xb_shard_pool_records(const xb_table_desc* const* tables, const int64_t* table_segments, int32_t n_tables,
+                          const int64_t* records, int64_t bucket_cap, const int32_t* offsets, int32_t sources,
+                          int64_t n_rows_estimate, int32_t dim, void* out, int32_t out_dtype, xb_stream_t stream);
+
 
 /* The whole sharded step behind one call, with the two exchanges done by NCCL from inside the library (bound at
  * run time: libnccl.so.2 is needed only by processes that create a context for more than one rank). A context
@@ -282,7 +291,7 @@ int64_t xb_shard_ctx_bucket_capacity(const xb_shard_ctx* ctx);
 size_t xb_shard_ctx_device_bytes(const xb_shard_ctx* ctx);
 /* Optional phase timing of xb_sharded_pool (no reference counterpart): when enabled, the call records seven events on
  * its stream; after a stream synchronisation xb_shard_ctx_phase_ms gives the milliseconds of the last call's six
- * phases: bucket ids by owner, exchange ids, unpack + segment lengths + offsets, pool, exchange partial sums, combine. */
+ * phases: bucket ids by owner, exchange ids, segment lengths + offsets, pool, exchange partial sums, combine. */
 int xb_shard_ctx_profile(xb_shard_ctx* ctx, int32_t enable);
 int xb_shard_ctx_phase_ms(xb_shard_ctx* ctx, float* ms6);
 

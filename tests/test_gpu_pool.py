@@ -208,3 +208,18 @@ def test_pool_benchmark_config_full_size():
     ops.embedding_pool(groups2)
     torch.cuda.synchronize()
     np.testing.assert_array_equal(got2.cpu().numpy(), 2 * got)       # scaling by 2 is exact in fp32
+
+
+def test_gather_probe_runs_and_rejects_wide_rows():
+    """The measurement aid touches every requested row and nothing else; rows wider than 64 bytes are refused."""
+    pkg.load()
+    from x_deeplearning_b200 import ops, capi
+    t = ops.Table(torch.randn(5000, 32), torch.float16)
+    rows = torch.randint(0, 5000, (100_000,), dtype=torch.int32, device="cuda")
+    sink = torch.zeros(1, device="cuda")
+    ops.check(capi.lib().xb_gather_probe(t.desc, rows.data_ptr(), rows.numel(), sink.data_ptr(), ops.stream()))
+    torch.cuda.synchronize()
+    assert float(sink.item()) == 0.0 and ops.device_status() == 0
+    wide = ops.Table(torch.randn(16, 64), torch.float32)
+    with pytest.raises(capi.XbError, match="at most 64 bytes"):
+        ops.check(capi.lib().xb_gather_probe(wide.desc, rows.data_ptr(), 16, sink.data_ptr(), ops.stream()))

@@ -295,9 +295,15 @@ def test_one_call_sharded_step_on_one_rank_matches_the_unsharded_oracle(partial_
         all_counts = np.concatenate([f[1] for f in feeds])
         off = np.zeros(len(all_counts) + 1, np.int32)
         np.cumsum(all_counts, out=off[1:])
+        if step == 1:
+            ctx.profile(True)                       # phase timing changes nothing but the event records
         ctx.pool(torch.from_numpy(all_ids).cuda(), torch.from_numpy(off).cuda(), n_tables * gpt, out)
         torch.cuda.synchronize()
         assert not ctx.overflow()
+        if step == 1:
+            phases = ctx.phase_ms()
+            assert list(phases) == list(ctx.PHASES) and all(v >= 0.0 for v in phases.values()) and sum(phases.values()) > 0.0
+            ctx.profile(False)
         got = out.float().cpu().numpy()
         for t, (ids, counts) in enumerate(feeds):
             want = np.zeros((gpt * B, dim), np.float32)

@@ -7,6 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libxdlb200.so")
 
 XB_F32, XB_I32, XB_I64, XB_F16, XB_BF16 = 1, 2, 10, 12, 14
+XB_REC64 = 110
 XB_UDF_SUM, XB_UDF_AVG, XB_UDF_ASSIGN = 0, 1, 2
 XB_TRUNC_ORDER, XB_TRUNC_REVERSE = 0, 1
 XB_EPI_NONE, XB_EPI_PRELU, XB_EPI_DICE, XB_EPI_SIGMOID = 0, 1, 2, 3
@@ -111,6 +112,8 @@ SYMBOLS = {
     "xb_shard_ctx_status": (i32, [vp, C.POINTER(i32)]),
     "xb_shard_ctx_bucket_capacity": (i64, [vp]),
     "xb_shard_ctx_device_bytes": (C.c_size_t, [vp]),
+    "xb_record_counts_padded": (C.c_int, [vp, i32, i64, vp, i64, vp]),
+    "xb_shard_pool_records": (C.c_int, [vp, vp, i32, vp, i64, vp, i32, i64, i32, vp, i32, vp]),
     "xb_gather_probe": (C.c_int, [C.POINTER(TableDesc), vp, i64, vp, vp]),
     "xb_shard_ctx_profile": (C.c_int, [vp, i32]),
     "xb_shard_ctx_phase_ms": (C.c_int, [vp, vp]),

@@ -311,15 +311,16 @@ __global__ void __launch_bounds__(256) pool_kernel(const __grid_constant__ PoolP
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 
   if (loads) {
-    const bool id64 = g.id_dtype == XB_I64;
+    const bool id64 = g.id_dtype != XB_I32;
+    const int64_t kmask = g.id_dtype == XB_REC64 ? 0xffffffffll : -1ll;     // routing records: the row is the low half
     for (int64_t j = sub; j < num; j += 2 * ns) {
       // two ids in flight per sub-team
       const int64_t j1 = j + ns;
       const bool has1 = j1 < num;
-      int64_t key0 = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j)
+      int64_t key0 = id64 ? (__ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j) & kmask)
                           : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + start + j);
       int64_t key1 = 0;
-      if (has1) key1 = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j1)
+      if (has1) key1 = id64 ? (__ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j1) & kmask)
                             : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + start + j1);
       float v0 = 1.f, v1 = 1.f;
       if (g.values) {
@@ -479,7 +480,8 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
   const int dim = g.dim, col0 = chunk * EPC;
   const bool cvalid = col0 < dim;
   const int nvalid = min(EPC, dim - col0);
-  const bool id64 = g.id_dtype == XB_I64, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
+  const bool id64 = g.id_dtype != XB_I32, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
+  const int64_t kmask = g.id_dtype == XB_REC64 ? 0xffffffffll : -1ll;       // routing records: the row is the low half
   const int vmode = g.values ? (g.vhalf ? 2 : 1) : 0;
   const bool assign = it.udf == XB_UDF_ASSIGN, avg = it.udf == XB_UDF_AVG;
   const int tn = it.trunc_num, as = it.assign_stride ? it.assign_stride : dim;
@@ -506,7 +508,7 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
     row = -1; v = 1.f;
     if (idx < nm) {
       const int64_t at = (int64_t)st + idx;
-      const int64_t key = id64 ? (int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at)
+      const int64_t key = id64 ? ((int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at) & kmask)
                                : (int64_t)__ldcs(reinterpret_cast<const int32_t*>(g.ids) + at);
       if (has_table) row = (int)lookup_row(g, key);
       if (vmode == 1) v = __ldcs(reinterpret_cast<const float*>(g.values) + at);
@@ -628,7 +630,8 @@ __global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constan
   const int dim = g.dim, col0 = tlane * EPC;
   const bool cvalid = col0 < dim;
   const int nvalid = min(EPC, dim - col0);
-  const bool id64 = g.id_dtype == XB_I64, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
+  const bool id64 = g.id_dtype != XB_I32, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
+  const int64_t kmask = g.id_dtype == XB_REC64 ? 0xffffffffll : -1ll;       // routing records: the row is the low half
   const int vmode = g.values ? (g.vhalf ? 2 : 1) : 0;
   const bool avg = it.udf == XB_UDF_AVG;
   const char* wrow = g.weights + tlane * 16;
@@ -648,7 +651,7 @@ __global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constan
     row = -1; v = 1.f;
     if (idx < nm) {
       const int64_t at = (int64_t)st + idx;
-      const int64_t key = id64 ? (int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at)
+      const int64_t key = id64 ? ((int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at) & kmask)
                                : (int64_t)__ldcs(reinterpret_cast<const int32_t*>(g.ids) + at);
       if (has_table) row = (int)lookup_row(g, key);
       if (vmode == 1) v = __ldcs(reinterpret_cast<const float*>(g.values) + at);
@@ -915,8 +918,8 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
                "xb_embedding_pool: group %d has %d items (1..%d)", i, h.n_items, XB_MAX_POOL_ITEMS);
     XB_REQUIRE(h.segments, XB_ERR_ARG, "xb_embedding_pool: group %d without segments", i);
     XB_REQUIRE(h.n_ids == 0 || h.ids, XB_ERR_ARG, "xb_embedding_pool: group %d without ids", i);
-    XB_REQUIRE(h.id_dtype == XB_I64 || h.id_dtype == XB_I32, XB_ERR_UNSUPPORTED,
-               "xb_embedding_pool: group %d id dtype %d (int64 or int32)", i, h.id_dtype);
+    XB_REQUIRE(h.id_dtype == XB_I64 || h.id_dtype == XB_I32 || h.id_dtype == XB_REC64, XB_ERR_UNSUPPORTED,
+               "xb_embedding_pool: group %d id dtype %d (int64, int32 or routing records)", i, h.id_dtype);
     XB_REQUIRE(h.out_dtype == XB_F32 || h.out_dtype == XB_F16, XB_ERR_UNSUPPORTED,
                "xb_embedding_pool: group %d output dtype %d", i, h.out_dtype);
     XB_REQUIRE(h.batch < ((int64_t)1 << 31) && h.n_ids < ((int64_t)1 << 31), XB_ERR_LIMIT,
@@ -1645,6 +1648,81 @@ extern "C" int xb_shard_pool_padded(const xb_table_desc* const* tables, const in
       g.n_ids = sources * S ? n_rows_estimate * table_segments[t] / ((int64_t)sources * S) : 0;   // sizes the work split only
       g.dim = dim;
       g.id_dtype = XB_I32;
+      g.out_dtype = out_dtype;
+      g.n_items = 1;
+      g.items[0].udf = XB_UDF_SUM;
+      g.items[0].out = reinterpret_cast<char*>(out) + ((size_t)s * S + lo) * dim * out_esz;
+      g.items[0].stride = dim;
+      lo += table_segments[t];
+      if (++n == XB_MAX_POOL_GROUPS) {
+        if (int rc = xb_embedding_pool(groups, n, nullptr, 0, stream)) return rc;
+        n = 0;
+      }
+    }
+  }
+  return n ? xb_embedding_pool(groups, n, nullptr, 0, stream) : 0;
+}
+
+// Segment lengths at the owner straight from the received fixed-capacity buckets (no unpacked copy): slot 0 of a
+// bucket is its record count, records arrive sorted by segment within a source, so the lanes of a warp that hold the
+// same segment number add once. counts[src * segments + tag]; a tag outside [0, segments) is dropped.
+__global__ void record_count_kernel(const int64_t* __restrict__ packed, int sources, int64_t cap, int64_t segments,
+                                    int32_t* __restrict__ counts) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  for (int src = 0; src < sources; ++src) {
+    int64_t cnt = __ldg(packed + (int64_t)src * cap);
+    cnt = cnt < 0 ? 0 : (cnt > cap - 1 ? cap - 1 : cnt);            // the header comes from a peer: bounded here
+    const int64_t rounds = (cnt + nthreads - 1) / nthreads;         // the same for every thread: whole warps stay together
+    for (int64_t r = 0; r < rounds; ++r) {
+      const int64_t j = r * nthreads + tid;
+      uint32_t tag = 0xffffffffu;
+      if (j < cnt) tag = (uint32_t)((uint64_t)__ldcs(packed + (int64_t)src * cap + 1 + j) >> 32);
+      const unsigned same = __match_any_sync(0xffffffffu, tag);
+      if (tag < (uint64_t)segments && (same & ((1u << lane) - 1)) == 0)
+        atomicAdd(&counts[(int64_t)src * segments + tag], __popc(same));
+    }
+  }
+}
+
+extern "C" int xb_record_counts_padded(const int64_t* packed, int32_t sources, int64_t bucket_cap, int32_t* counts,
+                                       int64_t segments, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(packed && counts && sources >= 1 && sources <= ROUTE_MAX_SHARDS && bucket_cap >= 2 && segments >= 0, XB_ERR_ARG,
+             "xb_record_counts_padded: bad arguments");
+  XB_CUDA(cudaMemsetAsync(counts, 0, (size_t)sources * (size_t)segments * sizeof(int32_t), stream));
+  record_count_kernel<<<sm_count() * 8, 256, 0, stream>>>(packed, sources, bucket_cap, segments, counts);
+  return check_launch("record_count_kernel");
+}
+
+// xb_shard_pool_padded reading the received records themselves (id dtype XB_REC64: the row is the low 32 bits).
+extern "C" int xb_shard_pool_records(const xb_table_desc* const* tables, const int64_t* table_segments, int32_t n_tables,
+                                     const int64_t* records, int64_t bucket_cap, const int32_t* offsets, int32_t sources,
+                                     int64_t n_rows_estimate, int32_t dim, void* out, int32_t out_dtype, xb_stream_t stream) {
+  XB_REQUIRE(tables && table_segments && n_tables >= 1 && sources >= 1 && offsets && records && out && dim >= 1 && bucket_cap >= 2,
+             XB_ERR_ARG, "xb_shard_pool_records: bad arguments");
+  XB_REQUIRE(out_dtype == XB_F32 || out_dtype == XB_F16, XB_ERR_UNSUPPORTED, "xb_shard_pool_records: partial dtype %d", out_dtype);
+  const size_t out_esz = out_dtype == XB_F32 ? 4 : 2;
+  int64_t S = 0;
+  for (int t = 0; t < n_tables; ++t) {
+    XB_REQUIRE(table_segments[t] >= 0, XB_ERR_ARG, "xb_shard_pool_records: negative segment count");
+    S += table_segments[t];
+  }
+  xb_pool_group groups[XB_MAX_POOL_GROUPS];
+  int n = 0;
+  for (int s = 0; s < sources; ++s) {
+    int64_t lo = 0;
+    for (int t = 0; t < n_tables; ++t) {
+      xb_pool_group& g = groups[n];
+      memset(&g, 0, sizeof(g));
+      g.table = tables[t];
+      g.ids = records + (int64_t)s * bucket_cap + 1;         // the records of source s follow its header slot
+      g.segments = offsets + (int64_t)s * (S + 1) + lo;      // offsets of source s count from its first record
+      g.segments_are_offsets = 1;
+      g.batch = table_segments[t];
+      g.n_ids = sources * S ? n_rows_estimate * table_segments[t] / ((int64_t)sources * S) : 0;   // sizes the work split only
+      g.dim = dim;
+      g.id_dtype = XB_REC64;
       g.out_dtype = out_dtype;
       g.n_items = 1;
       g.items[0].udf = XB_UDF_SUM;

@@ -89,14 +89,12 @@ struct xb_shard_ctx {
   char* arena = nullptr;
   size_t arena_bytes = 0;
   int64_t *send = nullptr, *recv = nullptr;         // [world * cap] packed records
-  int32_t *rows = nullptr, *tags = nullptr;         // [world * cap]
   int32_t *counts = nullptr, *offsets = nullptr;    // [world * S], [world * (S + 1)]
   char *partial = nullptr, *back = nullptr;         // [world * S * dim] partial sums (partial_dtype)
   void* route_scratch = nullptr; size_t route_scratch_bytes = 0;
   void* scan_scratch = nullptr; size_t scan_scratch_bytes = 0;
   int32_t* overflow_dev = nullptr;                  // device view of the mapped flag
   volatile int32_t* overflow_host = nullptr;
-  std::vector<int64_t> source_counts;               // world x cap: slice lengths of the received buffer
   // optional phase timing: events recorded at the phase boundaries of the last xb_sharded_pool call
   bool profile = false;
   cudaEvent_t ev[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -166,14 +164,12 @@ extern "C" int xb_shard_ctx_create(xb_shard_ctx** out, const void* unique_id128,
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t at = off; off += align256(bytes); return at; };
   const size_t o_send = take((size_t)W * c->cap * 8), o_recv = take((size_t)W * c->cap * 8);
-  const size_t o_rows = take((size_t)W * c->cap * 4), o_tags = take((size_t)W * c->cap * 4);
   const size_t o_counts = take((size_t)W * c->S * 4), o_offsets = take((size_t)W * (c->S + 1) * 4);
   const size_t o_partial = take((size_t)W * c->S * c->dim * esz), o_back = take((size_t)W * c->S * c->dim * esz);
   const size_t o_route = take(c->route_scratch_bytes), o_scan = take(c->scan_scratch_bytes);
   c->arena_bytes = off;
   XB_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->arena), c->arena_bytes));
   c->send = reinterpret_cast<int64_t*>(c->arena + o_send); c->recv = reinterpret_cast<int64_t*>(c->arena + o_recv);
-  c->rows = reinterpret_cast<int32_t*>(c->arena + o_rows); c->tags = reinterpret_cast<int32_t*>(c->arena + o_tags);
   c->counts = reinterpret_cast<int32_t*>(c->arena + o_counts); c->offsets = reinterpret_cast<int32_t*>(c->arena + o_offsets);
   c->partial = c->arena + o_partial; c->back = c->arena + o_back;
   c->route_scratch = c->arena + o_route; c->scan_scratch = c->arena + o_scan;
@@ -182,7 +178,6 @@ extern "C" int xb_shard_ctx_create(xb_shard_ctx** out, const void* unique_id128,
   *flag = 0;
   c->overflow_host = flag;
   XB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->overflow_dev), flag, 0));
-  c->source_counts.assign(W, c->cap);
   if (W > 1) {
     XB_REQUIRE(nccl().ok, XB_ERR_UNSUPPORTED, "xb_shard_ctx_create: %s", nccl().why.c_str());
     NcclUniqueId id;
@@ -236,9 +231,8 @@ extern "C" int xb_sharded_pool(xb_shard_ctx* c, const int64_t* ids, const int32_
   // 1. bucket the ids by owner (fixed-capacity buckets) and exchange them
   if (int rc = xb_a2a_route(c, ids, seg_offsets, n_ids, stream)) return rc;
   mark(c, 2, (cudaStream_t)stream);
-  // 2. at the owner: records -> rows and segment numbers, segment lengths per source, offsets per source
-  if (int rc = xb_unpack_routed_padded(c->recv, W, c->cap, c->rows, c->tags, stream)) return rc;
-  if (int rc = xb_tag_counts_sources(c->tags, c->source_counts.data(), W, c->counts, c->S, stream)) return rc;
+  // 2. at the owner: segment lengths per source from the received records, offsets per source
+  if (int rc = xb_record_counts_padded(c->recv, W, c->cap, c->counts, c->S, stream)) return rc;
   for (int s0 = 0; s0 < W; s0 += XB_MAX_POOL_GROUPS) {
     const int n = std::min(W - s0, (int)XB_MAX_POOL_GROUPS);
     if (int rc = xb_scan_counts(c->counts + (int64_t)s0 * c->S, c->S, c->offsets + (int64_t)s0 * (c->S + 1), c->S + 1, n, c->S,
@@ -246,8 +240,8 @@ extern "C" int xb_sharded_pool(xb_shard_ctx* c, const int64_t* ids, const int32_
   }
   mark(c, 3, (cudaStream_t)stream);
   // 3. pool every (source, table) segment range against that table's shard
-  if (int rc = xb_shard_pool_padded(c->tables.data(), c->table_segments.data(), c->n_tables, c->rows, c->cap, c->offsets, W,
-                                    n_ids, c->dim, c->partial, c->partial_dtype, stream)) return rc;
+  if (int rc = xb_shard_pool_records(c->tables.data(), c->table_segments.data(), c->n_tables, c->recv, c->cap, c->offsets, W,
+                                     n_ids, c->dim, c->partial, c->partial_dtype, stream)) return rc;
   mark(c, 4, (cudaStream_t)stream);
   // 4. partial sums back to the sources, 5. owner-ordered combine
   if (int rc = xb_a2a_return(c, stream)) return rc;
@@ -270,7 +264,7 @@ extern "C" int xb_shard_ctx_profile(xb_shard_ctx* c, int32_t enable) {
 }
 
 // Milliseconds of the six phases of the last profiled call, after the caller has synchronised its stream:
-// bucket ids by owner, exchange ids, unpack + segment lengths + offsets, pool, exchange partial sums, combine.
+// bucket ids by owner, exchange ids, segment lengths + offsets, pool, exchange partial sums, combine.
 extern "C" int xb_shard_ctx_phase_ms(xb_shard_ctx* c, float* ms6) {
   XB_REQUIRE(c && ms6 && c->profile, XB_ERR_ARG, "xb_shard_ctx_phase_ms: profiling is off");
   for (int i = 0; i < 6; ++i) XB_CUDA(cudaEventElapsedTime(&ms6[i], c->ev[i], c->ev[i + 1]));

@@ -242,7 +242,7 @@ class ShardContext:
     def device_bytes(self):
         return int(lib().xb_shard_ctx_device_bytes(self.h))
 
-    PHASES = ("bucket_ids", "exchange_ids", "unpack_scan", "pool", "exchange_partials", "combine")
+    PHASES = ("bucket_ids", "exchange_ids", "lengths_offsets", "pool", "exchange_partials", "combine")
 
     def profile(self, enable=True):
         """Record events at the phase boundaries of every pool() call from now on (off by default)."""
