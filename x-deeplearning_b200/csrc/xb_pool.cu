@@ -1149,9 +1149,16 @@ __global__ void __launch_bounds__(256) route_count_kernel(const int64_t* __restr
   if (threadIdx.x < ROUTE_MAX_SHARDS) hist[threadIdx.x] = 0;
   __syncthreads();
   const int64_t base = (int64_t)blockIdx.x * ROUTE_CHUNK;
+  const int lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < ROUTE_CHUNK; i += 256) {
     const int64_t idx = base + i;
-    if (idx < n) atomicAdd(&hist[route_owner((uint64_t)ids[idx], shards)], 1);           // integer: order-free
+    const int owner = idx < n ? route_owner((uint64_t)__ldcs(ids + idx), shards) : -1;
+    // one shared-memory atomic per warp and owner instead of one per id (with two owners every id of a CTA would
+    // queue on the same two words)
+    for (int w = 0; w < shards; ++w) {
+      const unsigned m = __ballot_sync(0xffffffffu, owner == w);
+      if (lane == 0 && m) atomicAdd(&hist[w], __popc(m));                                // integer: order-free
+    }
   }
   __syncthreads();
   if (threadIdx.x < shards) block_hist[(int64_t)blockIdx.x * shards + threadIdx.x] = hist[threadIdx.x];
