@@ -991,6 +991,14 @@ class ShardedLeg:
             stats = self.sharded.sharded_pool_tables(self.comm, self.gops, self.tables, self.DIM, [f[0] for f in self.feeds],
                                                      [None] * self.N_TABLES, [f[1] for f in self.feeds],
                                                      [self.GPT] * self.N_TABLES, self.pooled, mark=mark if timed else None)
+        self.mlp()
+        if timed:
+            mark("mlp")
+            self.phases.append(events)
+        return stats
+
+    def mlp(self):
+        ops, capi = self.ops, self.capi
         x = self.pooled
         for i in range(4):
             last = i == 3
@@ -998,10 +1006,30 @@ class ShardedLeg:
                      epilogue=capi.XB_EPI_SIGMOID if last else capi.XB_EPI_PRELU,
                      ep=(None if last else self.slope, None, None), ep_count=0 if last else 1)
             x = self.acts[i]
-        if timed:
-            mark("mlp")
-            self.phases.append(events)
-        return stats
+
+    def run_pipelined(self, steps):
+        """Two steps in flight: the id routing and exchange of step i+1 (xb_sharded_pool_begin on a side stream) overlap
+        the pooling, partial-sum exchange, combine and MLP of step i (xb_sharded_pool_finish on the main stream). Every
+        rank issues begin(i+1) before finish(i). Returns the CUDA-event time of `steps` steps on this rank."""
+        torch = self.torch
+        if not hasattr(self, "side"):
+            self.side = torch.cuda.Stream()
+        main = torch.cuda.current_stream()
+        groups = self.N_TABLES * self.GPT
+        self.side.wait_stream(main)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        with torch.cuda.stream(self.side):
+            self.ctx.begin(self.all_ids, self.all_off)
+        for i in range(steps):
+            if i + 1 < steps:
+                with torch.cuda.stream(self.side):
+                    self.ctx.begin(self.all_ids, self.all_off)
+            self.ctx.finish(groups, self.pooled)
+            self.mlp()
+        e1.record()
+        main.wait_stream(self.side)
+        return e0, e1
 
     def check(self, n_check=48):
         """One step, then this rank's first `n_check` samples against the CPU oracle: pooled vectors (un-sharded
@@ -1063,6 +1091,24 @@ class ShardedLeg:
         dist.barrier(); torch.cuda.synchronize()
         t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pipelined = None
+        if self.ctx is not None:
+            serial_prob = self.acts[3].clone()
+            for _ in range(2):
+                self.run_pipelined(3)
+            dist.barrier(); torch.cuda.synchronize()
+            p0, p1 = self.run_pipelined(steps)
+            dist.barrier(); torch.cuda.synchronize()
+            tp = torch.tensor([p0.elapsed_time(p1)], dtype=torch.float64, device="cuda")
+            dist.all_reduce(tp, op=dist.ReduceOp.MAX)
+            same = torch.tensor([1.0 if torch.equal(serial_prob, self.acts[3]) else 0.0], dtype=torch.float64, device="cuda")
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            pms = float(tp.item()) / steps
+            pipelined = {"ms_per_step": pms, "samples_per_s": self.BATCH / (pms * 1e-3),
+                         "same_bits_as_one_step_at_a_time": bool(same.item() == 1.0),
+                         "how": "xb_sharded_pool_begin of step i+1 on a side stream, xb_sharded_pool_finish + MLP of step i "
+                                "on the main stream: the id exchange overlaps the pooling, the routing overlaps the "
+                                "partial-sum exchange"}
         # where a step spends its time on this rank: a few more steps with an event after every phase (outside the
         # timed region; the host gaps between phases show up here too)
         if self.ctx is not None:
@@ -1089,7 +1135,7 @@ class ShardedLeg:
                 "table_rows": self.rows_total, "tables": self.N_TABLES, "dim": self.DIM,
                 "ids_per_rank_step": sum(f[2] for f in self.feeds),
                 "routed_bytes_per_rank_step": stats["routed_bytes"], "returned_bytes_per_rank_step": stats["returned_bytes"],
-                "partial_dtype": self.partial_dtype,
+                "partial_dtype": self.partial_dtype, "two_steps_in_flight": pipelined,
                 "bucket_overflow": overflowed if self.ctx is not None else False,
                 "impl": ("xb_sharded_pool: one C-ABI call per step, NCCL inside the library, fixed-capacity id buckets, "
                          "no host synchronisation" if self.ctx is not None else

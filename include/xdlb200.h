@@ -284,6 +284,16 @@ int xb_shard_ctx_create(xb_shard_ctx** out, const void* unique_id128, const xb_s
 void xb_shard_ctx_destroy(xb_shard_ctx* ctx);
 int xb_sharded_pool(xb_shard_ctx* ctx, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids, int64_t groups,
                     int32_t avg, void* out, int64_t out_stride, int32_t out_dtype, xb_stream_t stream);
+/* The same step in two halves, so that a caller can overlap the id exchange of step i+1 with the pooling of step i
+ * (no reference counterpart): xb_sharded_pool_begin buckets the ids and enqueues their exchange on `stream`;
+ * xb_sharded_pool_finish takes the oldest begun step, makes `stream` wait for that exchange and enqueues the rest.
+ * At most two steps may be begun and not finished; every rank must issue begin and finish calls in the same order
+ * (exchanges of one communicator run in issue order); the id and offset arrays of a begun step stay untouched
+ * until its work has run. xb_sharded_pool is begin followed by finish on one stream. */
+int xb_sharded_pool_begin(xb_shard_ctx* ctx, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids, xb_stream_t stream);
+int xb_sharded_pool_finish(xb_shard_ctx* ctx, int64_t groups, int32_t avg, void* out, int64_t out_stride, int32_t out_dtype,
+                           xb_stream_t stream);
+
 int xb_a2a_route(xb_shard_ctx* ctx, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids, xb_stream_t stream);
 int xb_a2a_return(xb_shard_ctx* ctx, xb_stream_t stream);
 int xb_shard_ctx_status(xb_shard_ctx* ctx, int32_t* overflow);

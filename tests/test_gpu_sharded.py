@@ -319,6 +319,53 @@ def test_one_call_sharded_step_on_one_rank_matches_the_unsharded_oracle(partial_
     ctx.close()
 
 
+def test_two_steps_in_flight_give_the_same_bits_as_one_at_a_time():
+    """xb_sharded_pool_begin / _finish: begin(i+1) on a side stream before finish(i) on the main stream, different ids
+    every step; the results equal those of the one-call step bit for bit, and a third begin is refused."""
+    pkg.load()
+    from x_deeplearning_b200 import capi, ops, sharded, workloads
+    rng = np.random.default_rng(47)
+    n_tables, gpt, dim, B, rows_total = 2, 6, 32, 1024, 50_000
+    tables = [ops.Table(torch.from_numpy(workloads.fp16_round(rng.normal(0, 0.01, (rows_total, dim)))), torch.float16)
+              for _ in range(n_tables)]
+    ctx = sharded.ShardContext(0, 1, tables, [gpt * B] * n_tables, dim, max_ids=n_tables * gpt * B * 20)
+    steps = []
+    for _ in range(5):
+        counts = rng.integers(0, 21, n_tables * gpt * B).astype(np.int32)
+        ids = workloads.zipf_ids(rng, rows_total, int(counts.sum()), 1.05)
+        off = np.zeros(len(counts) + 1, np.int32)
+        np.cumsum(counts, out=off[1:])
+        steps.append((torch.from_numpy(ids).cuda(), torch.from_numpy(off).cuda()))
+    G = n_tables * gpt
+    want = []
+    for ids, off in steps:
+        out = torch.zeros((B, G * dim), dtype=torch.float16, device="cuda")
+        ctx.pool(ids, off, G, out)
+        want.append(out)
+    torch.cuda.synchronize()
+    side, main = torch.cuda.Stream(), torch.cuda.current_stream()
+    side.wait_stream(main)
+    got = [torch.zeros((B, G * dim), dtype=torch.float16, device="cuda") for _ in steps]
+    with torch.cuda.stream(side):
+        ctx.begin(*steps[0])
+    for i in range(len(steps)):
+        if i + 1 < len(steps):
+            with torch.cuda.stream(side):
+                ctx.begin(*steps[i + 1])
+                if i == 0:
+                    with pytest.raises(capi.XbError, match="already in flight"):
+                        ctx.begin(*steps[2])
+        ctx.finish(G, got[i])
+    main.wait_stream(side)
+    torch.cuda.synchronize()
+    assert not ctx.overflow() and ops.device_status() == 0
+    for w, g in zip(want, got):
+        assert torch.equal(w, g)
+    with pytest.raises(capi.XbError, match="no step has been begun"):
+        ctx.finish(G, got[0])
+    ctx.close()
+
+
 def test_fixed_capacity_buckets_carry_the_same_records_and_flag_overflow():
     """xb_route_ids_padded against the compact packed routing: same records in the same order behind each bucket's
     count; a capacity that is too small cuts the bucket and raises the flag."""

@@ -88,7 +88,12 @@ struct xb_shard_ctx {
   // device buffers, allocated once
   char* arena = nullptr;
   size_t arena_bytes = 0;
-  int64_t *send = nullptr, *recv = nullptr;         // [world * cap] packed records
+  int64_t *send = nullptr, *recv = nullptr;         // [world * cap] packed records: the slot in use
+  int64_t *send2[2] = {nullptr, nullptr}, *recv2[2] = {nullptr, nullptr};   // two slots: a begun step and the one before it
+  int64_t slot_ids[2] = {0, 0};                     // ids of the step each slot holds
+  cudaEvent_t slot_ready[2] = {nullptr, nullptr};   // recorded when a slot's id exchange has been enqueued
+  cudaEvent_t slot_free[2] = {nullptr, nullptr};    // recorded when the pooling that reads a slot has been enqueued
+  int begun = 0, finished = 0;                      // steps begun / finished so far (begun - finished <= 2)
   int32_t *counts = nullptr, *offsets = nullptr;    // [world * S], [world * (S + 1)]
   char *partial = nullptr, *back = nullptr;         // [world * S * dim] partial sums (partial_dtype)
   void* route_scratch = nullptr; size_t route_scratch_bytes = 0;
@@ -119,6 +124,10 @@ extern "C" void xb_shard_ctx_destroy(xb_shard_ctx* c) {
   if (c->arena) cudaFree(c->arena);
   if (c->overflow_host) cudaFreeHost((void*)c->overflow_host);
   for (cudaEvent_t e : c->ev)
+    if (e) cudaEventDestroy(e);
+  for (cudaEvent_t e : c->slot_ready)
+    if (e) cudaEventDestroy(e);
+  for (cudaEvent_t e : c->slot_free)
     if (e) cudaEventDestroy(e);
   delete c;
 }
@@ -164,12 +173,17 @@ extern "C" int xb_shard_ctx_create(xb_shard_ctx** out, const void* unique_id128,
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t at = off; off += align256(bytes); return at; };
   const size_t o_send = take((size_t)W * c->cap * 8), o_recv = take((size_t)W * c->cap * 8);
+  const size_t o_send1 = take((size_t)W * c->cap * 8), o_recv1 = take((size_t)W * c->cap * 8);
   const size_t o_counts = take((size_t)W * c->S * 4), o_offsets = take((size_t)W * (c->S + 1) * 4);
   const size_t o_partial = take((size_t)W * c->S * c->dim * esz), o_back = take((size_t)W * c->S * c->dim * esz);
   const size_t o_route = take(c->route_scratch_bytes), o_scan = take(c->scan_scratch_bytes);
   c->arena_bytes = off;
   XB_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->arena), c->arena_bytes));
-  c->send = reinterpret_cast<int64_t*>(c->arena + o_send); c->recv = reinterpret_cast<int64_t*>(c->arena + o_recv);
+  c->send2[0] = reinterpret_cast<int64_t*>(c->arena + o_send); c->recv2[0] = reinterpret_cast<int64_t*>(c->arena + o_recv);
+  c->send2[1] = reinterpret_cast<int64_t*>(c->arena + o_send1); c->recv2[1] = reinterpret_cast<int64_t*>(c->arena + o_recv1);
+  c->send = c->send2[0]; c->recv = c->recv2[0];
+  for (cudaEvent_t& e : c->slot_ready) XB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  for (cudaEvent_t& e : c->slot_free) XB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   c->counts = reinterpret_cast<int32_t*>(c->arena + o_counts); c->offsets = reinterpret_cast<int32_t*>(c->arena + o_offsets);
   c->partial = c->arena + o_partial; c->back = c->arena + o_back;
   c->route_scratch = c->arena + o_route; c->scan_scratch = c->arena + o_scan;
@@ -221,36 +235,75 @@ extern "C" int xb_a2a_return(xb_shard_ctx* c, xb_stream_t stream_) {
   return all_to_all_equal(c, c->partial, c->back, (size_t)c->S * c->dim * esz, (cudaStream_t)stream_);
 }
 
-extern "C" int xb_sharded_pool(xb_shard_ctx* c, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids, int64_t groups,
-                               int32_t avg, void* out, int64_t out_stride, int32_t out_dtype, xb_stream_t stream) {
-  XB_REQUIRE(c && out && groups >= 1 && c->S % groups == 0, XB_ERR_ARG, "xb_sharded_pool: bad arguments");
+// First half of a step: bucket the ids by owner and exchange the buckets. Two steps may be begun before the first is
+// finished (two sets of exchange buffers), so a caller can overlap the id exchange of step i+1 with the pooling of
+// step i: begin(i+1) on one stream, finish(i) on another, always in that order on every rank (the exchanges of one
+// communicator run in the order they were issued). All begin calls go to one stream, all finish calls to one stream.
+// `ids` and `seg_offsets` must stay valid until the work enqueued here has run.
+extern "C" int xb_sharded_pool_begin(xb_shard_ctx* c, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids,
+                                     xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(c, XB_ERR_ARG, "xb_sharded_pool_begin: null context");
   int dev = -1;
   XB_CUDA(cudaGetDevice(&dev));
-  XB_REQUIRE(dev == c->device, XB_ERR_ARG, "xb_sharded_pool: the context belongs to device %d, current device is %d", c->device, dev);
+  XB_REQUIRE(dev == c->device, XB_ERR_ARG, "xb_sharded_pool_begin: the context belongs to device %d, current device is %d", c->device, dev);
+  XB_REQUIRE(c->begun - c->finished < 2, XB_ERR_ARG, "xb_sharded_pool_begin: two steps are already in flight; finish one first");
+  const int slot = c->begun & 1;
+  c->send = c->send2[slot]; c->recv = c->recv2[slot];
+  // the step that used this slot two begins ago has been finished (checked above): its pooling, which reads the
+  // slot's receive buffer, may still be running on another stream
+  if (c->begun >= 2) XB_CUDA(cudaStreamWaitEvent(stream, c->slot_free[slot], 0));
+  if (int rc = xb_a2a_route(c, ids, seg_offsets, n_ids, stream)) return rc;      // 1. bucket + exchange
+  XB_CUDA(cudaEventRecord(c->slot_ready[slot], stream));
+  c->slot_ids[slot] = n_ids;
+  ++c->begun;
+  return 0;
+}
+
+// Second half of the oldest begun step, on `stream` (which is made to wait for that step's id exchange): segment
+// lengths and offsets per source, owner pooling, exchange of the partial sums, combine into `out`.
+extern "C" int xb_sharded_pool_finish(xb_shard_ctx* c, int64_t groups, int32_t avg, void* out, int64_t out_stride,
+                                      int32_t out_dtype, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(c && out && groups >= 1 && c->S % groups == 0, XB_ERR_ARG, "xb_sharded_pool_finish: bad arguments");
+  XB_REQUIRE(c->begun > c->finished, XB_ERR_ARG, "xb_sharded_pool_finish: no step has been begun");
+  XB_REQUIRE(!avg, XB_ERR_UNSUPPORTED, "xb_sharded_pool: average pooling needs the segment lengths; use kSum and scale");
   const int W = c->world;
-  // 1. bucket the ids by owner (fixed-capacity buckets) and exchange them
-  if (int rc = xb_a2a_route(c, ids, seg_offsets, n_ids, stream)) return rc;
-  mark(c, 2, (cudaStream_t)stream);
+  const int slot = c->finished & 1;
+  const int64_t* recv = c->recv2[slot];
+  const int64_t n_ids = c->slot_ids[slot];
+  XB_CUDA(cudaStreamWaitEvent(stream, c->slot_ready[slot], 0));
+  mark(c, 2, stream);
   // 2. at the owner: segment lengths per source from the received records, offsets per source
-  if (int rc = xb_record_counts_padded(c->recv, W, c->cap, c->counts, c->S, stream)) return rc;
+  if (int rc = xb_record_counts_padded(recv, W, c->cap, c->counts, c->S, stream)) return rc;
   for (int s0 = 0; s0 < W; s0 += XB_MAX_POOL_GROUPS) {
     const int n = std::min(W - s0, (int)XB_MAX_POOL_GROUPS);
     if (int rc = xb_scan_counts(c->counts + (int64_t)s0 * c->S, c->S, c->offsets + (int64_t)s0 * (c->S + 1), c->S + 1, n, c->S,
                                 c->scan_scratch, c->scan_scratch_bytes, stream)) return rc;
   }
-  mark(c, 3, (cudaStream_t)stream);
+  mark(c, 3, stream);
   // 3. pool every (source, table) segment range against that table's shard
-  if (int rc = xb_shard_pool_records(c->tables.data(), c->table_segments.data(), c->n_tables, c->recv, c->cap, c->offsets, W,
+  if (int rc = xb_shard_pool_records(c->tables.data(), c->table_segments.data(), c->n_tables, recv, c->cap, c->offsets, W,
                                      n_ids, c->dim, c->partial, c->partial_dtype, stream)) return rc;
-  mark(c, 4, (cudaStream_t)stream);
+  XB_CUDA(cudaEventRecord(c->slot_free[slot], stream));
+  mark(c, 4, stream);
   // 4. partial sums back to the sources, 5. owner-ordered combine
   if (int rc = xb_a2a_return(c, stream)) return rc;
-  mark(c, 5, (cudaStream_t)stream);
-  const int32_t* seg_len = nullptr;
-  XB_REQUIRE(!avg, XB_ERR_UNSUPPORTED, "xb_sharded_pool: average pooling needs the segment lengths; use kSum and scale");
-  const int rc = xb_shard_combine(c->back, c->partial_dtype, W, c->S, c->dim, seg_len, 0, out, out_stride, groups, out_dtype, stream);
-  mark(c, 6, (cudaStream_t)stream);
+  mark(c, 5, stream);
+  const int rc = xb_shard_combine(c->back, c->partial_dtype, W, c->S, c->dim, nullptr, 0, out, out_stride, groups, out_dtype, stream);
+  mark(c, 6, stream);
+  ++c->finished;
   return rc;
+}
+
+// The whole step on one stream.
+extern "C" int xb_sharded_pool(xb_shard_ctx* c, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids, int64_t groups,
+                               int32_t avg, void* out, int64_t out_stride, int32_t out_dtype, xb_stream_t stream) {
+  XB_REQUIRE(c && out && groups >= 1 && c->S % groups == 0, XB_ERR_ARG, "xb_sharded_pool: bad arguments");
+  XB_REQUIRE(!avg, XB_ERR_UNSUPPORTED, "xb_sharded_pool: average pooling needs the segment lengths; use kSum and scale");
+  XB_REQUIRE(c->begun == c->finished, XB_ERR_ARG, "xb_sharded_pool: a step begun with xb_sharded_pool_begin is still open");
+  if (int rc = xb_sharded_pool_begin(c, ids, seg_offsets, n_ids, stream)) return rc;
+  return xb_sharded_pool_finish(c, groups, avg, out, out_stride, out_dtype, stream);
 }
 
 // Phase timing of xb_sharded_pool: off by default (seven event records per call when on).

@@ -228,6 +228,15 @@ class ShardContext:
                                     out.stride(0), xops.dt(out), xops.stream()))
         return out
 
+    def begin(self, ids, seg_offsets):
+        """First half of a step on the current stream: bucket the ids and exchange them (see xb_sharded_pool_begin)."""
+        check(lib().xb_sharded_pool_begin(self.h, xops.ptr(ids), xops.ptr(seg_offsets), ids.numel(), xops.stream()))
+
+    def finish(self, groups, out):
+        """Second half of the oldest begun step on the current stream: pooling, exchange of partial sums, combine."""
+        check(lib().xb_sharded_pool_finish(self.h, groups, 0, xops.ptr(out), out.stride(0), xops.dt(out), xops.stream()))
+        return out
+
     def overflow(self):
         """After a stream synchronisation: True when a step since the last call dropped ids (bucket capacity)."""
         f = C.c_int32(0)
