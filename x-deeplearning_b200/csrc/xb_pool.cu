@@ -1143,10 +1143,22 @@ __device__ __forceinline__ int64_t route_segment(const int32_t* __restrict__ seg
 }
 
 // pass 1: per-CTA histogram of owners
+// the segment of the first id of every scatter CTA (one search per thread); the entry after the last CTA closes the
+// last window
+__global__ void route_windows_kernel(const int32_t* __restrict__ seg_offsets, int64_t segments, int64_t n, int64_t blocks,
+                                     int32_t* __restrict__ block_first_seg) {
+  const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b > blocks) return;
+  const int64_t first = b * ROUTE_CHUNK;
+  const int32_t last_seg = (int32_t)(segments > 0 ? segments - 1 : 0);
+  block_first_seg[b] = (b < blocks && first < n && segments > 0) ? (int32_t)route_segment(seg_offsets, 0, segments, first) : last_seg;
+}
+
 __global__ void __launch_bounds__(256) route_count_kernel(const int64_t* __restrict__ ids, int64_t n, int shards,
                                                           int32_t* __restrict__ block_hist) {
   __shared__ int32_t hist[ROUTE_MAX_SHARDS];
   if (threadIdx.x < ROUTE_MAX_SHARDS) hist[threadIdx.x] = 0;
+
   __syncthreads();
   const int64_t base = (int64_t)blockIdx.x * ROUTE_CHUNK;
   const int lane = threadIdx.x & 31;
@@ -1215,60 +1227,95 @@ __global__ void __launch_bounds__(256) route_scatter_kernel(const int64_t* __res
                                                             const int32_t* __restrict__ seg_offsets, int64_t segments,
                                                             int64_t n, int shards, const int32_t* __restrict__ block_base,
                                                             int64_t* __restrict__ out_rows, float* __restrict__ out_values,
-                                                            int32_t* __restrict__ out_tags, int64_t bucket_cap) {
-  __shared__ int32_t running[ROUTE_MAX_SHARDS];
-  __shared__ int32_t warp_cnt[8][ROUTE_MAX_SHARDS];
-  __shared__ int64_t window[2];
+                                                            int32_t* __restrict__ out_tags, int64_t bucket_cap,
+                                                            const int32_t* __restrict__ block_first_seg) {
+  // The kernel is bound by instructions per id, not by memory, so the per-id work is kept to a handful: the segment
+  // of every id of the CTA is tabulated once in shared memory (each segment of the CTA's window writes its number
+  // over its own positions), and the ranks come from prefix sums that `shards` threads make once per round.
+  constexpr int RK = 4;                                       // sub-rounds of 256 ids per round
+  constexpr int WIN = 65536;                                  // the table holds 16-bit segment numbers relative to the window
+  __shared__ int32_t running[2][ROUTE_MAX_SHARDS];
+  __shared__ int32_t warp_cnt[2][RK][8][ROUTE_MAX_SHARDS];     // counts, then exclusive prefixes in (sub-round, warp) order
+  __shared__ __align__(16) uint16_t seg_rel[ROUTE_CHUNK];
   const int64_t base = (int64_t)blockIdx.x * ROUTE_CHUNK;
-  if (threadIdx.x < shards) running[threadIdx.x] = block_base[(int64_t)blockIdx.x * shards + threadIdx.x];
-  // the ids of this CTA are consecutive, so their segments lie between those of its first and last id:
-  // two searches over all segments per CTA, then each id searches that window only (its offsets stay in L1)
-  if (threadIdx.x < 2 && base < n) {
-    const int64_t idx = threadIdx.x == 0 ? base : min(base + ROUTE_CHUNK, n) - 1;
-    window[threadIdx.x] = route_segment(seg_offsets, 0, segments, idx);
+  if (threadIdx.x < shards) running[0][threadIdx.x] = block_base[(int64_t)blockIdx.x * shards + threadIdx.x];
+  // the ids of this CTA are consecutive, so their segments lie between the segment of its first id and that of
+  // the next CTA's first id (both found by route_windows_kernel)
+  const int64_t win_lo = __ldg(block_first_seg + blockIdx.x), win_hi = (int64_t)__ldg(block_first_seg + blockIdx.x + 1) + 1;
+  const bool tabulated = win_hi - win_lo <= WIN;              // otherwise (mostly empty segments) every id searches the offsets
+  if (tabulated) {
+    // positions no segment claims (ids past the last offset) get the window's last segment, as the search would give
+    const uint32_t fill = (uint32_t)(win_hi - 1 - win_lo) * 0x00010001u;
+    for (int i = threadIdx.x; i < ROUTE_CHUNK / 8; i += 256) reinterpret_cast<uint4*>(seg_rel)[i] = make_uint4(fill, fill, fill, fill);
+    __syncthreads();
+    const int64_t end = min(base + (int64_t)ROUTE_CHUNK, n);
+    for (int64_t sgm = win_lo + threadIdx.x; sgm < win_hi; sgm += 256) {
+      const int64_t p0 = max((int64_t)__ldg(seg_offsets + sgm), base), p1 = min((int64_t)__ldg(seg_offsets + sgm + 1), end);
+      for (int64_t pp = p0; pp < p1; ++pp) seg_rel[pp - base] = (uint16_t)(sgm - win_lo);
+    }
   }
   __syncthreads();
-  const int64_t win_lo = window[0], win_hi = window[1] + 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i0 = 0; i0 < ROUTE_CHUNK; i0 += 256) {
-    const int64_t idx = base + i0 + threadIdx.x;
-    const bool live = idx < n;
-    uint64_t id = 0;
-    int owner = -1;
-    if (live) { id = (uint64_t)ids[idx]; owner = route_owner(id, shards); }
-    int rank_in_warp = 0;
-    for (int w = 0; w < shards; ++w) {
-      const unsigned m = __ballot_sync(0xffffffffu, owner == w);
-      if (owner == w) rank_in_warp = __popc(m & ((1u << lane) - 1));
-      if (lane == 0) warp_cnt[warp][w] = __popc(m);
+  // Rounds of RK x 256 consecutive ids: thread t takes the ids t, t + 256, ... of a round, so every load and (per
+  // owner) every store is coalesced and all RK loads are in flight together. The ranking stays stable: an id is
+  // preceded by the ids of earlier rounds, of earlier sub-rounds, of lower warps in its sub-round and of lower lanes
+  // in its warp.
+  for (int i0 = 0, rnd = 0; i0 < ROUTE_CHUNK; i0 += RK * 256, rnd ^= 1) {
+    uint64_t id[RK];
+    int owner[RK], rank_in_warp[RK];
+#pragma unroll
+    for (int k = 0; k < RK; ++k) {
+      const int64_t idx = base + i0 + k * 256 + threadIdx.x;
+      id[k] = idx < n ? (uint64_t)__ldcs(ids + idx) : 0;
     }
-    __syncthreads();
-    if (live) {
-      int before = 0;
-      for (int ww = 0; ww < warp; ++ww) before += warp_cnt[ww][owner];
-      const int64_t pos = (int64_t)running[owner] + before + rank_in_warp;
-      // segment of this id: last offset <= idx
-      const int64_t lo = route_segment(seg_offsets, win_lo, win_hi, idx);
-      const uint64_t row = route_row(id, shards);
-      if (bucket_cap > 0 && pos >= (int64_t)(owner + 1) * bucket_cap) {
-        // beyond the bucket's capacity: dropped (route_scan_kernel has raised the overflow flag)
-      } else if (out_tags) {
-        out_rows[pos] = (int64_t)row;
-        out_tags[pos] = (int32_t)lo;
-      } else {
-        // packed record: segment number in the high half, local row in the low half; a row that does not
-        // fit 31 bits cannot exist in a shard and is sent as 0x7fffffff, which no shard holds either
-        out_rows[pos] = (int64_t)(((uint64_t)lo << 32) | (row < 0x7fffffffull ? row : 0x7fffffffull));
+#pragma unroll
+    for (int k = 0; k < RK; ++k) {
+      const int64_t idx = base + i0 + k * 256 + threadIdx.x;
+      owner[k] = idx < n ? route_owner(id[k], shards) : -1;
+      rank_in_warp[k] = 0;
+      for (int w = 0; w < shards; ++w) {
+        const unsigned m = __ballot_sync(0xffffffffu, owner[k] == w);
+        if (owner[k] == w) rank_in_warp[k] = __popc(m & ((1u << lane) - 1));
+        if (lane == 0) warp_cnt[rnd][k][warp][w] = __popc(m);
       }
-      if (out_values && bucket_cap == 0) out_values[pos] = values ? values[idx] : 1.f;
     }
-    __syncthreads();
+    __syncthreads();                                          // the counts of this round are written
     if (threadIdx.x < shards) {
-      int add = 0;
-      for (int ww = 0; ww < 8; ++ww) add += warp_cnt[ww][threadIdx.x];
-      running[threadIdx.x] += add;
+      // counts -> exclusive prefixes in (sub-round, warp) order, starting from the ids of the rounds before
+      int acc = running[rnd][threadIdx.x];
+      for (int k = 0; k < RK; ++k)
+        for (int ww = 0; ww < 8; ++ww) {
+          const int c = warp_cnt[rnd][k][ww][threadIdx.x];
+          warp_cnt[rnd][k][ww][threadIdx.x] = acc;
+          acc += c;
+        }
+      running[rnd ^ 1][threadIdx.x] = acc;
     }
-    __syncthreads();
+    __syncthreads();                                          // the prefixes are written
+#pragma unroll
+    for (int k = 0; k < RK; ++k) {
+      const int64_t idx = base + i0 + k * 256 + threadIdx.x;
+      if (idx < n) {
+        const int ow = owner[k];
+        const int64_t pos = (int64_t)warp_cnt[rnd][k][warp][ow] + rank_in_warp[k];
+        // segment of this id: last offset <= idx
+        const int64_t lo = tabulated ? win_lo + seg_rel[i0 + k * 256 + threadIdx.x] : route_segment(seg_offsets, win_lo, win_hi, idx);
+        const uint64_t row = route_row(id[k], shards);
+        if (bucket_cap > 0 && pos >= (int64_t)(ow + 1) * bucket_cap) {
+          // beyond the bucket's capacity: dropped (route_scan_kernel has raised the overflow flag)
+        } else if (out_tags) {
+          out_rows[pos] = (int64_t)row;
+          out_tags[pos] = (int32_t)lo;
+        } else {
+          // packed record: segment number in the high half, local row in the low half; a row that does not
+          // fit 31 bits cannot exist in a shard and is sent as 0x7fffffff, which no shard holds either
+          out_rows[pos] = (int64_t)(((uint64_t)lo << 32) | (row < 0x7fffffffull ? row : 0x7fffffffull));
+        }
+        if (out_values && bucket_cap == 0) out_values[pos] = values ? values[idx] : 1.f;
+      }
+    }
+    // the next round counts into the other buffer and reads the other `running`; two rounds on, every thread has
+    // passed two more barriers, so nothing of this round is still being read when its buffer is written again
   }
 }
 
@@ -1443,8 +1490,9 @@ __global__ void shard_combine_h_kernel(const __half* __restrict__ partial, int s
 }  // namespace xb
 
 extern "C" size_t xb_route_scratch_bytes(int64_t n_ids, int32_t shards) {
-  const int64_t blocks = (n_ids + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
-  return (size_t)std::max<int64_t>(blocks, 1) * shards * sizeof(int32_t);
+  const int64_t blocks = std::max<int64_t>((n_ids + ROUTE_CHUNK - 1) / ROUTE_CHUNK, 1);
+  // per-CTA owner histogram, then the first segment of every CTA's ids (one more entry closes the last window)
+  return (size_t)blocks * shards * sizeof(int32_t) + (size_t)(blocks + 1) * sizeof(int32_t);
 }
 
 extern "C" int xb_route_ids(const int64_t* ids, const float* values, const int32_t* seg_offsets, int64_t segments,
@@ -1459,10 +1507,12 @@ extern "C" int xb_route_ids(const int64_t* ids, const float* values, const int32
   XB_REQUIRE(scratch_bytes >= xb_route_scratch_bytes(n_ids, shards) && scratch, XB_ERR_SCRATCH, "xb_route_ids: scratch too small");
   const int64_t blocks = std::max<int64_t>((n_ids + ROUTE_CHUNK - 1) / ROUTE_CHUNK, 1);
   int32_t* hist = reinterpret_cast<int32_t*>(scratch);
+  int32_t* first_seg = hist + blocks * shards;
   route_count_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, n_ids, shards, hist);
+  route_windows_kernel<<<(unsigned)((blocks + 256) / 256), 256, 0, stream>>>(seg_offsets, segments, n_ids, blocks, first_seg);
   route_scan_kernel<<<1, 256, 0, stream>>>(hist, blocks, shards, owner_counts, 0, nullptr, nullptr);
   route_scatter_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, values, seg_offsets, segments, n_ids, shards, hist, out_rows,
-                                                             out_values, out_tags, 0);
+                                                             out_values, out_tags, 0, first_seg);
   return check_launch("route kernels");
 }
 
@@ -1480,10 +1530,12 @@ extern "C" int xb_route_ids_padded(const int64_t* ids, const int32_t* seg_offset
   XB_REQUIRE(scratch_bytes >= xb_route_scratch_bytes(n_ids, shards) && scratch, XB_ERR_SCRATCH, "xb_route_ids_padded: scratch too small");
   const int64_t blocks = std::max<int64_t>((n_ids + ROUTE_CHUNK - 1) / ROUTE_CHUNK, 1);
   int32_t* hist = reinterpret_cast<int32_t*>(scratch);
+  int32_t* first_seg = hist + blocks * shards;
   route_count_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, n_ids, shards, hist);
+  route_windows_kernel<<<(unsigned)((blocks + 256) / 256), 256, 0, stream>>>(seg_offsets, segments, n_ids, blocks, first_seg);
   route_scan_kernel<<<1, 256, 0, stream>>>(hist, blocks, shards, nullptr, bucket_cap, out_records, overflow);
   route_scatter_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ids, nullptr, seg_offsets, segments, n_ids, shards, hist, out_records,
-                                                             nullptr, nullptr, bucket_cap);
+                                                             nullptr, nullptr, bucket_cap, first_seg);
   return check_launch("route kernels (fixed-capacity buckets)");
 }
 
