@@ -201,6 +201,31 @@ def run_ours(args):
     assert ops.device_status() == 0, "a bounded wait ran out inside a tensor-core kernel"
     pool_ms = statistics.mean(m[0].elapsed_time(m[1]) for m in marks)
     att_ms = statistics.mean(m[2].elapsed_time(m[3]) for m in marks)
+    # the same K steps with consecutive steps on two streams (every step has buffers of its own): the pooling launch of
+    # one step, bound by memory latency, then shares the SMs with the attention kernel of the other, bound by the SFU
+    side = [torch.cuda.Stream(), torch.cuda.Stream()]
+    main = torch.cuda.current_stream()
+    for st in side:
+        st.wait_stream(main)
+    for i in range(W):
+        with torch.cuda.stream(side[i & 1]):
+            net.forward_device(plans[i % NB])
+    for st in side:
+        main.wait_stream(st)
+    barrier()
+    o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    o0.record()
+    for st in side:
+        st.wait_stream(main)
+    for i in range(K):
+        with torch.cuda.stream(side[i & 1]):
+            net.forward_device(plans[i % NB])
+    for st in side:
+        main.wait_stream(st)
+    o1.record()
+    barrier()
+    two_stream_ms = max_over_ranks(o0.elapsed_time(o1))
+    assert ops.device_status() == 0
 
     # ---- end to end through the reference-facing API: PredictorManager / Predictor of the C++ host
     # runtime, pinned HOST buffers fed every step, probabilities copied back to the host every step
@@ -293,11 +318,13 @@ def run_ours(args):
     att_flops = ATT_FLOP_PER_PAIR * N_CAND * T_STEPS * R
     achieved_tf = att_flops / (att_ms * 1e-3) / 1e12
     line = {
-        "metric": "DIN predictions/sec", "value": preds / (dev_ms * 1e-3), "unit": "predictions/s",
-        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
+        "metric": "DIN predictions/sec", "value": preds / (two_stream_ms * 1e-3), "unit": "predictions/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": two_stream_ms / K, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "DIN-style model, 1 user x 1000 candidates per request, T=100, tables 5M/10k/8x100k x 18 fp16",
                    "requests_per_step": R, "parallelism": "replicas x%d (one process per GPU, no collective)" % world,
+                   "streams": "consecutive steps alternate between two CUDA streams (each step has buffers of its own), as "
+                              "the serving threads of the end-to-end leg do; one stream alone is under one_stream",
                    "l2": "rotating %d pre-generated batches; tables (240 MB) and per-step intermediates exceed L2" % NB},
         "e2e": {"value": preds / (e2e_ms * 1e-3), "unit": "predictions/s",
                 "h2d_bytes_per_step": h2d_bytes,
@@ -313,6 +340,8 @@ def run_ours(args):
                      "traffic": 103872 * R, "traffic_source": "ncu capture of 4 requests scaled by requests per launch",
                      "peak_source": pk["source"] + " (sustained bf16)", "ms_per_launch": att_ms,
                      "pool_ms_per_step": pool_ms},
+        "one_stream": {"ms_per_step": dev_ms / K, "value": preds / (dev_ms * 1e-3),
+                       "how": "the same K steps on one stream; the per-kernel times of the roofline entry come from this pass"},
         "clocks": clocks,
         "parity": {"checked": "request 0 of batch 0 (1000 candidates) against the CPU oracle before timing",
                    "max_abs_err": parity_err, "tol": 2e-3},
@@ -1170,7 +1199,7 @@ def main():
     ap.add_argument("--requests", type=int, default=74,
                     help="requests per step (each 1 user x 1000 candidates); 74 requests = 592 attention tiles = 4 x 148 SMs")
     ap.add_argument("--batches", type=int, default=8, help="distinct pre-generated request batches that are cycled")
-    ap.add_argument("--serving-threads", type=int, default=3,
+    ap.add_argument("--serving-threads", type=int, default=4,
                     help="Predictors (one per host thread, each with its own stream) of the end-to-end leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and pooling side measurements")

@@ -147,7 +147,10 @@ class DinModel:
             marks[3].record()
         E = capi
         if fused_tower:
-            return self.tower(p["user_emb"], p["q"], p["k"].view(R * T, d), p["att"], R, n_cand, T, out=p["prob"])
+            if "tower_ws" not in p:
+                p["tower_ws"] = self.tower.workspace(R, self.dev)       # per buffer set: launches may overlap
+            return self.tower(p["user_emb"], p["q"], p["k"].view(R * T, d), p["att"], R, n_cand, T, out=p["prob"],
+                              ws=p["tower_ws"])
         if pruned:
             check(lib().xb_din_tower_input_split(ops.ptr(p["user_emb"]), p["user_emb"].stride(0), ops.ptr(p["q"]), d,
                                                  ops.ptr(p["k"]), d, ops.ptr(p["att"]), d, ops.ptr(p["Xu"]), self.ldxu,

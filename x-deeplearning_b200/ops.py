@@ -227,11 +227,24 @@ class DinTower:
         a.packed = self.packed.data_ptr()
         return a
 
-    def __call__(self, user, q, k, att, requests, n_cand, T, out=None):
-        """user [R, du], q / att [R*n_cand, d], k [R*T, d] fp16 -> probabilities [R*n_cand, n3] fp32."""
+    def workspace(self, requests, device="cuda"):
+        """A workspace of its own for callers that keep several launches in flight on different streams."""
+        return torch.empty(int(lib().xb_din_tower_workspace_bytes(requests, self.d, self.n1)), dtype=torch.uint8, device=device)
+
+    def __call__(self, user, q, k, att, requests, n_cand, T, out=None, ws=None):
+        """user [R, du], q / att [R*n_cand, d], k [R*T, d] fp16 -> probabilities [R*n_cand, n3] fp32.
+        `ws`: workspace from workspace(); the default one is shared by all calls of this object (one stream)."""
         if out is None:
             out = torch.empty((requests * n_cand, self.n3), dtype=torch.float32, device=q.device)
         need = lib().xb_din_tower_workspace_bytes(requests, self.d, self.n1)
+        if ws is not None:
+            assert ws.numel() >= need
+            a = self._args()
+            a.user, a.ldu, a.q, a.ldq = user.data_ptr(), user.stride(0), q.data_ptr(), q.stride(0)
+            a.k, a.ldk, a.att, a.ldatt = k.data_ptr(), k.stride(0), att.data_ptr(), att.stride(0)
+            a.prob, a.requests, a.n_cand, a.T = out.data_ptr(), requests, n_cand, T
+            check(lib().xb_din_tower(C.byref(a), ptr(ws), ws.numel(), stream()))
+            return out
         if self._ws is None or self._ws.numel() < need:
             self._ws = torch.empty(need, dtype=torch.uint8, device=q.device)
         a = self._args()
