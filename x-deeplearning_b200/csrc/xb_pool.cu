@@ -312,16 +312,17 @@ __global__ void __launch_bounds__(256) pool_kernel(const __grid_constant__ PoolP
 
   if (loads) {
     const bool id64 = g.id_dtype != XB_I32;
-    const int64_t kmask = g.id_dtype == XB_REC64 ? 0xffffffffll : -1ll;     // routing records: the row is the low half
+    const bool rec = g.id_dtype == XB_REC64;                                // routing records: the row is the low half
     for (int64_t j = sub; j < num; j += 2 * ns) {
       // two ids in flight per sub-team
       const int64_t j1 = j + ns;
       const bool has1 = j1 < num;
-      int64_t key0 = id64 ? (__ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j) & kmask)
+      int64_t key0 = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j)
                           : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + start + j);
       int64_t key1 = 0;
-      if (has1) key1 = id64 ? (__ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j1) & kmask)
+      if (has1) key1 = id64 ? __ldg(reinterpret_cast<const int64_t*>(g.ids) + start + j1)
                             : (int64_t)__ldg(reinterpret_cast<const int32_t*>(g.ids) + start + j1);
+      if (rec) { key0 &= 0xffffffffll; key1 &= 0xffffffffll; }
       float v0 = 1.f, v1 = 1.f;
       if (g.values) {
         if (g.vhalf) {
@@ -481,7 +482,7 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
   const bool cvalid = col0 < dim;
   const int nvalid = min(EPC, dim - col0);
   const bool id64 = g.id_dtype != XB_I32, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
-  const int64_t kmask = g.id_dtype == XB_REC64 ? 0xffffffffll : -1ll;       // routing records: the row is the low half
+  const bool rec = g.id_dtype == XB_REC64;                                  // routing records: the row is the low half
   const int vmode = g.values ? (g.vhalf ? 2 : 1) : 0;
   const bool assign = it.udf == XB_UDF_ASSIGN, avg = it.udf == XB_UDF_AVG;
   const int tn = it.trunc_num, as = it.assign_stride ? it.assign_stride : dim;
@@ -508,8 +509,9 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
     row = -1; v = 1.f;
     if (idx < nm) {
       const int64_t at = (int64_t)st + idx;
-      const int64_t key = id64 ? ((int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at) & kmask)
-                               : (int64_t)__ldcs(reinterpret_cast<const int32_t*>(g.ids) + at);
+      int64_t key = id64 ? (int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at)
+                         : (int64_t)__ldcs(reinterpret_cast<const int32_t*>(g.ids) + at);
+      if (rec) key &= 0xffffffffll;
       if (has_table) row = (int)lookup_row(g, key);
       if (vmode == 1) v = __ldcs(reinterpret_cast<const float*>(g.values) + at);
       else if (vmode == 2) v = __half2float(reinterpret_cast<const __half*>(g.values)[at]);
@@ -613,7 +615,9 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
 // finish theirs, so lanes stay busy whatever the spread of segment lengths. A sub-team adds the ids of its
 // segment strictly in order (no cross-lane combine). The ids of the batch after the current one are
 // requested before the rows of the current one, so both latencies overlap.
-template <int TD, int LPR>
+// REC: the id lists are routing records (XB_REC64); a template parameter so that the usual instantiation carries
+// nothing for it (a run-time test here cost 15 % on tables that do not fit L2)
+template <int TD, int LPR, bool REC>
 __global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constant__ PoolParams p) {
   constexpr int EPC = TD == XB_F32 ? 4 : 8;
   constexpr unsigned FULL = 0xffffffffu;
@@ -630,8 +634,7 @@ __global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constan
   const int dim = g.dim, col0 = tlane * EPC;
   const bool cvalid = col0 < dim;
   const int nvalid = min(EPC, dim - col0);
-  const bool id64 = g.id_dtype != XB_I32, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
-  const int64_t kmask = g.id_dtype == XB_REC64 ? 0xffffffffll : -1ll;       // routing records: the row is the low half
+  const bool id64 = REC || g.id_dtype == XB_I64, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
   const int vmode = g.values ? (g.vhalf ? 2 : 1) : 0;
   const bool avg = it.udf == XB_UDF_AVG;
   const char* wrow = g.weights + tlane * 16;
@@ -651,8 +654,9 @@ __global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constan
     row = -1; v = 1.f;
     if (idx < nm) {
       const int64_t at = (int64_t)st + idx;
-      const int64_t key = id64 ? ((int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at) & kmask)
-                               : (int64_t)__ldcs(reinterpret_cast<const int32_t*>(g.ids) + at);
+      int64_t key = id64 ? (int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at)
+                         : (int64_t)__ldcs(reinterpret_cast<const int32_t*>(g.ids) + at);
+      if (REC) key &= 0xffffffffll;                           // the row is the low half of a record
       if (has_table) row = (int)lookup_row(g, key);
       if (vmode == 1) v = __ldcs(reinterpret_cast<const float*>(g.values) + at);
       else if (vmode == 2) v = __half2float(reinterpret_cast<const __half*>(g.values)[at]);
@@ -731,13 +735,13 @@ __global__ void __launch_bounds__(256, 4) pool_queue_kernel(const __grid_constan
   }
 }
 
-template <int TD>
+template <int TD, bool REC>
 static int launch_pool_queue(const PoolParams& p, int lpr, unsigned blocks, cudaStream_t stream) {
   switch (lpr) {
-    case 1: case 2: pool_queue_kernel<TD, 2><<<blocks, 256, 0, stream>>>(p); break;
-    case 4: pool_queue_kernel<TD, 4><<<blocks, 256, 0, stream>>>(p); break;
-    case 8: pool_queue_kernel<TD, 8><<<blocks, 256, 0, stream>>>(p); break;
-    default: pool_queue_kernel<TD, 16><<<blocks, 256, 0, stream>>>(p); break;
+    case 1: case 2: pool_queue_kernel<TD, 2, REC><<<blocks, 256, 0, stream>>>(p); break;
+    case 4: pool_queue_kernel<TD, 4, REC><<<blocks, 256, 0, stream>>>(p); break;
+    case 8: pool_queue_kernel<TD, 8, REC><<<blocks, 256, 0, stream>>>(p); break;
+    default: pool_queue_kernel<TD, 16, REC><<<blocks, 256, 0, stream>>>(p); break;
   }
   return check_launch("pool_queue_kernel");
 }
@@ -998,14 +1002,17 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     // sum / average groups with plenty of segments go to the segment-queue kernel: 32 segments per warp
     const bool queue = fast && d.tl == d.lpr && h.items[0].udf != XB_UDF_ASSIGN && avg >= 3.0 &&
                        (call_segments + 31) / 32 >= (int64_t)sm_count() * 8;
-    PoolParams& dst = queue ? qp[bucket] : fast ? fp[bucket] : p;
+    // the queue kernel is instantiated per kind of id list: a bucket takes records only or none
+    const bool queue_ok = queue && (qp[bucket].n_groups == 0 ||
+                                    (qp[bucket].g[0].id_dtype == XB_REC64) == (h.id_dtype == XB_REC64));
+    PoolParams& dst = queue_ok ? qp[bucket] : fast ? fp[bucket] : p;
     d.warp_begin = dst.total_warps;
     const int spw = 32 / d.tl;
     const int64_t rounds = (h.batch + spw - 1) / spw;
     // the specialised kernel gives a warp several rounds, as long as every SM still gets dozens of warps
     d.segs = 1;
     if (fast) d.segs = (int)std::max<int64_t>(1, std::min<int64_t>(8, rounds / ((int64_t)sm_count() * 48)));
-    dst.total_warps += queue ? (h.batch + 31) / 32 : (rounds + d.segs - 1) / d.segs;
+    dst.total_warps += queue_ok ? (h.batch + 31) / 32 : (rounds + d.segs - 1) / d.segs;
     dst.g[dst.n_groups++] = d;
   }
   if (sp.n) {
@@ -1034,8 +1041,11 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     const int64_t blocks = (qp[b].total_warps + 7) / 8;
     XB_REQUIRE(blocks < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_embedding_pool: too many segments");
     const int lpr = 2 << (b & 3);
-    const int rc = b < 4 ? launch_pool_queue<XB_F32>(qp[b], lpr, (unsigned)blocks, stream)
-                         : launch_pool_queue<XB_F16>(qp[b], lpr, (unsigned)blocks, stream);
+    const bool rec = qp[b].g[0].id_dtype == XB_REC64;       // a queue bucket holds records only or none (see above)
+    const int rc = b < 4 ? (rec ? launch_pool_queue<XB_F32, true>(qp[b], lpr, (unsigned)blocks, stream)
+                                : launch_pool_queue<XB_F32, false>(qp[b], lpr, (unsigned)blocks, stream))
+                         : (rec ? launch_pool_queue<XB_F16, true>(qp[b], lpr, (unsigned)blocks, stream)
+                                : launch_pool_queue<XB_F16, false>(qp[b], lpr, (unsigned)blocks, stream));
     if (rc) return rc;
   }
   if (p.n_groups == 0) return 0;
