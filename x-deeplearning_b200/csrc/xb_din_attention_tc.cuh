@@ -54,10 +54,7 @@ __device__ long long g_att_trace[7 * 128 * 4];
 #define ATT_CLK() 0ll
 #endif
 
-#ifndef XB_TC_BUILD_WARPS
-#define XB_TC_BUILD_WARPS 2
-#endif
-constexpr int TC_BUILD_WARPS = XB_TC_BUILD_WARPS;          // 2 (two rows per thread) or 4 (one)
+constexpr int TC_BUILD_WARPS = 2;                          // 2 (two rows per thread) or 4 (one)
 constexpr int TC_BROWS = 4 / TC_BUILD_WARPS;
 // warps 0-11 layer 1, 12-19 layer 2, then the A1 builder warps, then one MMA-issuing warp per layer
 constexpr int TC_L2_WARP0 = 12, TC_BUILD_WARP0 = 20, MMA1_TC_WARP = 20 + TC_BUILD_WARPS, MMA2_TC_WARP = 21 + TC_BUILD_WARPS;
@@ -88,9 +85,6 @@ __host__ __device__ constexpr TcGeom tc_geom(int d, int h0, int h1, int T) {
     const int n2 = c == 0 ? 3 : 2;
     if (3 * g.h0p + 2 * g.h1p + n2 * (g.h0p / 2) + 8 <= TMEM_COLS) { g.na1 = 3; g.na2 = n2; break; }
   }
-#ifdef XB_ATT_FORCE_NA1_2
-  g.na1 = 2;
-#endif
   g.c_acc2 = g.na1 * g.h0p;
   g.c_a2 = g.c_acc2 + 2 * g.h1p;
   g.c_ones = g.c_a2 + g.na2 * (g.h0p / 2);
