@@ -1037,27 +1037,42 @@ class ShardedLeg:
             x = self.acts[i]
 
     def run_pipelined(self, steps):
-        """Two steps in flight: the id routing and exchange of step i+1 (xb_sharded_pool_begin on a side stream) overlap
-        the pooling, partial-sum exchange, combine and MLP of step i (xb_sharded_pool_finish on the main stream). Every
-        rank issues begin(i+1) before finish(i). Returns the CUDA-event time of `steps` steps on this rank."""
+        """Three steps in flight on three streams: xb_sharded_pool_begin of step i+2 (bucket ids, id exchange),
+        xb_sharded_pool_pool of step i+1 (owner pooling, partial-sum exchange) and xb_sharded_pool_combine + MLP of step
+        i. Every rank issues them in that order, so the exchanges of the one communicator run in the same order
+        everywhere. Returns the CUDA events around `steps` steps on this rank's main stream."""
         torch = self.torch
         if not hasattr(self, "side"):
-            self.side = torch.cuda.Stream()
+            self.side = (torch.cuda.Stream(), torch.cuda.Stream())
+        s_begin, s_pool = self.side
         main = torch.cuda.current_stream()
         groups = self.N_TABLES * self.GPT
-        self.side.wait_stream(main)
+        s_begin.wait_stream(main)
+        s_pool.wait_stream(main)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        with torch.cuda.stream(self.side):
-            self.ctx.begin(self.all_ids, self.all_off)
+
+        def begin():
+            with torch.cuda.stream(s_begin):
+                self.ctx.begin(self.all_ids, self.all_off)
+
+        def pool():
+            with torch.cuda.stream(s_pool):
+                self.ctx.pool_stage()
+        begin()
+        if steps > 1:
+            begin()
+        pool()
         for i in range(steps):
+            if i + 2 < steps:
+                begin()
             if i + 1 < steps:
-                with torch.cuda.stream(self.side):
-                    self.ctx.begin(self.all_ids, self.all_off)
-            self.ctx.finish(groups, self.pooled)
+                pool()
+            self.ctx.combine(groups, self.pooled)
             self.mlp()
         e1.record()
-        main.wait_stream(self.side)
+        main.wait_stream(s_begin)
+        main.wait_stream(s_pool)
         return e0, e1
 
     def check(self, n_check=48):
@@ -1135,9 +1150,9 @@ class ShardedLeg:
             pms = float(tp.item()) / steps
             pipelined = {"ms_per_step": pms, "samples_per_s": self.BATCH / (pms * 1e-3),
                          "same_bits_as_one_step_at_a_time": bool(same.item() == 1.0),
-                         "how": "xb_sharded_pool_begin of step i+1 on a side stream, xb_sharded_pool_finish + MLP of step i "
-                                "on the main stream: the id exchange overlaps the pooling, the routing overlaps the "
-                                "partial-sum exchange"}
+                         "how": "three streams: xb_sharded_pool_begin of step i+2, xb_sharded_pool_pool of step i+1, "
+                                "xb_sharded_pool_combine + MLP of step i; both exchanges of a step overlap kernels of its "
+                                "neighbours"}
         # where a step spends its time on this rank: a few more steps with an event after every phase (outside the
         # timed region; the host gaps between phases show up here too)
         if self.ctx is not None:
@@ -1164,7 +1179,7 @@ class ShardedLeg:
                 "table_rows": self.rows_total, "tables": self.N_TABLES, "dim": self.DIM,
                 "ids_per_rank_step": sum(f[2] for f in self.feeds),
                 "routed_bytes_per_rank_step": stats["routed_bytes"], "returned_bytes_per_rank_step": stats["returned_bytes"],
-                "partial_dtype": self.partial_dtype, "two_steps_in_flight": pipelined,
+                "partial_dtype": self.partial_dtype, "steps_in_flight": pipelined,
                 "bucket_overflow": overflowed if self.ctx is not None else False,
                 "impl": ("xb_sharded_pool: one C-ABI call per step, NCCL inside the library, fixed-capacity id buckets, "
                          "no host synchronisation" if self.ctx is not None else

@@ -293,6 +293,14 @@ int xb_sharded_pool(xb_shard_ctx* ctx, const int64_t* ids, const int32_t* seg_of
 int xb_sharded_pool_begin(xb_shard_ctx* ctx, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids, xb_stream_t stream);
 int xb_sharded_pool_finish(xb_shard_ctx* ctx, int64_t groups, int32_t avg, void* out, int64_t out_stride, int32_t out_dtype,
                            xb_stream_t stream);
+/* xb_sharded_pool_finish itself in two parts, for a third pipeline stage: xb_sharded_pool_pool (segment lengths, owner
+ * pooling, exchange of the partial sums; waits for the step's id exchange) and xb_sharded_pool_combine (waits for the
+ * step's partial-sum exchange). Two steps may be pooled and not combined. With begin(i+2), pool(i+1), combine(i) issued
+ * in that order on three streams, both exchanges of a step overlap kernels of its neighbours. */
+int xb_sharded_pool_pool(xb_shard_ctx* ctx, xb_stream_t stream);
+int xb_sharded_pool_combine(xb_shard_ctx* ctx, int64_t groups, int32_t avg, void* out, int64_t out_stride, int32_t out_dtype,
+                            xb_stream_t stream);
+
 
 int xb_a2a_route(xb_shard_ctx* ctx, const int64_t* ids, const int32_t* seg_offsets, int64_t n_ids, xb_stream_t stream);
 int xb_a2a_return(xb_shard_ctx* ctx, xb_stream_t stream);

@@ -363,6 +363,33 @@ def test_two_steps_in_flight_give_the_same_bits_as_one_at_a_time():
         assert torch.equal(w, g)
     with pytest.raises(capi.XbError, match="no step has been begun"):
         ctx.finish(G, got[0])
+    # three stages on three streams: begin(i+2), pool(i+1), combine(i)
+    s_pool = torch.cuda.Stream()
+    side.wait_stream(main); s_pool.wait_stream(main)
+    got3 = [torch.zeros((B, G * dim), dtype=torch.float16, device="cuda") for _ in steps]
+    n = len(steps)
+
+    def begin(i):
+        with torch.cuda.stream(side):
+            ctx.begin(*steps[i])
+
+    def pool():
+        with torch.cuda.stream(s_pool):
+            ctx.pool_stage()
+    begin(0); begin(1); pool()
+    for i in range(n):
+        if i + 2 < n:
+            begin(i + 2)
+        if i + 1 < n:
+            pool()
+        ctx.combine(G, got3[i])
+    main.wait_stream(side); main.wait_stream(s_pool)
+    torch.cuda.synchronize()
+    assert not ctx.overflow() and ops.device_status() == 0
+    for w, g in zip(want, got3):
+        assert torch.equal(w, g)
+    with pytest.raises(capi.XbError, match="no pooled step is waiting"):
+        ctx.combine(G, got3[0])
     ctx.close()
 
 

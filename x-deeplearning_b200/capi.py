@@ -114,6 +114,8 @@ SYMBOLS = {
     "xb_shard_ctx_device_bytes": (C.c_size_t, [vp]),
     "xb_sharded_pool_begin": (C.c_int, [vp, vp, vp, i64, vp]),
     "xb_sharded_pool_finish": (C.c_int, [vp, i64, i32, vp, i64, i32, vp]),
+    "xb_sharded_pool_pool": (C.c_int, [vp, vp]),
+    "xb_sharded_pool_combine": (C.c_int, [vp, i64, i32, vp, i64, i32, vp]),
     "xb_record_counts_padded": (C.c_int, [vp, i32, i64, vp, i64, vp]),
     "xb_shard_pool_records": (C.c_int, [vp, vp, i32, vp, i64, vp, i32, i64, i32, vp, i32, vp]),
     "xb_gather_probe": (C.c_int, [C.POINTER(TableDesc), vp, i64, vp, vp]),

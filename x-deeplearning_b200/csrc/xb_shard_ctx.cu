@@ -95,7 +95,11 @@ struct xb_shard_ctx {
   cudaEvent_t slot_free[2] = {nullptr, nullptr};    // recorded when the pooling that reads a slot has been enqueued
   int begun = 0, finished = 0;                      // steps begun / finished so far (begun - finished <= 2)
   int32_t *counts = nullptr, *offsets = nullptr;    // [world * S], [world * (S + 1)]
-  char *partial = nullptr, *back = nullptr;         // [world * S * dim] partial sums (partial_dtype)
+  char *partial = nullptr, *back = nullptr;         // [world * S * dim] partial sums (partial_dtype): the slot in use
+  char *partial2[2] = {nullptr, nullptr}, *back2[2] = {nullptr, nullptr};   // two slots: a pooled step and the one before it
+  cudaEvent_t back_ready[2] = {nullptr, nullptr};   // recorded when a slot's partial-sum exchange has been enqueued
+  cudaEvent_t back_free[2] = {nullptr, nullptr};    // recorded when the combine that reads a slot has been enqueued
+  int pooled = 0;                                   // steps whose middle part has been enqueued (finished counts combines)
   void* route_scratch = nullptr; size_t route_scratch_bytes = 0;
   void* scan_scratch = nullptr; size_t scan_scratch_bytes = 0;
   int32_t* overflow_dev = nullptr;                  // device view of the mapped flag
@@ -128,6 +132,10 @@ extern "C" void xb_shard_ctx_destroy(xb_shard_ctx* c) {
   for (cudaEvent_t e : c->slot_ready)
     if (e) cudaEventDestroy(e);
   for (cudaEvent_t e : c->slot_free)
+    if (e) cudaEventDestroy(e);
+  for (cudaEvent_t e : c->back_ready)
+    if (e) cudaEventDestroy(e);
+  for (cudaEvent_t e : c->back_free)
     if (e) cudaEventDestroy(e);
   delete c;
 }
@@ -176,6 +184,7 @@ extern "C" int xb_shard_ctx_create(xb_shard_ctx** out, const void* unique_id128,
   const size_t o_send1 = take((size_t)W * c->cap * 8), o_recv1 = take((size_t)W * c->cap * 8);
   const size_t o_counts = take((size_t)W * c->S * 4), o_offsets = take((size_t)W * (c->S + 1) * 4);
   const size_t o_partial = take((size_t)W * c->S * c->dim * esz), o_back = take((size_t)W * c->S * c->dim * esz);
+  const size_t o_partial1 = take((size_t)W * c->S * c->dim * esz), o_back1 = take((size_t)W * c->S * c->dim * esz);
   const size_t o_route = take(c->route_scratch_bytes), o_scan = take(c->scan_scratch_bytes);
   c->arena_bytes = off;
   XB_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->arena), c->arena_bytes));
@@ -185,7 +194,11 @@ extern "C" int xb_shard_ctx_create(xb_shard_ctx** out, const void* unique_id128,
   for (cudaEvent_t& e : c->slot_ready) XB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   for (cudaEvent_t& e : c->slot_free) XB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   c->counts = reinterpret_cast<int32_t*>(c->arena + o_counts); c->offsets = reinterpret_cast<int32_t*>(c->arena + o_offsets);
-  c->partial = c->arena + o_partial; c->back = c->arena + o_back;
+  c->partial2[0] = c->arena + o_partial; c->back2[0] = c->arena + o_back;
+  c->partial2[1] = c->arena + o_partial1; c->back2[1] = c->arena + o_back1;
+  c->partial = c->partial2[0]; c->back = c->back2[0];
+  for (cudaEvent_t& e : c->back_ready) XB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  for (cudaEvent_t& e : c->back_free) XB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   c->route_scratch = c->arena + o_route; c->scan_scratch = c->arena + o_scan;
   int32_t* flag = nullptr;
   XB_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&flag), 64, cudaHostAllocMapped | cudaHostAllocPortable));
@@ -247,7 +260,7 @@ extern "C" int xb_sharded_pool_begin(xb_shard_ctx* c, const int64_t* ids, const 
   int dev = -1;
   XB_CUDA(cudaGetDevice(&dev));
   XB_REQUIRE(dev == c->device, XB_ERR_ARG, "xb_sharded_pool_begin: the context belongs to device %d, current device is %d", c->device, dev);
-  XB_REQUIRE(c->begun - c->finished < 2, XB_ERR_ARG, "xb_sharded_pool_begin: two steps are already in flight; finish one first");
+  XB_REQUIRE(c->begun - c->pooled < 2, XB_ERR_ARG, "xb_sharded_pool_begin: two steps are already in flight; finish one first");
   const int slot = c->begun & 1;
   c->send = c->send2[slot]; c->recv = c->recv2[slot];
   // the step that used this slot two begins ago has been finished (checked above): its pooling, which reads the
@@ -260,19 +273,22 @@ extern "C" int xb_sharded_pool_begin(xb_shard_ctx* c, const int64_t* ids, const 
   return 0;
 }
 
-// Second half of the oldest begun step, on `stream` (which is made to wait for that step's id exchange): segment
-// lengths and offsets per source, owner pooling, exchange of the partial sums, combine into `out`.
-extern "C" int xb_sharded_pool_finish(xb_shard_ctx* c, int64_t groups, int32_t avg, void* out, int64_t out_stride,
-                                      int32_t out_dtype, xb_stream_t stream_) {
+// Middle part of the oldest begun step, on `stream` (which is made to wait for that step's id exchange): segment
+// lengths and offsets per source, owner pooling, exchange of the partial sums. Two steps may be pooled before the
+// first is combined (two sets of partial-sum buffers). All calls of this function go to one stream.
+extern "C" int xb_sharded_pool_pool(xb_shard_ctx* c, xb_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  XB_REQUIRE(c && out && groups >= 1 && c->S % groups == 0, XB_ERR_ARG, "xb_sharded_pool_finish: bad arguments");
-  XB_REQUIRE(c->begun > c->finished, XB_ERR_ARG, "xb_sharded_pool_finish: no step has been begun");
-  XB_REQUIRE(!avg, XB_ERR_UNSUPPORTED, "xb_sharded_pool: average pooling needs the segment lengths; use kSum and scale");
+  XB_REQUIRE(c, XB_ERR_ARG, "xb_sharded_pool_pool: null context");
+  XB_REQUIRE(c->begun > c->pooled, XB_ERR_ARG, "xb_sharded_pool_pool: no step has been begun");
+  XB_REQUIRE(c->pooled - c->finished < 2, XB_ERR_ARG, "xb_sharded_pool_pool: two pooled steps are waiting for their combine");
   const int W = c->world;
-  const int slot = c->finished & 1;
+  const int slot = c->pooled & 1;
   const int64_t* recv = c->recv2[slot];
   const int64_t n_ids = c->slot_ids[slot];
+  c->partial = c->partial2[slot]; c->back = c->back2[slot];
   XB_CUDA(cudaStreamWaitEvent(stream, c->slot_ready[slot], 0));
+  // the combine that read this slot's partial sums two steps ago may still be running on another stream
+  if (c->pooled >= 2) XB_CUDA(cudaStreamWaitEvent(stream, c->back_free[slot], 0));
   mark(c, 2, stream);
   // 2. at the owner: segment lengths per source from the received records, offsets per source
   if (int rc = xb_record_counts_padded(recv, W, c->cap, c->counts, c->S, stream)) return rc;
@@ -287,13 +303,42 @@ extern "C" int xb_sharded_pool_finish(xb_shard_ctx* c, int64_t groups, int32_t a
                                      n_ids, c->dim, c->partial, c->partial_dtype, stream)) return rc;
   XB_CUDA(cudaEventRecord(c->slot_free[slot], stream));
   mark(c, 4, stream);
-  // 4. partial sums back to the sources, 5. owner-ordered combine
+  // 4. partial sums back to the sources
   if (int rc = xb_a2a_return(c, stream)) return rc;
+  XB_CUDA(cudaEventRecord(c->back_ready[slot], stream));
   mark(c, 5, stream);
-  const int rc = xb_shard_combine(c->back, c->partial_dtype, W, c->S, c->dim, nullptr, 0, out, out_stride, groups, out_dtype, stream);
+  ++c->pooled;
+  return 0;
+}
+
+// Last part of the oldest pooled step, on `stream` (which is made to wait for that step's partial-sum exchange):
+// the owner-ordered combine into `out`.
+extern "C" int xb_sharded_pool_combine(xb_shard_ctx* c, int64_t groups, int32_t avg, void* out, int64_t out_stride,
+                                       int32_t out_dtype, xb_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  XB_REQUIRE(c && out && groups >= 1 && c->S % groups == 0, XB_ERR_ARG, "xb_sharded_pool_combine: bad arguments");
+  XB_REQUIRE(c->pooled > c->finished, XB_ERR_ARG, "xb_sharded_pool_combine: no pooled step is waiting");
+  XB_REQUIRE(!avg, XB_ERR_UNSUPPORTED, "xb_sharded_pool: average pooling needs the segment lengths; use kSum and scale");
+  const int slot = c->finished & 1;
+  XB_CUDA(cudaStreamWaitEvent(stream, c->back_ready[slot], 0));
+  // 5. owner-ordered combine
+  const int rc = xb_shard_combine(c->back2[slot], c->partial_dtype, c->world, c->S, c->dim, nullptr, 0, out, out_stride, groups,
+                                  out_dtype, stream);
+  XB_CUDA(cudaEventRecord(c->back_free[slot], stream));
   mark(c, 6, stream);
   ++c->finished;
   return rc;
+}
+
+// Middle and last part of the oldest begun step on one stream.
+extern "C" int xb_sharded_pool_finish(xb_shard_ctx* c, int64_t groups, int32_t avg, void* out, int64_t out_stride,
+                                      int32_t out_dtype, xb_stream_t stream) {
+  XB_REQUIRE(c && out && groups >= 1 && c->S % groups == 0, XB_ERR_ARG, "xb_sharded_pool_finish: bad arguments");
+  XB_REQUIRE(c->begun > c->finished, XB_ERR_ARG, "xb_sharded_pool_finish: no step has been begun");
+  XB_REQUIRE(!avg, XB_ERR_UNSUPPORTED, "xb_sharded_pool: average pooling needs the segment lengths; use kSum and scale");
+  if (c->pooled == c->finished)
+    if (int rc = xb_sharded_pool_pool(c, stream)) return rc;
+  return xb_sharded_pool_combine(c, groups, avg, out, out_stride, out_dtype, stream);
 }
 
 // The whole step on one stream.

@@ -237,6 +237,15 @@ class ShardContext:
         check(lib().xb_sharded_pool_finish(self.h, groups, 0, xops.ptr(out), out.stride(0), xops.dt(out), xops.stream()))
         return out
 
+    def pool_stage(self):
+        """Middle part of the oldest begun step on the current stream: owner pooling and exchange of the partial sums."""
+        check(lib().xb_sharded_pool_pool(self.h, xops.stream()))
+
+    def combine(self, groups, out):
+        """Last part of the oldest pooled step on the current stream."""
+        check(lib().xb_sharded_pool_combine(self.h, groups, 0, xops.ptr(out), out.stride(0), xops.dt(out), xops.stream()))
+        return out
+
     def overflow(self):
         """After a stream synchronisation: True when a step since the last call dropped ids (bucket capacity)."""
         f = C.c_int32(0)
