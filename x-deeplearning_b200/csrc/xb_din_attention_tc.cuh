@@ -5,10 +5,10 @@
 // step: layer-1 warpgroup w (one per acc1 buffer: three, or two when tensor
 // memory is short) runs the layer-1 activations of the steps j with j % na1 == w,
 // layer-2 warpgroup b (b = 0, 1) the layer-2 activations of the steps of parity b,
-// two builder warps write A1 of every step two steps ahead; two more warps issue
-// the MMAs, one per layer (the closing product goes with layer 2).
-// The layer-1 accumulator and the layer-2 operand are three deep when tensor
-// memory has room (two otherwise), the rest is double-buffered by step parity,
+// two builder warps write A1 of every step up to na1 steps ahead; two more warps
+// issue the MMAs, one per layer (the closing product goes with layer 2).
+// The layer-1 accumulator, its operand A1 and the layer-2 operand are three deep
+// when tensor memory has room (two otherwise), acc2 is double-buffered by step parity,
 // and the activation math of up to five steps is in flight on each scheduler,
 // so in steady state the tensor pipe, the SFU and the FP16 pipe overlap: the
 // layer-1 MMA of a later step runs while the layer-1 warps still work on this one.
@@ -232,8 +232,9 @@ __global__ void att_pack_kernel(const __grid_constant__ AttParams p, uint8_t* ds
 }
 
 // D0 / H0 / H1: the shape as compile-time constants (0 = read it from the arguments). With the shape known the
-// block loops of both activation phases unroll completely and every tensor-memory column, shared-memory offset and
-// padding test folds into the instruction stream: the kernel is bound by issue slots, so this is time.
+// block loops of both activation phases and the MMA chains unroll completely and every tensor-memory column,
+// shared-memory offset and padding test folds into the instruction stream (issue slots are the second scarcest
+// resource of this kernel after the SFU).
 template <int ACT, int D0, int H0, int H1>
 __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_constant__ AttParams p) {
   using namespace umma;
