@@ -156,6 +156,20 @@ def test_pool_single_item_large_batch_segment_queue(udf, dim, tdtype, out_dtype,
                      with_values=dim != 3, id32=dim == 3)
 
 
+@pytest.mark.parametrize("udf", [0, 1])
+@pytest.mark.parametrize("dim,tdtype,out_dtype,max_len", [(32, torch.float16, torch.float16, 3),
+                                                          (16, torch.float32, torch.float32, 2),
+                                                          (18, torch.float16, torch.float32, 4),
+                                                          (3, torch.float32, torch.float16, 1),
+                                                          (100, torch.float16, torch.float32, 3)])
+def test_pool_very_short_segments_large_batch(udf, dim, tdtype, out_dtype, max_len):
+    """Fewer than three ids per segment on average in a large call: the short-segment kernel; empty segments,
+    missing keys, hashed and identity tables, counts and offsets, int32 ids, per-id values."""
+    rng = np.random.default_rng(2500 + 10 * dim + udf)
+    _run_single_item(rng, 5000, dim, 70003, max_len, tdtype, out_dtype, udf, hashed=dim == 18, use_offsets=dim != 16,
+                     with_values=dim != 3, id32=dim == 3)
+
+
 def test_pool_single_item_long_segments_few_samples():
     rng = np.random.default_rng(3000)
     _run_single_item(rng, 4000, 16, 9, 700, torch.float32, torch.float32, 0, min_len=300)

@@ -610,6 +610,107 @@ __global__ void __launch_bounds__(256, 4) pool_fast_kernel(const __grid_constant
   }
 }
 
+// Sum / average pooling of very short segments (fewer than three ids on average, large calls): LPR lanes per
+// segment, 32 / LPR segments per warp, four row loads in flight per lane, nothing else - no shuffles, no queue,
+// no sub-teams. The other kernels spend about 1500 warp instructions per round whatever the segments hold; with
+// one or two ids per segment that, not memory, is what a launch costs (an owner rank of an 8-way sharded table
+// pools 2.6 M segments of 1.9 ids). A segment's rows are added in id order, as everywhere.
+template <int TD, int LPR, bool REC>
+__global__ void __launch_bounds__(256) pool_short_kernel(const __grid_constant__ PoolParams p) {
+  constexpr int EPC = TD == XB_F32 ? 4 : 8;          // elements per 16-byte chunk
+  constexpr int SPW = 32 / LPR;                      // segments per warp and round
+  constexpr int U = 4;                               // ids of a segment fetched together
+  const int64_t warp_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (warp_id >= p.total_warps) return;
+  const int lane = threadIdx.x & 31;
+  int gi = 0;
+  while (gi + 1 < p.n_groups && p.g[gi + 1].warp_begin <= warp_id) ++gi;
+  const PoolGroupDev& g = p.g[gi];
+  const PoolItemDev& it = g.items[0];
+  const int chunk = lane & (LPR - 1);
+  const int rounds = g.segs;                         // consecutive rounds of SPW segments this warp walks
+  const int64_t seg0 = (warp_id - g.warp_begin) * rounds * SPW + lane / LPR;
+  const int64_t batch = g.batch;
+  const int dim = g.dim, col0 = chunk * EPC;
+  const bool cvalid = col0 < dim;
+  const int nvalid = min(EPC, dim - col0);
+  const bool id64 = REC || g.id_dtype == XB_I64, has_table = g.has_table != 0, out16 = g.out_dtype == XB_F16;
+  const int vmode = g.values ? (g.vhalf ? 2 : 1) : 0;
+  const bool avg = it.udf == XB_UDF_AVG;
+  const char* wrow = g.weights + chunk * 16;
+  const int pitch = (int)g.pitch;
+  const uint64_t keep = l2_policy_keep();
+
+  // the offsets of round i+2 and the ids of round i+1 are requested while the rows of round i are in flight, so
+  // a round exposes one fetch latency (its rows), not three
+  auto load_span = [&](int i, int& st, int& nm) {
+    const int64_t sg = seg0 + (int64_t)i * SPW;
+    st = 0; nm = 0;
+    if (i < rounds && sg < batch) {
+      st = __ldg(g.offsets + sg);
+      nm = __ldg(g.offsets + sg + 1) - st;
+    }
+  };
+  auto load_ids = [&](int st, int nm, int j, int (&rr)[U], float (&vv)[U]) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      rr[u] = -1; vv[u] = 1.f;
+      if (j + u < nm) {
+        const int64_t at = (int64_t)st + j + u;
+        int64_t key = id64 ? (int64_t)__ldcs(reinterpret_cast<const long long*>(g.ids) + at)
+                           : (int64_t)__ldcs(reinterpret_cast<const int32_t*>(g.ids) + at);
+        if (REC) key &= 0xffffffffll;                           // the row is the low half of a record
+        if (has_table) rr[u] = (int)lookup_row(g, key);
+        if (vmode == 1) vv[u] = __ldcs(reinterpret_cast<const float*>(g.values) + at);
+        else if (vmode == 2) vv[u] = __half2float(reinterpret_cast<const __half*>(g.values)[at]);
+      }
+    }
+  };
+  int st0, nm0, st1, nm1, st2, nm2;
+  int rr[U], rr_next[U];
+  float vv[U], vv_next[U];
+  load_span(0, st0, nm0);
+  load_span(1, st1, nm1);
+  load_ids(st0, nm0, 0, rr, vv);
+  for (int i = 0; i < rounds; ++i) {
+    const int64_t seg = seg0 + (int64_t)i * SPW;
+    load_span(i + 2, st2, nm2);
+    load_ids(st1, nm1, 0, rr_next, vv_next);
+    float acc[EPC];
+#pragma unroll
+    for (int e = 0; e < EPC; ++e) acc[e] = 0.f;
+    for (int j = 0; j < nm0; j += U) {
+      if (j > 0) load_ids(st0, nm0, j, rr, vv);                 // a segment longer than U ids: the rare case here
+      uint4 raw[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        raw[u] = make_uint4(0, 0, 0, 0);
+        if (rr[u] >= 0 && cvalid) raw[u] = ld_row16(wrow + (int64_t)rr[u] * pitch, keep);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (rr[u] >= 0) {                                       // a missing key contributes nothing
+          float w[8];
+          unpack_chunk(raw[u], TD, w);
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) acc[e] = acc[e] + vv[u] * w[e];
+        }
+      }
+    }
+    if (seg < batch && cvalid) {
+      if (avg && nm0 != 0) {
+        const float scale = (float)(1.0 / (double)nm0);
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) acc[e] = acc[e] * scale;
+      }
+      store_vec<EPC>(it.out, seg * it.stride + col0, out16, acc, nvalid);
+    }
+    st0 = st1; nm0 = nm1; st1 = st2; nm1 = nm2;
+#pragma unroll
+    for (int u = 0; u < U; ++u) { rr[u] = rr_next[u]; vv[u] = vv_next[u]; }
+  }
+}
+
 // Sum / average pooling with one sub-team (LPR lanes) per segment and a per-warp segment queue: a warp
 // owns 32 consecutive segments, its 32/LPR sub-teams each take the next unclaimed one as soon as they
 // finish theirs, so lanes stay busy whatever the spread of segment lengths. A sub-team adds the ids of its
@@ -757,6 +858,17 @@ static int launch_pool_fast(const PoolParams& p, int lpr, unsigned blocks, cudaS
   return check_launch("pool_fast_kernel");
 }
 
+template <int TD, bool REC>
+static int launch_pool_short(const PoolParams& p, int lpr, unsigned blocks, cudaStream_t stream) {
+  switch (lpr) {
+    case 1: case 2: pool_short_kernel<TD, 2, REC><<<blocks, 256, 0, stream>>>(p); break;
+    case 4: pool_short_kernel<TD, 4, REC><<<blocks, 256, 0, stream>>>(p); break;
+    case 8: pool_short_kernel<TD, 8, REC><<<blocks, 256, 0, stream>>>(p); break;
+    default: pool_short_kernel<TD, 16, REC><<<blocks, 256, 0, stream>>>(p); break;
+  }
+  return check_launch("pool_short_kernel");
+}
+
 static int next_pow2(int v) { int p = 1; while (p < v) p <<= 1; return p; }
 
 }  // namespace xb
@@ -901,10 +1013,13 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
   static thread_local PoolParams p;
   static thread_local PoolParams fp[kBuckets];
   static thread_local PoolParams qp[kBuckets];       // segment-queue kernel (sum / average, large batches)
+  static thread_local PoolParams hp[kBuckets];       // short-segment kernel (sum / average, fewer than 3 ids a segment)
   static thread_local ScanParams sp;
   p.n_groups = 0;
   p.total_warps = 0;
-  for (int b = 0; b < kBuckets; ++b) { fp[b].n_groups = 0; fp[b].total_warps = 0; qp[b].n_groups = 0; qp[b].total_warps = 0; }
+  for (int b = 0; b < kBuckets; ++b) {
+    fp[b].n_groups = 0; fp[b].total_warps = 0; qp[b].n_groups = 0; qp[b].total_warps = 0; hp[b].n_groups = 0; hp[b].total_warps = 0;
+  }
   sp.n = 0;
   sp.chunk_begin[0] = 0;
   size_t soff = 0;
@@ -912,8 +1027,16 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
   // wider teams (more warps, for small calls) and one sub-team per segment (fewest instructions per id, for
   // large ones) looks at all single-output groups together
   int64_t call_segments = 0;
-  for (int i = 0; i < n_groups; ++i)
+  // the short-segment kernel serves a call only as a whole (a call keeps its number of launches): every group must
+  // be a single sum / average output with fewer than three ids per segment on average
+  bool all_short = true;
+  for (int i = 0; i < n_groups; ++i) {
     if (groups[i].n_items == 1 && groups[i].batch > 0) call_segments += groups[i].batch;
+    if (groups[i].batch > 0 &&
+        (groups[i].n_items != 1 || groups[i].items[0].udf == XB_UDF_ASSIGN || (double)groups[i].n_ids >= 3.0 * (double)groups[i].batch))
+      all_short = false;
+  }
+  all_short = all_short && (call_segments + 31) / 32 >= (int64_t)sm_count() * 8;
   for (int i = 0; i < n_groups; ++i) {
     const xb_pool_group& h = groups[i];
     XB_REQUIRE(h.batch >= 0 && h.n_ids >= 0, XB_ERR_ARG, "xb_embedding_pool: group %d negative size", i);
@@ -1005,14 +1128,19 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     // the queue kernel is instantiated per kind of id list: a bucket takes records only or none
     const bool queue_ok = queue && (qp[bucket].n_groups == 0 ||
                                     (qp[bucket].g[0].id_dtype == XB_REC64) == (h.id_dtype == XB_REC64));
-    PoolParams& dst = queue_ok ? qp[bucket] : fast ? fp[bucket] : p;
+    // likewise one instantiation per kind of id list for the short-segment kernel
+    const bool short_ok = all_short && fast && d.tl == d.lpr &&
+                          (hp[bucket].n_groups == 0 || (hp[bucket].g[0].id_dtype == XB_REC64) == (h.id_dtype == XB_REC64));
+    PoolParams& dst = short_ok ? hp[bucket] : queue_ok ? qp[bucket] : fast ? fp[bucket] : p;
     d.warp_begin = dst.total_warps;
     const int spw = 32 / d.tl;
     const int64_t rounds = (h.batch + spw - 1) / spw;
     // the specialised kernel gives a warp several rounds, as long as every SM still gets dozens of warps
     d.segs = 1;
     if (fast) d.segs = (int)std::max<int64_t>(1, std::min<int64_t>(8, rounds / ((int64_t)sm_count() * 48)));
-    dst.total_warps += queue_ok ? (h.batch + 31) / 32 : (rounds + d.segs - 1) / d.segs;
+    // the short-segment kernel walks 8 rounds per warp (its prefetch needs a few), fewer only for small groups
+    if (short_ok) d.segs = (int)std::max<int64_t>(1, std::min<int64_t>(8, rounds / ((int64_t)sm_count() * 16)));
+    dst.total_warps += queue_ok && !short_ok ? (h.batch + 31) / 32 : (rounds + d.segs - 1) / d.segs;
     dst.g[dst.n_groups++] = d;
   }
   if (sp.n) {
@@ -1034,6 +1162,18 @@ extern "C" int xb_embedding_pool(const xb_pool_group* groups, int32_t n_groups, 
     const int lpr = 2 << (b & 3);
     const int rc = b < 4 ? launch_pool_fast<XB_F32>(fp[b], lpr, (unsigned)blocks, stream)
                          : launch_pool_fast<XB_F16>(fp[b], lpr, (unsigned)blocks, stream);
+    if (rc) return rc;
+  }
+  for (int b = 0; b < kBuckets; ++b) {
+    if (hp[b].n_groups == 0) continue;
+    const int64_t blocks = (hp[b].total_warps + 7) / 8;
+    XB_REQUIRE(blocks < ((int64_t)1 << 31), XB_ERR_LIMIT, "xb_embedding_pool: too many segments");
+    const int lpr = 2 << (b & 3);
+    const bool rec = hp[b].g[0].id_dtype == XB_REC64;
+    const int rc = b < 4 ? (rec ? launch_pool_short<XB_F32, true>(hp[b], lpr, (unsigned)blocks, stream)
+                                : launch_pool_short<XB_F32, false>(hp[b], lpr, (unsigned)blocks, stream))
+                         : (rec ? launch_pool_short<XB_F16, true>(hp[b], lpr, (unsigned)blocks, stream)
+                                : launch_pool_short<XB_F16, false>(hp[b], lpr, (unsigned)blocks, stream));
     if (rc) return rc;
   }
   for (int b = 0; b < kBuckets; ++b) {
