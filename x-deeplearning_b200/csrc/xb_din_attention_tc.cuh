@@ -552,7 +552,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) din_att_tc_kernel(const __grid_
         }
       }
       if (!ok) break;
-      const long long tr1 = ATT_CLK();
+      [[maybe_unused]] const long long tr1 = ATT_CLK();
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
