@@ -725,7 +725,7 @@ def run_reference(args):
     }))
 
 
-def bench_dien(reps=20, R=16):
+def bench_dien(reps=20, R=74):
     """C4: the DIEN-style model (GRU over the behaviour list, attention scores, AUGRU per candidate, tower) on
     R requests x 1000 candidates, device-resident inputs, CUDA events. Parity of this path is a test
     (tests/test_gpu_dien.py); here it is timed."""
